@@ -1,0 +1,383 @@
+#!/usr/bin/env python
+"""Benchmark of the Field-recurrence operator on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one forward + backward pass of the fused Field read over one batch of
+synthetic input: batch 8 x 2,048 tokens, d_model 1024 (C = 512 complex channels),
+bf16-rounded activations held in fp32 at the operator boundary, fp32 state.
+Under torchrun every rank runs that workload on its own GPU (batch-sharded,
+no collective on the data path; weak scaling); rank 0 prints ONE JSON line.
+
+`value` is tokens/s with inputs resident in HBM, timed with CUDA events on the
+launching stream; `e2e` is the same metric from pinned host buffers through the
+public Python call and back to the host; `roofline` relates the step to the
+measured HBM copy bandwidth; `cpu_baseline` times the CPU port of the reference's
+complex64 PyTorch path on the host cores (a reported baseline, not the target).
+`--impl reference` times only that CPU path, as the reference arm.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+B, L, D_MODEL = 8, 2048, 1024
+C = D_MODEL // 2
+BYTES_PER_TOKEN_FWD = (3 * C + 4 * C) * 4           # read raw, write read
+BYTES_PER_TOKEN_BWD = (3 * C + 4 * C + 3 * C) * 4   # read raw + grad_read, write grad_raw
+BYTES_PER_TOKEN = BYTES_PER_TOKEN_FWD + BYTES_PER_TOKEN_BWD
+FP32_TOL, BF16_TOL = 1e-5, 2e-2
+KERNEL_LAUNCHES_PER_STEP = 7   # forward 3 (summary, carry, materialize) + backward 4 (+ reduce)
+FALLBACK_HBM_GBS = 6650.0
+LONG_L = 65536
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def init_parameters(device):
+    """lambda and gamma of a freshly initialised mixer (reference :1156-1173)."""
+    ring = torch.linspace(0.85, 0.999, C)
+    theta = torch.linspace(0.03, torch.pi * 0.97, C)
+    tr, ti = ring * torch.cos(theta), ring * torch.sin(theta)
+    gamma = torch.sqrt((1 - ring.square()).clamp_min(1e-4))
+    return tr.to(device), ti.to(device), gamma.to(device)
+
+
+def synthetic_inputs(seed: int, batch: int, length: int):
+    """raw ~ N(0, 0.577^2) (what write_proj gives at init on N(0,1) input) and N(0,1) upstream
+    gradients, rounded to bf16 and held in fp32 as autocast hands them to the operator."""
+    gen = torch.Generator().manual_seed(seed)
+    raw = (torch.randn(batch, length, 3 * C, generator=gen) * 0.577).bfloat16().float()
+    grad_read = torch.randn(batch, length, 4 * C, generator=gen).bfloat16().float()
+    return raw, grad_read
+
+
+class ClockSampler:
+    """Polls SM clock and throttle reasons through NVML while the timed region runs."""
+
+    REASONS = {
+        0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+        0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+        0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting",
+    }
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------
+# CPU side: the port of the reference's complex64 PyTorch path, on the host cores
+# ---------------------------------------------------------------------------
+def cpu_step(raw, grad_read, tr, ti, gamma):
+    """One forward + backward of the CPU port; returns seconds."""
+    from oracle import torch_port
+    raw = raw.clone().requires_grad_(True)
+    tr, ti, gamma = (p.clone().requires_grad_(True) for p in (tr, ti, gamma))
+    t0 = time.perf_counter()
+    read = torch_port.field_read(raw, tr, ti, gamma, 32)
+    read.backward(grad_read)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(sample_batch: int = B, iters: int = 3):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    tr, ti, gamma = init_parameters("cpu")
+    raw, grad_read = synthetic_inputs(1, sample_batch, L)
+    cpu_step(raw, grad_read, tr, ti, gamma)  # warm-up
+    secs = [cpu_step(raw, grad_read, tr, ti, gamma) for _ in range(iters)]
+    return {"value": sample_batch * L / statistics.median(secs), "unit": "tokens/s",
+            "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"forward+backward of {sample_batch} x {L} tokens (of the {B} x {L} "
+                      f"workload), median of {iters} after 1 warm-up, complex64 PyTorch port of "
+                      "the reference's reference_field_read + autograd"}
+
+
+def run_reference_arm(args, rank: int):
+    """The reference's CPU implementation of the path, all host threads, bounded sample per step."""
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    tr, ti, gamma = init_parameters("cpu")
+    raw, grad_read = synthetic_inputs(1, B, L)
+    # bound the whole run to a few minutes: use fewer batch rows per step if the full batch is too slow
+    t_full = cpu_step(raw, grad_read, tr, ti, gamma)
+    budget_s = 150.0
+    sample_batch = B
+    if (args.steps + args.warmup) * t_full > budget_s:
+        sample_batch = max(1, min(B, int(B * budget_s / ((args.steps + args.warmup) * t_full))))
+        raw, grad_read = raw[:sample_batch].contiguous(), grad_read[:sample_batch].contiguous()
+    for _ in range(args.warmup):
+        cpu_step(raw, grad_read, tr, ti, gamma)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(raw, grad_read, tr, ti, gamma)
+    total = time.perf_counter() - t0
+    value = sample_batch * L * args.steps / total
+    sample = (f"each step = forward+backward of {sample_batch} x {L} tokens (of the {B} x {L} "
+              "workload), complex64 PyTorch port of the reference's CPU path")
+    line = {
+        "impl": "reference", "metric": "field_tokens_per_s_fwd_bwd", "value": value,
+        "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int):
+    return {"workload": "field_block_recurrence_fwd_bwd_8x2048_d1024",
+            "batch_per_gpu": B, "seq_len": L, "d_model": D_MODEL, "channels": C,
+            "global_batch": B * n_gpus, "parallelism": f"batch-sharded x{n_gpus}, no collective",
+            "boundary": "fused_field_read fp32 I/O (bf16-rounded activations), fp32 state",
+            "cache": "inputs+outputs 448 MiB per step, larger than the 126 MB L2",
+            "tolerances": {"fp32_rel": FP32_TOL, "bf16_rel_max_abs": BF16_TOL}}
+
+
+# ---------------------------------------------------------------------------
+# GPU side
+# ---------------------------------------------------------------------------
+def gpu_step(raw, grad_read, tr, ti, gamma):
+    """One forward + backward through the public operator; returns (read, grad_raw)."""
+    from fields_lm_b200 import fused_field_read
+    raw.grad = tr.grad = ti.grad = gamma.grad = None
+    read = fused_field_read(raw, tr, ti, gamma, 32, 64)
+    read.backward(grad_read)
+    return read, raw.grad
+
+
+def timed_loop(fn, steps: int, stream) -> float:
+    """Milliseconds for `steps` calls of fn, CUDA events on the launching stream."""
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    for _ in range(steps):
+        fn()
+    stop.record(stream)
+    stop.synchronize()
+    return start.elapsed_time(stop)
+
+
+def barrier(dist_on: bool):
+    if dist_on:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x: float, dist_on: bool, device) -> float:
+    if not dist_on:
+        return x
+    t = torch.tensor([x], device=device, dtype=torch.float64)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return float(t.item())
+
+
+def parity_check(device, tr, ti, gamma):
+    """Small live check against the CPU oracle so the line carries its own parity figure."""
+    from oracle import field_oracle
+    raw, grad_read = synthetic_inputs(7, 2, 256)
+    r = raw.to(device).requires_grad_(True)
+    p = [x.clone().requires_grad_(True) for x in (tr, ti, gamma)]
+    read, grad_raw = gpu_step(r, grad_read.to(device), *p)
+    ref_read, _ = field_oracle.forward(raw.numpy(), tr.cpu().numpy(), ti.cpu().numpy(),
+                                       gamma.cpu().numpy())
+    ref_grad = field_oracle.backward(raw.numpy(), tr.cpu().numpy(), ti.cpu().numpy(),
+                                     gamma.cpu().numpy(), grad_read.numpy())[0]
+
+    def rel(a, b):
+        return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-6))
+
+    return {"read_rel": rel(read.detach().cpu().numpy().astype(np.float64), ref_read),
+            "grad_raw_rel": rel(grad_raw.cpu().numpy().astype(np.float64), ref_grad),
+            "tolerance": FP32_TOL}
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    from fields_lm_b200 import _lib, fused_field_read
+    _lib.load()  # raises if the CUDA library is missing: there is no fallback
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (use --impl reference for the CPU arm)")
+    dist_on = world > 1
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if dist_on:
+        torch.distributed.init_process_group("nccl", device_id=device)
+    stream = torch.cuda.current_stream(device)
+
+    tr, ti, gamma = (p.requires_grad_(True) for p in init_parameters(device))
+    raw_h, grad_h = synthetic_inputs(1 + rank, B, L)
+    raw = raw_h.to(device).requires_grad_(True)
+    grad_read = grad_h.to(device)
+
+    step = lambda: gpu_step(raw, grad_read, tr, ti, gamma)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    with ClockSampler(local_rank) as clocks:
+        barrier(dist_on)
+        ms = timed_loop(step, args.steps, stream)
+        barrier(dist_on)
+        # keep the same steps running long enough for NVML to see clocks under this load
+        t_end = time.perf_counter() + 0.4
+        while time.perf_counter() < t_end:
+            step()
+            torch.cuda.synchronize()
+    ms = max_over_ranks(ms, dist_on, device)
+    ms_per_step = ms / args.steps
+    tokens_per_s = world * B * L / (ms_per_step * 1e-3)
+
+    # forward-only and backward-only, to split the step for the roofline report
+    def fwd_only():
+        with torch.no_grad():
+            fused_field_read(raw, tr, ti, gamma, 32, 64)
+    for _ in range(3):
+        fwd_only()
+    ms_fwd = timed_loop(fwd_only, args.steps, stream) / args.steps
+
+    # end to end: pinned host -> device, forward + backward, results back to pinned host
+    raw_pin, grad_pin = raw_h.pin_memory(), grad_h.pin_memory()
+    read_pin = torch.empty(B, L, 4 * C).pin_memory()
+    graw_pin = torch.empty(B, L, 3 * C).pin_memory()
+    gpar_pin = torch.empty(3, C).pin_memory()
+
+    def e2e_step():
+        r = raw_pin.to(device, non_blocking=True).requires_grad_(True)
+        g = grad_pin.to(device, non_blocking=True)
+        tr.grad = ti.grad = gamma.grad = None
+        read = fused_field_read(r, tr, ti, gamma, 32, 64)
+        read.backward(g)
+        read_pin.copy_(read.detach(), non_blocking=True)
+        graw_pin.copy_(r.grad, non_blocking=True)
+        gpar_pin.copy_(torch.stack((tr.grad, ti.grad, gamma.grad)), non_blocking=True)
+    for _ in range(2):
+        e2e_step()
+    e2e_steps = max(3, min(args.steps, 10))
+    barrier(dist_on)
+    ms_e2e = max_over_ranks(timed_loop(e2e_step, e2e_steps, stream) / e2e_steps, dist_on, device)
+    barrier(dist_on)
+
+    if rank != 0:
+        if dist_on:
+            torch.distributed.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peaks()
+    achieved = B * L * BYTES_PER_TOKEN / (ms_per_step * 1e-3) / 1e9 if world == 1 else \
+        B * L * BYTES_PER_TOKEN / (ms_per_step * 1e-3) / 1e9
+    fwd_gbs = B * L * BYTES_PER_TOKEN_FWD / (ms_fwd * 1e-3) / 1e9
+    bwd_ms = max(ms_per_step - ms_fwd, 1e-6)
+    line = {
+        "metric": "field_tokens_per_s_fwd_bwd", "value": tokens_per_s, "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(world),
+        "roofline": {
+            "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "traffic": None, "peak_source": f"of {peak_kind}",
+            "kernel": "whole step per GPU: 3 forward + 4 backward launches",
+            "algorithmic_bytes_per_token": BYTES_PER_TOKEN,
+            "forward": {"ms": ms_fwd, "achieved": fwd_gbs, "frac": fwd_gbs / peak},
+            "backward": {"ms": bwd_ms,
+                         "achieved": B * L * BYTES_PER_TOKEN_BWD / (bwd_ms * 1e-3) / 1e9,
+                         "frac": B * L * BYTES_PER_TOKEN_BWD / (bwd_ms * 1e-3) / 1e9 / peak},
+        },
+        "e2e": {"value": world * B * L / (ms_e2e * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": raw_pin.numel() * 4 + grad_pin.numel() * 4,
+                "d2h_bytes_per_step": (read_pin.numel() + graw_pin.numel() + gpar_pin.numel()) * 4,
+                "ms_per_step": ms_e2e},
+        "gpu_launches": KERNEL_LAUNCHES_PER_STEP * args.steps,
+        "clocks": clocks.summary(),
+        "parity": parity_check(device, tr.detach(), ti.detach(), gamma.detach()),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline()
+    print(json.dumps(line), flush=True)
+    if dist_on:
+        torch.distributed.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true",
+                    help="skip the CPU baseline leg (used for profiler runs)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

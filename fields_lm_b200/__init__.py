@@ -1,0 +1,17 @@
+"""B200-native (sm_100a) replacement for the fields-lm fused Field read.
+
+Public surface:
+
+* :func:`fused_field_read` - drop-in for the reference operator of the same name;
+* :func:`field_read_with_state` - the operator with carried state in and out;
+* :func:`install` / :func:`uninstall` - rebind the operator inside a built model;
+* :mod:`fields_lm_b200.mixer` - mirror of the reference's mixer/block modules;
+* :mod:`fields_lm_b200.build` - compiles the CUDA library.
+
+The CUDA library is required: nothing here falls back to a CPU or PyTorch path.
+"""
+from .field_read import FieldReadFunction, field_read_with_state, fused_field_read
+from .install import install, uninstall
+
+__all__ = ["FieldReadFunction", "field_read_with_state", "fused_field_read", "install",
+           "uninstall"]

@@ -1,0 +1,57 @@
+"""Loads ``libfields_read.so`` and declares the C ABI of ``include/fields_read.h``.
+
+There is no fallback: if the CUDA library has not been built, loading raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "libfields_read.so"
+
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_SZ = ctypes.c_size_t
+
+# name -> (restype, argtypes); every symbol include/fields_read.h declares
+SYMBOLS = {
+    "fields_status_string": (ctypes.c_char_p, [_I]),
+    "fields_read_version": (_I, []),
+    "fields_last_cuda_error": (ctypes.c_char_p, []),
+    "fields_read_workspace_bytes": (_SZ, [_I, _I, _I, _I]),
+    "fields_read_forward": (_I, [_P] * 8 + [_SZ, _I, _I, _I, _P]),
+    "fields_read_backward": (_I, [_P] * 14 + [_SZ, _I, _I, _I, _P]),
+}
+
+_lib = None
+
+
+class FieldsLibraryError(RuntimeError):
+    """The CUDA library is missing or a call into it returned a non-zero status."""
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise FieldsLibraryError(
+            f"{LIB_PATH.name} has not been built; run `python -m fields_lm_b200.build` "
+            "(needs nvcc). There is no CPU fallback for the Field kernels.")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SYMBOLS.items():
+        fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def check(status: int, what: str) -> None:
+    if status:
+        lib = load()
+        text = lib.fields_status_string(status).decode()
+        if status == 3:
+            text += ": " + lib.fields_last_cuda_error().decode()
+        raise FieldsLibraryError(f"{what}: {text} (status {status})")

@@ -1,0 +1,214 @@
+// Scalar and small-vector arithmetic shared by every Field kernel.
+//
+// Everything here is a plain inline function of its arguments, marked for host
+// and device, so that the same source can be compiled by nvcc for sm_100a and
+// by g++ for the host-side kernel emulation used by the CPU tests
+// (FIELDS_HOST_EMU).
+//
+// Reference arithmetic being reproduced (file field_only_v4_chunked_triton_wiki100.py):
+//   gates          :493-501   inj = tanh(z_r) + i tanh(z_i), v = 0.9 sigmoid(z_v)
+//   coefficients   :497-501   a = (1 - v) lambda, b = gamma v inj
+//   compose        :503-509   (A, B) <- (a A, a B + b)
+#pragma once
+
+#include <cmath>
+#include <cstddef>
+#include <cstdint>
+#include <cstring>
+
+#ifdef FIELDS_HOST_EMU
+#define FL_HD inline
+#define FL_DEVICE_CODE 0
+#else
+#include <cuda_runtime.h>
+#define FL_HD __host__ __device__ __forceinline__
+#ifdef __CUDA_ARCH__
+#define FL_DEVICE_CODE 1
+#else
+#define FL_DEVICE_CODE 0
+#endif
+#endif
+
+namespace fields {
+
+constexpr float kVacMax = 0.90f;  // VAC_MAX, field_only_v4_chunked_triton_wiki100.py:68
+
+// ---------------------------------------------------------------------------
+// Transcendentals. exp2-based forms with one approximate reciprocal each: about
+// 2 ulp, which the recurrence carries to well under the 1e-5 parity bound. The
+// arguments are clamped so that exp never overflows to infinity.
+// ---------------------------------------------------------------------------
+FL_HD float fast_exp(float x) {
+#if FL_DEVICE_CODE
+    return __expf(x);
+#else
+    return std::exp(x);
+#endif
+}
+
+FL_HD float fast_rcp(float x) {
+#if FL_DEVICE_CODE
+    return __fdividef(1.0f, x);
+#else
+    return 1.0f / x;
+#endif
+}
+
+FL_HD float sigmoidf_fast(float x) {
+    x = fminf(fmaxf(x, -80.0f), 80.0f);
+    return fast_rcp(1.0f + fast_exp(-x));
+}
+
+// tanh(x) = 1 - 2 / (exp(2x) + 1)
+FL_HD float tanhf_fast(float x) {
+    x = fminf(fmaxf(x, -20.0f), 20.0f);
+    return 1.0f - 2.0f * fast_rcp(fast_exp(2.0f * x) + 1.0f);
+}
+
+// ---------------------------------------------------------------------------
+// Vec<V>: V consecutive channels held by one thread. V = 4 moves 128 bits per
+// access and needs 16-byte aligned addresses; V = 1 is the fallback for channel
+// counts that are not a multiple of four.
+// ---------------------------------------------------------------------------
+template <int V>
+struct Vec {
+    float v[V];
+};
+
+template <int V>
+FL_HD Vec<V> vec_fill(float x) {
+    Vec<V> r;
+#pragma unroll
+    for (int k = 0; k < V; ++k) r.v[k] = x;
+    return r;
+}
+
+// Ordinary load (data that is read again soon: stays in L2).
+template <int V>
+FL_HD Vec<V> vec_load(const float* p) {
+    Vec<V> r;
+#if FL_DEVICE_CODE
+    if constexpr (V == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
+    } else if constexpr (V == 2) {
+        const float2 t = *reinterpret_cast<const float2*>(p);
+        r.v[0] = t.x; r.v[1] = t.y;
+    } else {
+#pragma unroll
+        for (int k = 0; k < V; ++k) r.v[k] = p[k];
+    }
+#else
+    std::memcpy(r.v, p, sizeof(float) * V);
+#endif
+    return r;
+}
+
+// Streaming load (data read once: evict first).
+template <int V>
+FL_HD Vec<V> vec_load_stream(const float* p) {
+    Vec<V> r;
+#if FL_DEVICE_CODE
+    if constexpr (V == 4) {
+        const float4 t = __ldcs(reinterpret_cast<const float4*>(p));
+        r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
+    } else if constexpr (V == 2) {
+        const float2 t = __ldcs(reinterpret_cast<const float2*>(p));
+        r.v[0] = t.x; r.v[1] = t.y;
+    } else {
+#pragma unroll
+        for (int k = 0; k < V; ++k) r.v[k] = __ldcs(p + k);
+    }
+#else
+    std::memcpy(r.v, p, sizeof(float) * V);
+#endif
+    return r;
+}
+
+template <int V>
+FL_HD void vec_store(float* p, const Vec<V>& x) {
+#if FL_DEVICE_CODE
+    if constexpr (V == 4) {
+        *reinterpret_cast<float4*>(p) = make_float4(x.v[0], x.v[1], x.v[2], x.v[3]);
+    } else if constexpr (V == 2) {
+        *reinterpret_cast<float2*>(p) = make_float2(x.v[0], x.v[1]);
+    } else {
+#pragma unroll
+        for (int k = 0; k < V; ++k) p[k] = x.v[k];
+    }
+#else
+    std::memcpy(p, x.v, sizeof(float) * V);
+#endif
+}
+
+// Streaming store (output that this kernel never reads back).
+template <int V>
+FL_HD void vec_store_stream(float* p, const Vec<V>& x) {
+#if FL_DEVICE_CODE
+    if constexpr (V == 4) {
+        __stcs(reinterpret_cast<float4*>(p), make_float4(x.v[0], x.v[1], x.v[2], x.v[3]));
+    } else if constexpr (V == 2) {
+        __stcs(reinterpret_cast<float2*>(p), make_float2(x.v[0], x.v[1]));
+    } else {
+#pragma unroll
+        for (int k = 0; k < V; ++k) __stcs(p + k, x.v[k]);
+    }
+#else
+    std::memcpy(p, x.v, sizeof(float) * V);
+#endif
+}
+
+// ---------------------------------------------------------------------------
+// Per-channel gate values of one time step.
+// ---------------------------------------------------------------------------
+struct Gate {
+    float inj_r, inj_i;  // tanh(z_r), tanh(z_i)
+    float sig;           // sigmoid(z_v)
+    float vac;           // 0.9 * sig
+};
+
+FL_HD Gate make_gate(float zr, float zi, float zv) {
+    Gate g;
+    g.inj_r = tanhf_fast(zr);
+    g.inj_i = tanhf_fast(zi);
+    g.sig = sigmoidf_fast(zv);
+    g.vac = kVacMax * g.sig;
+    return g;
+}
+
+// Complex helpers on (re, im) pairs.
+FL_HD void cmul(float ar, float ai, float br, float bi, float& or_, float& oi) {
+    or_ = ar * br - ai * bi;
+    oi = ar * bi + ai * br;
+}
+// conj(a) * b
+FL_HD void cmul_conj(float ar, float ai, float br, float bi, float& or_, float& oi) {
+    or_ = ar * br + ai * bi;
+    oi = ar * bi - ai * br;
+}
+
+// Affine map s -> A s + B on one complex channel.
+struct Affine {
+    float ar, ai, br, bi;
+};
+
+FL_HD Affine affine_identity() { return Affine{1.0f, 0.0f, 0.0f, 0.0f}; }
+
+// The map "first m, then step (a, b)":  s -> a (A s + B) + b.
+FL_HD Affine affine_then(const Affine& m, float a_r, float a_i, float b_r, float b_i) {
+    Affine o;
+    o.br = a_r * m.br - a_i * m.bi + b_r;
+    o.bi = a_r * m.bi + a_i * m.br + b_i;
+    o.ar = a_r * m.ar - a_i * m.ai;
+    o.ai = a_r * m.ai + a_i * m.ar;
+    return o;
+}
+
+FL_HD void affine_apply(const Affine& m, float& sr, float& si) {
+    const float nr = m.ar * sr - m.ai * si + m.br;
+    const float ni = m.ar * si + m.ai * sr + m.bi;
+    sr = nr;
+    si = ni;
+}
+
+}  // namespace fields

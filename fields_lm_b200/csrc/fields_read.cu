@@ -1,0 +1,255 @@
+// C ABI of the Field-recurrence library: argument checks, the launch plan and
+// the kernel launches. Declarations and the contract of every entry point are
+// in include/fields_read.h.
+//
+// Compiled by nvcc for sm_100a into libfields_read.so. The CPU tests compile
+// this same file with g++ and FIELDS_HOST_EMU defined: launches then become
+// nested loops over (block, phase, thread) on host memory, so the plan, the
+// index arithmetic and the formulas are checked without a GPU. That build is
+// test infrastructure; it is never loaded by the package.
+#include "field_kernels.cuh"
+
+#include "../../include/fields_read.h"
+
+#include <vector>
+
+namespace fields {
+
+// ---------------------------------------------------------------------------
+// Launch machinery
+// ---------------------------------------------------------------------------
+#ifdef FIELDS_HOST_EMU
+
+using Stream = void*;
+static thread_local const char* g_last_error = "no error";
+
+template <class K>
+static int launch(const typename K::Params& p, long long grid, Stream) {
+    std::vector<double> smem_store((K::kSmemFloats + 1) / 2 + 1);  // double-aligned
+    float* smem = reinterpret_cast<float*>(smem_store.data());
+    for (long long block = 0; block < grid; ++block) {
+        for (int thread = 0; thread < K::kThreads; ++thread) K::phase0(p, (int)block, thread, smem);
+        if constexpr (K::kPhases > 1) {
+            for (int thread = 0; thread < K::kThreads; ++thread)
+                K::phase1(p, (int)block, thread, smem);
+        }
+    }
+    return FIELDS_OK;
+}
+
+static int fill_zero(float* p, size_t n, Stream) {
+    for (size_t i = 0; i < n; ++i) p[i] = 0.0f;
+    return FIELDS_OK;
+}
+
+#else  // real CUDA build
+
+using Stream = cudaStream_t;
+static thread_local const char* g_last_error = "no error";
+
+template <class K>
+__global__ void __launch_bounds__(K::kThreads) kernel_entry(const typename K::Params p) {
+    extern __shared__ __align__(16) float smem[];
+    K::phase0(p, (int)blockIdx.x, (int)threadIdx.x, smem);
+    if constexpr (K::kPhases > 1) {
+        __syncthreads();
+        K::phase1(p, (int)blockIdx.x, (int)threadIdx.x, smem);
+    }
+}
+
+static int check_cuda(cudaError_t e) {
+    if (e == cudaSuccess) return FIELDS_OK;
+    g_last_error = cudaGetErrorString(e);
+    return FIELDS_ERR_LAUNCH;
+}
+
+template <class K>
+static int launch(const typename K::Params& p, long long grid, Stream st) {
+    if (grid <= 0) return FIELDS_OK;
+    if (grid > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
+    kernel_entry<K><<<(unsigned)grid, K::kThreads, K::kSmemFloats * sizeof(float), st>>>(p);
+    return check_cuda(cudaGetLastError());
+}
+
+static int fill_zero(float* p, size_t n, Stream st) {
+    return check_cuda(cudaMemsetAsync(p, 0, n * sizeof(float), st));
+}
+
+#endif
+
+// ---------------------------------------------------------------------------
+// Plan: chunk length and workspace layout, a function of the extents only.
+// ---------------------------------------------------------------------------
+constexpr long long kTargetWarps = 148LL * 32;  // enough warps to fill every SM of a B200
+
+struct Plan {
+    Shape s;             // with G for the vector width in use
+    size_t plane;        // B * N * C floats
+    size_t sum_off, carry_off, partial_off;  // in floats
+    size_t fwd_floats, bwd_floats;
+};
+
+static size_t round_up(size_t x, size_t m) { return (x + m - 1) / m * m; }
+
+static Plan make_plan(int B, int L, int C, int vec) {
+    Plan pl{};
+    const int nominal_vec = (C % 4 == 0) ? 4 : 1;
+    const long long groups = (C + 32 * nominal_vec - 1) / (32 * nominal_vec);
+    int ts = 16;
+    const int candidates[3] = {64, 32, 16};
+    for (int k = 0; k < 3; ++k) {
+        const long long n = (L + candidates[k] - 1) / candidates[k];
+        if ((long long)B * n * groups >= kTargetWarps) { ts = candidates[k]; break; }
+    }
+    pl.s.B = B; pl.s.L = L; pl.s.C = C;
+    pl.s.ts = ts;
+    pl.s.N = (L + ts - 1) / ts;
+    pl.s.G = (C + 32 * vec - 1) / (32 * vec);
+    pl.plane = (size_t)B * pl.s.N * C;
+    pl.sum_off = 0;
+    pl.carry_off = round_up(4 * pl.plane, 64);
+    pl.partial_off = pl.carry_off + round_up(2 * pl.plane, 64);
+    pl.fwd_floats = pl.partial_off;
+    pl.bwd_floats = pl.partial_off + round_up(3 * pl.plane, 64);
+    return pl;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static long long tile_blocks(const Shape& s) {
+    const long long tasks = (long long)s.B * s.N * s.G;
+    return (tasks + kWarpsPerBlock - 1) / kWarpsPerBlock;
+}
+
+template <int VEC>
+static int run_forward(const FwdParams& p, Stream st) {
+    const Shape& s = p.s;
+    int rc = launch<FwdSummary<VEC, 4>>(p, tile_blocks(s), st);
+    if (rc) return rc;
+    CarryScan<false>::Params cp{p.sum, p.carry, p.state_in, nullptr, s};
+    rc = launch<CarryScan<false>>(cp, (long long)s.B * ((s.C + 31) / 32), st);
+    if (rc) return rc;
+    return launch<FwdMaterialize<VEC, 4>>(p, tile_blocks(s), st);
+}
+
+template <int VEC>
+static int run_backward(const BwdParams& p, Stream st) {
+    const Shape& s = p.s;
+    int rc = launch<BwdSummary<VEC, 4>>(p, tile_blocks(s), st);
+    if (rc) return rc;
+    CarryScan<true>::Params cp{p.sum, p.carry, p.grad_state_out, p.grad_state_in, s};
+    rc = launch<CarryScan<true>>(cp, (long long)s.B * ((s.C + 31) / 32), st);
+    if (rc) return rc;
+    rc = launch<BwdMaterialize<VEC, 2>>(p, tile_blocks(s), st);
+    if (rc) return rc;
+    return launch<BwdReduce>(p, 3LL * ((s.C + 31) / 32), st);
+}
+
+}  // namespace fields
+
+using namespace fields;
+
+extern "C" {
+
+const char* fields_status_string(int status) {
+    switch (status) {
+        case FIELDS_OK: return "ok";
+        case FIELDS_ERR_ARGUMENT: return "invalid argument (null pointer or bad extent)";
+        case FIELDS_ERR_WORKSPACE: return "workspace missing, too small or not 256-byte aligned";
+        case FIELDS_ERR_LAUNCH: return "CUDA launch failed";
+        case FIELDS_ERR_TIMEOUT: return "device-side wait timed out";
+        case FIELDS_ERR_UNSUPPORTED: return "unsupported extent";
+        default: return "unknown status";
+    }
+}
+
+int fields_read_version(void) { return 100; }
+
+const char* fields_last_cuda_error(void) { return g_last_error; }
+
+size_t fields_read_workspace_bytes(int B, int L, int C, int pass) {
+    if (B <= 0 || L <= 0 || C <= 0) return 0;
+    const Plan pl = make_plan(B, L, C, 1);
+    const size_t floats = pass == FIELDS_PASS_BACKWARD ? pl.bwd_floats : pl.fwd_floats;
+    return floats * sizeof(float);
+}
+
+int fields_read_forward(const float* raw, const float* tr, const float* ti, const float* gamma,
+                        const float* state_in, float* read, float* state_out, void* workspace,
+                        size_t workspace_bytes, int B, int L, int C, void* stream) {
+    if (B < 0 || L < 0 || C <= 0) return FIELDS_ERR_ARGUMENT;
+    Stream st = reinterpret_cast<Stream>(stream);
+    if (B == 0) return FIELDS_OK;
+    if (!tr || !ti || !gamma) return FIELDS_ERR_ARGUMENT;
+    if (L == 0) {
+        // no steps: the state passes through unchanged
+        if (state_out) {
+            if (!state_in) return fill_zero(state_out, (size_t)B * 2 * C, st);
+#ifdef FIELDS_HOST_EMU
+            std::memcpy(state_out, state_in, (size_t)B * 2 * C * sizeof(float));
+#else
+            return check_cuda(cudaMemcpyAsync(state_out, state_in, (size_t)B * 2 * C * sizeof(float),
+                                              cudaMemcpyDeviceToDevice, st));
+#endif
+        }
+        return FIELDS_OK;
+    }
+    if (!raw || !read) return FIELDS_ERR_ARGUMENT;
+    const bool vec4 = C % 4 == 0 && aligned16(raw) && aligned16(read) && aligned16(tr) &&
+                      aligned16(ti) && aligned16(gamma) && aligned16(state_in) &&
+                      aligned16(state_out) && aligned16(workspace);
+    const Plan pl = make_plan(B, L, C, vec4 ? 4 : 1);
+    if (!workspace || workspace_bytes < pl.fwd_floats * sizeof(float) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return FIELDS_ERR_WORKSPACE;
+    float* ws = static_cast<float*>(workspace);
+    FwdParams p{raw, tr, ti, gamma, state_in, read, state_out,
+                ws + pl.sum_off, ws + pl.carry_off, pl.s};
+    return vec4 ? run_forward<4>(p, st) : run_forward<1>(p, st);
+}
+
+int fields_read_backward(const float* raw, const float* tr, const float* ti, const float* gamma,
+                         const float* state_in, const float* read, const float* grad_read,
+                         const float* grad_state_out, float* grad_raw, float* grad_tr,
+                         float* grad_ti, float* grad_gamma, float* grad_state_in, void* workspace,
+                         size_t workspace_bytes, int B, int L, int C, void* stream) {
+    if (B < 0 || L < 0 || C <= 0) return FIELDS_ERR_ARGUMENT;
+    if (!grad_tr || !grad_ti || !grad_gamma) return FIELDS_ERR_ARGUMENT;
+    Stream st = reinterpret_cast<Stream>(stream);
+    if (B == 0 || L == 0) {
+        // nothing depends on the parameters; the state gradient passes through
+        int rc = fill_zero(grad_tr, C, st);
+        if (!rc) rc = fill_zero(grad_ti, C, st);
+        if (!rc) rc = fill_zero(grad_gamma, C, st);
+        if (!rc && grad_state_in && B > 0) {
+            if (!grad_state_out) {
+                rc = fill_zero(grad_state_in, (size_t)B * 2 * C, st);
+            } else {
+#ifdef FIELDS_HOST_EMU
+                std::memcpy(grad_state_in, grad_state_out, (size_t)B * 2 * C * sizeof(float));
+#else
+                rc = check_cuda(cudaMemcpyAsync(grad_state_in, grad_state_out,
+                                                (size_t)B * 2 * C * sizeof(float),
+                                                cudaMemcpyDeviceToDevice, st));
+#endif
+            }
+        }
+        return rc;
+    }
+    if (!raw || !tr || !ti || !gamma || !read || !grad_read || !grad_raw)
+        return FIELDS_ERR_ARGUMENT;
+    const bool vec4 = C % 4 == 0 && aligned16(raw) && aligned16(read) && aligned16(grad_read) &&
+                      aligned16(grad_raw) && aligned16(tr) && aligned16(ti) && aligned16(gamma) &&
+                      aligned16(state_in) && aligned16(workspace);
+    const Plan pl = make_plan(B, L, C, vec4 ? 4 : 1);
+    if (!workspace || workspace_bytes < pl.bwd_floats * sizeof(float) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return FIELDS_ERR_WORKSPACE;
+    float* ws = static_cast<float*>(workspace);
+    BwdParams p{raw, tr, ti, gamma, state_in, read, grad_read, grad_state_out, grad_raw,
+                grad_state_in, ws + pl.sum_off, ws + pl.carry_off, ws + pl.partial_off,
+                grad_tr, grad_ti, grad_gamma, pl.s};
+    return vec4 ? run_backward<4>(p, st) : run_backward<1>(p, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,111 @@
+"""``fused_field_read`` on the CUDA library: the drop-in for the reference's operator.
+
+Mirrors ``_ChunkedFieldReadFunction`` / ``fused_field_read`` of the reference
+(``field_only_v4_chunked_triton_wiki100.py:912-1123``): same arguments, same
+output layout, same gradients, same argument errors. ``block_c`` and ``chunk_t``
+are launch hints of the reference's Triton kernels and are accepted and ignored.
+
+``field_read_with_state`` is the same operator with an incoming state and the
+outgoing state returned - what the sequence-sharded forward and incremental
+decoding need; the reference always starts from the zero state.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_FWD, _BWD = 0, 1
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _workspace(B: int, L: int, C: int, which: int, device) -> Tuple[torch.Tensor, int]:
+    nbytes = _lib.load().fields_read_workspace_bytes(B, L, C, which)
+    # the caching allocator hands out 512-byte aligned blocks
+    return torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device), nbytes
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class FieldReadFunction(torch.autograd.Function):
+    """read, state_out = F(raw, tr, ti, gamma, state_in)."""
+
+    @staticmethod
+    def forward(ctx, raw, transition_r, transition_i, gamma, state_in):
+        if not raw.is_cuda:
+            raise RuntimeError("Chunked Field kernel requires CUDA")
+        if raw.dtype != torch.float32:
+            raise TypeError(f"raw must be float32, got {raw.dtype}")
+        if raw.dim() != 3:
+            raise ValueError(tuple(raw.shape))
+        raw = raw.contiguous()
+        tr = transition_r.contiguous().float()
+        ti = transition_i.contiguous().float()
+        gm = gamma.contiguous().float()
+        B, L, three_c = raw.shape
+        if three_c % 3:
+            raise ValueError(tuple(raw.shape))
+        C = three_c // 3
+        if tr.numel() != C or ti.numel() != C or gm.numel() != C:
+            raise ValueError((tuple(raw.shape), tuple(tr.shape)))
+        if state_in is not None:
+            if tuple(state_in.shape) != (B, 2 * C):
+                raise ValueError((tuple(raw.shape), tuple(state_in.shape)))
+            state_in = state_in.contiguous().float()
+        lib = _lib.load()
+        with torch.cuda.device(raw.device):
+            read = torch.empty((B, L, 4 * C), device=raw.device, dtype=torch.float32)
+            state_out = torch.empty((B, 2 * C), device=raw.device, dtype=torch.float32)
+            ws, nbytes = _workspace(B, L, C, _FWD, raw.device)
+            rc = lib.fields_read_forward(_ptr(raw), _ptr(tr), _ptr(ti), _ptr(gm), _ptr(state_in),
+                                         _ptr(read), _ptr(state_out), _ptr(ws), nbytes,
+                                         B, L, C, _stream(raw.device))
+        _lib.check(rc, "fields_read_forward")
+        ctx.set_materialize_grads(False)
+        ctx.save_for_backward(raw, tr, ti, gm, read, state_in)
+        ctx.dims = (B, L, C)
+        return read, state_out
+
+    @staticmethod
+    def backward(ctx, grad_read, grad_state_out):
+        raw, tr, ti, gm, read, state_in = ctx.saved_tensors
+        B, L, C = ctx.dims
+        lib = _lib.load()
+        with torch.cuda.device(raw.device):
+            if grad_read is None:
+                grad_read = torch.zeros_like(read)
+            grad_read = grad_read.contiguous().float()
+            if grad_state_out is not None:
+                grad_state_out = grad_state_out.contiguous().float()
+            grad_raw = torch.empty_like(raw)
+            g_par = torch.empty((3, C), device=raw.device, dtype=torch.float32)
+            g_sin = (torch.empty((B, 2 * C), device=raw.device, dtype=torch.float32)
+                     if state_in is not None and ctx.needs_input_grad[4] else None)
+            ws, nbytes = _workspace(B, L, C, _BWD, raw.device)
+            rc = lib.fields_read_backward(
+                _ptr(raw), _ptr(tr), _ptr(ti), _ptr(gm), _ptr(state_in), _ptr(read),
+                _ptr(grad_read), _ptr(grad_state_out), _ptr(grad_raw), _ptr(g_par[0]),
+                _ptr(g_par[1]), _ptr(g_par[2]), _ptr(g_sin), _ptr(ws), nbytes, B, L, C,
+                _stream(raw.device))
+        _lib.check(rc, "fields_read_backward")
+        return grad_raw, g_par[0], g_par[1], g_par[2], g_sin
+
+
+def fused_field_read(raw: torch.Tensor, transition_r: torch.Tensor, transition_i: torch.Tensor,
+                     gamma: torch.Tensor, block_c: int = 32, chunk_t: int = 64) -> torch.Tensor:
+    """Drop-in for the reference's ``fused_field_read``; returns ``read [B, L, 4C]`` fp32."""
+    read, _ = FieldReadFunction.apply(raw, transition_r, transition_i, gamma, None)
+    return read
+
+
+def field_read_with_state(raw, transition_r, transition_i, gamma,
+                          state_in: Optional[torch.Tensor] = None):
+    """Same operator with a carried state: returns ``(read, state_out [B, 2C])``."""
+    return FieldReadFunction.apply(raw, transition_r, transition_i, gamma, state_in)

@@ -1,0 +1,114 @@
+"""Host-side mirror of the reference's Field mixer and Field block.
+
+Same parameters, names, initialisation order and arithmetic as
+``IndependentVacancyField`` and ``FieldBlock``
+(``field_only_v4_chunked_triton_wiki100.py:1131-1221``), so a ``state_dict`` moves
+between the two unchanged and a block built under the same seed holds the same
+weights. The recurrence is the CUDA operator; the three projections, the RMS
+norms and the SwiGLU feed-forward stay PyTorch library calls, as in the
+reference. It exists so that the block-level call site can be exercised where the
+reference checkout is not present; with the reference at hand, use
+``fields_lm_b200.install`` on the reference's own modules instead.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .field_read import field_read_with_state, fused_field_read
+
+
+class RMSNorm(nn.Module):
+    """fp32 RMS norm with a learned scale (reference :300-309)."""
+
+    def __init__(self, dim: int, eps: float = 1e-6):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.eps = eps
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        xf = x.float()
+        inv = torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + self.eps)
+        return (xf * inv * self.weight.float()).to(x.dtype)
+
+
+class PackedSwiGLU(nn.Module):
+    """SwiGLU feed-forward with gate and value in one projection (reference :312-325)."""
+
+    def __init__(self, dim: int, hidden: Optional[int] = None):
+        super().__init__()
+        self.hidden = int(hidden) if hidden is not None else ((int(8 * dim / 3) + 63) // 64) * 64
+        self.w12 = nn.Linear(dim, 2 * self.hidden, bias=False)
+        self.w3 = nn.Linear(self.hidden, dim, bias=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        gate, value = self.w12(x).chunk(2, dim=-1)
+        return self.w3(F.silu(gate) * value)
+
+
+def transition_parameters(radius_logit: torch.Tensor, theta: torch.Tensor):
+    """``lambda = r e^{i theta}``, ``gamma = sqrt(max(1 - r^2, 1e-4))`` (reference :1169-1173)."""
+    radius = torch.sigmoid(radius_logit).clamp(0.50, 0.99995).float()
+    theta = theta.float()
+    return (radius * torch.cos(theta), radius * torch.sin(theta),
+            torch.sqrt((1.0 - radius.square()).clamp_min(1e-4)))
+
+
+class IndependentVacancyField(nn.Module):
+    """Field mixer: write projection -> recurrence -> norm, output projection, gate, residual."""
+
+    def __init__(self, dim: int, backend: str = "triton", field_chunk: int = 32,
+                 triton_block_c: int = 32, triton_chunk_t: int = 64):
+        super().__init__()
+        if dim % 2:
+            raise ValueError("Field dim must be even")
+        if backend not in ("reference", "triton"):
+            raise ValueError(backend)
+        self.dim = dim
+        self.channels = dim // 2
+        self.backend = backend
+        self.field_chunk = int(field_chunk)
+        self.triton_block_c = int(triton_block_c)
+        self.triton_chunk_t = int(triton_chunk_t)
+        self.write_proj = nn.Linear(dim, dim + self.channels)
+        ring = torch.linspace(0.85, 0.999, self.channels)
+        self.radius_logit = nn.Parameter(torch.log(ring / (1.0 - ring)))
+        self.theta = nn.Parameter(torch.linspace(0.03, math.pi * 0.97, self.channels))
+        self.read_norm = RMSNorm(2 * dim)
+        self.out_proj = nn.Linear(2 * dim, dim)
+        self.gate_proj = nn.Linear(dim, dim)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raw = self.write_proj(x).contiguous().float()
+        tr, ti, gamma = transition_parameters(self.radius_logit, self.theta)
+        read = fused_field_read(raw, tr, ti, gamma, self.triton_block_c, self.triton_chunk_t)
+        out = self.out_proj(self.read_norm(read))
+        return x + (out * torch.sigmoid(self.gate_proj(x))).to(x.dtype)
+
+    def forward_with_state(self, x: torch.Tensor, state_in: Optional[torch.Tensor] = None):
+        """Same as ``forward`` for a span that continues from ``state_in``; also returns the end state."""
+        raw = self.write_proj(x).contiguous().float()
+        tr, ti, gamma = transition_parameters(self.radius_logit, self.theta)
+        read, state_out = field_read_with_state(raw, tr, ti, gamma, state_in)
+        out = self.out_proj(self.read_norm(read))
+        return x + (out * torch.sigmoid(self.gate_proj(x))).to(x.dtype), state_out
+
+
+class FieldBlock(nn.Module):
+    """Field mixer followed by a pre-norm SwiGLU feed-forward (reference :1198-1221)."""
+
+    def __init__(self, dim: int, backend: str = "triton", field_chunk: int = 32,
+                 triton_block_c: int = 32, triton_chunk_t: int = 64, ff_hidden: Optional[int] = None):
+        super().__init__()
+        self.mixer = IndependentVacancyField(dim, backend, field_chunk, triton_block_c,
+                                             triton_chunk_t)
+        self.ff_norm = RMSNorm(dim)
+        self.ff = PackedSwiGLU(dim, hidden=ff_hidden)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        x = self.mixer(x)
+        return x + self.ff(self.ff_norm(x))

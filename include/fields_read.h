@@ -1,0 +1,100 @@
+/*
+ * fields_read.h - C ABI of the B200 (sm_100a) Field-recurrence library.
+ *
+ * The library replaces one operator of Multisymboliccore/fields-lm: the fused
+ * Field read, `fused_field_read(raw, transition_r, transition_i, gamma,
+ * block_c, chunk_t)` (src/fields_official/reference/
+ * field_only_v4_chunked_triton_wiki100.py:1108-1123), forward and backward.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer to memory owned by the caller; the
+ *     library allocates nothing, frees nothing and keeps no state between calls;
+ *   - all tensors are contiguous float32 with the reference's layouts, channel
+ *     fastest:  raw [B, L, 3C] = z_r | z_i | z_v,   read [B, L, 4C] =
+ *     Re s | Im s | Re d | Im d,   states [B, 2C] = Re s | Im s;
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it and the
+ *     call returns without synchronising;
+ *   - the return value is a status code (0 = success); nothing aborts, traps or
+ *     asserts on the device;
+ *   - `workspace` must hold at least fields_read_workspace_bytes(...) bytes and
+ *     be 256-byte aligned; its contents are scratch.
+ *   - 128-bit accesses are used when C is a multiple of 4 and every tensor
+ *     pointer is 16-byte aligned; otherwise a scalar path with identical results
+ *     runs.
+ */
+#ifndef FIELDS_READ_H_
+#define FIELDS_READ_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum fields_status {
+    FIELDS_OK = 0,
+    FIELDS_ERR_ARGUMENT = 1,  /* null pointer or negative / zero extent */
+    FIELDS_ERR_WORKSPACE = 2, /* workspace missing, too small or misaligned */
+    FIELDS_ERR_LAUNCH = 3,    /* the CUDA runtime refused a launch (see fields_last_cuda_error) */
+    FIELDS_ERR_TIMEOUT = 4,   /* a bounded device-side wait ran out */
+    FIELDS_ERR_UNSUPPORTED = 5
+};
+
+/* which pass a workspace is sized for */
+enum fields_pass {
+    FIELDS_PASS_FORWARD = 0,
+    FIELDS_PASS_BACKWARD = 1
+};
+
+/* Human-readable text for a status code. Never null. */
+const char *fields_status_string(int status);
+
+/* Library version as major * 10000 + minor * 100 + patch. */
+int fields_read_version(void);
+
+/* Bytes of scratch the given pass needs for these extents (0 for empty inputs). */
+size_t fields_read_workspace_bytes(int B, int L, int C, int pass);
+
+/*
+ * Forward of the fused Field read. Replaces _ChunkedFieldReadFunction.forward
+ * (field_only_v4_chunked_triton_wiki100.py:912-1018): gates, independent
+ * vacancy, complex diagonal recurrence and displaced readout.
+ *   raw        [B, L, 3C]
+ *   tr, ti, gamma [C]      lambda = tr + i ti
+ *   state_in   [B, 2C] or NULL  (NULL = zero state, the reference's contract,
+ *                                 same file :535-536)
+ *   read       [B, L, 4C]  output
+ *   state_out  [B, 2C] or NULL  state after the last step (extension)
+ */
+int fields_read_forward(const float *raw, const float *tr, const float *ti,
+                        const float *gamma, const float *state_in, float *read,
+                        float *state_out, void *workspace, size_t workspace_bytes,
+                        int B, int L, int C, void *stream);
+
+/*
+ * Backward of the fused Field read. Replaces _ChunkedFieldReadFunction.backward
+ * (field_only_v4_chunked_triton_wiki100.py:1020-1105) including the three
+ * sums over (batch, chunk) that follow it (:1098-1105).
+ *   read            saved forward output [B, L, 4C] (source of s_{t-1})
+ *   grad_read       [B, L, 4C]
+ *   grad_state_out  [B, 2C] or NULL  gradient flowing into state_out (extension)
+ *   grad_raw        [B, L, 3C] output
+ *   grad_tr, grad_ti, grad_gamma  [C] outputs (overwritten, not accumulated)
+ *   grad_state_in   [B, 2C] or NULL  output (extension)
+ */
+int fields_read_backward(const float *raw, const float *tr, const float *ti,
+                         const float *gamma, const float *state_in,
+                         const float *read, const float *grad_read,
+                         const float *grad_state_out, float *grad_raw,
+                         float *grad_tr, float *grad_ti, float *grad_gamma,
+                         float *grad_state_in, void *workspace,
+                         size_t workspace_bytes, int B, int L, int C, void *stream);
+
+/* Text of the last CUDA runtime error seen by the calling thread inside this library. */
+const char *fields_last_cuda_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FIELDS_READ_H_ */

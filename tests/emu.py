@@ -1,0 +1,118 @@
+"""Host emulation of the CUDA library for the CPU test-suite (test infrastructure).
+
+Compiles ``fields_lm_b200/csrc/fields_read.cu`` with g++ and FIELDS_HOST_EMU:
+every kernel launch becomes a loop over (block, phase, thread) on host memory.
+The exported C ABI is the same, so the tests drive it exactly as they drive the
+CUDA library, with numpy arrays in place of device buffers. The package never
+loads this build.
+"""
+from __future__ import annotations
+
+import ctypes
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent.parent
+SRC = ROOT / "fields_lm_b200" / "csrc" / "fields_read.cu"
+OUT = ROOT / "tests" / "_emu" / "libfields_read_emu.so"
+_LIB = None
+
+P = ctypes.c_void_p
+I = ctypes.c_int
+SZ = ctypes.c_size_t
+
+
+def build() -> Path:
+    deps = list((ROOT / "fields_lm_b200" / "csrc").glob("*")) + [ROOT / "include" / "fields_read.h"]
+    if OUT.exists() and OUT.stat().st_mtime >= max(d.stat().st_mtime for d in deps):
+        return OUT
+    OUT.parent.mkdir(parents=True, exist_ok=True)
+    cmd = ["g++", "-x", "c++", "-std=c++17", "-O2", "-fPIC", "-shared", "-DFIELDS_HOST_EMU",
+           "-Wall", "-Wno-unknown-pragmas", "-Wno-maybe-uninitialized", "-o", str(OUT), str(SRC)]
+    subprocess.run(cmd, check=True)
+    return OUT
+
+
+def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
+    """ctypes signatures of include/fields_read.h (shared with the real library's tests)."""
+    lib.fields_status_string.argtypes = [I]
+    lib.fields_status_string.restype = ctypes.c_char_p
+    lib.fields_read_version.restype = I
+    lib.fields_read_workspace_bytes.argtypes = [I, I, I, I]
+    lib.fields_read_workspace_bytes.restype = SZ
+    lib.fields_read_forward.argtypes = [P] * 8 + [SZ, I, I, I, P]
+    lib.fields_read_forward.restype = I
+    lib.fields_read_backward.argtypes = [P] * 14 + [SZ, I, I, I, P]
+    lib.fields_read_backward.restype = I
+    return lib
+
+
+def lib() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        _LIB = declare(ctypes.CDLL(str(build())))
+    return _LIB
+
+
+def _aligned(nbytes: int, align: int = 256) -> np.ndarray:
+    buf = np.zeros(nbytes + align, dtype=np.uint8)
+    off = (-buf.ctypes.data) % align
+    return buf[off:off + nbytes]
+
+
+def _f32(x, align=256):
+    x = np.asarray(x, dtype=np.float32)
+    out = _aligned(max(x.nbytes, 4), align).view(np.float32)[:x.size].reshape(x.shape)
+    out[...] = x
+    return out
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(P)
+
+
+def forward(raw, tr, ti, gamma, state_in=None, want_state=True, misalign=False):
+    """Runs the emulated forward. ``misalign`` offsets raw by 4 bytes to force the scalar path."""
+    B, L, C3 = raw.shape
+    C = tr.size
+    if misalign:
+        store = _f32(np.concatenate([[0.0], np.asarray(raw, np.float32).ravel()]))
+        raw_a = store[1:].reshape(raw.shape)
+    else:
+        raw_a = _f32(raw)
+    tr_a, ti_a, gm_a = _f32(tr), _f32(ti), _f32(gamma)
+    sin_a = None if state_in is None else _f32(state_in)
+    read = _f32(np.full((B, L, 4 * C), np.nan))
+    sout = _f32(np.full((B, 2 * C), np.nan)) if want_state else None
+    nbytes = lib().fields_read_workspace_bytes(B, L, C, 0)
+    ws = _aligned(max(nbytes, 256))
+    ws[...] = 0xFF  # poison: nothing may rely on a zeroed workspace
+    rc = lib().fields_read_forward(_ptr(raw_a), _ptr(tr_a), _ptr(ti_a), _ptr(gm_a), _ptr(sin_a),
+                                   _ptr(read), _ptr(sout), _ptr(ws), nbytes, B, L, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return read, sout
+
+
+def backward(raw, tr, ti, gamma, read, grad_read, state_in=None, grad_state_out=None):
+    B, L, C3 = raw.shape
+    C = tr.size
+    a = [_f32(x) for x in (raw, tr, ti, gamma)]
+    sin_a = None if state_in is None else _f32(state_in)
+    gso_a = None if grad_state_out is None else _f32(grad_state_out)
+    read_a, gr_a = _f32(read), _f32(grad_read)
+    g_raw = _f32(np.full((B, L, 3 * C), np.nan))
+    g_tr, g_ti, g_gm = (_f32(np.full(C, np.nan)) for _ in range(3))
+    g_sin = _f32(np.full((B, 2 * C), np.nan))
+    nbytes = lib().fields_read_workspace_bytes(B, L, C, 1)
+    ws = _aligned(max(nbytes, 256))
+    ws[...] = 0xFF
+    rc = lib().fields_read_backward(_ptr(a[0]), _ptr(a[1]), _ptr(a[2]), _ptr(a[3]), _ptr(sin_a),
+                                    _ptr(read_a), _ptr(gr_a), _ptr(gso_a), _ptr(g_raw), _ptr(g_tr),
+                                    _ptr(g_ti), _ptr(g_gm), _ptr(g_sin), _ptr(ws), nbytes,
+                                    B, L, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return g_raw, g_tr, g_ti, g_gm, g_sin

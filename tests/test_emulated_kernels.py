@@ -1,0 +1,104 @@
+"""Runs the CUDA kernels' own source on the host (see tests/emu.py) against the oracle.
+
+This checks, without a GPU, the launch plan, every index computation and every
+formula of the shipped kernels. The fp32 parity bound (1e-5 relative) is applied
+here too.
+"""
+import numpy as np
+import pytest
+
+import emu
+from conftest import FP32_TOL, rel_err
+from oracle import field_oracle
+
+
+def _params(C, rng):
+    radius = rng.uniform(0.5, 0.99995, C).astype(np.float32)
+    theta = rng.uniform(-np.pi, np.pi, C).astype(np.float32)
+    return (radius * np.cos(theta)).astype(np.float32), (radius * np.sin(theta)).astype(np.float32), \
+        np.sqrt(np.maximum(1 - radius ** 2, 1e-4)).astype(np.float32)
+
+
+SHAPES = [(1, 1, 4), (2, 37, 32), (3, 130, 20), (1, 64, 4), (2, 65, 12), (2, 33, 7),
+          (1, 48, 160), (1, 300, 132), (2, 16, 512), (5, 17, 1)]
+
+
+@pytest.mark.parametrize("B,L,C", SHAPES)
+@pytest.mark.parametrize("with_state", [False, True])
+def test_forward_backward_against_oracle(B, L, C, with_state):
+    rng = np.random.default_rng(B * 1000 + L * 10 + C)
+    tr, ti, gm = _params(C, rng)
+    raw = (rng.standard_normal((B, L, 3 * C)) * 1.5).astype(np.float32)
+    grad_read = rng.standard_normal((B, L, 4 * C)).astype(np.float32)
+    s_in = rng.standard_normal((B, 2 * C)).astype(np.float32) if with_state else None
+    g_out = rng.standard_normal((B, 2 * C)).astype(np.float32) if with_state else None
+
+    ref_read, ref_state = field_oracle.forward(raw, tr, ti, gm, state_in=s_in)
+    read, state = emu.forward(raw, tr, ti, gm, state_in=s_in)
+    assert rel_err(read, ref_read) < FP32_TOL
+    assert rel_err(state, ref_state) < FP32_TOL
+
+    ref = field_oracle.backward(raw, tr, ti, gm, grad_read, state_in=s_in, grad_state_out=g_out)
+    got = emu.backward(raw, tr, ti, gm, read, grad_read, state_in=s_in, grad_state_out=g_out)
+    names = ("grad_raw", "grad_tr", "grad_ti", "grad_gamma", "grad_state_in")
+    for name, a, b in zip(names, got, ref):
+        assert rel_err(a, b) < FP32_TOL, name
+
+
+def test_scalar_path_equals_vector_path():
+    rng = np.random.default_rng(3)
+    B, L, C = 2, 70, 24
+    tr, ti, gm = _params(C, rng)
+    raw = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+    a, sa = emu.forward(raw, tr, ti, gm)
+    b, sb = emu.forward(raw, tr, ti, gm, misalign=True)
+    np.testing.assert_array_equal(a, b)
+    np.testing.assert_array_equal(sa, sb)
+
+
+def test_golden_small_cases(golden_small):
+    for name in golden_small["cases"]:
+        c = {k: golden_small[f"{name}/{k}"] for k in
+             ("raw", "tr", "ti", "gamma", "grad_read", "read", "grad_raw", "grad_tr", "grad_ti",
+              "grad_gamma")}
+        read, _ = emu.forward(c["raw"], c["tr"], c["ti"], c["gamma"])
+        assert rel_err(read, c["read"]) < FP32_TOL, name
+        g = emu.backward(c["raw"], c["tr"], c["ti"], c["gamma"], read, c["grad_read"])
+        assert rel_err(g[0], c["grad_raw"]) < FP32_TOL, name
+        assert rel_err(g[1], c["grad_tr"]) < FP32_TOL, name
+        assert rel_err(g[2], c["grad_ti"]) < FP32_TOL, name
+        assert rel_err(g[3], c["grad_gamma"]) < FP32_TOL, name
+
+
+def test_long_sequence_many_chunks():
+    """More chunks than carry-scan warps, ragged tail, several channel groups."""
+    rng = np.random.default_rng(9)
+    B, L, C = 1, 16 * 37 + 5, 136
+    tr, ti, gm = _params(C, rng)
+    raw = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+    ref, _ = field_oracle.forward(raw, tr, ti, gm)
+    read, _ = emu.forward(raw, tr, ti, gm)
+    assert rel_err(read, ref) < FP32_TOL
+
+
+def test_empty_inputs():
+    C = 8
+    tr = ti = gm = np.ones(C, np.float32)
+    read, state = emu.forward(np.zeros((2, 0, 3 * C), np.float32), tr, ti, gm,
+                              state_in=np.full((2, 2 * C), 3.0, np.float32))
+    assert read.shape == (2, 0, 4 * C)
+    np.testing.assert_array_equal(state, 3.0)
+    g = emu.backward(np.zeros((2, 0, 3 * C), np.float32), tr, ti, gm,
+                     np.zeros((2, 0, 4 * C), np.float32), np.zeros((2, 0, 4 * C), np.float32),
+                     grad_state_out=np.full((2, 2 * C), 2.0, np.float32))
+    np.testing.assert_array_equal(g[1], 0.0)
+    np.testing.assert_array_equal(g[4], 2.0)
+
+
+def test_bad_arguments_return_status():
+    L = emu.lib()
+    assert L.fields_read_forward(None, None, None, None, None, None, None, None, 0, 1, 4, 4, None) == 1
+    assert L.fields_read_forward(None, None, None, None, None, None, None, None, 0, 1, 4, 0, None) == 1
+    assert L.fields_read_workspace_bytes(0, 5, 4, 0) == 0
+    assert L.fields_read_workspace_bytes(2, 100, 512, 1) > L.fields_read_workspace_bytes(2, 100, 512, 0)
+    assert b"workspace" in L.fields_status_string(2)
