@@ -277,6 +277,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     step = lambda: gpu_step(raw, grad_read, tr, ti, gamma)
     for _ in range(max(args.warmup, 3)):
         step()
+    if args.profile:
+        # short path for profiler captures: a few plain steps, no host work, no JSON line
+        for _ in range(args.steps):
+            step()
+        torch.cuda.synchronize()
+        print(f"profile run: {args.steps} steps done")
+        return
     with ClockSampler(local_rank) as clocks:
         barrier(dist_on)
         ms = timed_loop(step, args.steps, stream)
@@ -369,6 +376,8 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true",
                     help="skip the CPU baseline leg (used for profiler runs)")
+    ap.add_argument("--profile", action="store_true",
+                    help="run warm-up + steps only (for ncu captures); prints no bench line")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
