@@ -19,8 +19,8 @@
  *   - `workspace` must hold at least fields_read_workspace_bytes(...) bytes and
  *     be 256-byte aligned; its contents are scratch.
  *   - 128-bit accesses are used when C is a multiple of 4 and every tensor
- *     pointer is 16-byte aligned; otherwise a scalar path with identical results
- *     runs.
+ *     pointer is 16-byte aligned; otherwise a scalar path with the same arithmetic
+ *     (equal up to the last bit or two) runs.
  */
 #ifndef FIELDS_READ_H_
 #define FIELDS_READ_H_
