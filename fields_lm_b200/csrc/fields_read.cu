@@ -11,6 +11,7 @@
 
 #include "../../include/fields_read.h"
 
+#include <mutex>
 #include <vector>
 
 namespace fields {
@@ -145,6 +146,47 @@ static int run_backward(const BwdParams& p, Stream st) {
     return launch<BwdReduce>(p, 3LL * ((s.C + 31) / 32), st);
 }
 
+
+// ---------------------------------------------------------------------------
+// Built-in scratch for fields_read_forward_noalloc: one fixed buffer per GPU that
+// has loaded this library, held until the process exits.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = FIELDS_STATIC_SCRATCH_BYTES;
+
+#ifdef FIELDS_HOST_EMU
+alignas(256) static unsigned char g_static_scratch[kStaticScratchBytes];
+
+static int static_scratch(float** out) {
+    *out = reinterpret_cast<float*>(g_static_scratch);
+    return FIELDS_OK;
+}
+#else
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_scratch_mutex;
+static float* g_scratch_ptr[kMaxDevices] = {};
+
+// In host code `g_static_scratch` is only a handle for the runtime, not an address a
+// kernel may use: the device address is looked up once per device, with that device
+// current, and cached.
+static int static_scratch(float** out) {
+    int dev = -1;
+    int rc = check_cuda(cudaGetDevice(&dev));
+    if (rc) return rc;
+    if (dev < 0 || dev >= kMaxDevices) return FIELDS_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (!g_scratch_ptr[dev]) {
+        void* p = nullptr;
+        rc = check_cuda(cudaGetSymbolAddress(&p, g_static_scratch));
+        if (rc) return rc;
+        g_scratch_ptr[dev] = static_cast<float*>(p);
+    }
+    *out = g_scratch_ptr[dev];
+    return FIELDS_OK;
+}
+#endif
+
 }  // namespace fields
 
 using namespace fields;
@@ -159,6 +201,8 @@ const char* fields_status_string(int status) {
         case FIELDS_ERR_LAUNCH: return "CUDA launch failed";
         case FIELDS_ERR_TIMEOUT: return "device-side wait timed out";
         case FIELDS_ERR_UNSUPPORTED: return "unsupported extent";
+        case FIELDS_ERR_SCRATCH_LIMIT:
+            return "extents need more scratch than the built-in static buffer holds";
         default: return "unknown status";
     }
 }
@@ -250,6 +294,24 @@ int fields_read_backward(const float* raw, const float* tr, const float* ti, con
                 grad_state_in, ws + pl.sum_off, ws + pl.carry_off, ws + pl.partial_off,
                 grad_tr, grad_ti, grad_gamma, pl.s};
     return vec4 ? run_backward<4>(p, st) : run_backward<1>(p, st);
+}
+
+
+size_t fields_read_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int fields_read_forward_noalloc(const float* raw, const float* tr, const float* ti,
+                                const float* gamma, const float* state_in, float* read,
+                                float* state_out, int B, int L, int C, void* stream) {
+    if (B < 0 || L < 0 || C <= 0) return FIELDS_ERR_ARGUMENT;
+    const size_t need = fields_read_workspace_bytes(B, L, C, FIELDS_PASS_FORWARD);
+    if (need > kStaticScratchBytes) return FIELDS_ERR_SCRATCH_LIMIT;
+    float* scratch = nullptr;
+    const int rc = static_scratch(&scratch);
+    if (rc) return rc;
+    // The forward kernels write every scratch word before they read it, so nothing has to
+    // be cleared between calls.
+    return fields_read_forward(raw, tr, ti, gamma, state_in, read, state_out, scratch,
+                               kStaticScratchBytes, B, L, C, stream);
 }
 
 }  // extern "C"

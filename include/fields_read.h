@@ -37,7 +37,8 @@ enum fields_status {
     FIELDS_ERR_WORKSPACE = 2, /* workspace missing, too small or misaligned */
     FIELDS_ERR_LAUNCH = 3,    /* the CUDA runtime refused a launch (see fields_last_cuda_error) */
     FIELDS_ERR_TIMEOUT = 4,   /* a bounded device-side wait ran out */
-    FIELDS_ERR_UNSUPPORTED = 5
+    FIELDS_ERR_UNSUPPORTED = 5,
+    FIELDS_ERR_SCRATCH_LIMIT = 6 /* fields_read_forward_noalloc: extents exceed the built-in scratch */
 };
 
 /* which pass a workspace is sized for */
@@ -92,6 +93,43 @@ int fields_read_backward(const float *raw, const float *tr, const float *ti,
 
 /* Text of the last CUDA runtime error seen by the calling thread inside this library. */
 const char *fields_last_cuda_error(void);
+
+/*
+ * Forward of the fused Field read for callers that have no memory to give.
+ * (No counterpart in the reference, whose operator allocates its work buffers
+ * with torch.empty on every call.)
+ *
+ * Some hosts of this library cannot hand over a workspace: an operator running
+ * inside an inference runtime's execution hook, a plug-in of a serving engine
+ * whose memory plan was fixed at start-up, or a real-time loop that must not
+ * stall - cudaMalloc synchronises the device and may fail under a full pool,
+ * and such callers often have no allocator they are allowed to call at that
+ * point. For them the library carries its own scratch: a fixed
+ * FIELDS_STATIC_SCRATCH_BYTES buffer in device memory that every GPU which
+ * loads the library holds until the process exits. This entry point runs the
+ * same kernels as fields_read_forward on that buffer and calls no cudaMalloc,
+ * cudaFree or other allocating routine. Inputs and outputs are still the
+ * caller's, with the meanings given at fields_read_forward.
+ *
+ *   - Limit: extents whose fields_read_workspace_bytes(B, L, C,
+ *     FIELDS_PASS_FORWARD) exceeds FIELDS_STATIC_SCRATCH_BYTES are refused with
+ *     FIELDS_ERR_SCRATCH_LIMIT and nothing is launched. 16 MiB covers the
+ *     training shape, 8 x 2,048 tokens at C = 512 (12 MiB), and 1 x 8,192.
+ *   - The first call on each device looks the buffer's device address up
+ *     (once, cached, with that device current); make that first call before
+ *     any stream capture begins.
+ *   - All calls on a device share the one buffer, which keeps whatever the last
+ *     call left in it. The kernels overwrite what they later read, so no
+ *     clearing is needed, but two calls that overlap on the GPU (different
+ *     streams without an ordering between them, or host threads launching at
+ *     the same time) race on it: serialise them.
+ */
+#define FIELDS_STATIC_SCRATCH_BYTES ((size_t)16 << 20)
+size_t fields_read_static_scratch_bytes(void);
+int fields_read_forward_noalloc(const float *raw, const float *tr, const float *ti,
+                                const float *gamma, const float *state_in,
+                                float *read, float *state_out, int B, int L, int C,
+                                void *stream);
 
 #ifdef __cplusplus
 }
