@@ -22,6 +22,7 @@ SYMBOLS = {
     "fields_read_workspace_bytes": (_SZ, [_I, _I, _I, _I]),
     "fields_read_forward": (_I, [_P] * 8 + [_SZ, _I, _I, _I, _P]),
     "fields_read_backward": (_I, [_P] * 14 + [_SZ, _I, _I, _I, _P]),
+    "fields_read_device_status": (_I, [_P, _P]),
     "fields_read_static_scratch_bytes": (_SZ, []),
     "fields_read_forward_noalloc": (_I, [_P] * 7 + [_I, _I, _I, _P]),
 }

@@ -1,0 +1,475 @@
+// Single-pass Field kernels: every input is read from HBM once and every output
+// written once; the carry between time tiles is resolved inside the kernel by a
+// decoupled look-back over per-tile aggregates published in global memory
+// (field_sync.cuh).
+//
+// A block owns one tile = (batch row, 128-channel group, TT = WARPS * TS time steps).
+// Warp w owns TS consecutive steps of the tile, a lane owns 4 consecutive channels
+// (128-bit accesses, 512 contiguous bytes per warp per plane and step). Tiles are taken
+// in block-index order, time-major, so every tile a block may wait for belongs to a
+// block with a smaller index, which the hardware has already started.
+//
+// Forward, per block:
+//   1. load the warp's TS steps into registers, turn them into (b_r, b_i, vacancy) in
+//      place and compose the warp's affine map (gates: reference :493-501);
+//   2. 128 threads (one per channel) compose the tile's map from the warp maps and
+//      publish it, then walk back over earlier tiles of the chain, composing published
+//      aggregates until they meet a tile whose end state is known, which gives the state
+//      entering this tile; they publish this tile's end state;
+//   3. every warp runs the recurrence over its registers from its incoming state and
+//      writes read = [Re s | Im s | Re d | Im d] (reference :599-622).
+// Every wait is bounded; on expiry the block records an error word, poisons its carry
+// with NaN and carries on, so the kernel always terminates.
+//
+// Kernel bodies are split into phases. Per-thread values that live across phases sit in
+// a State struct: registers on the device, an array per block in the host emulation
+// used by the CPU tests.
+#pragma once
+
+#include "field_kernels.cuh"
+#include "field_sync.cuh"
+
+namespace fields {
+
+constexpr int kCtrlHeader = 64;  // unsigned words before the slots: [0] error word
+constexpr int kGroup = 128;      // channels per tile
+
+struct SpShape {
+    int B, L, C;
+    int NT;  // time tiles per chain
+    int G;   // 128-channel groups
+};
+
+struct SpFwdParams {
+    const float* raw;
+    const float* tr;
+    const float* ti;
+    const float* gamma;
+    const float* state_in;  // [B, 2C] or null
+    float* read;
+    float* state_out;       // [B, 2C] or null
+    float* agg;             // [tiles][128][4]  tile maps (Re A, Im A, Re B, Im B)
+    float* incl;            // [tiles][128][2]  state after each tile
+    unsigned* ctrl;         // error word; filled with 0xFF like the slots before the launch
+    SpShape s;
+};
+
+struct SpTile {
+    int b, cg, n;        // batch row, channel group, position in scan order
+    long long chain;     // b * G + cg
+    long long idx;       // chain * NT + n : slot index into agg / incl
+};
+
+FL_HD SpTile sp_decode(const SpShape& s, unsigned ticket) {
+    SpTile t;
+    const long long chains = (long long)s.B * s.G;
+    t.n = (int)(ticket / chains);
+    t.chain = ticket % chains;
+    t.b = (int)(t.chain / s.G);
+    t.cg = (int)(t.chain % s.G);
+    t.idx = t.chain * s.NT + t.n;
+    return t;
+}
+
+template <int TS, int WARPS>
+struct FwdSinglePass {
+    using Params = SpFwdParams;
+    static constexpr int kThreads = 32 * WARPS;
+    static constexpr int kMinBlocks = TS >= 8 ? 2 : 3;  // blocks per SM the register budget must allow
+    static constexpr int kTile = TS * WARPS;
+    static constexpr int kPhases = 4;
+    static constexpr int kSplitPhase = 2;  // host emulation: phases < 2 of all blocks run first
+    static constexpr int kSumFloats = WARPS * 4 * kGroup;
+    static constexpr int kCarryFloats = WARPS * 2 * kGroup;
+    static constexpr int kSmemFloats = kSumFloats + kCarryFloats;
+    FL_HD static constexpr bool barrier_after(int ph) { return ph != 1; }
+
+    struct State {
+        Vec<4> br[TS], bi[TS], vac[TS];  // raw on load, then gamma*v*inj and vacancy
+    };
+
+    FL_HD static float* sum_at(float* smem, int w, int k) { return smem + (w * 4 + k) * kGroup; }
+    FL_HD static float* carry_at(float* smem, int w, int k) {
+        return smem + kSumFloats + (w * 2 + k) * kGroup;
+    }
+
+    template <int PH>
+    FL_HD static void phase(const Params& p, int block, int thread, float* smem, State& st) {
+        const SpShape& s = p.s;
+        const SpTile tl = sp_decode(s, (unsigned)block);
+        const int lane = thread & 31, warp = thread >> 5;
+        const int C = s.C;
+        const int c0 = tl.cg * kGroup + lane * 4;
+        const bool chan_ok = c0 < C;
+        const int tw = tl.n * kTile + warp * TS;
+
+        if constexpr (PH == 0) {
+            Affine m[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) m[k] = affine_identity();
+            if (chan_ok) {
+                const Vec<4> lr = vec_load<4>(p.tr + c0);
+                const Vec<4> li = vec_load<4>(p.ti + c0);
+                const Vec<4> gm = vec_load<4>(p.gamma + c0);
+                const float* base = p.raw + ((size_t)tl.b * s.L) * 3 * C + c0;
+#pragma unroll
+                for (int u = 0; u < TS; ++u) {
+                    if (tw + u < s.L) {
+                        const float* row = base + (size_t)(tw + u) * 3 * C;
+                        st.br[u] = vec_load_stream<4>(row);
+                        st.bi[u] = vec_load_stream<4>(row + C);
+                        st.vac[u] = vec_load_stream<4>(row + 2 * C);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < TS; ++u) {
+                    if (tw + u < s.L) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const Gate g = make_gate(st.br[u].v[k], st.bi[u].v[k], st.vac[u].v[k]);
+                            const float keep = 1.0f - g.vac;
+                            const float bs = gm.v[k] * g.vac;
+                            st.br[u].v[k] = bs * g.inj_r;
+                            st.bi[u].v[k] = bs * g.inj_i;
+                            st.vac[u].v[k] = g.vac;
+                            m[k] = affine_then(m[k], keep * lr.v[k], keep * li.v[k],
+                                               st.br[u].v[k], st.bi[u].v[k]);
+                        }
+                    }
+                }
+            }
+            Vec<4> o0, o1, o2, o3;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                o0.v[k] = m[k].ar; o1.v[k] = m[k].ai; o2.v[k] = m[k].br; o3.v[k] = m[k].bi;
+            }
+            vec_store<4>(sum_at(smem, warp, 0) + lane * 4, o0);
+            vec_store<4>(sum_at(smem, warp, 1) + lane * 4, o1);
+            vec_store<4>(sum_at(smem, warp, 2) + lane * 4, o2);
+            vec_store<4>(sum_at(smem, warp, 3) + lane * 4, o3);
+        } else if constexpr (PH == 1) {
+            // tile aggregate, one thread per channel; the first tile of a chain publishes
+            // only its end state
+            if (thread < kGroup && tl.cg * kGroup + thread < C && tl.n > 0) {
+                Affine a = affine_identity();
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w)
+                    a = affine_then(a, sum_at(smem, w, 0)[thread], sum_at(smem, w, 1)[thread],
+                                    sum_at(smem, w, 2)[thread], sum_at(smem, w, 3)[thread]);
+                publish4(p.agg + ((size_t)tl.idx * kGroup + thread) * 4, a.ar, a.ai, a.br, a.bi);
+            }
+        } else if constexpr (PH == 2) {
+            const int ch = tl.cg * kGroup + thread;
+            if (thread < kGroup && ch < C) {
+                float sr, si;
+                if (tl.n == 0) {
+                    sr = p.state_in ? p.state_in[(size_t)tl.b * 2 * C + ch] : 0.0f;
+                    si = p.state_in ? p.state_in[(size_t)tl.b * 2 * C + C + ch] : 0.0f;
+                } else {
+                    look_back(p.agg, p.incl, tl.chain * s.NT, tl.n, thread, p.ctrl, sr, si);
+                }
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) {
+                    carry_at(smem, w, 0)[thread] = sr;
+                    carry_at(smem, w, 1)[thread] = si;
+                    affine_apply(Affine{sum_at(smem, w, 0)[thread], sum_at(smem, w, 1)[thread],
+                                        sum_at(smem, w, 2)[thread], sum_at(smem, w, 3)[thread]},
+                                 sr, si);
+                }
+                publish2(p.incl + ((size_t)tl.idx * kGroup + thread) * 2, sr, si);
+                if (p.state_out && tl.n == s.NT - 1) {
+                    p.state_out[(size_t)tl.b * 2 * C + ch] = sr;
+                    p.state_out[(size_t)tl.b * 2 * C + C + ch] = si;
+                }
+            }
+        } else {  // PH == 3
+            if (!chan_ok) return;
+            const Vec<4> lr = vec_load<4>(p.tr + c0);
+            const Vec<4> li = vec_load<4>(p.ti + c0);
+            Vec<4> sr = vec_load<4>(carry_at(smem, warp, 0) + lane * 4);
+            Vec<4> si = vec_load<4>(carry_at(smem, warp, 1) + lane * 4);
+            float* obase = p.read + ((size_t)tl.b * s.L) * 4 * C + c0;
+#pragma unroll
+            for (int u = 0; u < TS; ++u) {
+                if (tw + u < s.L) {
+                    Vec<4> dr, di;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        float mr, mi;
+                        cmul(lr.v[k], li.v[k], sr.v[k], si.v[k], mr, mi);
+                        const float v = st.vac[u].v[k];
+                        dr.v[k] = v * mr;
+                        di.v[k] = v * mi;
+                        sr.v[k] = (1.0f - v) * mr + st.br[u].v[k];
+                        si.v[k] = (1.0f - v) * mi + st.bi[u].v[k];
+                    }
+                    float* orow = obase + (size_t)(tw + u) * 4 * C;
+                    vec_store_stream<4>(orow, sr);
+                    vec_store_stream<4>(orow + C, si);
+                    vec_store_stream<4>(orow + 2 * C, dr);
+                    vec_store_stream<4>(orow + 3 * C, di);
+                }
+            }
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------
+// Backward, single pass over HBM in two sweeps per tile.
+//
+// The dual recurrence runs from the last step to the first, so tiles are handed out
+// from the end of the sequence and "earlier in scan order" means later in time.
+// Per block (WARPS warps, warp w owns TS consecutive steps):
+//   sweep 1  walk the warp's steps backwards reading z_v and grad_read (5 planes) and
+//            compose the warp's dual map (P, Q)            (reference :655-705);
+//   publish the tile's map, look back over later-in-time tiles for the gradient carry
+//            entering this tile, publish this tile's outgoing carry;
+//   sweep 2  walk the same steps again from the warp's carry: the 5 planes come back
+//            from L2 (the tile was read microseconds ago), z_r, z_i and s_{t-1} (from
+//            the saved forward output) come from HBM; write grad_raw and accumulate
+//            d lambda_r, d lambda_i, d gamma            (reference :794-909);
+//   reduce the warps' parameter-gradient partials in a fixed order into one row per
+//            tile; BwdReduce adds the rows.
+// HBM traffic per channel-step: 20 B (sweep 1) + 16 B (z_r, z_i, s_{t-1}) + 12 B written.
+// ---------------------------------------------------------------------------
+struct SpBwdParams {
+    const float* raw;
+    const float* tr;
+    const float* ti;
+    const float* gamma;
+    const float* state_in;        // [B, 2C] or null
+    const float* read;            // saved forward output
+    const float* grad_read;
+    const float* grad_state_out;  // [B, 2C] or null
+    float* grad_raw;
+    float* grad_state_in;         // [B, 2C] or null
+    float* agg;                   // [tiles][128][4]
+    float* incl;                  // [tiles][128][2]
+    unsigned* ctrl;               // error word
+    float* partial;               // [3][B][NT][C]
+    SpShape s;
+};
+
+template <int TS, int WARPS, int U2_>
+struct BwdSinglePass {
+    using Params = SpBwdParams;
+    static constexpr int kThreads = 32 * WARPS;
+    static constexpr int kMinBlocks = 1;
+    static constexpr int kTile = TS * WARPS;
+    static constexpr int kPhases = 5;
+    static constexpr int kSplitPhase = 2;
+    static constexpr int kSumFloats = WARPS * 4 * kGroup;   // warp maps, later warp partials
+    static constexpr int kCarryFloats = WARPS * 2 * kGroup;
+    static constexpr int kSmemFloats = kSumFloats + kCarryFloats;
+    FL_HD static constexpr bool barrier_after(int ph) { return ph != 1; }
+    static constexpr int U1 = 4;  // steps loaded together in sweep 1
+    static constexpr int U2 = U2_;  // steps loaded together in sweep 2
+    static_assert(kThreads >= kGroup, "one thread per channel is needed for the look-back");
+    static_assert(TS % U1 == 0 && TS % U2 == 0, "sub-chunk must be a multiple of the unroll");
+
+    struct State {};  // nothing lives in registers across barriers
+
+    FL_HD static float* sum_at(float* smem, int w, int k) { return smem + (w * 4 + k) * kGroup; }
+    FL_HD static float* carry_at(float* smem, int w, int k) {
+        return smem + kSumFloats + (w * 2 + k) * kGroup;
+    }
+    template <int PH>
+    FL_HD static void phase(const Params& p, int block, int thread, float* smem, State&) {
+        const SpShape& s = p.s;
+        // tl.n is the position in scan order; the tile covers time tile NT-1-n
+        const SpTile tl = sp_decode(s, (unsigned)block);
+        const int time_tile = s.NT - 1 - tl.n;
+        const int lane = thread & 31, warp = thread >> 5;
+        const int slot = WARPS - 1 - warp;  // position of this warp's steps in scan order
+        const int C = s.C;
+        const int c0 = tl.cg * kGroup + lane * 4;
+        const bool chan_ok = c0 < C;
+        const int tbeg = time_tile * kTile + warp * TS;           // first step of the warp
+        const int tend = tbeg + TS < s.L ? tbeg + TS : s.L;       // one past its last valid step
+
+        if constexpr (PH == 0) {
+            Affine m[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) m[k] = affine_identity();
+            if (chan_ok) {
+                const Vec<4> lr = vec_load<4>(p.tr + c0);
+                const Vec<4> li = vec_load<4>(p.ti + c0);
+                const float* zbase = p.raw + ((size_t)tl.b * s.L) * 3 * C + 2 * C + c0;
+                const float* gbase = p.grad_read + ((size_t)tl.b * s.L) * 4 * C + c0;
+                for (int t0 = tend; t0 > tbeg; t0 -= U1) {
+                    Vec<4> zv[U1], ur[U1], ui[U1], gr[U1], gi[U1];
+#pragma unroll
+                    for (int u = 0; u < U1; ++u) {
+                        const int t = t0 - 1 - u;
+                        if (t >= tbeg) {
+                            zv[u] = vec_load<4>(zbase + (size_t)t * 3 * C);
+                            const float* grow = gbase + (size_t)t * 4 * C;
+                            ur[u] = vec_load<4>(grow);
+                            ui[u] = vec_load<4>(grow + C);
+                            gr[u] = vec_load<4>(grow + 2 * C);
+                            gi[u] = vec_load<4>(grow + 3 * C);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < U1; ++u) {
+                        if (t0 - 1 - u >= tbeg) {
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const float vac = kVacMax * sigmoidf_fast(zv[u].v[k]);
+                                const float keep = 1.0f - vac;
+                                const float car = keep * lr.v[k];
+                                const float cai = -keep * li.v[k];
+                                float qr, qi, xr, xi;
+                                cmul(car, cai, ur[u].v[k], ui[u].v[k], qr, qi);
+                                cmul_conj(lr.v[k], li.v[k], gr[u].v[k], gi[u].v[k], xr, xi);
+                                m[k] = affine_then(m[k], car, cai, qr + vac * xr, qi + vac * xi);
+                            }
+                        }
+                    }
+                }
+            }
+            Vec<4> o0, o1, o2, o3;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                o0.v[k] = m[k].ar; o1.v[k] = m[k].ai; o2.v[k] = m[k].br; o3.v[k] = m[k].bi;
+            }
+            vec_store<4>(sum_at(smem, slot, 0) + lane * 4, o0);
+            vec_store<4>(sum_at(smem, slot, 1) + lane * 4, o1);
+            vec_store<4>(sum_at(smem, slot, 2) + lane * 4, o2);
+            vec_store<4>(sum_at(smem, slot, 3) + lane * 4, o3);
+        } else if constexpr (PH == 1) {
+            if (thread < kGroup && tl.cg * kGroup + thread < C && tl.n > 0) {
+                Affine a = affine_identity();
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w)
+                    a = affine_then(a, sum_at(smem, w, 0)[thread], sum_at(smem, w, 1)[thread],
+                                    sum_at(smem, w, 2)[thread], sum_at(smem, w, 3)[thread]);
+                publish4(p.agg + ((size_t)tl.idx * kGroup + thread) * 4, a.ar, a.ai, a.br, a.bi);
+            }
+        } else if constexpr (PH == 2) {
+            const int ch = tl.cg * kGroup + thread;
+            if (thread < kGroup && ch < C) {
+                float sr, si;
+                if (tl.n == 0) {
+                    sr = p.grad_state_out ? p.grad_state_out[(size_t)tl.b * 2 * C + ch] : 0.0f;
+                    si = p.grad_state_out ? p.grad_state_out[(size_t)tl.b * 2 * C + C + ch] : 0.0f;
+                } else {
+                    look_back(p.agg, p.incl, tl.chain * s.NT, tl.n, thread, p.ctrl, sr, si);
+                }
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) {
+                    carry_at(smem, w, 0)[thread] = sr;
+                    carry_at(smem, w, 1)[thread] = si;
+                    affine_apply(Affine{sum_at(smem, w, 0)[thread], sum_at(smem, w, 1)[thread],
+                                        sum_at(smem, w, 2)[thread], sum_at(smem, w, 3)[thread]},
+                                 sr, si);
+                }
+                publish2(p.incl + ((size_t)tl.idx * kGroup + thread) * 2, sr, si);
+                if (p.grad_state_in && tl.n == s.NT - 1) {
+                    p.grad_state_in[(size_t)tl.b * 2 * C + ch] = sr;
+                    p.grad_state_in[(size_t)tl.b * 2 * C + C + ch] = si;
+                }
+            }
+        } else if constexpr (PH == 3) {
+            Vec<4> dtr = vec_fill<4>(0.0f), dti = vec_fill<4>(0.0f), dgm = vec_fill<4>(0.0f);
+            if (chan_ok) {
+                const Vec<4> lr = vec_load<4>(p.tr + c0);
+                const Vec<4> li = vec_load<4>(p.ti + c0);
+                const Vec<4> gm = vec_load<4>(p.gamma + c0);
+                Vec<4> cr = vec_load<4>(carry_at(smem, slot, 0) + lane * 4);
+                Vec<4> ci = vec_load<4>(carry_at(smem, slot, 1) + lane * 4);
+                const float* zbase = p.raw + ((size_t)tl.b * s.L) * 3 * C + c0;
+                const float* gbase = p.grad_read + ((size_t)tl.b * s.L) * 4 * C + c0;
+                const float* rbase = p.read + ((size_t)tl.b * s.L) * 4 * C + c0;
+                float* obase = p.grad_raw + ((size_t)tl.b * s.L) * 3 * C + c0;
+                for (int t0 = tend; t0 > tbeg; t0 -= U2) {
+                    Vec<4> zr[U2], zi[U2], zv[U2], ur[U2], ui[U2], gr[U2], gi[U2], pr[U2], pi[U2];
+#pragma unroll
+                    for (int u = 0; u < U2; ++u) {
+                        const int t = t0 - 1 - u;
+                        if (t >= tbeg) {
+                            const float* zrow = zbase + (size_t)t * 3 * C;
+                            zr[u] = vec_load_stream<4>(zrow);
+                            zi[u] = vec_load_stream<4>(zrow + C);
+                            zv[u] = vec_load_stream<4>(zrow + 2 * C);
+                            const float* grow = gbase + (size_t)t * 4 * C;
+                            ur[u] = vec_load_stream<4>(grow);
+                            ui[u] = vec_load_stream<4>(grow + C);
+                            gr[u] = vec_load_stream<4>(grow + 2 * C);
+                            gi[u] = vec_load_stream<4>(grow + 3 * C);
+                            if (t > 0) {
+                                const float* prow = rbase + (size_t)(t - 1) * 4 * C;
+                                pr[u] = vec_load_stream<4>(prow);
+                                pi[u] = vec_load_stream<4>(prow + C);
+                            } else if (p.state_in) {
+                                const float* prow = p.state_in + (size_t)tl.b * 2 * C + c0;
+                                pr[u] = vec_load<4>(prow);
+                                pi[u] = vec_load<4>(prow + C);
+                            } else {
+                                pr[u] = vec_fill<4>(0.0f);
+                                pi[u] = vec_fill<4>(0.0f);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < U2; ++u) {
+                        const int t = t0 - 1 - u;
+                        if (t >= tbeg) {
+                            Vec<4> ozr, ozi, ozv;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const Gate g = make_gate(zr[u].v[k], zi[u].v[k], zv[u].v[k]);
+                                const float keep = 1.0f - g.vac;
+                                const float Gr = ur[u].v[k] + cr.v[k];
+                                const float Gi = ui[u].v[k] + ci.v[k];
+                                const float gdr = gr[u].v[k], gdi = gi[u].v[k];
+                                const float sr = pr[u].v[k], si = pi[u].v[k];
+                                float mr, mi, dar, dai, xr, xi, yr, yi, nr, ni;
+                                cmul(lr.v[k], li.v[k], sr, si, mr, mi);
+                                cmul_conj(sr, si, Gr, Gi, dar, dai);
+                                cmul_conj(sr, si, gdr, gdi, xr, xi);
+                                cmul_conj(lr.v[k], li.v[k], gdr, gdi, yr, yi);
+                                cmul_conj(keep * lr.v[k], keep * li.v[k], Gr, Gi, nr, ni);
+                                const float common_b = g.inj_r * Gr + g.inj_i * Gi;
+                                const float dv = -lr.v[k] * dar - li.v[k] * dai +
+                                                 gm.v[k] * common_b + gdr * mr + gdi * mi;
+                                dtr.v[k] += keep * dar + g.vac * xr;
+                                dti.v[k] += keep * dai + g.vac * xi;
+                                dgm.v[k] += g.vac * common_b;
+                                const float bs = gm.v[k] * g.vac;
+                                ozr.v[k] = bs * Gr * (1.0f - g.inj_r * g.inj_r);
+                                ozi.v[k] = bs * Gi * (1.0f - g.inj_i * g.inj_i);
+                                ozv.v[k] = dv * kVacMax * g.sig * (1.0f - g.sig);
+                                cr.v[k] = nr + g.vac * yr;
+                                ci.v[k] = ni + g.vac * yi;
+                            }
+                            float* orow = obase + (size_t)t * 3 * C;
+                            vec_store_stream<4>(orow, ozr);
+                            vec_store_stream<4>(orow + C, ozi);
+                            vec_store_stream<4>(orow + 2 * C, ozv);
+                        }
+                    }
+                }
+            }
+            // warp partials into the (now free) map area: [warp][3][128]
+            vec_store<4>(sum_at(smem, warp, 0) + lane * 4, dtr);
+            vec_store<4>(sum_at(smem, warp, 1) + lane * 4, dti);
+            vec_store<4>(sum_at(smem, warp, 2) + lane * 4, dgm);
+        } else {  // PH == 4: one partial row per tile, warps added in a fixed order
+            const int ch = tl.cg * kGroup + thread;
+            if (thread < kGroup && ch < C) {
+                const size_t plane = (size_t)s.B * s.NT * C;
+                float* out = p.partial + ((size_t)tl.b * s.NT + time_tile) * C + ch;
+#pragma unroll
+                for (int k = 0; k < 3; ++k) {
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < WARPS; ++w) acc += sum_at(smem, w, k)[thread];
+                    out[k * plane] = acc;
+                }
+            }
+        }
+    }
+};
+
+}  // namespace fields

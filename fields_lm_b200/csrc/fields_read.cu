@@ -8,10 +8,14 @@
 // index arithmetic and the formulas are checked without a GPU. That build is
 // test infrastructure; it is never loaded by the package.
 #include "field_kernels.cuh"
+#include "field_singlepass.cuh"
+#include "field_walk.cuh"
 
 #include "../../include/fields_read.h"
 
+#include <cstdlib>
 #include <mutex>
+#include <string>
 #include <vector>
 
 namespace fields {
@@ -40,6 +44,64 @@ static int launch(const typename K::Params& p, long long grid, Stream) {
 
 static int fill_zero(float* p, size_t n, Stream) {
     for (size_t i = 0; i < n; ++i) p[i] = 0.0f;
+    return FIELDS_OK;
+}
+
+template <class K, int PH>
+static void emu_phase_range(const typename K::Params& p, int block, float* smem,
+                            typename K::State* st, int lo, int hi) {
+    if constexpr (PH < K::kPhases) {
+        if (PH >= lo && PH < hi)
+            for (int thread = 0; thread < K::kThreads; ++thread)
+                K::template phase<PH>(p, block, thread, smem, st[thread]);
+        emu_phase_range<K, PH + 1>(p, block, smem, st, lo, hi);
+    }
+}
+
+// Kernels whose blocks wait for one another: every block first runs up to the point
+// where it has published its aggregate, then the blocks finish one at a time. With
+// FIELDS_EMU_ORDER=reverse the later tiles finish first (after the first tile of each
+// chain), which drives the look-back through whole chains of aggregates; the default
+// order meets an inclusive state at the first step back.
+template <class K>
+static int launch_stateful(const typename K::Params& p, long long grid, long long first_wave,
+                           Stream) {
+    std::vector<double> smem_store((size_t)grid * (K::kSmemFloats / 2 + 1));
+    std::vector<typename K::State> states((size_t)grid * K::kThreads);
+    auto smem_of = [&](long long b) {
+        return reinterpret_cast<float*>(smem_store.data() + (size_t)b * (K::kSmemFloats / 2 + 1));
+    };
+    for (long long b = 0; b < grid; ++b)
+        emu_phase_range<K, 0>(p, (int)b, smem_of(b), &states[(size_t)b * K::kThreads], 0,
+                              K::kSplitPhase);
+    const char* order = std::getenv("FIELDS_EMU_ORDER");
+    const bool reverse = order && std::string(order) == "reverse";
+    std::vector<long long> seq;
+    for (long long b = 0; b < first_wave && b < grid; ++b) seq.push_back(b);
+    if (reverse) for (long long b = grid - 1; b >= first_wave; --b) seq.push_back(b);
+    else for (long long b = first_wave; b < grid; ++b) seq.push_back(b);
+    for (long long b : seq)
+        emu_phase_range<K, 0>(p, (int)b, smem_of(b), &states[(size_t)b * K::kThreads],
+                              K::kSplitPhase, K::kPhases);
+    return FIELDS_OK;
+}
+
+static int fill_unset(void* p, size_t bytes, Stream) {
+    std::memset(p, kUnsetByte, bytes);
+    return FIELDS_OK;
+}
+
+// Kernels whose number of barrier-separated phases depends on the extents.
+template <class K>
+static int launch_walk(const typename K::Params& p, long long grid, Stream) {
+    std::vector<double> smem_store(K::kSmemFloats / 2 + 1);
+    float* smem = reinterpret_cast<float*>(smem_store.data());
+    std::vector<typename K::State> states(K::kThreads);
+    const int n = K::phases(p);
+    for (long long block = 0; block < grid; ++block)
+        for (int ph = 0; ph < n; ++ph)
+            for (int thread = 0; thread < K::kThreads; ++thread)
+                K::phase(ph, p, (int)block, thread, smem, states[thread]);
     return FIELDS_OK;
 }
 
@@ -74,6 +136,73 @@ static int launch(const typename K::Params& p, long long grid, Stream st) {
 
 static int fill_zero(float* p, size_t n, Stream st) {
     return check_cuda(cudaMemsetAsync(p, 0, n * sizeof(float), st));
+}
+
+template <class K, int PH>
+__device__ __forceinline__ void run_phases(const typename K::Params& p, float* smem,
+                                           typename K::State& st) {
+    K::template phase<PH>(p, (int)blockIdx.x, (int)threadIdx.x, smem, st);
+    if constexpr (PH + 1 < K::kPhases) {
+        if constexpr (K::barrier_after(PH)) __syncthreads();
+        run_phases<K, PH + 1>(p, smem, st);
+    }
+}
+
+template <class K>
+__global__ void __launch_bounds__(K::kThreads, K::kMinBlocks) stateful_entry(const typename K::Params p) {
+    extern __shared__ __align__(16) float smem[];
+    typename K::State st;
+    run_phases<K, 0>(p, smem, st);
+}
+
+template <class K>
+static int launch_stateful(const typename K::Params& p, long long grid, long long, Stream st) {
+    if (grid <= 0) return FIELDS_OK;
+    if (grid > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
+    stateful_entry<K><<<(unsigned)grid, K::kThreads, K::kSmemFloats * sizeof(float), st>>>(p);
+    return check_cuda(cudaGetLastError());
+}
+
+static int fill_unset(void* p, size_t bytes, Stream st) {
+    return check_cuda(cudaMemsetAsync(p, kUnsetByte, bytes, st));
+}
+
+template <class K>
+__global__ void __launch_bounds__(K::kThreads, K::kMinBlocks) walk_entry(const typename K::Params p) {
+    extern __shared__ __align__(16) float smem[];
+    typename K::State st;
+    const int n = K::phases(p);
+    for (int ph = 0; ph < n; ++ph) {
+        K::phase(ph, p, (int)blockIdx.x, (int)threadIdx.x, smem, st);
+        __syncthreads();
+    }
+}
+
+// Kernels that need more than the default 48 KB of dynamic shared memory opt in once per
+// device.
+template <class K>
+static int launch_walk(const typename K::Params& p, long long grid, Stream st) {
+    if (grid <= 0) return FIELDS_OK;
+    if (grid > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
+    constexpr size_t bytes = K::kSmemFloats * sizeof(float);
+    static std::mutex mu;
+    static bool ready[64] = {};
+    int dev = 0;
+    int rc = check_cuda(cudaGetDevice(&dev));
+    if (rc) return rc;
+    if (dev < 0 || dev >= 64) return FIELDS_ERR_UNSUPPORTED;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!ready[dev]) {
+            rc = check_cuda(cudaFuncSetAttribute(walk_entry<K>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)bytes));
+            if (rc) return rc;
+            ready[dev] = true;
+        }
+    }
+    walk_entry<K><<<(unsigned)grid, K::kThreads, bytes, st>>>(p);
+    return check_cuda(cudaGetLastError());
 }
 
 #endif
@@ -148,6 +277,129 @@ static int run_backward(const BwdParams& p, Stream st) {
 
 
 // ---------------------------------------------------------------------------
+// Single-pass forward: plan and launch.
+// ---------------------------------------------------------------------------
+struct SpPlan {
+    SpShape s;
+    long long tiles;
+    size_t ctrl_words;               // header holding the error word
+    size_t agg_off, incl_off;        // byte offsets into the workspace
+    size_t bytes;
+};
+
+static SpPlan make_sp_plan(int B, int L, int C, int tile_steps) {
+    SpPlan pl{};
+    pl.s.B = B; pl.s.L = L; pl.s.C = C;
+    pl.s.NT = (L + tile_steps - 1) / tile_steps;
+    pl.s.G = (C + kGroup - 1) / kGroup;
+    pl.tiles = (long long)B * pl.s.G * pl.s.NT;
+    pl.ctrl_words = kCtrlHeader;
+    pl.agg_off = pl.ctrl_words * sizeof(unsigned);
+    pl.incl_off = pl.agg_off + (size_t)pl.tiles * 4 * kGroup * sizeof(float);
+    pl.bytes = pl.incl_off + (size_t)pl.tiles * 2 * kGroup * sizeof(float);
+    return pl;
+}
+
+constexpr int kSpMinTile = 32;  // smallest time tile of any single-pass instantiation
+
+enum Algo { kAlgoAuto = 0, kAlgoThreePhase = 1, kAlgoSinglePass = 2, kAlgoWalk = 3 };
+
+// FIELDS_READ_ALGO = three_phase | single_pass | walk selects the kernels (default: the chain
+// walkers when there are enough chains, else single pass, whenever 16-byte accesses are possible). FIELDS_READ_TILE = 32 | 64 selects the time tile.
+static Algo algo_from_env() {
+    const char* e = std::getenv("FIELDS_READ_ALGO");
+    if (!e) return kAlgoAuto;
+    const std::string v(e);
+    if (v == "three_phase") return kAlgoThreePhase;
+    if (v == "single_pass") return kAlgoSinglePass;
+    if (v == "walk") return kAlgoWalk;
+    return kAlgoAuto;
+}
+
+#define COMMA ,
+
+// FIELDS_READ_U2 = 1 | 2: steps loaded together in the backward's second sweep.
+static int unroll_from_env(int fallback) {
+    const char* e = std::getenv("FIELDS_READ_U2");
+    if (!e) return fallback;
+    const int v = std::atoi(e);
+    return (v == 1 || v == 2) ? v : fallback;
+}
+
+static int tile_from_env(int fallback) {
+    const char* e = std::getenv("FIELDS_READ_TILE");
+    if (!e) return fallback;
+    const int v = std::atoi(e);
+    return (v == 32 || v == 64) ? v : fallback;
+}
+
+template <class K>
+static int run_forward_single_pass(const float* raw, const float* tr, const float* ti,
+                                   const float* gamma, const float* state_in, float* read,
+                                   float* state_out, void* workspace, int B, int L, int C,
+                                   Stream st) {
+    const SpPlan pl = make_sp_plan(B, L, C, K::kTile);
+    char* ws = static_cast<char*>(workspace);
+    unsigned* ctrl = reinterpret_cast<unsigned*>(ws);
+    int rc = fill_unset(ws, pl.bytes, st);  // error word and every publication slot
+    if (rc) return rc;
+    SpFwdParams p{raw, tr, ti, gamma, state_in, read, state_out,
+                  reinterpret_cast<float*>(ws + pl.agg_off),
+                  reinterpret_cast<float*>(ws + pl.incl_off), ctrl, pl.s};
+    return launch_stateful<K>(p, pl.tiles, (long long)B * pl.s.G, st);
+}
+
+template <class K>
+static int run_backward_single_pass(const float* raw, const float* tr, const float* ti,
+                                    const float* gamma, const float* state_in, const float* read,
+                                    const float* grad_read, const float* grad_state_out,
+                                    float* grad_raw, float* grad_tr, float* grad_ti,
+                                    float* grad_gamma, float* grad_state_in, void* workspace,
+                                    int B, int L, int C, Stream st) {
+    const SpPlan pl = make_sp_plan(B, L, C, K::kTile);
+    char* ws = static_cast<char*>(workspace);
+    unsigned* ctrl = reinterpret_cast<unsigned*>(ws);
+    int rc = fill_unset(ws, pl.bytes, st);
+    if (rc) return rc;
+    float* partial = reinterpret_cast<float*>(ws + pl.bytes);
+    SpBwdParams p{raw, tr, ti, gamma, state_in, read, grad_read, grad_state_out, grad_raw,
+                  grad_state_in, reinterpret_cast<float*>(ws + pl.agg_off),
+                  reinterpret_cast<float*>(ws + pl.incl_off), ctrl, partial, pl.s};
+    rc = launch_stateful<K>(p, pl.tiles, (long long)B * pl.s.G, st);
+    if (rc) return rc;
+    BwdParams rp{};
+    rp.partial = partial;
+    rp.grad_tr = grad_tr; rp.grad_ti = grad_ti; rp.grad_gamma = grad_gamma;
+    rp.s = Shape{B, L, C, K::kTile, pl.s.NT, pl.s.G};
+    return launch<BwdReduce>(rp, 3LL * ((C + 31) / 32), st);
+}
+
+static size_t sp_backward_bytes(int B, int L, int C, int tile_steps) {
+    const SpPlan pl = make_sp_plan(B, L, C, tile_steps);
+    return pl.bytes + (size_t)3 * B * pl.s.NT * C * sizeof(float);
+}
+
+// ---------------------------------------------------------------------------
+// Chain walkers: used when batch x (C / 32) gives enough independent chains to fill
+// the GPU (training shapes); no workspace except one partial row per chain (backward).
+// ---------------------------------------------------------------------------
+constexpr long long kWalkMinChains = 96;
+
+using FwdWalker = FwdWalk<16, 8, 3>;  // tile 128 steps, 3 x 48 KB ring
+using BwdWalker = BwdWalk<4, 8, 4>;   // tile 32 steps, 4 x 36 KB ring
+
+template <class K>
+static WalkShape walk_shape(int B, int L, int C) {
+    return WalkShape{B, L, C, (L + K::kTile - 1) / K::kTile, (C + kLane - 1) / kLane};
+}
+
+static bool walk_wanted(int B, int C, Algo algo) {
+    if (algo == kAlgoWalk) return true;
+    if (algo != kAlgoAuto) return false;
+    return (long long)B * ((C + kLane - 1) / kLane) >= kWalkMinChains;
+}
+
+// ---------------------------------------------------------------------------
 // Built-in scratch for fields_read_forward_noalloc: one fixed buffer per GPU that
 // has loaded this library, held until the process exits.
 // ---------------------------------------------------------------------------
@@ -215,7 +467,10 @@ size_t fields_read_workspace_bytes(int B, int L, int C, int pass) {
     if (B <= 0 || L <= 0 || C <= 0) return 0;
     const Plan pl = make_plan(B, L, C, 1);
     const size_t floats = pass == FIELDS_PASS_BACKWARD ? pl.bwd_floats : pl.fwd_floats;
-    return floats * sizeof(float);
+    size_t bytes = floats * sizeof(float);
+    const size_t sp = pass == FIELDS_PASS_BACKWARD ? sp_backward_bytes(B, L, C, kSpMinTile)
+                                                   : make_sp_plan(B, L, C, kSpMinTile).bytes;
+    return sp > bytes ? sp : bytes;
 }
 
 int fields_read_forward(const float* raw, const float* tr, const float* ti, const float* gamma,
@@ -243,9 +498,22 @@ int fields_read_forward(const float* raw, const float* tr, const float* ti, cons
                       aligned16(ti) && aligned16(gamma) && aligned16(state_in) &&
                       aligned16(state_out) && aligned16(workspace);
     const Plan pl = make_plan(B, L, C, vec4 ? 4 : 1);
-    if (!workspace || workspace_bytes < pl.fwd_floats * sizeof(float) ||
+    if (!workspace || workspace_bytes < fields_read_workspace_bytes(B, L, C, FIELDS_PASS_FORWARD) ||
         (reinterpret_cast<uintptr_t>(workspace) & 255u))
         return FIELDS_ERR_WORKSPACE;
+    const Algo algo = algo_from_env();
+    if (vec4 && walk_wanted(B, C, algo)) {
+        WalkFwdParams wp{raw, tr, ti, gamma, state_in, read, state_out,
+                         walk_shape<FwdWalker>(B, L, C)};
+        return launch_walk<FwdWalker>(wp, (long long)B * wp.s.G, st);
+    }
+    if (vec4 && algo != kAlgoThreePhase) {
+        if (tile_from_env(64) == 32)
+            return run_forward_single_pass<FwdSinglePass<4, 8>>(raw, tr, ti, gamma, state_in, read,
+                                                                state_out, workspace, B, L, C, st);
+        return run_forward_single_pass<FwdSinglePass<8, 8>>(raw, tr, ti, gamma, state_in, read,
+                                                            state_out, workspace, B, L, C, st);
+    }
     float* ws = static_cast<float*>(workspace);
     FwdParams p{raw, tr, ti, gamma, state_in, read, state_out,
                 ws + pl.sum_off, ws + pl.carry_off, pl.s};
@@ -286,9 +554,35 @@ int fields_read_backward(const float* raw, const float* tr, const float* ti, con
                       aligned16(grad_raw) && aligned16(tr) && aligned16(ti) && aligned16(gamma) &&
                       aligned16(state_in) && aligned16(workspace);
     const Plan pl = make_plan(B, L, C, vec4 ? 4 : 1);
-    if (!workspace || workspace_bytes < pl.bwd_floats * sizeof(float) ||
+    if (!workspace ||
+        workspace_bytes < fields_read_workspace_bytes(B, L, C, FIELDS_PASS_BACKWARD) ||
         (reinterpret_cast<uintptr_t>(workspace) & 255u))
         return FIELDS_ERR_WORKSPACE;
+    if (vec4 && walk_wanted(B, C, algo_from_env())) {
+        float* partial = static_cast<float*>(workspace);
+        WalkBwdParams wp{raw, tr, ti, gamma, state_in, read, grad_read, grad_state_out, grad_raw,
+                         grad_state_in, partial, walk_shape<BwdWalker>(B, L, C)};
+        int rc = launch_walk<BwdWalker>(wp, (long long)B * wp.s.G, st);
+        if (rc) return rc;
+        BwdParams rp{};
+        rp.partial = partial;
+        rp.grad_tr = grad_tr; rp.grad_ti = grad_ti; rp.grad_gamma = grad_gamma;
+        rp.s = Shape{B, L, C, L, 1, wp.s.G};
+        return launch<BwdReduce>(rp, 3LL * ((C + 31) / 32), st);
+    }
+    if (vec4 && algo_from_env() != kAlgoThreePhase) {
+#define FIELDS_BWD_SP(K)                                                                        \
+    return run_backward_single_pass<K>(raw, tr, ti, gamma, state_in, read, grad_read,          \
+                                       grad_state_out, grad_raw, grad_tr, grad_ti, grad_gamma, \
+                                       grad_state_in, workspace, B, L, C, st)
+        const bool wide = tile_from_env(32) == 64;
+        const bool pair = unroll_from_env(2) == 2;
+        if (wide && pair) FIELDS_BWD_SP(BwdSinglePass<16 COMMA 4 COMMA 2>);
+        if (wide) FIELDS_BWD_SP(BwdSinglePass<16 COMMA 4 COMMA 1>);
+        if (pair) FIELDS_BWD_SP(BwdSinglePass<8 COMMA 4 COMMA 2>);
+        FIELDS_BWD_SP(BwdSinglePass<8 COMMA 4 COMMA 1>);
+#undef FIELDS_BWD_SP
+    }
     float* ws = static_cast<float*>(workspace);
     BwdParams p{raw, tr, ti, gamma, state_in, read, grad_read, grad_state_out, grad_raw,
                 grad_state_in, ws + pl.sum_off, ws + pl.carry_off, ws + pl.partial_off,
@@ -312,6 +606,23 @@ int fields_read_forward_noalloc(const float* raw, const float* tr, const float* 
     // be cleared between calls.
     return fields_read_forward(raw, tr, ti, gamma, state_in, read, state_out, scratch,
                                kStaticScratchBytes, B, L, C, stream);
+}
+
+
+int fields_read_device_status(const void* workspace, void* stream) {
+    if (!workspace) return FIELDS_ERR_ARGUMENT;
+    int word = 0;
+#ifdef FIELDS_HOST_EMU
+    (void)stream;
+    word = static_cast<const int*>(workspace)[0];
+#else
+    Stream st = reinterpret_cast<Stream>(stream);
+    int rc = check_cuda(cudaMemcpyAsync(&word, static_cast<const int*>(workspace), sizeof(int),
+                                        cudaMemcpyDeviceToHost, st));
+    if (!rc) rc = check_cuda(cudaStreamSynchronize(st));
+    if (rc) return rc;
+#endif
+    return word != -1 ? FIELDS_ERR_TIMEOUT : FIELDS_OK;
 }
 
 }  // extern "C"

@@ -95,6 +95,15 @@ int fields_read_backward(const float *raw, const float *tr, const float *ti,
 const char *fields_last_cuda_error(void);
 
 /*
+ * Reads back the error word that the single-pass kernels keep in the workspace they
+ * were given, after waiting for `stream`. Returns FIELDS_OK, or FIELDS_ERR_TIMEOUT if a
+ * block gave up a bounded wait for an earlier tile (its outputs then hold NaN). Only
+ * meaningful directly after fields_read_forward / fields_read_backward on that
+ * workspace. The reference has no counterpart (its kernels never wait on each other).
+ */
+int fields_read_device_status(const void *workspace, void *stream);
+
+/*
  * Forward of the fused Field read for callers that have no memory to give.
  * (No counterpart in the reference, whose operator allocates its work buffers
  * with torch.empty on every call.)

@@ -46,6 +46,8 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.fields_read_forward.restype = I
     lib.fields_read_backward.argtypes = [P] * 14 + [SZ, I, I, I, P]
     lib.fields_read_backward.restype = I
+    lib.fields_read_device_status.argtypes = [P, P]
+    lib.fields_read_device_status.restype = I
     return lib
 
 
@@ -73,7 +75,8 @@ def _ptr(a):
     return None if a is None else a.ctypes.data_as(P)
 
 
-def forward(raw, tr, ti, gamma, state_in=None, want_state=True, misalign=False):
+def forward(raw, tr, ti, gamma, state_in=None, want_state=True, misalign=False,
+            return_workspace=False):
     """Runs the emulated forward. ``misalign`` offsets raw by 4 bytes to force the scalar path."""
     B, L, C3 = raw.shape
     C = tr.size
@@ -93,6 +96,8 @@ def forward(raw, tr, ti, gamma, state_in=None, want_state=True, misalign=False):
                                    _ptr(read), _ptr(sout), _ptr(ws), nbytes, B, L, C, None)
     if rc:
         raise RuntimeError(lib().fields_status_string(rc).decode())
+    if return_workspace:
+        return read, sout, ws
     return read, sout
 
 

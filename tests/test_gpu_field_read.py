@@ -15,6 +15,13 @@ from oracle import field_oracle
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["walk", "single_pass", "three_phase"])
+def algo(request, monkeypatch):
+    """Every test runs on both kernel families (the library reads the variable at each call)."""
+    monkeypatch.setenv("FIELDS_READ_ALGO", request.param)
+    return request.param
+
+
 @pytest.fixture(scope="module")
 def dev():
     assert torch.cuda.is_available(), "GPU tests need a CUDA device"
@@ -178,7 +185,7 @@ def test_bitwise_deterministic(dev):
         np.testing.assert_array_equal(a[key], b[key])
 
 
-def test_outputs_stay_inside_their_buffers(dev):
+def test_outputs_stay_inside_their_buffers(dev, algo):
     """Direct C-ABI call with sentinel guard bands around every output and the workspace."""
     from fields_lm_b200 import _lib
     lib = _lib.load()
@@ -207,6 +214,8 @@ def test_outputs_stay_inside_their_buffers(dev):
                                  t["gm"].data_ptr(), None, read.data_ptr(), state.data_ptr(),
                                  ws.data_ptr(), wsf, B, L, C, s)
     assert rc == 0
+    if algo == "single_pass":  # the error word exists only in the single-pass workspace layout
+        assert lib.fields_read_device_status(ws.data_ptr(), s) == 0
     torch.cuda.synchronize()
     assert intact(read_buf, n_read) and intact(state_buf, B * 2 * C) and intact(ws_buf, wsf // 4)
     ref, _ = field_oracle.forward(raw, tr, ti, gm)
@@ -222,6 +231,8 @@ def test_outputs_stay_inside_their_buffers(dev):
                                   gp[:C].data_ptr(), gp[C:2 * C].data_ptr(), gp[2 * C:].data_ptr(),
                                   None, wsb_t.data_ptr(), wsb, B, L, C, s)
     assert rc == 0
+    if algo == "single_pass":
+        assert lib.fields_read_device_status(wsb_t.data_ptr(), s) == 0
     torch.cuda.synchronize()
     assert intact(graw_buf, n_raw) and intact(gp_buf, 3 * C) and intact(wsb_buf, wsb // 4)
     # too-small workspace and null pointers are refused with a status, nothing is launched
