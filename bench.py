@@ -9,8 +9,8 @@ bf16-rounded activations held in fp32 at the operator boundary, fp32 state.
 Under torchrun every rank runs that workload on its own GPU (batch-sharded,
 no collective on the data path; weak scaling); rank 0 prints ONE JSON line.
 
-`value` is tokens/s with inputs resident in HBM, timed with CUDA events on the
-launching stream; `e2e` is the same metric from pinned host buffers through the
+`value` is tokens/s with inputs resident in HBM, through the C ABI on preallocated
+buffers, timed with CUDA events on the launching stream; `e2e` is the same metric from pinned host buffers through the
 public Python call and back to the host; `roofline` relates the step to the
 measured HBM copy bandwidth; `cpu_baseline` times the CPU port of the reference's
 complex64 PyTorch path on the host cores (a reported baseline, not the target).
@@ -39,7 +39,7 @@ BYTES_PER_TOKEN_FWD = (3 * C + 4 * C) * 4           # read raw, write read
 BYTES_PER_TOKEN_BWD = (3 * C + 4 * C + 3 * C) * 4   # read raw + grad_read, write grad_raw
 BYTES_PER_TOKEN = BYTES_PER_TOKEN_FWD + BYTES_PER_TOKEN_BWD
 FP32_TOL, BF16_TOL = 1e-5, 2e-2
-KERNEL_LAUNCHES_PER_STEP = 7   # forward 3 (summary, carry, materialize) + backward 4 (+ reduce)
+KERNEL_LAUNCHES_PER_STEP = 3   # chain-walk forward 1 + backward 2 (walk, parameter-gradient reduce)
 FALLBACK_HBM_GBS = 6650.0
 LONG_L = 65536
 
@@ -212,6 +212,45 @@ def gpu_step(raw, grad_read, tr, ti, gamma):
     return read, raw.grad
 
 
+class DirectOp:
+    """Forward and backward through the C ABI on preallocated buffers (what the autograd
+    function does, minus the allocations): the device-resident hot path that `value` times."""
+
+    def __init__(self, device, batch, length):
+        from fields_lm_b200 import _lib
+        self.lib = _lib.load()
+        self.dims = (batch, length, C)
+        self.read = torch.empty(batch, length, 4 * C, device=device)
+        self.grad_raw = torch.empty(batch, length, 3 * C, device=device)
+        self.grad_par = torch.empty(3, C, device=device)
+        self.nf = self.lib.fields_read_workspace_bytes(batch, length, C, 0)
+        self.nb = self.lib.fields_read_workspace_bytes(batch, length, C, 1)
+        self.wsf = torch.empty(max(self.nf, 256), dtype=torch.uint8, device=device)
+        self.wsb = torch.empty(max(self.nb, 256), dtype=torch.uint8, device=device)
+        self.stream = torch.cuda.current_stream(device).cuda_stream
+
+    def forward(self, raw, tr, ti, gamma):
+        rc = self.lib.fields_read_forward(raw.data_ptr(), tr.data_ptr(), ti.data_ptr(),
+                                          gamma.data_ptr(), None, self.read.data_ptr(), None,
+                                          self.wsf.data_ptr(), self.nf, *self.dims, self.stream)
+        if rc:
+            raise RuntimeError(f"fields_read_forward status {rc}")
+
+    def backward(self, raw, tr, ti, gamma, grad_read):
+        g = self.grad_par
+        rc = self.lib.fields_read_backward(raw.data_ptr(), tr.data_ptr(), ti.data_ptr(),
+                                           gamma.data_ptr(), None, self.read.data_ptr(),
+                                           grad_read.data_ptr(), None, self.grad_raw.data_ptr(),
+                                           g[0].data_ptr(), g[1].data_ptr(), g[2].data_ptr(), None,
+                                           self.wsb.data_ptr(), self.nb, *self.dims, self.stream)
+        if rc:
+            raise RuntimeError(f"fields_read_backward status {rc}")
+
+    def status(self):
+        """Error word of the last forward (single-pass kernels only write it)."""
+        return self.lib.fields_read_device_status(self.wsf.data_ptr(), self.stream)
+
+
 def timed_loop(fn, steps: int, stream) -> float:
     """Milliseconds for `steps` calls of fn, CUDA events on the launching stream."""
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -274,7 +313,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     raw = raw_h.to(device).requires_grad_(True)
     grad_read = grad_h.to(device)
 
-    step = lambda: gpu_step(raw, grad_read, tr, ti, gamma)
+    op = DirectOp(device, B, L)
+    raw_d, tr_d, ti_d, gm_d = raw.detach(), tr.detach(), ti.detach(), gamma.detach()
+
+    def step():
+        op.forward(raw_d, tr_d, ti_d, gm_d)
+        op.backward(raw_d, tr_d, ti_d, gm_d, grad_read)
     for _ in range(max(args.warmup, 3)):
         step()
     if args.profile:
@@ -299,11 +343,20 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     # forward-only and backward-only, to split the step for the roofline report
     def fwd_only():
-        with torch.no_grad():
-            fused_field_read(raw, tr, ti, gamma, 32, 64)
+        op.forward(raw_d, tr_d, ti_d, gm_d)
     for _ in range(3):
         fwd_only()
     ms_fwd = timed_loop(fwd_only, args.steps, stream) / args.steps
+
+    # secondary workload of the metric: forward of one 65,536-token sequence on this GPU
+    long_op = DirectOp(device, 1, LONG_L)
+    long_raw = synthetic_inputs(2, 1, LONG_L)[0].to(device)
+    long_fwd = lambda: long_op.forward(long_raw, tr_d, ti_d, gm_d)
+    for _ in range(3):
+        long_fwd()
+    long_steps = max(5, min(args.steps, 50))
+    ms_long = timed_loop(long_fwd, long_steps, stream) / long_steps
+    del long_op, long_raw
 
     # end to end: pinned host -> device, forward + backward, results back to pinned host
     raw_pin, grad_pin = raw_h.pin_memory(), grad_h.pin_memory()
@@ -346,7 +399,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "roofline": {
             "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
             "frac": achieved / peak, "traffic": None, "peak_source": f"of {peak_kind}",
-            "kernel": "whole step per GPU: 3 forward + 4 backward launches",
+            "kernel": "whole step per GPU: FwdWalk + BwdWalk + BwdReduce",
             "algorithmic_bytes_per_token": BYTES_PER_TOKEN,
             "forward": {"ms": ms_fwd, "achieved": fwd_gbs, "frac": fwd_gbs / peak},
             "backward": {"ms": bwd_ms,
@@ -357,6 +410,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                 "h2d_bytes_per_step": raw_pin.numel() * 4 + grad_pin.numel() * 4,
                 "d2h_bytes_per_step": (read_pin.numel() + graw_pin.numel() + gpar_pin.numel()) * 4,
                 "ms_per_step": ms_e2e},
+        "forward_64k": {"workload": "forward of 1 x 65,536 tokens on one GPU",
+                        "ms": ms_long, "tokens_per_s": LONG_L / (ms_long * 1e-3),
+                        "achieved": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9,
+                        "frac": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9 / peak},
         "gpu_launches": KERNEL_LAUNCHES_PER_STEP * args.steps,
         "clocks": clocks.summary(),
         "parity": parity_check(device, tr.detach(), ti.detach(), gamma.detach()),

@@ -23,6 +23,10 @@ SYMBOLS = {
     "fields_read_forward": (_I, [_P] * 8 + [_SZ, _I, _I, _I, _P]),
     "fields_read_backward": (_I, [_P] * 14 + [_SZ, _I, _I, _I, _P]),
     "fields_read_device_status": (_I, [_P, _P]),
+    "fields_read_step": (_I, [_P] * 6 + [_I, _I, _P]),
+    "fields_read_step_bf16": (_I, [_P] * 6 + [_I, _I, _P]),
+    "fields_read_span_summary": (_I, [_P] * 6 + [_SZ, _I, _I, _I, _P]),
+    "fields_read_fold_summaries": (_I, [_P, _P, _P, _I, _I, _I, _I, _P]),
     "fields_read_static_scratch_bytes": (_SZ, []),
     "fields_read_forward_noalloc": (_I, [_P] * 7 + [_I, _I, _I, _P]),
 }

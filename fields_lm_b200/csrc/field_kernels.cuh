@@ -540,4 +540,164 @@ struct BwdReduce {
     }
 };
 
+
+// ---------------------------------------------------------------------------
+// Span summary: the affine map of a whole span per (batch, channel), composed from
+// the chunk maps that FwdSummary wrote. One block owns 32 channels of one batch row;
+// warp w composes its slice of chunks (phase 0), warp 0 composes the slices (phase 1).
+// This pair is what sequence-sharded ranks exchange.
+// ---------------------------------------------------------------------------
+struct SpanCompose {
+    struct Params {
+        const float* sum;  // [4][B][N][C]
+        float* summary;    // [B][4][C]  Re A | Im A | Re B | Im B
+        Shape s;
+    };
+    static constexpr int kThreads = 32 * kCarryWarps;
+    static constexpr int kPhases = 2;
+    static constexpr int kSmemFloats = 4 * kThreads;
+
+    FL_HD static void phase0(const Params& p, int block, int thread, float* smem) {
+        const Shape& s = p.s;
+        const int cgroups = (s.C + 31) / 32;
+        const int lane = thread & 31, w = thread >> 5;
+        const int b = block / cgroups;
+        const int c = (block % cgroups) * 32 + lane;
+        if (c >= s.C) return;
+        const int per = (s.N + kCarryWarps - 1) / kCarryWarps;
+        const int lo = w * per < s.N ? w * per : s.N;
+        const int hi = lo + per < s.N ? lo + per : s.N;
+        const size_t plane = (size_t)s.B * s.N * s.C;
+        Affine m = affine_identity();
+        for (int i = lo; i < hi; ++i) {
+            const size_t idx = ((size_t)b * s.N + i) * s.C + c;
+            m = affine_then(m, p.sum[idx], p.sum[idx + plane], p.sum[idx + 2 * plane],
+                            p.sum[idx + 3 * plane]);
+        }
+        float* o = smem + 4 * thread;
+        o[0] = m.ar; o[1] = m.ai; o[2] = m.br; o[3] = m.bi;
+    }
+
+    FL_HD static void phase1(const Params& p, int block, int thread, float* smem) {
+        const Shape& s = p.s;
+        if (thread >= 32) return;
+        const int cgroups = (s.C + 31) / 32;
+        const int b = block / cgroups;
+        const int c = (block % cgroups) * 32 + thread;
+        if (c >= s.C) return;
+        Affine m = affine_identity();
+        for (int w = 0; w < kCarryWarps; ++w) {
+            const float* q = smem + 4 * (w * 32 + thread);
+            m = affine_then(m, q[0], q[1], q[2], q[3]);
+        }
+        float* o = p.summary + (size_t)b * 4 * s.C + c;
+        o[0] = m.ar; o[s.C] = m.ai; o[2 * s.C] = m.br; o[3 * s.C] = m.bi;
+    }
+};
+
+// ---------------------------------------------------------------------------
+// Fold of the span summaries of the ranks before `rank` onto the sequence's initial
+// state: the state entering rank's span. One thread per (batch, channel).
+// ---------------------------------------------------------------------------
+struct FoldSummaries {
+    struct Params {
+        const float* summaries;  // [P][B][4][C]
+        const float* state0;     // [B, 2C] or null: state before the first span
+        float* state;            // [B, 2C]
+        int rank, P, B, C;
+    };
+    static constexpr int kThreads = 128;
+    static constexpr int kPhases = 1;
+    static constexpr int kSmemFloats = 0;
+
+    FL_HD static void phase0(const Params& p, int block, int thread, float*) {
+        const long long i = (long long)block * kThreads + thread;
+        if (i >= (long long)p.B * p.C) return;
+        const int b = (int)(i / p.C), c = (int)(i % p.C);
+        float sr = p.state0 ? p.state0[(size_t)b * 2 * p.C + c] : 0.0f;
+        float si = p.state0 ? p.state0[(size_t)b * 2 * p.C + p.C + c] : 0.0f;
+        for (int r = 0; r < p.rank; ++r) {
+            const float* m = p.summaries + (((size_t)r * p.B + b) * 4) * p.C + c;
+            affine_apply(Affine{m[0], m[p.C], m[2 * (size_t)p.C], m[3 * (size_t)p.C]}, sr, si);
+        }
+        p.state[(size_t)b * 2 * p.C + c] = sr;
+        p.state[(size_t)b * 2 * p.C + p.C + c] = si;
+    }
+};
+
+
+// ---------------------------------------------------------------------------
+// One recurrent step for incremental decoding: the state is carried by the caller,
+// one token per sequence enters, one row of `read` comes out. One thread per
+// (sequence, channel); all accesses coalesced over channels. The arithmetic is one
+// iteration of the forward recurrence (reference :599-622); the reference itself has no
+// incremental path, its full-sequence forward over prefix + new tokens is the oracle.
+// IO = float or bf16 bits (uint16_t) for raw and read; the state is always fp32.
+// ---------------------------------------------------------------------------
+FL_HD float bf16_bits_to_float(uint16_t h) {
+    const uint32_t u = (uint32_t)h << 16;
+    float f;
+#if FL_DEVICE_CODE
+    f = __uint_as_float(u);
+#else
+    std::memcpy(&f, &u, 4);
+#endif
+    return f;
+}
+
+// round to nearest even; NaN stays NaN
+FL_HD uint16_t float_to_bf16_bits(float f) {
+    uint32_t u;
+#if FL_DEVICE_CODE
+    u = __float_as_uint(f);
+#else
+    std::memcpy(&u, &f, 4);
+#endif
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+
+FL_HD float io_load(const float* p, size_t i) { return p[i]; }
+FL_HD float io_load(const uint16_t* p, size_t i) { return bf16_bits_to_float(p[i]); }
+FL_HD void io_store(float* p, size_t i, float v) { p[i] = v; }
+FL_HD void io_store(uint16_t* p, size_t i, float v) { p[i] = float_to_bf16_bits(v); }
+
+template <typename IO>
+struct DecodeStep {
+    struct Params {
+        const IO* raw;  // [B, 3C]
+        const float* tr;
+        const float* ti;
+        const float* gamma;
+        float* state;   // [B, 2C] in and out
+        IO* read;       // [B, 4C]
+        int B, C;
+    };
+    static constexpr int kThreads = 128;
+    static constexpr int kPhases = 1;
+    static constexpr int kSmemFloats = 0;
+
+    FL_HD static void phase0(const Params& p, int block, int thread, float*) {
+        const long long i = (long long)block * kThreads + thread;
+        if (i >= (long long)p.B * p.C) return;
+        const int b = (int)(i / p.C), c = (int)(i % p.C);
+        const size_t C = p.C;
+        const Gate g = make_gate(io_load(p.raw, b * 3 * C + c), io_load(p.raw, b * 3 * C + C + c),
+                                 io_load(p.raw, b * 3 * C + 2 * C + c));
+        float sr = p.state[b * 2 * C + c], si = p.state[b * 2 * C + C + c];
+        float mr, mi;
+        cmul(p.tr[c], p.ti[c], sr, si, mr, mi);
+        const float bs = p.gamma[c] * g.vac;
+        sr = (1.0f - g.vac) * mr + bs * g.inj_r;
+        si = (1.0f - g.vac) * mi + bs * g.inj_i;
+        p.state[b * 2 * C + c] = sr;
+        p.state[b * 2 * C + C + c] = si;
+        io_store(p.read, b * 4 * C + c, sr);
+        io_store(p.read, b * 4 * C + C + c, si);
+        io_store(p.read, b * 4 * C + 2 * C + c, g.vac * mr);
+        io_store(p.read, b * 4 * C + 3 * C + c, g.vac * mi);
+    }
+};
+
 }  // namespace fields

@@ -625,4 +625,68 @@ int fields_read_device_status(const void* workspace, void* stream) {
     return word != -1 ? FIELDS_ERR_TIMEOUT : FIELDS_OK;
 }
 
+
+int fields_read_span_summary(const float* raw, const float* tr, const float* ti,
+                             const float* gamma, float* summary, void* workspace,
+                             size_t workspace_bytes, int B, int L, int C, void* stream) {
+    if (B < 0 || L < 0 || C <= 0) return FIELDS_ERR_ARGUMENT;
+    if (B == 0) return FIELDS_OK;
+    if (!raw || !tr || !ti || !gamma || !summary) return FIELDS_ERR_ARGUMENT;
+    if (L == 0) return FIELDS_ERR_ARGUMENT;  // an empty span has no summary to exchange
+    Stream st = reinterpret_cast<Stream>(stream);
+    const bool vec4 = C % 4 == 0 && aligned16(raw) && aligned16(tr) && aligned16(ti) &&
+                      aligned16(gamma) && aligned16(workspace);
+    const Plan pl = make_plan(B, L, C, vec4 ? 4 : 1);
+    if (!workspace || workspace_bytes < pl.fwd_floats * sizeof(float) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return FIELDS_ERR_WORKSPACE;
+    float* ws = static_cast<float*>(workspace);
+    FwdParams p{raw, tr, ti, gamma, nullptr, nullptr, nullptr, ws + pl.sum_off, ws + pl.carry_off,
+                pl.s};
+    int rc = vec4 ? launch<FwdSummary<4, 4>>(p, tile_blocks(pl.s), st)
+                  : launch<FwdSummary<1, 4>>(p, tile_blocks(pl.s), st);
+    if (rc) return rc;
+    SpanCompose::Params cp{p.sum, summary, pl.s};
+    return launch<SpanCompose>(cp, (long long)B * ((C + 31) / 32), st);
+}
+
+int fields_read_fold_summaries(const float* summaries, const float* state0, float* state,
+                               int rank, int P, int B, int C, void* stream) {
+    if (B < 0 || C <= 0 || P <= 0 || rank < 0 || rank >= P) return FIELDS_ERR_ARGUMENT;
+    if (B == 0) return FIELDS_OK;
+    if (!summaries || !state) return FIELDS_ERR_ARGUMENT;
+    FoldSummaries::Params p{summaries, state0, state, rank, P, B, C};
+    const long long n = (long long)B * C;
+    return launch<FoldSummaries>(p, (n + FoldSummaries::kThreads - 1) / FoldSummaries::kThreads,
+                                 reinterpret_cast<Stream>(stream));
+}
+
+
+}  // extern "C"
+
+template <typename IO>
+static int run_step(const IO* raw, const float* tr, const float* ti, const float* gamma,
+                    float* state, IO* read, int B, int C, void* stream) {
+    if (B < 0 || C <= 0) return FIELDS_ERR_ARGUMENT;
+    if (B == 0) return FIELDS_OK;
+    if (!raw || !tr || !ti || !gamma || !state || !read) return FIELDS_ERR_ARGUMENT;
+    typename DecodeStep<IO>::Params p{raw, tr, ti, gamma, state, read, B, C};
+    const long long n = (long long)B * C;
+    return launch<DecodeStep<IO>>(p, (n + DecodeStep<IO>::kThreads - 1) / DecodeStep<IO>::kThreads,
+                                  reinterpret_cast<Stream>(stream));
+}
+
+extern "C" {
+
+int fields_read_step(const float* raw, const float* tr, const float* ti, const float* gamma,
+                     float* state, float* read, int B, int C, void* stream) {
+    return run_step<float>(raw, tr, ti, gamma, state, read, B, C, stream);
+}
+
+int fields_read_step_bf16(const void* raw, const float* tr, const float* ti, const float* gamma,
+                          float* state, void* read, int B, int C, void* stream) {
+    return run_step<uint16_t>(static_cast<const uint16_t*>(raw), tr, ti, gamma, state,
+                              static_cast<uint16_t*>(read), B, C, stream);
+}
+
 }  // extern "C"

@@ -1,0 +1,89 @@
+"""Sequence-sharded forward of the Field read across the GPUs of one node.
+
+A long sequence is cut into P contiguous spans, one per rank. The recurrence is an
+affine map per (batch, channel), so a span is summarised by one complex pair
+``s_out = A s_in + Bv``: ranks exchange those pairs (``[B, 4, C]`` floats each, 8 KB at
+B = 1), every rank folds the pairs of the spans before it onto the initial state and
+then runs its span from that state. Everything else in a Field block is token-parallel.
+The reference runs a sequence on one GPU only; its single-device full-sequence output is
+the oracle for this path.
+
+Steps on rank r (all on the current CUDA stream):
+  1. ``fields_read_span_summary``  - one read of the span, chunk maps composed to (A, Bv);
+  2. ``all_gather`` of the summaries over NCCL (NVLink/NVSwitch);
+  3. ``fields_read_fold_summaries`` - state entering span r;
+  4. ``fields_read_forward`` with that state.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+class CudaOps:
+    """The three device operations, on the CUDA library."""
+
+    def span_summary(self, raw, tr, ti, gamma):
+        lib = _lib.load()
+        B, L, C3 = raw.shape
+        C = C3 // 3
+        out = torch.empty((B, 4, C), device=raw.device, dtype=torch.float32)
+        n = lib.fields_read_workspace_bytes(B, L, C, 0)
+        ws = torch.empty(max(n, 256), dtype=torch.uint8, device=raw.device)
+        rc = lib.fields_read_span_summary(raw.data_ptr(), tr.data_ptr(), ti.data_ptr(),
+                                          gamma.data_ptr(), out.data_ptr(), ws.data_ptr(), n,
+                                          B, L, C, torch.cuda.current_stream(raw.device).cuda_stream)
+        _lib.check(rc, "fields_read_span_summary")
+        return out
+
+    def fold(self, summaries, rank, state0):
+        lib = _lib.load()
+        P, B, _, C = summaries.shape
+        out = torch.empty((B, 2 * C), device=summaries.device, dtype=torch.float32)
+        rc = lib.fields_read_fold_summaries(
+            summaries.data_ptr(), None if state0 is None else state0.data_ptr(), out.data_ptr(),
+            rank, P, B, C, torch.cuda.current_stream(summaries.device).cuda_stream)
+        _lib.check(rc, "fields_read_fold_summaries")
+        return out
+
+    def forward(self, raw, tr, ti, gamma, state_in):
+        from .field_read import field_read_with_state
+        with torch.no_grad():
+            return field_read_with_state(raw, tr, ti, gamma, state_in)
+
+
+def span_bounds(length: int, world: int, rank: int) -> Tuple[int, int]:
+    """Contiguous, near-equal spans: the first ``length % world`` ranks get one step more."""
+    base, extra = divmod(length, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def sequence_parallel_field_read(raw_span: torch.Tensor, tr: torch.Tensor, ti: torch.Tensor,
+                                 gamma: torch.Tensor, group=None,
+                                 state0: Optional[torch.Tensor] = None, ops=None):
+    """Forward of this rank's span of a sequence sharded over ``group``.
+
+    ``raw_span`` is ``[B, L_r, 3C]`` fp32 (spans may differ in length but not be empty);
+    ``state0`` is the state before the first span (same on every rank, or None for zero).
+    Returns ``(read_span [B, L_r, 4C], state_after_span [B, 2C])``.
+    """
+    ops = ops or CudaOps()
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    if raw_span.dim() != 3 or raw_span.shape[1] == 0:
+        raise ValueError(f"every rank needs a non-empty span, got {tuple(raw_span.shape)}")
+    raw_span = raw_span.contiguous()
+    if world == 1:
+        return ops.forward(raw_span, tr, ti, gamma, state0)
+    summary = ops.span_summary(raw_span, tr, ti, gamma)
+    B = summary.shape[0]
+    gathered = torch.empty((world * B,) + tuple(summary.shape[1:]), device=summary.device,
+                           dtype=summary.dtype)
+    dist.all_gather_into_tensor(gathered, summary, group=group)  # rank-major along dim 0
+    state_in = ops.fold(gathered.view(world, B, *summary.shape[1:]), rank, state0)
+    return ops.forward(raw_span, tr, ti, gamma, state_in)

@@ -91,6 +91,40 @@ int fields_read_backward(const float *raw, const float *tr, const float *ti,
                          float *grad_state_in, void *workspace,
                          size_t workspace_bytes, int B, int L, int C, void *stream);
 
+/*
+ * Sequence sharding (no counterpart in the reference, which runs a sequence on one GPU;
+ * the arithmetic is the chunk-summary composition of
+ * field_only_v4_chunked_triton_wiki100.py:503-509 and :539-550 applied to a whole span).
+ *
+ * fields_read_span_summary: the affine map  s_out = A s_in + Bv  of a span of L steps per
+ * (batch, channel), as summary [B, 4, C] = Re A | Im A | Re Bv | Im Bv. Workspace as for
+ * the forward pass.
+ *
+ * fields_read_fold_summaries: given the summaries of all P spans, [P, B, 4, C] in span
+ * order, and the state before the first span (state0 [B, 2C] or NULL = zero), writes the
+ * state entering span `rank` into state [B, 2C]. That state is the state_in of
+ * fields_read_forward for that span.
+ */
+int fields_read_span_summary(const float *raw, const float *tr, const float *ti,
+                             const float *gamma, float *summary, void *workspace,
+                             size_t workspace_bytes, int B, int L, int C, void *stream);
+int fields_read_fold_summaries(const float *summaries, const float *state0, float *state,
+                               int rank, int P, int B, int C, void *stream);
+
+/*
+ * One recurrent step for incremental decoding (no counterpart in the reference, whose
+ * inference is always a full-sequence pass; the arithmetic is one iteration of
+ * field_only_v4_chunked_triton_wiki100.py:599-622).
+ *   raw    [B, 3C]  the new token's z_r | z_i | z_v for every sequence
+ *   state  [B, 2C]  fp32, read and overwritten in place
+ *   read   [B, 4C]  output row
+ * fields_read_step_bf16 takes raw and writes read as bfloat16; the state stays fp32.
+ */
+int fields_read_step(const float *raw, const float *tr, const float *ti, const float *gamma,
+                     float *state, float *read, int B, int C, void *stream);
+int fields_read_step_bf16(const void *raw, const float *tr, const float *ti, const float *gamma,
+                          float *state, void *read, int B, int C, void *stream);
+
 /* Text of the last CUDA runtime error seen by the calling thread inside this library. */
 const char *fields_last_cuda_error(void);
 

@@ -46,6 +46,14 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.fields_read_forward.restype = I
     lib.fields_read_backward.argtypes = [P] * 14 + [SZ, I, I, I, P]
     lib.fields_read_backward.restype = I
+    lib.fields_read_span_summary.argtypes = [P] * 6 + [SZ, I, I, I, P]
+    lib.fields_read_span_summary.restype = I
+    lib.fields_read_fold_summaries.argtypes = [P, P, P, I, I, I, I, P]
+    lib.fields_read_fold_summaries.restype = I
+    lib.fields_read_step.argtypes = [P] * 6 + [I, I, P]
+    lib.fields_read_step.restype = I
+    lib.fields_read_step_bf16.argtypes = [P] * 6 + [I, I, P]
+    lib.fields_read_step_bf16.restype = I
     lib.fields_read_device_status.argtypes = [P, P]
     lib.fields_read_device_status.restype = I
     return lib
@@ -121,3 +129,51 @@ def backward(raw, tr, ti, gamma, read, grad_read, state_in=None, grad_state_out=
     if rc:
         raise RuntimeError(lib().fields_status_string(rc).decode())
     return g_raw, g_tr, g_ti, g_gm, g_sin
+
+
+def span_summary(raw, tr, ti, gamma):
+    B, L, C3 = raw.shape
+    C = tr.size
+    a = [_f32(x) for x in (raw, tr, ti, gamma)]
+    out = _f32(np.full((B, 4, C), np.nan))
+    nbytes = lib().fields_read_workspace_bytes(B, L, C, 0)
+    ws = _aligned(max(nbytes, 256))
+    ws[...] = 0xFF
+    rc = lib().fields_read_span_summary(_ptr(a[0]), _ptr(a[1]), _ptr(a[2]), _ptr(a[3]), _ptr(out),
+                                        _ptr(ws), nbytes, B, L, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return out
+
+
+def fold_summaries(summaries, rank, state0=None):
+    P_, B, four, C = summaries.shape
+    s = _f32(summaries)
+    s0 = None if state0 is None else _f32(state0)
+    out = _f32(np.full((B, 2 * C), np.nan))
+    rc = lib().fields_read_fold_summaries(_ptr(s), _ptr(s0), _ptr(out), rank, P_, B, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return out
+
+
+def step(raw_row, tr, ti, gamma, state, bf16=False):
+    """One decode step; returns (read_row, new_state). With bf16, raw/read are uint16 bit patterns."""
+    B, C3 = raw_row.shape
+    C = tr.size
+    a = [_f32(x) for x in (tr, ti, gamma)]
+    st = _f32(state)
+    if bf16:
+        store = _aligned(B * C3 * 2).view(np.uint16).reshape(B, C3)
+        store[...] = raw_row
+        out = _aligned(B * 4 * C * 2).view(np.uint16).reshape(B, 4 * C)
+        rc = lib().fields_read_step_bf16(_ptr(store), _ptr(a[0]), _ptr(a[1]), _ptr(a[2]), _ptr(st),
+                                         _ptr(out), B, C, None)
+    else:
+        r = _f32(raw_row)
+        out = _f32(np.full((B, 4 * C), np.nan))
+        rc = lib().fields_read_step(_ptr(r), _ptr(a[0]), _ptr(a[1]), _ptr(a[2]), _ptr(st),
+                                    _ptr(out), B, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return out, st

@@ -129,3 +129,51 @@ def test_bad_arguments_return_status():
     assert L.fields_read_workspace_bytes(0, 5, 4, 0) == 0
     assert L.fields_read_workspace_bytes(2, 100, 512, 1) > L.fields_read_workspace_bytes(2, 100, 512, 0)
     assert b"workspace" in L.fields_status_string(2)
+
+
+@pytest.mark.parametrize("B,L,C", [(2, 333, 20), (1, 64, 512), (3, 17, 7)])
+def test_span_summary_and_fold(B, L, C):
+    """Spans summarised separately and folded in order give the state a single pass reaches."""
+    rng = np.random.default_rng(L + C)
+    tr, ti, gm = _params(C, rng)
+    raw = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+    s0 = rng.standard_normal((B, 2 * C)).astype(np.float32)
+    assert rel_err(emu.span_summary(raw, tr, ti, gm), field_oracle.span_summary(raw, tr, ti, gm)) < FP32_TOL
+    cuts = [0, L // 3, L // 3 + 1, L]
+    spans = [raw[:, a:b] for a, b in zip(cuts[:-1], cuts[1:]) if b > a]
+    summaries = np.stack([emu.span_summary(x, tr, ti, gm) for x in spans])
+    state = s0.astype(np.float64)
+    for r, x in enumerate(spans):
+        got = emu.fold_summaries(summaries, r, state0=s0)
+        assert rel_err(got, state) < FP32_TOL
+        _, state = field_oracle.forward(x, tr, ti, gm, state_in=state)
+    np.testing.assert_array_equal(emu.fold_summaries(summaries, 0), 0.0)
+
+
+def test_decode_steps_continue_a_prefix():
+    """Prefix in one pass, then token-by-token steps == one pass over prefix + tokens (causality)."""
+    rng = np.random.default_rng(8)
+    B, L, C, K = 3, 40, 12, 5
+    tr, ti, gm = _params(C, rng)
+    raw = rng.standard_normal((B, L + K, 3 * C)).astype(np.float32)
+    full, _ = field_oracle.forward(raw, tr, ti, gm)
+    _, state = emu.forward(raw[:, :L], tr, ti, gm)
+    for k in range(K):
+        row, state = emu.step(raw[:, L + k], tr, ti, gm, state)
+        assert rel_err(row, full[:, L + k]) < FP32_TOL
+        assert rel_err(state, full[:, L + k, :2 * C]) < FP32_TOL
+
+
+def test_decode_step_bf16_io():
+    import torch
+    rng = np.random.default_rng(9)
+    B, C = 4, 16
+    tr, ti, gm = _params(C, rng)
+    raw = torch.from_numpy(rng.standard_normal((B, 3 * C)).astype(np.float32)).bfloat16()
+    state = rng.standard_normal((B, 2 * C)).astype(np.float32)
+    bits = raw.view(torch.int16).numpy().view(np.uint16)
+    row_bits, new_state = emu.step(bits, tr, ti, gm, state, bf16=True)
+    ref, ref_state = field_oracle.forward(raw.float().numpy()[:, None], tr, ti, gm, state_in=state)
+    got = torch.from_numpy(np.array(row_bits).view(np.int16)).view(torch.bfloat16).float().numpy()
+    assert rel_err(new_state, ref_state) < FP32_TOL          # the state never leaves fp32
+    assert rel_err(got, ref[:, 0]) < 2 ** -8                 # one bf16 rounding of the output
