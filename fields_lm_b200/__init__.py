@@ -4,14 +4,17 @@ Public surface:
 
 * :func:`fused_field_read` - drop-in for the reference operator of the same name;
 * :func:`field_read_with_state` - the operator with carried state in and out;
+* :func:`field_read_step` - one recurrent step for incremental decoding;
+* :func:`fields_lm_b200.seqpar.sequence_parallel_field_read` - sequence-sharded forward;
 * :func:`install` / :func:`uninstall` - rebind the operator inside a built model;
 * :mod:`fields_lm_b200.mixer` - mirror of the reference's mixer/block modules;
 * :mod:`fields_lm_b200.build` - compiles the CUDA library.
 
 The CUDA library is required: nothing here falls back to a CPU or PyTorch path.
 """
+from .decode import field_read_step
 from .field_read import FieldReadFunction, field_read_with_state, fused_field_read
 from .install import install, uninstall
 
-__all__ = ["FieldReadFunction", "field_read_with_state", "fused_field_read", "install",
+__all__ = ["FieldReadFunction", "field_read_step", "field_read_with_state", "fused_field_read", "install",
            "uninstall"]

@@ -19,6 +19,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .decode import field_read_step
 from .field_read import field_read_with_state, fused_field_read
 
 
@@ -98,6 +99,18 @@ class IndependentVacancyField(nn.Module):
         return x + (out * torch.sigmoid(self.gate_proj(x))).to(x.dtype), state_out
 
 
+    @torch.no_grad()
+    def step(self, x: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
+        """One new token per sequence: ``x [B, dim]``, ``state [B, dim]`` fp32 updated in place."""
+        raw = self.write_proj(x).contiguous()
+        if raw.dtype not in (torch.float32, torch.bfloat16):
+            raw = raw.float()
+        tr, ti, gamma = transition_parameters(self.radius_logit, self.theta)
+        read = field_read_step(raw, tr, ti, gamma, state)
+        out = self.out_proj(self.read_norm(read))
+        return x + (out * torch.sigmoid(self.gate_proj(x))).to(x.dtype)
+
+
 class FieldBlock(nn.Module):
     """Field mixer followed by a pre-norm SwiGLU feed-forward (reference :1198-1221)."""
 
@@ -111,4 +124,15 @@ class FieldBlock(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         x = self.mixer(x)
+        return x + self.ff(self.ff_norm(x))
+
+    @torch.no_grad()
+    def prefill(self, x: torch.Tensor):
+        """Full pass over a prefix ``[B, L, dim]``; returns the output and the mixer's end state."""
+        x, state = self.mixer.forward_with_state(x, None)
+        return x + self.ff(self.ff_norm(x)), state
+
+    @torch.no_grad()
+    def step(self, x: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
+        x = self.mixer.step(x, state)
         return x + self.ff(self.ff_norm(x))

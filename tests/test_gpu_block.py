@@ -95,3 +95,45 @@ def test_state_dict_keys_match_the_reference_block():
         "mixer.read_norm.weight", "mixer.out_proj.weight", "mixer.out_proj.bias",
         "mixer.gate_proj.weight", "mixer.gate_proj.bias", "ff_norm.weight", "ff.w12.weight",
         "ff.w3.weight"])
+
+
+def test_prefill_then_decode_steps_equal_one_full_pass():
+    """Three stacked blocks: a prefix pass that returns states, then single-token steps, must
+    reproduce the full pass over prefix + tokens (the model is causal)."""
+    from fields_lm_b200.mixer import FieldBlock
+    torch.manual_seed(5)
+    blocks = [FieldBlock(256, "triton", 32, 32, 64, 512).cuda().eval() for _ in range(3)]
+    gen = torch.Generator().manual_seed(6)
+    B, L, K = 4, 96, 6
+    x = torch.randn(B, L + K, 256, generator=gen).cuda()
+    with torch.no_grad():
+        full = x
+        for blk in blocks:
+            full = blk(full)
+        h, states = x[:, :L], []
+        for blk in blocks:
+            h, s = blk.prefill(h)
+            states.append(s)
+        assert rel_err(h.cpu().numpy(), full[:, :L].cpu().numpy()) < 5e-5
+        for k in range(K):
+            t = x[:, L + k]
+            for blk, s in zip(blocks, states):
+                t = blk.step(t, s)
+            assert rel_err(t.cpu().numpy(), full[:, L + k].cpu().numpy()) < 5e-5
+
+
+def test_decode_step_bf16_matches_fp32_step():
+    from fields_lm_b200 import field_read_step
+    gen = torch.Generator().manual_seed(7)
+    B, C = 256, 512
+    radius = torch.rand(C, generator=gen) * 0.49 + 0.5
+    theta = (torch.rand(C, generator=gen) * 2 - 1) * torch.pi
+    tr, ti = (radius * torch.cos(theta)).cuda(), (radius * torch.sin(theta)).cuda()
+    gm = torch.sqrt(1 - radius ** 2).cuda()
+    raw = torch.randn(B, 3 * C, generator=gen).cuda().bfloat16()
+    s32 = torch.randn(B, 2 * C, generator=gen).cuda()
+    s16 = s32.clone()
+    r32 = field_read_step(raw.float(), tr, ti, gm, s32)
+    r16 = field_read_step(raw, tr, ti, gm, s16)
+    torch.testing.assert_close(s16, s32, rtol=0, atol=0)      # same fp32 state either way
+    assert rel_err(r16.float().cpu().numpy(), r32.cpu().numpy()) < BF16_TOL
