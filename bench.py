@@ -348,15 +348,24 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         fwd_only()
     ms_fwd = timed_loop(fwd_only, args.steps, stream) / args.steps
 
-    # secondary workload of the metric: forward of one 65,536-token sequence on this GPU
-    long_op = DirectOp(device, 1, LONG_L)
-    long_raw = synthetic_inputs(2, 1, LONG_L)[0].to(device)
-    long_fwd = lambda: long_op.forward(long_raw, tr_d, ti_d, gm_d)
+    # secondary workload of the metric: forward of one 65,536-token sequence, on one GPU or
+    # sharded over the sequence across all ranks (span summaries exchanged with NCCL)
+    long_steps = max(5, min(args.steps, 50))
+    if dist_on:
+        from fields_lm_b200 import seqpar
+        lo, hi = seqpar.span_bounds(LONG_L, world, rank)
+        long_raw = synthetic_inputs(2, 1, LONG_L)[0][:, lo:hi].contiguous().to(device)
+        long_fwd = lambda: seqpar.sequence_parallel_field_read(long_raw, tr_d, ti_d, gm_d)
+    else:
+        long_op = DirectOp(device, 1, LONG_L)
+        long_raw = synthetic_inputs(2, 1, LONG_L)[0].to(device)
+        long_fwd = lambda: long_op.forward(long_raw, tr_d, ti_d, gm_d)
     for _ in range(3):
         long_fwd()
-    long_steps = max(5, min(args.steps, 50))
-    ms_long = timed_loop(long_fwd, long_steps, stream) / long_steps
-    del long_op, long_raw
+    barrier(dist_on)
+    ms_long = max_over_ranks(timed_loop(long_fwd, long_steps, stream) / long_steps, dist_on, device)
+    barrier(dist_on)
+    del long_raw
 
     # end to end: pinned host -> device, forward + backward, results back to pinned host
     raw_pin, grad_pin = raw_h.pin_memory(), grad_h.pin_memory()
@@ -364,15 +373,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     graw_pin = torch.empty(B, L, 3 * C).pin_memory()
     gpar_pin = torch.empty(3, C).pin_memory()
 
+    from fields_lm_b200.host import HostFieldRead
+    pipe = HostFieldRead(device, B, L, C, rows_per_chunk=1)
+
     def e2e_step():
-        r = raw_pin.to(device, non_blocking=True).requires_grad_(True)
-        g = grad_pin.to(device, non_blocking=True)
-        tr.grad = ti.grad = gamma.grad = None
-        read = fused_field_read(r, tr, ti, gamma, 32, 64)
-        read.backward(g)
-        read_pin.copy_(read.detach(), non_blocking=True)
-        graw_pin.copy_(r.grad, non_blocking=True)
-        gpar_pin.copy_(torch.stack((tr.grad, ti.grad, gamma.grad)), non_blocking=True)
+        gpar = pipe.fwd_bwd(raw_pin, grad_pin, tr_d, ti_d, gm_d, read_pin, graw_pin)
+        gpar_pin.copy_(gpar, non_blocking=True)
     for _ in range(2):
         e2e_step()
     e2e_steps = max(3, min(args.steps, 10))
@@ -409,11 +415,15 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "e2e": {"value": world * B * L / (ms_e2e * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": raw_pin.numel() * 4 + grad_pin.numel() * 4,
                 "d2h_bytes_per_step": (read_pin.numel() + graw_pin.numel() + gpar_pin.numel()) * 4,
-                "ms_per_step": ms_e2e},
-        "forward_64k": {"workload": "forward of 1 x 65,536 tokens on one GPU",
+                "ms_per_step": ms_e2e,
+                "api": "fields_lm_b200.host.HostFieldRead.fwd_bwd: pinned host in/out, one batch "
+                       "row per chunk, upload / kernels / download overlapped on three streams"},
+        "forward_64k": {"workload": "forward of 1 x 65,536 tokens" +
+                                    (f", sequence-sharded over {world} GPUs" if dist_on else " on one GPU"),
+                        "scaling": "strong", "n_gpus": world,
                         "ms": ms_long, "tokens_per_s": LONG_L / (ms_long * 1e-3),
                         "achieved": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9,
-                        "frac": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9 / peak},
+                        "frac": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9 / (peak * world)},
         "gpu_launches": KERNEL_LAUNCHES_PER_STEP * args.steps,
         "clocks": clocks.summary(),
         "parity": parity_check(device, tr.detach(), ti.detach(), gamma.detach()),
