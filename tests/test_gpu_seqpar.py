@@ -1,0 +1,61 @@
+"""Sequence-sharded forward on real GPUs (needs at least two): every rank's span must equal the
+corresponding slice of a single-GPU full-sequence pass and of the CPU oracle."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, L, out_dir):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from fields_lm_b200 import field_read_with_state, seqpar
+        gen = torch.Generator().manual_seed(123)
+        B, C = 1, 512
+        ring = torch.linspace(0.85, 0.999, C)
+        theta = torch.linspace(0.03, torch.pi * 0.97, C)
+        tr, ti = (ring * torch.cos(theta)).to(dev), (ring * torch.sin(theta)).to(dev)
+        gm = torch.sqrt(1 - ring ** 2).to(dev)
+        raw = (torch.randn(B, L, 3 * C, generator=gen) * 0.577)
+        lo, hi = seqpar.span_bounds(L, world, rank)
+        read, state = seqpar.sequence_parallel_field_read(raw[:, lo:hi].to(dev), tr, ti, gm)
+        torch.cuda.synchronize()
+        if rank == 0:
+            with torch.no_grad():
+                full, full_state = field_read_with_state(raw.to(dev), tr, ti, gm, None)
+            np.savez(os.path.join(out_dir, "full.npz"), read=full.cpu().numpy(),
+                     state=full_state.cpu().numpy(), raw=raw.numpy(), tr=tr.cpu().numpy(),
+                     ti=ti.cpu().numpy(), gm=gm.cpu().numpy())
+        np.savez(os.path.join(out_dir, f"rank{rank}.npz"), read=read.cpu().numpy(),
+                 state=state.cpu().numpy(), lo=lo, hi=hi)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+@pytest.mark.parametrize("L", [4096, 16384 + 37])
+def test_sequence_sharded_forward_matches_single_gpu_and_oracle(tmp_path, L):
+    import torch.multiprocessing as mp
+    from conftest import FP32_TOL, rel_err
+    from oracle import field_oracle
+    world = min(torch.cuda.device_count(), 4)
+    port = 29600 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(world, port, L, str(tmp_path)), nprocs=world, join=True)
+    full = np.load(tmp_path / "full.npz")
+    parts = [np.load(tmp_path / f"rank{r}.npz") for r in range(world)]
+    got = np.concatenate([p["read"] for p in parts], axis=1)
+    assert rel_err(got, full["read"]) < 2e-6
+    ref, ref_state = field_oracle.forward(full["raw"], full["tr"], full["ti"], full["gm"])
+    assert rel_err(got, ref) < FP32_TOL
+    assert rel_err(parts[-1]["state"], ref_state) < FP32_TOL
