@@ -19,6 +19,7 @@ HEADERS = [CSRC / "field_math.cuh", CSRC / "field_kernels.cuh",
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
+    "-ftz=true",  # denormals flush to zero: far below the parity bound, saves instructions
     "-Xcompiler", "-fPIC", "-shared",
 ]
 

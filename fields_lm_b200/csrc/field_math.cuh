@@ -34,35 +34,40 @@ namespace fields {
 constexpr float kVacMax = 0.90f;  // VAC_MAX, field_only_v4_chunked_triton_wiki100.py:68
 
 // ---------------------------------------------------------------------------
-// Transcendentals. exp2-based forms with one approximate reciprocal each: about
-// 2 ulp, which the recurrence carries to well under the 1e-5 parity bound. The
-// arguments are clamped so that exp never overflows to infinity.
+// Transcendentals: one ex2.approx and one rcp.approx each (about 2 ulp), which the
+// recurrence carries to well under the 1e-5 parity bound. No clamping is needed: the
+// hardware returns +inf / +0 for large arguments of ex2 and +0 for rcp(+inf), so tanh
+// saturates to +-1 and sigmoid to 0 or 1; the host forms below do the same in IEEE
+// arithmetic.
+//   tanh(x)    = 1 - 2 / (2^(2 log2e x) + 1)
+//   sigmoid(x) = 1 / (1 + 2^(-log2e x))
 // ---------------------------------------------------------------------------
-FL_HD float fast_exp(float x) {
+constexpr float kLog2e = 1.4426950408889634f;
+
+FL_HD float fast_exp2(float x) {
 #if FL_DEVICE_CODE
-    return __expf(x);
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 #else
-    return std::exp(x);
+    return std::exp2(x);
 #endif
 }
 
 FL_HD float fast_rcp(float x) {
 #if FL_DEVICE_CODE
-    return __fdividef(1.0f, x);
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 #else
     return 1.0f / x;
 #endif
 }
 
-FL_HD float sigmoidf_fast(float x) {
-    x = fminf(fmaxf(x, -80.0f), 80.0f);
-    return fast_rcp(1.0f + fast_exp(-x));
-}
+FL_HD float sigmoidf_fast(float x) { return fast_rcp(1.0f + fast_exp2(-kLog2e * x)); }
 
-// tanh(x) = 1 - 2 / (exp(2x) + 1)
 FL_HD float tanhf_fast(float x) {
-    x = fminf(fmaxf(x, -20.0f), 20.0f);
-    return 1.0f - 2.0f * fast_rcp(fast_exp(2.0f * x) + 1.0f);
+    return 1.0f - 2.0f * fast_rcp(fast_exp2((2.0f * kLog2e) * x) + 1.0f);
 }
 
 // ---------------------------------------------------------------------------

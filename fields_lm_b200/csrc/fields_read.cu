@@ -385,8 +385,17 @@ static size_t sp_backward_bytes(int B, int L, int C, int tile_steps) {
 // ---------------------------------------------------------------------------
 constexpr long long kWalkMinChains = 96;
 
-using FwdWalker = FwdWalk<16, 8, 3>;  // tile 128 steps, 3 x 48 KB ring
-using BwdWalker = BwdWalk<4, 8, 4>;   // tile 32 steps, 4 x 36 KB ring
+using FwdWalker = FwdWalk<16, 8, 3>;   // tile 128 steps, 3 x 48 KB ring, 8 warps
+using FwdWalkerB = FwdWalk<8, 16, 3>;  // same tile, 16 warps
+using BwdWalker = BwdWalk<4, 8, 4>;    // tile 32 steps, 4 x 36 KB ring, 8 warps
+using BwdWalkerB = BwdWalk<8, 8, 3>;   // tile 64 steps, 3 x 72 KB ring
+using BwdWalkerC = BwdWalk<4, 16, 3>;  // tile 64 steps, 16 warps
+
+// FIELDS_WALK_VARIANT = 0 | 1 | 2 picks among the instantiations above (tuning aid).
+static int walk_variant_from_env() {
+    const char* e = std::getenv("FIELDS_WALK_VARIANT");
+    return e ? std::atoi(e) : 0;
+}
 
 template <class K>
 static WalkShape walk_shape(int B, int L, int C) {
@@ -504,7 +513,10 @@ int fields_read_forward(const float* raw, const float* tr, const float* ti, cons
     const Algo algo = algo_from_env();
     if (vec4 && walk_wanted(B, C, algo)) {
         WalkFwdParams wp{raw, tr, ti, gamma, state_in, read, state_out,
-                         walk_shape<FwdWalker>(B, L, C)};
+                         walk_shape<FwdWalker>(B, L, C)};  // both variants share the tile length
+        static_assert(FwdWalker::kTile == FwdWalkerB::kTile, "variants must share the tile");
+        if (walk_variant_from_env() == 1)
+            return launch_walk<FwdWalkerB>(wp, (long long)B * wp.s.G, st);
         return launch_walk<FwdWalker>(wp, (long long)B * wp.s.G, st);
     }
     if (vec4 && algo != kAlgoThreePhase) {
@@ -560,9 +572,15 @@ int fields_read_backward(const float* raw, const float* tr, const float* ti, con
         return FIELDS_ERR_WORKSPACE;
     if (vec4 && walk_wanted(B, C, algo_from_env())) {
         float* partial = static_cast<float*>(workspace);
+        const int variant = walk_variant_from_env();
         WalkBwdParams wp{raw, tr, ti, gamma, state_in, read, grad_read, grad_state_out, grad_raw,
-                         grad_state_in, partial, walk_shape<BwdWalker>(B, L, C)};
-        int rc = launch_walk<BwdWalker>(wp, (long long)B * wp.s.G, st);
+                         grad_state_in, partial,
+                         variant == 0 ? walk_shape<BwdWalker>(B, L, C)
+                                      : walk_shape<BwdWalkerB>(B, L, C)};
+        static_assert(BwdWalkerB::kTile == BwdWalkerC::kTile, "variants must share the tile");
+        int rc = variant == 1   ? launch_walk<BwdWalkerB>(wp, (long long)B * wp.s.G, st)
+                 : variant == 2 ? launch_walk<BwdWalkerC>(wp, (long long)B * wp.s.G, st)
+                                : launch_walk<BwdWalker>(wp, (long long)B * wp.s.G, st);
         if (rc) return rc;
         BwdParams rp{};
         rp.partial = partial;

@@ -176,13 +176,19 @@ def test_config4_full_size_forward(dev):
     assert rel_err(got["state"], ref_state) < FP32_TOL
 
 
-def test_bitwise_deterministic(dev):
+def test_run_to_run_reproducibility(dev, algo):
+    """The chain-walking and three-phase kernels are bitwise reproducible. The single-pass
+    kernels compose whatever aggregates have been published when a block looks back, so the
+    association of the floating-point products depends on timing: equal to rounding only."""
     raw, grad_read = _config2_inputs(B=2, L=777)
     tr, ti, gm = _init_params(512)
     a = run_op(dev, raw, tr, ti, gm, grad_read)
     b = run_op(dev, raw, tr, ti, gm, grad_read)
     for key in a:
-        np.testing.assert_array_equal(a[key], b[key])
+        if algo == "single_pass":
+            assert rel_err(a[key], b[key]) < 2e-6, key
+        else:
+            np.testing.assert_array_equal(a[key], b[key])
 
 
 def test_outputs_stay_inside_their_buffers(dev, algo):
