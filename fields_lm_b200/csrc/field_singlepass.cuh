@@ -36,9 +36,24 @@ constexpr int kGroup = 128;      // channels per tile
 
 struct SpShape {
     int B, L, C;
-    int NT;  // time tiles per chain
-    int G;   // 128-channel groups
+    int NT;        // time tiles per chain
+    int G;         // 128-channel groups
+    int prefetch;  // how many tiles ahead a block warms L2 (about the number of resident blocks); 0 = off
 };
+
+// Prefetches `planes` consecutive 128-channel plane chunks of `steps` rows into L2:
+// row r, plane q is the 512 bytes at base + r * row_floats + q * plane_floats.
+FL_HD void prefetch_rows(const float* base, int steps, int valid_steps, int planes, size_t row_floats,
+                         size_t plane_floats, int valid_floats, int thread, int threads) {
+    const int lines = steps * planes * 4;  // 4 lines of 128 bytes per chunk
+    for (int q = thread; q < lines; q += threads) {
+        const int t = q / (planes * 4);
+        const int r = q % (planes * 4);
+        const int plane = r >> 2, line = r & 3;
+        if (t < valid_steps && line * 32 < valid_floats)
+            prefetch_l2(base + (size_t)t * row_floats + (size_t)plane * plane_floats + line * 32);
+    }
+}
 
 struct SpFwdParams {
     const float* raw;
@@ -147,6 +162,18 @@ struct FwdSinglePass {
             vec_store<4>(sum_at(smem, warp, 1) + lane * 4, o1);
             vec_store<4>(sum_at(smem, warp, 2) + lane * 4, o2);
             vec_store<4>(sum_at(smem, warp, 3) + lane * 4, o3);
+            // This block's loads are done and the memory system is about to go quiet: warm L2
+            // with the tile that the block taking this one's place will read.
+            if (s.prefetch > 0) {
+                const long long ahead = (long long)block + s.prefetch;
+                if (ahead < (long long)s.B * s.G * s.NT) {
+                    const SpTile nx = sp_decode(s, (unsigned)ahead);
+                    const int t0 = nx.n * kTile;
+                    prefetch_rows(p.raw + ((size_t)nx.b * s.L + t0) * 3 * C + nx.cg * kGroup, kTile,
+                                  s.L - t0, 3, (size_t)3 * C, (size_t)C, C - nx.cg * kGroup, thread,
+                                  kThreads);
+                }
+            }
         } else if constexpr (PH == 1) {
             // tile aggregate, one thread per channel; the first tile of a chain publishes
             // only its end state
@@ -288,6 +315,17 @@ struct BwdSinglePass {
         const int tend = tbeg + TS < s.L ? tbeg + TS : s.L;       // one past its last valid step
 
         if constexpr (PH == 0) {
+            // Second-sweep inputs of this tile that the first sweep does not touch (z_r, z_i and
+            // the previous states): start them towards L2 now, they are needed after the look-back.
+            if (s.prefetch > 0) {
+                const int t_lo = time_tile * kTile;
+                const int width = C - tl.cg * kGroup;
+                prefetch_rows(p.raw + ((size_t)tl.b * s.L + t_lo) * 3 * C + tl.cg * kGroup, kTile,
+                              s.L - t_lo, 2, (size_t)3 * C, (size_t)C, width, thread, kThreads);
+                const int first = t_lo > 0 ? t_lo - 1 : 0;  // row of s_{t-1} for the tile's first step
+                prefetch_rows(p.read + ((size_t)tl.b * s.L + first) * 4 * C + tl.cg * kGroup, kTile,
+                              s.L - 1 - first, 2, (size_t)4 * C, (size_t)C, width, thread, kThreads);
+            }
             Affine m[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) m[k] = affine_identity();
@@ -337,6 +375,21 @@ struct BwdSinglePass {
             vec_store<4>(sum_at(smem, slot, 1) + lane * 4, o1);
             vec_store<4>(sum_at(smem, slot, 2) + lane * 4, o2);
             vec_store<4>(sum_at(smem, slot, 3) + lane * 4, o3);
+            // first-sweep inputs (z_v, grad_read) of the tile that will replace this one
+            if (s.prefetch > 0) {
+                const long long ahead = (long long)block + s.prefetch;
+                if (ahead < (long long)s.B * s.G * s.NT) {
+                    const SpTile nx = sp_decode(s, (unsigned)ahead);
+                    const int t_lo = (s.NT - 1 - nx.n) * kTile;
+                    const int width = C - nx.cg * kGroup;
+                    prefetch_rows(p.raw + ((size_t)nx.b * s.L + t_lo) * 3 * C + 2 * C + nx.cg * kGroup,
+                                  kTile, s.L - t_lo, 1, (size_t)3 * C, (size_t)C, width, thread,
+                                  kThreads);
+                    prefetch_rows(p.grad_read + ((size_t)nx.b * s.L + t_lo) * 4 * C + nx.cg * kGroup,
+                                  kTile, s.L - t_lo, 4, (size_t)4 * C, (size_t)C, width, thread,
+                                  kThreads);
+                }
+            }
         } else if constexpr (PH == 1) {
             if (thread < kGroup && tl.cg * kGroup + thread < C && tl.n > 0) {
                 Affine a = affine_identity();

@@ -80,6 +80,15 @@ FL_HD Pub2 peek2(const float* p) {
     return r;
 }
 
+// Asks the memory system to bring one 128-byte line into L2 (no register, no wait).
+FL_HD void prefetch_l2(const void* p) {
+#if FL_DEVICE_CODE
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+#else
+    (void)p;
+#endif
+}
+
 FL_HD void backoff(unsigned polls) {
 #if FL_DEVICE_CODE
     __nanosleep(polls < 32 ? 32 : 256);

@@ -91,6 +91,9 @@ static int fill_unset(void* p, size_t bytes, Stream) {
     return FIELDS_OK;
 }
 
+template <class K>
+static int resident_blocks() { return 4; }  // any positive distance exercises the prefetch path
+
 // Kernels whose number of barrier-separated phases depends on the extents.
 template <class K>
 static int launch_walk(const typename K::Params& p, long long grid, Stream) {
@@ -165,6 +168,21 @@ static int launch_stateful(const typename K::Params& p, long long grid, long lon
 
 static int fill_unset(void* p, size_t bytes, Stream st) {
     return check_cuda(cudaMemsetAsync(p, kUnsetByte, bytes, st));
+}
+
+// Blocks of kernel K that the GPU holds at once (occupancy x SM count), asked once.
+template <class K>
+static int resident_blocks() {
+    static int cached = 0;
+    if (cached > 0) return cached;
+    int per_sm = 0, dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, stateful_entry<K>, K::kThreads,
+                                                      K::kSmemFloats * sizeof(float)) != cudaSuccess)
+        return 0;
+    cached = per_sm * sms;
+    return cached;
 }
 
 template <class K>
@@ -326,6 +344,13 @@ static int unroll_from_env(int fallback) {
     return (v == 1 || v == 2) ? v : fallback;
 }
 
+// FIELDS_READ_PREFETCH: 0 switches the L2 prefetch of the single-pass kernels off, a positive
+// number sets how many tiles ahead they prefetch; unset = the number of resident blocks.
+static int prefetch_from_env(int resident) {
+    const char* e = std::getenv("FIELDS_READ_PREFETCH");
+    return e ? std::atoi(e) : resident;
+}
+
 static int tile_from_env(int fallback) {
     const char* e = std::getenv("FIELDS_READ_TILE");
     if (!e) return fallback;
@@ -338,7 +363,8 @@ static int run_forward_single_pass(const float* raw, const float* tr, const floa
                                    const float* gamma, const float* state_in, float* read,
                                    float* state_out, void* workspace, int B, int L, int C,
                                    Stream st) {
-    const SpPlan pl = make_sp_plan(B, L, C, K::kTile);
+    SpPlan pl = make_sp_plan(B, L, C, K::kTile);
+    pl.s.prefetch = prefetch_from_env(resident_blocks<K>());
     char* ws = static_cast<char*>(workspace);
     unsigned* ctrl = reinterpret_cast<unsigned*>(ws);
     int rc = fill_unset(ws, pl.bytes, st);  // error word and every publication slot
@@ -356,7 +382,8 @@ static int run_backward_single_pass(const float* raw, const float* tr, const flo
                                     float* grad_raw, float* grad_tr, float* grad_ti,
                                     float* grad_gamma, float* grad_state_in, void* workspace,
                                     int B, int L, int C, Stream st) {
-    const SpPlan pl = make_sp_plan(B, L, C, K::kTile);
+    SpPlan pl = make_sp_plan(B, L, C, K::kTile);
+    pl.s.prefetch = prefetch_from_env(resident_blocks<K>());
     char* ws = static_cast<char*>(workspace);
     unsigned* ctrl = reinterpret_cast<unsigned*>(ws);
     int rc = fill_unset(ws, pl.bytes, st);
