@@ -38,7 +38,7 @@ struct SpShape {
     int B, L, C;
     int NT;        // time tiles per chain
     int G;         // 128-channel groups
-    int prefetch;  // how many tiles ahead a block warms L2 (about the number of resident blocks); 0 = off
+    int prefetch;  // non-zero: blocks warm L2 with the inputs of the tile they claim next
 };
 
 // Prefetches `planes` consecutive 128-channel plane chunks of `steps` rows into L2:
@@ -90,13 +90,15 @@ template <int TS, int WARPS>
 struct FwdSinglePass {
     using Params = SpFwdParams;
     static constexpr int kThreads = 32 * WARPS;
-    static constexpr int kMinBlocks = TS >= 8 ? 2 : 3;  // blocks per SM the register budget must allow
+    static constexpr int kMinBlocks = TS >= 6 ? 2 : 3;  // blocks per SM the register budget must allow
     static constexpr int kTile = TS * WARPS;
     static constexpr int kPhases = 4;
     static constexpr int kSplitPhase = 2;  // host emulation: phases < 2 of all blocks run first
     static constexpr int kSumFloats = WARPS * 4 * kGroup;
     static constexpr int kCarryFloats = WARPS * 2 * kGroup;
     static constexpr int kSmemFloats = kSumFloats + kCarryFloats;
+    static constexpr int kClaimAfter = 2;  // the next tile is claimed after the look-back phase
+    static constexpr bool kBarrierAtEnd = false;  // phase 3 reads only carries; phase 0 writes maps
     FL_HD static constexpr bool barrier_after(int ph) { return ph != 1; }
 
     struct State {
@@ -106,6 +108,15 @@ struct FwdSinglePass {
     FL_HD static float* sum_at(float* smem, int w, int k) { return smem + (w * 4 + k) * kGroup; }
     FL_HD static float* carry_at(float* smem, int w, int k) {
         return smem + kSumFloats + (w * 2 + k) * kGroup;
+    }
+
+    // Warms L2 with the raw rows of the tile this block will process next.
+    FL_HD static void prefetch(const Params& p, int tile, int thread) {
+        const SpShape& s = p.s;
+        const SpTile nx = sp_decode(s, (unsigned)tile);
+        const int t0 = nx.n * kTile;
+        prefetch_rows(p.raw + ((size_t)nx.b * s.L + t0) * 3 * s.C + nx.cg * kGroup, kTile, s.L - t0, 3,
+                      (size_t)3 * s.C, (size_t)s.C, s.C - nx.cg * kGroup, thread, kThreads);
     }
 
     template <int PH>
@@ -162,18 +173,6 @@ struct FwdSinglePass {
             vec_store<4>(sum_at(smem, warp, 1) + lane * 4, o1);
             vec_store<4>(sum_at(smem, warp, 2) + lane * 4, o2);
             vec_store<4>(sum_at(smem, warp, 3) + lane * 4, o3);
-            // This block's loads are done and the memory system is about to go quiet: warm L2
-            // with the tile that the block taking this one's place will read.
-            if (s.prefetch > 0) {
-                const long long ahead = (long long)block + s.prefetch;
-                if (ahead < (long long)s.B * s.G * s.NT) {
-                    const SpTile nx = sp_decode(s, (unsigned)ahead);
-                    const int t0 = nx.n * kTile;
-                    prefetch_rows(p.raw + ((size_t)nx.b * s.L + t0) * 3 * C + nx.cg * kGroup, kTile,
-                                  s.L - t0, 3, (size_t)3 * C, (size_t)C, C - nx.cg * kGroup, thread,
-                                  kThreads);
-                }
-            }
         } else if constexpr (PH == 1) {
             // tile aggregate, one thread per channel; the first tile of a chain publishes
             // only its end state
@@ -281,13 +280,15 @@ template <int TS, int WARPS, int U2_>
 struct BwdSinglePass {
     using Params = SpBwdParams;
     static constexpr int kThreads = 32 * WARPS;
-    static constexpr int kMinBlocks = 1;
+    static constexpr int kMinBlocks = (U2_ == 1) ? 512 / (32 * WARPS) : 1;  // U2 = 1: cap at 128 registers
     static constexpr int kTile = TS * WARPS;
     static constexpr int kPhases = 5;
     static constexpr int kSplitPhase = 2;
     static constexpr int kSumFloats = WARPS * 4 * kGroup;   // warp maps, later warp partials
     static constexpr int kCarryFloats = WARPS * 2 * kGroup;
     static constexpr int kSmemFloats = kSumFloats + kCarryFloats;
+    static constexpr int kClaimAfter = 2;
+    static constexpr bool kBarrierAtEnd = true;  // phase 4 reads the area phase 0 writes
     FL_HD static constexpr bool barrier_after(int ph) { return ph != 1; }
     static constexpr int U1 = 4;  // steps loaded together in sweep 1
     static constexpr int U2 = U2_;  // steps loaded together in sweep 2
@@ -300,6 +301,18 @@ struct BwdSinglePass {
     FL_HD static float* carry_at(float* smem, int w, int k) {
         return smem + kSumFloats + (w * 2 + k) * kGroup;
     }
+    // Warms L2 with the first-sweep inputs (z_v, grad_read) of the tile this block takes next.
+    FL_HD static void prefetch(const Params& p, int tile, int thread) {
+        const SpShape& s = p.s;
+        const SpTile nx = sp_decode(s, (unsigned)tile);
+        const int t_lo = (s.NT - 1 - nx.n) * kTile;
+        const int width = s.C - nx.cg * kGroup;
+        prefetch_rows(p.raw + ((size_t)nx.b * s.L + t_lo) * 3 * s.C + 2 * s.C + nx.cg * kGroup, kTile,
+                      s.L - t_lo, 1, (size_t)3 * s.C, (size_t)s.C, width, thread, kThreads);
+        prefetch_rows(p.grad_read + ((size_t)nx.b * s.L + t_lo) * 4 * s.C + nx.cg * kGroup, kTile,
+                      s.L - t_lo, 4, (size_t)4 * s.C, (size_t)s.C, width, thread, kThreads);
+    }
+
     template <int PH>
     FL_HD static void phase(const Params& p, int block, int thread, float* smem, State&) {
         const SpShape& s = p.s;
@@ -375,21 +388,6 @@ struct BwdSinglePass {
             vec_store<4>(sum_at(smem, slot, 1) + lane * 4, o1);
             vec_store<4>(sum_at(smem, slot, 2) + lane * 4, o2);
             vec_store<4>(sum_at(smem, slot, 3) + lane * 4, o3);
-            // first-sweep inputs (z_v, grad_read) of the tile that will replace this one
-            if (s.prefetch > 0) {
-                const long long ahead = (long long)block + s.prefetch;
-                if (ahead < (long long)s.B * s.G * s.NT) {
-                    const SpTile nx = sp_decode(s, (unsigned)ahead);
-                    const int t_lo = (s.NT - 1 - nx.n) * kTile;
-                    const int width = C - nx.cg * kGroup;
-                    prefetch_rows(p.raw + ((size_t)nx.b * s.L + t_lo) * 3 * C + 2 * C + nx.cg * kGroup,
-                                  kTile, s.L - t_lo, 1, (size_t)3 * C, (size_t)C, width, thread,
-                                  kThreads);
-                    prefetch_rows(p.grad_read + ((size_t)nx.b * s.L + t_lo) * 4 * C + nx.cg * kGroup,
-                                  kTile, s.L - t_lo, 4, (size_t)4 * C, (size_t)C, width, thread,
-                                  kThreads);
-                }
-            }
         } else if constexpr (PH == 1) {
             if (thread < kGroup && tl.cg * kGroup + thread < C && tl.n > 0) {
                 Affine a = affine_identity();

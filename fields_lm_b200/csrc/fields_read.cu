@@ -91,6 +91,9 @@ static int fill_unset(void* p, size_t bytes, Stream) {
     return FIELDS_OK;
 }
 
+// third argument of launch_stateful: the emulation wants the number of chains
+#define FIELDS_STATEFUL_ARG(K, B, pl) ((long long)(B) * (pl).s.G)
+
 template <class K>
 static int resident_blocks() { return 4; }  // any positive distance exercises the prefetch path
 
@@ -141,27 +144,53 @@ static int fill_zero(float* p, size_t n, Stream st) {
     return check_cuda(cudaMemsetAsync(p, 0, n * sizeof(float), st));
 }
 
-template <class K, int PH>
-__device__ __forceinline__ void run_phases(const typename K::Params& p, float* smem,
+// Phases FIRST..LAST of one tile, with the block barriers between them.
+template <class K, int PH, int LAST>
+__device__ __forceinline__ void run_phases(const typename K::Params& p, int tile, float* smem,
                                            typename K::State& st) {
-    K::template phase<PH>(p, (int)blockIdx.x, (int)threadIdx.x, smem, st);
-    if constexpr (PH + 1 < K::kPhases) {
+    K::template phase<PH>(p, tile, (int)threadIdx.x, smem, st);
+    if constexpr (PH < LAST) {
         if constexpr (K::barrier_after(PH)) __syncthreads();
-        run_phases<K, PH + 1>(p, smem, st);
+        run_phases<K, PH + 1, LAST>(p, tile, smem, st);
+    }
+}
+
+// Persistent blocks: each block claims tiles from a counter in the workspace until none are
+// left, so the work spreads evenly over the SMs whatever the tile count. Tickets are claimed
+// in increasing order by blocks that are already running, hence every tile a block may wait
+// for (an earlier one of its chain) is being processed or done. The next ticket is claimed
+// late - after the look-back, before the last sweep of the current tile - so that a claimed
+// tile is never left unstarted for long.
+template <class K>
+__global__ void __launch_bounds__(K::kThreads, K::kMinBlocks) stateful_entry(const typename K::Params p) {
+    extern __shared__ __align__(16) float smem[];
+    __shared__ unsigned s_ticket[2];
+    typename K::State st;
+    const unsigned total = (unsigned)((long long)p.s.B * p.s.G * p.s.NT);
+    unsigned* counter = p.ctrl + 1;  // starts at 0xFFFFFFFF (the fill value): first ticket is 0
+    if (threadIdx.x == 0) s_ticket[0] = atomicAdd(counter, 1u) + 1u;
+    __syncthreads();
+#pragma unroll 1
+    for (int par = 0;; par ^= 1) {
+        const unsigned tile = s_ticket[par];
+        if (tile >= total) break;
+        run_phases<K, 0, K::kClaimAfter>(p, (int)tile, smem, st);
+        if (threadIdx.x == 0) s_ticket[par ^ 1] = atomicAdd(counter, 1u) + 1u;
+        __syncthreads();
+        const unsigned next = s_ticket[par ^ 1];
+        if (p.s.prefetch > 0 && next < total) K::prefetch(p, (int)next, (int)threadIdx.x);
+        run_phases<K, K::kClaimAfter + 1, K::kPhases - 1>(p, (int)tile, smem, st);
+        // shared memory that the last phase reads must not be overwritten by the next tile yet
+        if constexpr (K::kBarrierAtEnd) __syncthreads();
     }
 }
 
 template <class K>
-__global__ void __launch_bounds__(K::kThreads, K::kMinBlocks) stateful_entry(const typename K::Params p) {
-    extern __shared__ __align__(16) float smem[];
-    typename K::State st;
-    run_phases<K, 0>(p, smem, st);
-}
-
-template <class K>
-static int launch_stateful(const typename K::Params& p, long long grid, long long, Stream st) {
-    if (grid <= 0) return FIELDS_OK;
-    if (grid > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
+static int launch_stateful(const typename K::Params& p, long long tiles, int resident, Stream st) {
+    if (tiles <= 0) return FIELDS_OK;
+    if (tiles > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
+    long long grid = resident > 0 ? resident : 1024;
+    if (grid > tiles) grid = tiles;
     stateful_entry<K><<<(unsigned)grid, K::kThreads, K::kSmemFloats * sizeof(float), st>>>(p);
     return check_cuda(cudaGetLastError());
 }
@@ -169,6 +198,8 @@ static int launch_stateful(const typename K::Params& p, long long grid, long lon
 static int fill_unset(void* p, size_t bytes, Stream st) {
     return check_cuda(cudaMemsetAsync(p, kUnsetByte, bytes, st));
 }
+
+#define FIELDS_STATEFUL_ARG(K, B, pl) resident_blocks<K>()
 
 // Blocks of kernel K that the GPU holds at once (occupancy x SM count), asked once.
 template <class K>
@@ -355,7 +386,7 @@ static int tile_from_env(int fallback) {
     const char* e = std::getenv("FIELDS_READ_TILE");
     if (!e) return fallback;
     const int v = std::atoi(e);
-    return (v == 32 || v == 64) ? v : fallback;
+    return (v == 32 || v == 48 || v == 56 || v == 64) ? v : fallback;
 }
 
 template <class K>
@@ -372,7 +403,7 @@ static int run_forward_single_pass(const float* raw, const float* tr, const floa
     SpFwdParams p{raw, tr, ti, gamma, state_in, read, state_out,
                   reinterpret_cast<float*>(ws + pl.agg_off),
                   reinterpret_cast<float*>(ws + pl.incl_off), ctrl, pl.s};
-    return launch_stateful<K>(p, pl.tiles, (long long)B * pl.s.G, st);
+    return launch_stateful<K>(p, pl.tiles, FIELDS_STATEFUL_ARG(K, B, pl), st);
 }
 
 template <class K>
@@ -392,7 +423,7 @@ static int run_backward_single_pass(const float* raw, const float* tr, const flo
     SpBwdParams p{raw, tr, ti, gamma, state_in, read, grad_read, grad_state_out, grad_raw,
                   grad_state_in, reinterpret_cast<float*>(ws + pl.agg_off),
                   reinterpret_cast<float*>(ws + pl.incl_off), ctrl, partial, pl.s};
-    rc = launch_stateful<K>(p, pl.tiles, (long long)B * pl.s.G, st);
+    rc = launch_stateful<K>(p, pl.tiles, FIELDS_STATEFUL_ARG(K, B, pl), st);
     if (rc) return rc;
     BwdParams rp{};
     rp.partial = partial;
@@ -547,8 +578,15 @@ int fields_read_forward(const float* raw, const float* tr, const float* ti, cons
         return launch_walk<FwdWalker>(wp, (long long)B * wp.s.G, st);
     }
     if (vec4 && algo != kAlgoThreePhase) {
-        if (tile_from_env(64) == 32)
+        const int tile_steps = tile_from_env(64);
+        if (tile_steps == 32)
             return run_forward_single_pass<FwdSinglePass<4, 8>>(raw, tr, ti, gamma, state_in, read,
+                                                                state_out, workspace, B, L, C, st);
+        if (tile_steps == 48)
+            return run_forward_single_pass<FwdSinglePass<6, 8>>(raw, tr, ti, gamma, state_in, read,
+                                                                state_out, workspace, B, L, C, st);
+        if (tile_steps == 56)
+            return run_forward_single_pass<FwdSinglePass<7, 8>>(raw, tr, ti, gamma, state_in, read,
                                                                 state_out, workspace, B, L, C, st);
         return run_forward_single_pass<FwdSinglePass<8, 8>>(raw, tr, ti, gamma, state_in, read,
                                                             state_out, workspace, B, L, C, st);

@@ -21,6 +21,7 @@ def _params(C, rng):
 
 ALGOS = [("three_phase", "64", "forward"), ("single_pass", "64", "forward"),
          ("single_pass", "64", "reverse"), ("single_pass", "32", "reverse"),
+         ("single_pass", "56", "reverse"), ("single_pass", "48", "forward"),
          ("walk", "64", "forward")]
 
 
