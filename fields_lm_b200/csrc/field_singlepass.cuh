@@ -98,7 +98,6 @@ struct FwdSinglePass {
     static constexpr int kCarryFloats = WARPS * 2 * kGroup;
     static constexpr int kSmemFloats = kSumFloats + kCarryFloats;
     static constexpr int kClaimAfter = 2;  // the next tile is claimed after the look-back phase
-    static constexpr bool kBarrierAtEnd = false;  // phase 3 reads only carries; phase 0 writes maps
     FL_HD static constexpr bool barrier_after(int ph) { return ph != 1; }
 
     struct State {
@@ -276,11 +275,11 @@ struct SpBwdParams {
     SpShape s;
 };
 
-template <int TS, int WARPS, int U2_>
+template <int TS, int WARPS, int U1_, int U2_>
 struct BwdSinglePass {
     using Params = SpBwdParams;
     static constexpr int kThreads = 32 * WARPS;
-    static constexpr int kMinBlocks = (U2_ == 1) ? 512 / (32 * WARPS) : 1;  // U2 = 1: cap at 128 registers
+    static constexpr int kMinBlocks = 1;
     static constexpr int kTile = TS * WARPS;
     static constexpr int kPhases = 5;
     static constexpr int kSplitPhase = 2;
@@ -288,9 +287,8 @@ struct BwdSinglePass {
     static constexpr int kCarryFloats = WARPS * 2 * kGroup;
     static constexpr int kSmemFloats = kSumFloats + kCarryFloats;
     static constexpr int kClaimAfter = 2;
-    static constexpr bool kBarrierAtEnd = true;  // phase 4 reads the area phase 0 writes
     FL_HD static constexpr bool barrier_after(int ph) { return ph != 1; }
-    static constexpr int U1 = 4;  // steps loaded together in sweep 1
+    static constexpr int U1 = U1_;  // steps loaded together in sweep 1
     static constexpr int U2 = U2_;  // steps loaded together in sweep 2
     static_assert(kThreads >= kGroup, "one thread per channel is needed for the look-back");
     static_assert(TS % U1 == 0 && TS % U2 == 0, "sub-chunk must be a multiple of the unroll");
@@ -366,14 +364,14 @@ struct BwdSinglePass {
                         if (t0 - 1 - u >= tbeg) {
 #pragma unroll
                             for (int k = 0; k < 4; ++k) {
+                                // carry_{t-1} = conj(lambda) (keep (u + carry_t) + v gd)
                                 const float vac = kVacMax * sigmoidf_fast(zv[u].v[k]);
                                 const float keep = 1.0f - vac;
-                                const float car = keep * lr.v[k];
-                                const float cai = -keep * li.v[k];
-                                float qr, qi, xr, xi;
-                                cmul(car, cai, ur[u].v[k], ui[u].v[k], qr, qi);
-                                cmul_conj(lr.v[k], li.v[k], gr[u].v[k], gi[u].v[k], xr, xi);
-                                m[k] = affine_then(m[k], car, cai, qr + vac * xr, qi + vac * xi);
+                                const float hr = keep * ur[u].v[k] + vac * gr[u].v[k];
+                                const float hi = keep * ui[u].v[k] + vac * gi[u].v[k];
+                                float qr, qi;
+                                cmul_conj(lr.v[k], li.v[k], hr, hi, qr, qi);
+                                m[k] = affine_then(m[k], keep * lr.v[k], -keep * li.v[k], qr, qi);
                             }
                         }
                     }
@@ -475,24 +473,25 @@ struct BwdSinglePass {
                                 const float Gi = ui[u].v[k] + ci.v[k];
                                 const float gdr = gr[u].v[k], gdi = gi[u].v[k];
                                 const float sr = pr[u].v[k], si = pi[u].v[k];
-                                float mr, mi, dar, dai, xr, xi, yr, yi, nr, ni;
+                                // m = lambda s_prev;  H = keep G + v gd
+                                float mr, mi, ar_, ai_;
                                 cmul(lr.v[k], li.v[k], sr, si, mr, mi);
-                                cmul_conj(sr, si, Gr, Gi, dar, dai);
-                                cmul_conj(sr, si, gdr, gdi, xr, xi);
-                                cmul_conj(lr.v[k], li.v[k], gdr, gdi, yr, yi);
-                                cmul_conj(keep * lr.v[k], keep * li.v[k], Gr, Gi, nr, ni);
+                                const float Hr = keep * Gr + g.vac * gdr;
+                                const float Hi = keep * Gi + g.vac * gdi;
+                                // d lambda += H conj(s_prev);  carry <- conj(lambda) H
+                                cmul_conj(sr, si, Hr, Hi, ar_, ai_);
+                                dtr.v[k] += ar_;
+                                dti.v[k] += ai_;
                                 const float common_b = g.inj_r * Gr + g.inj_i * Gi;
-                                const float dv = -lr.v[k] * dar - li.v[k] * dai +
-                                                 gm.v[k] * common_b + gdr * mr + gdi * mi;
-                                dtr.v[k] += keep * dar + g.vac * xr;
-                                dti.v[k] += keep * dai + g.vac * xi;
                                 dgm.v[k] += g.vac * common_b;
+                                // dv = G . (gamma inj - m) + gd . m
+                                const float dv = Gr * (gm.v[k] * g.inj_r - mr) +
+                                                 Gi * (gm.v[k] * g.inj_i - mi) + gdr * mr + gdi * mi;
                                 const float bs = gm.v[k] * g.vac;
                                 ozr.v[k] = bs * Gr * (1.0f - g.inj_r * g.inj_r);
                                 ozi.v[k] = bs * Gi * (1.0f - g.inj_i * g.inj_i);
-                                ozv.v[k] = dv * kVacMax * g.sig * (1.0f - g.sig);
-                                cr.v[k] = nr + g.vac * yr;
-                                ci.v[k] = ni + g.vac * yi;
+                                ozv.v[k] = dv * (g.vac - g.vac * g.sig);
+                                cmul_conj(lr.v[k], li.v[k], Hr, Hi, cr.v[k], ci.v[k]);
                             }
                             float* orow = obase + (size_t)t * 3 * C;
                             vec_store_stream<4>(orow, ozr);

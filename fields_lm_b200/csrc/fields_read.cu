@@ -155,43 +155,31 @@ __device__ __forceinline__ void run_phases(const typename K::Params& p, int tile
     }
 }
 
-// Persistent blocks: each block claims tiles from a counter in the workspace until none are
-// left, so the work spreads evenly over the SMs whatever the tile count. Tickets are claimed
-// in increasing order by blocks that are already running, hence every tile a block may wait
-// for (an earlier one of its chain) is being processed or done. The next ticket is claimed
-// late - after the look-back, before the last sweep of the current tile - so that a claimed
-// tile is never left unstarted for long.
+// One block per tile, taken in block-index order (time-major): every tile a block may wait
+// for has a smaller index, so the hardware has already started it. (A persistent variant
+// that claimed tiles from a counter was measured and was no faster: the claim sits on the
+// critical path and the loop costs registers.) After the look-back, while the last sweep
+// runs, the block can warm L2 with the inputs of the tile `prefetch` positions ahead, which
+// is about the tile that the block taking this one's place will read.
 template <class K>
 __global__ void __launch_bounds__(K::kThreads, K::kMinBlocks) stateful_entry(const typename K::Params p) {
     extern __shared__ __align__(16) float smem[];
-    __shared__ unsigned s_ticket[2];
     typename K::State st;
-    const unsigned total = (unsigned)((long long)p.s.B * p.s.G * p.s.NT);
-    unsigned* counter = p.ctrl + 1;  // starts at 0xFFFFFFFF (the fill value): first ticket is 0
-    if (threadIdx.x == 0) s_ticket[0] = atomicAdd(counter, 1u) + 1u;
+    const int tile = (int)blockIdx.x;
+    run_phases<K, 0, K::kClaimAfter>(p, tile, smem, st);
     __syncthreads();
-#pragma unroll 1
-    for (int par = 0;; par ^= 1) {
-        const unsigned tile = s_ticket[par];
-        if (tile >= total) break;
-        run_phases<K, 0, K::kClaimAfter>(p, (int)tile, smem, st);
-        if (threadIdx.x == 0) s_ticket[par ^ 1] = atomicAdd(counter, 1u) + 1u;
-        __syncthreads();
-        const unsigned next = s_ticket[par ^ 1];
-        if (p.s.prefetch > 0 && next < total) K::prefetch(p, (int)next, (int)threadIdx.x);
-        run_phases<K, K::kClaimAfter + 1, K::kPhases - 1>(p, (int)tile, smem, st);
-        // shared memory that the last phase reads must not be overwritten by the next tile yet
-        if constexpr (K::kBarrierAtEnd) __syncthreads();
+    if (p.s.prefetch > 0) {
+        const long long next = (long long)tile + p.s.prefetch;
+        if (next < (long long)p.s.B * p.s.G * p.s.NT) K::prefetch(p, (int)next, (int)threadIdx.x);
     }
+    run_phases<K, K::kClaimAfter + 1, K::kPhases - 1>(p, tile, smem, st);
 }
 
 template <class K>
-static int launch_stateful(const typename K::Params& p, long long tiles, int resident, Stream st) {
+static int launch_stateful(const typename K::Params& p, long long tiles, int, Stream st) {
     if (tiles <= 0) return FIELDS_OK;
     if (tiles > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
-    long long grid = resident > 0 ? resident : 1024;
-    if (grid > tiles) grid = tiles;
-    stateful_entry<K><<<(unsigned)grid, K::kThreads, K::kSmemFloats * sizeof(float), st>>>(p);
+    stateful_entry<K><<<(unsigned)tiles, K::kThreads, K::kSmemFloats * sizeof(float), st>>>(p);
     return check_cuda(cudaGetLastError());
 }
 
@@ -375,11 +363,13 @@ static int unroll_from_env(int fallback) {
     return (v == 1 || v == 2) ? v : fallback;
 }
 
-// FIELDS_READ_PREFETCH: 0 switches the L2 prefetch of the single-pass kernels off, a positive
-// number sets how many tiles ahead they prefetch; unset = the number of resident blocks.
+// FIELDS_READ_PREFETCH = 1 switches the L2 prefetch of the single-pass kernels on (distance =
+// number of resident blocks); any larger number sets the distance. Default: off - it gained
+// 5 to 9 % on the batch-8 forward and lost as much on the backward and on long sequences.
 static int prefetch_from_env(int resident) {
     const char* e = std::getenv("FIELDS_READ_PREFETCH");
-    return e ? std::atoi(e) : resident;
+    const int v = e ? std::atoi(e) : 0;
+    return v == 1 ? resident : (v > 1 ? v : 0);
 }
 
 static int tile_from_env(int fallback) {
@@ -660,10 +650,10 @@ int fields_read_backward(const float* raw, const float* tr, const float* ti, con
                                        grad_state_in, workspace, B, L, C, st)
         const bool wide = tile_from_env(32) == 64;
         const bool pair = unroll_from_env(2) == 2;
-        if (wide && pair) FIELDS_BWD_SP(BwdSinglePass<16 COMMA 4 COMMA 2>);
-        if (wide) FIELDS_BWD_SP(BwdSinglePass<16 COMMA 4 COMMA 1>);
-        if (pair) FIELDS_BWD_SP(BwdSinglePass<8 COMMA 4 COMMA 2>);
-        FIELDS_BWD_SP(BwdSinglePass<8 COMMA 4 COMMA 1>);
+        if (wide && pair) FIELDS_BWD_SP(BwdSinglePass<16 COMMA 4 COMMA 4 COMMA 2>);
+        if (wide) FIELDS_BWD_SP(BwdSinglePass<16 COMMA 4 COMMA 2 COMMA 1>);
+        if (pair) FIELDS_BWD_SP(BwdSinglePass<8 COMMA 4 COMMA 4 COMMA 2>);
+        FIELDS_BWD_SP(BwdSinglePass<8 COMMA 4 COMMA 2 COMMA 1>);
 #undef FIELDS_BWD_SP
     }
     float* ws = static_cast<float*>(workspace);
