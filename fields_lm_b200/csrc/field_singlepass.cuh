@@ -86,11 +86,11 @@ FL_HD SpTile sp_decode(const SpShape& s, unsigned ticket) {
     return t;
 }
 
-template <int TS, int WARPS>
+template <int TS, int WARPS, int MIN_BLOCKS>
 struct FwdSinglePass {
     using Params = SpFwdParams;
     static constexpr int kThreads = 32 * WARPS;
-    static constexpr int kMinBlocks = TS >= 6 ? 2 : 3;  // blocks per SM the register budget must allow
+    static constexpr int kMinBlocks = MIN_BLOCKS;  // blocks per SM the register budget must allow
     static constexpr int kTile = TS * WARPS;
     static constexpr int kPhases = 4;
     static constexpr int kSplitPhase = 2;  // host emulation: phases < 2 of all blocks run first
@@ -275,11 +275,11 @@ struct SpBwdParams {
     SpShape s;
 };
 
-template <int TS, int WARPS, int U1_, int U2_>
+template <int TS, int WARPS, int U1_, int U2_, int MIN_BLOCKS>
 struct BwdSinglePass {
     using Params = SpBwdParams;
     static constexpr int kThreads = 32 * WARPS;
-    static constexpr int kMinBlocks = 1;
+    static constexpr int kMinBlocks = MIN_BLOCKS;
     static constexpr int kTile = TS * WARPS;
     static constexpr int kPhases = 5;
     static constexpr int kSplitPhase = 2;

@@ -337,12 +337,11 @@ static SpPlan make_sp_plan(int B, int L, int C, int tile_steps) {
     return pl;
 }
 
-constexpr int kSpMinTile = 32;  // smallest time tile of any single-pass instantiation
 
 enum Algo { kAlgoAuto = 0, kAlgoThreePhase = 1, kAlgoSinglePass = 2, kAlgoWalk = 3 };
 
 // FIELDS_READ_ALGO = three_phase | single_pass | walk selects the kernels (default: the chain
-// walkers when there are enough chains, else single pass, whenever 16-byte accesses are possible). FIELDS_READ_TILE = 32 | 64 selects the time tile.
+// walkers when there are enough chains, else single pass, whenever 16-byte accesses are possible). FIELDS_FWD_VARIANT / FIELDS_BWD_VARIANT pick a tuning alternative.
 static Algo algo_from_env() {
     const char* e = std::getenv("FIELDS_READ_ALGO");
     if (!e) return kAlgoAuto;
@@ -355,12 +354,27 @@ static Algo algo_from_env() {
 
 #define COMMA ,
 
-// FIELDS_READ_U2 = 1 | 2: steps loaded together in the backward's second sweep.
-static int unroll_from_env(int fallback) {
-    const char* e = std::getenv("FIELDS_READ_U2");
-    if (!e) return fallback;
-    const int v = std::atoi(e);
-    return (v == 1 || v == 2) ? v : fallback;
+// Instantiations of the single-pass kernels. The first of each list is the default; the
+// others are tuning alternatives selected with FIELDS_FWD_VARIANT / FIELDS_BWD_VARIANT.
+//   forward  <steps per warp, warps, blocks per SM the registers must allow>
+using FwdSp0 = FwdSinglePass<6, 8, 2>;   // tile 48 steps, 128 registers, no spills
+using FwdSp1 = FwdSinglePass<8, 8, 2>;   // tile 64
+using FwdSp2 = FwdSinglePass<4, 8, 3>;   // tile 32, 3 blocks per SM
+using FwdSp3 = FwdSinglePass<7, 8, 2>;   // tile 56
+using FwdSp4 = FwdSinglePass<5, 8, 2>;   // tile 40
+using FwdSp5 = FwdSinglePass<4, 8, 2>;   // tile 32, 2 blocks per SM
+//   backward <steps per warp, warps, sweep-1 unroll, sweep-2 unroll, blocks per SM>
+using BwdSp0 = BwdSinglePass<8, 4, 2, 1, 5>;    // tile 32, 96 registers, 20 warps per SM
+using BwdSp1 = BwdSinglePass<8, 4, 2, 1, 4>;    // 127 registers, 16 warps per SM
+using BwdSp2 = BwdSinglePass<16, 4, 2, 1, 5>;   // tile 64
+using BwdSp3 = BwdSinglePass<8, 4, 4, 2, 2>;    // deep unroll, 8 warps per SM
+using BwdSp4 = BwdSinglePass<8, 4, 1, 1, 6>;    // shallow unroll, 24 warps per SM
+using BwdSp5 = BwdSinglePass<4, 8, 2, 1, 2>;    // 8 warps per block
+constexpr int kSpMinTile = 32;  // smallest time tile of any instantiation above (workspace bound)
+
+static int variant_from_env(const char* name) {
+    const char* e = std::getenv(name);
+    return e ? std::atoi(e) : 0;
 }
 
 // FIELDS_READ_PREFETCH = 1 switches the L2 prefetch of the single-pass kernels on (distance =
@@ -370,13 +384,6 @@ static int prefetch_from_env(int resident) {
     const char* e = std::getenv("FIELDS_READ_PREFETCH");
     const int v = e ? std::atoi(e) : 0;
     return v == 1 ? resident : (v > 1 ? v : 0);
-}
-
-static int tile_from_env(int fallback) {
-    const char* e = std::getenv("FIELDS_READ_TILE");
-    if (!e) return fallback;
-    const int v = std::atoi(e);
-    return (v == 32 || v == 48 || v == 56 || v == 64) ? v : fallback;
 }
 
 template <class K>
@@ -568,18 +575,18 @@ int fields_read_forward(const float* raw, const float* tr, const float* ti, cons
         return launch_walk<FwdWalker>(wp, (long long)B * wp.s.G, st);
     }
     if (vec4 && algo != kAlgoThreePhase) {
-        const int tile_steps = tile_from_env(64);
-        if (tile_steps == 32)
-            return run_forward_single_pass<FwdSinglePass<4, 8>>(raw, tr, ti, gamma, state_in, read,
-                                                                state_out, workspace, B, L, C, st);
-        if (tile_steps == 48)
-            return run_forward_single_pass<FwdSinglePass<6, 8>>(raw, tr, ti, gamma, state_in, read,
-                                                                state_out, workspace, B, L, C, st);
-        if (tile_steps == 56)
-            return run_forward_single_pass<FwdSinglePass<7, 8>>(raw, tr, ti, gamma, state_in, read,
-                                                                state_out, workspace, B, L, C, st);
-        return run_forward_single_pass<FwdSinglePass<8, 8>>(raw, tr, ti, gamma, state_in, read,
-                                                            state_out, workspace, B, L, C, st);
+#define FIELDS_FWD_SP(K)                                                                      \
+    return run_forward_single_pass<K>(raw, tr, ti, gamma, state_in, read, state_out, workspace, \
+                                      B, L, C, st)
+        switch (variant_from_env("FIELDS_FWD_VARIANT")) {
+            case 1: FIELDS_FWD_SP(FwdSp1);
+            case 2: FIELDS_FWD_SP(FwdSp2);
+            case 3: FIELDS_FWD_SP(FwdSp3);
+            case 4: FIELDS_FWD_SP(FwdSp4);
+            case 5: FIELDS_FWD_SP(FwdSp5);
+            default: FIELDS_FWD_SP(FwdSp0);
+        }
+#undef FIELDS_FWD_SP
     }
     float* ws = static_cast<float*>(workspace);
     FwdParams p{raw, tr, ti, gamma, state_in, read, state_out,
@@ -648,12 +655,14 @@ int fields_read_backward(const float* raw, const float* tr, const float* ti, con
     return run_backward_single_pass<K>(raw, tr, ti, gamma, state_in, read, grad_read,          \
                                        grad_state_out, grad_raw, grad_tr, grad_ti, grad_gamma, \
                                        grad_state_in, workspace, B, L, C, st)
-        const bool wide = tile_from_env(32) == 64;
-        const bool pair = unroll_from_env(2) == 2;
-        if (wide && pair) FIELDS_BWD_SP(BwdSinglePass<16 COMMA 4 COMMA 4 COMMA 2>);
-        if (wide) FIELDS_BWD_SP(BwdSinglePass<16 COMMA 4 COMMA 2 COMMA 1>);
-        if (pair) FIELDS_BWD_SP(BwdSinglePass<8 COMMA 4 COMMA 4 COMMA 2>);
-        FIELDS_BWD_SP(BwdSinglePass<8 COMMA 4 COMMA 2 COMMA 1>);
+        switch (variant_from_env("FIELDS_BWD_VARIANT")) {
+            case 1: FIELDS_BWD_SP(BwdSp1);
+            case 2: FIELDS_BWD_SP(BwdSp2);
+            case 3: FIELDS_BWD_SP(BwdSp3);
+            case 4: FIELDS_BWD_SP(BwdSp4);
+            case 5: FIELDS_BWD_SP(BwdSp5);
+            default: FIELDS_BWD_SP(BwdSp0);
+        }
 #undef FIELDS_BWD_SP
     }
     float* ws = static_cast<float*>(workspace);

@@ -19,18 +19,21 @@ def _params(C, rng):
         np.sqrt(np.maximum(1 - radius ** 2, 1e-4)).astype(np.float32)
 
 
-ALGOS = [("three_phase", "64", "forward"), ("single_pass", "64", "forward"),
-         ("single_pass", "64", "reverse"), ("single_pass", "32", "reverse"),
-         ("single_pass", "56", "reverse"), ("single_pass", "48", "forward"),
-         ("walk", "64", "forward")]
+ALGOS = [("three_phase", "0", "forward"), ("single_pass", "0", "forward"),
+         ("single_pass", "0", "reverse"), ("single_pass", "1", "reverse"),
+         ("single_pass", "2", "reverse"), ("single_pass", "3", "forward"),
+         ("single_pass", "4", "reverse"), ("single_pass", "5", "forward"),
+         ("walk", "0", "forward")]
 
 
 @pytest.fixture(params=ALGOS, ids=lambda a: "-".join(a))
 def algo(request, monkeypatch):
-    """Selects the kernels, the single-pass time tile and the order in which emulated blocks finish."""
-    name, tile, order = request.param
+    """Selects the kernel family, the tuning variant of the single-pass kernels (forward and
+    backward alike) and the order in which emulated blocks finish."""
+    name, variant, order = request.param
     monkeypatch.setenv("FIELDS_READ_ALGO", name)
-    monkeypatch.setenv("FIELDS_READ_TILE", tile)
+    monkeypatch.setenv("FIELDS_FWD_VARIANT", variant)
+    monkeypatch.setenv("FIELDS_BWD_VARIANT", variant)
     monkeypatch.setenv("FIELDS_EMU_ORDER", order)
     return request.param
 
