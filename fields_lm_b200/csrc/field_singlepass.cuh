@@ -275,7 +275,7 @@ struct SpBwdParams {
     SpShape s;
 };
 
-template <int TS, int WARPS, int U1_, int U2_, int MIN_BLOCKS>
+template <int TS, int WARPS, int U1_, int U2_, int MIN_BLOCKS, bool ASYNC = false>
 struct BwdSinglePass {
     using Params = SpBwdParams;
     static constexpr int kThreads = 32 * WARPS;
@@ -285,7 +285,12 @@ struct BwdSinglePass {
     static constexpr int kSplitPhase = 2;
     static constexpr int kSumFloats = WARPS * 4 * kGroup;   // warp maps, later warp partials
     static constexpr int kCarryFloats = WARPS * 2 * kGroup;
-    static constexpr int kSmemFloats = kSumFloats + kCarryFloats;
+    // ASYNC: every thread lands its next batch of inputs in a private two-slot ring in shared
+    // memory with cp.async while it computes on the current batch, so loads stay in flight
+    // without holding registers. A cell is one 16-byte vector of one thread.
+    static constexpr int kCells = U1_ * 5 > U2_ * 9 ? U1_ * 5 : U2_ * 9;
+    static constexpr int kRingFloats = ASYNC ? 2 * kCells * 32 * WARPS * 4 : 0;
+    static constexpr int kSmemFloats = kSumFloats + kCarryFloats + kRingFloats;
     static constexpr int kClaimAfter = 2;
     FL_HD static constexpr bool barrier_after(int ph) { return ph != 1; }
     static constexpr int U1 = U1_;  // steps loaded together in sweep 1
@@ -298,6 +303,10 @@ struct BwdSinglePass {
     FL_HD static float* sum_at(float* smem, int w, int k) { return smem + (w * 4 + k) * kGroup; }
     FL_HD static float* carry_at(float* smem, int w, int k) {
         return smem + kSumFloats + (w * 2 + k) * kGroup;
+    }
+    FL_HD static float* cell_at(float* smem, int stage, int idx, int thread) {
+        return smem + kSumFloats + kCarryFloats +
+               ((size_t)(stage * kCells + idx) * kThreads + thread) * 4;
     }
     // Warms L2 with the first-sweep inputs (z_v, grad_read) of the tile this block takes next.
     FL_HD static void prefetch(const Params& p, int tile, int thread) {
@@ -345,8 +354,40 @@ struct BwdSinglePass {
                 const Vec<4> li = vec_load<4>(p.ti + c0);
                 const float* zbase = p.raw + ((size_t)tl.b * s.L) * 3 * C + 2 * C + c0;
                 const float* gbase = p.grad_read + ((size_t)tl.b * s.L) * 4 * C + c0;
-                for (int t0 = tend; t0 > tbeg; t0 -= U1) {
+                // batch of U1 steps ending just before t0, into ring slot `stage`
+                auto issue1 = [&](int t0, int stage) {
+#pragma unroll
+                    for (int u = 0; u < U1; ++u) {
+                        const int t = t0 - 1 - u;
+                        if (t >= tbeg) {
+                            const float* grow = gbase + (size_t)t * 4 * C;
+                            async_copy16(cell_at(smem, stage, u * 5 + 0, thread), zbase + (size_t)t * 3 * C);
+                            async_copy16(cell_at(smem, stage, u * 5 + 1, thread), grow);
+                            async_copy16(cell_at(smem, stage, u * 5 + 2, thread), grow + C);
+                            async_copy16(cell_at(smem, stage, u * 5 + 3, thread), grow + 2 * C);
+                            async_copy16(cell_at(smem, stage, u * 5 + 4, thread), grow + 3 * C);
+                        }
+                    }
+                    async_commit();
+                };
+                if constexpr (ASYNC) issue1(tend, 0);
+                int stage = 0;
+                for (int t0 = tend; t0 > tbeg; t0 -= U1, stage ^= 1) {
                     Vec<4> zv[U1], ur[U1], ui[U1], gr[U1], gi[U1];
+                    if constexpr (ASYNC) {
+                        if (t0 - U1 > tbeg) issue1(t0 - U1, stage ^ 1); else async_commit();
+                        async_wait_pending<1>();
+#pragma unroll
+                        for (int u = 0; u < U1; ++u) {
+                            if (t0 - 1 - u >= tbeg) {
+                                zv[u] = vec_load<4>(cell_at(smem, stage, u * 5 + 0, thread));
+                                ur[u] = vec_load<4>(cell_at(smem, stage, u * 5 + 1, thread));
+                                ui[u] = vec_load<4>(cell_at(smem, stage, u * 5 + 2, thread));
+                                gr[u] = vec_load<4>(cell_at(smem, stage, u * 5 + 3, thread));
+                                gi[u] = vec_load<4>(cell_at(smem, stage, u * 5 + 4, thread));
+                            }
+                        }
+                    } else {
 #pragma unroll
                     for (int u = 0; u < U1; ++u) {
                         const int t = t0 - 1 - u;
@@ -358,6 +399,7 @@ struct BwdSinglePass {
                             gr[u] = vec_load<4>(grow + 2 * C);
                             gi[u] = vec_load<4>(grow + 3 * C);
                         }
+                    }
                     }
 #pragma unroll
                     for (int u = 0; u < U1; ++u) {
@@ -431,8 +473,61 @@ struct BwdSinglePass {
                 const float* gbase = p.grad_read + ((size_t)tl.b * s.L) * 4 * C + c0;
                 const float* rbase = p.read + ((size_t)tl.b * s.L) * 4 * C + c0;
                 float* obase = p.grad_raw + ((size_t)tl.b * s.L) * 3 * C + c0;
-                for (int t0 = tend; t0 > tbeg; t0 -= U2) {
+                auto issue2 = [&](int t0, int stage) {
+#pragma unroll
+                    for (int u = 0; u < U2; ++u) {
+                        const int t = t0 - 1 - u;
+                        if (t >= tbeg) {
+                            const float* zrow = zbase + (size_t)t * 3 * C;
+                            const float* grow = gbase + (size_t)t * 4 * C;
+                            async_copy16(cell_at(smem, stage, u * 9 + 0, thread), zrow);
+                            async_copy16(cell_at(smem, stage, u * 9 + 1, thread), zrow + C);
+                            async_copy16(cell_at(smem, stage, u * 9 + 2, thread), zrow + 2 * C);
+                            async_copy16(cell_at(smem, stage, u * 9 + 3, thread), grow);
+                            async_copy16(cell_at(smem, stage, u * 9 + 4, thread), grow + C);
+                            async_copy16(cell_at(smem, stage, u * 9 + 5, thread), grow + 2 * C);
+                            async_copy16(cell_at(smem, stage, u * 9 + 6, thread), grow + 3 * C);
+                            if (t > 0) {
+                                const float* prow = rbase + (size_t)(t - 1) * 4 * C;
+                                async_copy16(cell_at(smem, stage, u * 9 + 7, thread), prow);
+                                async_copy16(cell_at(smem, stage, u * 9 + 8, thread), prow + C);
+                            }
+                        }
+                    }
+                    async_commit();
+                };
+                if constexpr (ASYNC) issue2(tend, 0);
+                int stage = 0;
+                for (int t0 = tend; t0 > tbeg; t0 -= U2, stage ^= 1) {
                     Vec<4> zr[U2], zi[U2], zv[U2], ur[U2], ui[U2], gr[U2], gi[U2], pr[U2], pi[U2];
+                    if constexpr (ASYNC) {
+                        if (t0 - U2 > tbeg) issue2(t0 - U2, stage ^ 1); else async_commit();
+                        async_wait_pending<1>();
+#pragma unroll
+                        for (int u = 0; u < U2; ++u) {
+                            const int t = t0 - 1 - u;
+                            if (t >= tbeg) {
+                                zr[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 0, thread));
+                                zi[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 1, thread));
+                                zv[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 2, thread));
+                                ur[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 3, thread));
+                                ui[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 4, thread));
+                                gr[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 5, thread));
+                                gi[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 6, thread));
+                                if (t > 0) {
+                                    pr[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 7, thread));
+                                    pi[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 8, thread));
+                                } else if (p.state_in) {
+                                    const float* prow = p.state_in + (size_t)tl.b * 2 * C + c0;
+                                    pr[u] = vec_load<4>(prow);
+                                    pi[u] = vec_load<4>(prow + C);
+                                } else {
+                                    pr[u] = vec_fill<4>(0.0f);
+                                    pi[u] = vec_fill<4>(0.0f);
+                                }
+                            }
+                        }
+                    } else {
 #pragma unroll
                     for (int u = 0; u < U2; ++u) {
                         const int t = t0 - 1 - u;
@@ -459,6 +554,7 @@ struct BwdSinglePass {
                                 pi[u] = vec_fill<4>(0.0f);
                             }
                         }
+                    }
                     }
 #pragma unroll
                     for (int u = 0; u < U2; ++u) {

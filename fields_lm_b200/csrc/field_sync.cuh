@@ -80,6 +80,32 @@ FL_HD Pub2 peek2(const float* p) {
     return r;
 }
 
+// ---------------------------------------------------------------------------
+// Asynchronous 16-byte global -> shared copies.
+// ---------------------------------------------------------------------------
+FL_HD void async_copy16(float* smem_dst, const float* gmem_src) {
+#if FL_DEVICE_CODE
+    const unsigned saddr = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(saddr), "l"(gmem_src)
+                 : "memory");
+#else
+    std::memcpy(smem_dst, gmem_src, 16);
+#endif
+}
+
+FL_HD void async_commit() {
+#if FL_DEVICE_CODE
+    asm volatile("cp.async.commit_group;" ::: "memory");
+#endif
+}
+
+template <int N>
+FL_HD void async_wait_pending() {
+#if FL_DEVICE_CODE
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+#endif
+}
+
 // Asks the memory system to bring one 128-byte line into L2 (no register, no wait).
 FL_HD void prefetch_l2(const void* p) {
 #if FL_DEVICE_CODE

@@ -175,11 +175,34 @@ __global__ void __launch_bounds__(K::kThreads, K::kMinBlocks) stateful_entry(con
     run_phases<K, K::kClaimAfter + 1, K::kPhases - 1>(p, tile, smem, st);
 }
 
+// Kernels that need more than the default 48 KB of dynamic shared memory opt in once per device.
+template <class Fn>
+static int allow_shared_memory(Fn fn, size_t bytes) {
+    if (bytes <= 48 * 1024) return FIELDS_OK;
+    static std::mutex mu;
+    static bool ready[64] = {};
+    int dev = 0;
+    int rc = check_cuda(cudaGetDevice(&dev));
+    if (rc) return rc;
+    if (dev < 0 || dev >= 64) return FIELDS_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ready[dev]) {
+        rc = check_cuda(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)bytes));
+        if (rc) return rc;
+        ready[dev] = true;
+    }
+    return FIELDS_OK;
+}
+
 template <class K>
 static int launch_stateful(const typename K::Params& p, long long tiles, int, Stream st) {
     if (tiles <= 0) return FIELDS_OK;
     if (tiles > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
-    stateful_entry<K><<<(unsigned)tiles, K::kThreads, K::kSmemFloats * sizeof(float), st>>>(p);
+    constexpr size_t bytes = K::kSmemFloats * sizeof(float);
+    const int rc = allow_shared_memory(stateful_entry<K>, bytes);
+    if (rc) return rc;
+    stateful_entry<K><<<(unsigned)tiles, K::kThreads, bytes, st>>>(p);
     return check_cuda(cudaGetLastError());
 }
 
@@ -215,29 +238,13 @@ __global__ void __launch_bounds__(K::kThreads, K::kMinBlocks) walk_entry(const t
     }
 }
 
-// Kernels that need more than the default 48 KB of dynamic shared memory opt in once per
-// device.
 template <class K>
 static int launch_walk(const typename K::Params& p, long long grid, Stream st) {
     if (grid <= 0) return FIELDS_OK;
     if (grid > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
     constexpr size_t bytes = K::kSmemFloats * sizeof(float);
-    static std::mutex mu;
-    static bool ready[64] = {};
-    int dev = 0;
-    int rc = check_cuda(cudaGetDevice(&dev));
+    const int rc = allow_shared_memory(walk_entry<K>, bytes);
     if (rc) return rc;
-    if (dev < 0 || dev >= 64) return FIELDS_ERR_UNSUPPORTED;
-    {
-        std::lock_guard<std::mutex> lock(mu);
-        if (!ready[dev]) {
-            rc = check_cuda(cudaFuncSetAttribute(walk_entry<K>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 (int)bytes));
-            if (rc) return rc;
-            ready[dev] = true;
-        }
-    }
     walk_entry<K><<<(unsigned)grid, K::kThreads, bytes, st>>>(p);
     return check_cuda(cudaGetLastError());
 }
@@ -370,6 +377,9 @@ using BwdSp2 = BwdSinglePass<16, 4, 2, 1, 5>;   // tile 64
 using BwdSp3 = BwdSinglePass<8, 4, 4, 2, 2>;    // deep unroll, 8 warps per SM
 using BwdSp4 = BwdSinglePass<8, 4, 1, 1, 6>;    // shallow unroll, 24 warps per SM
 using BwdSp5 = BwdSinglePass<4, 8, 2, 1, 2>;    // 8 warps per block
+using BwdSp6 = BwdSinglePass<8, 4, 2, 1, 4, true>;   // cp.async rings, 40 KB + 12 KB per block
+using BwdSp7 = BwdSinglePass<8, 4, 2, 2, 3, true>;   // rings, two steps per batch in sweep 2
+using BwdSp8 = BwdSinglePass<16, 4, 2, 1, 4, true>;  // rings, tile 64
 constexpr int kSpMinTile = 32;  // smallest time tile of any instantiation above (workspace bound)
 
 static int variant_from_env(const char* name) {
@@ -661,6 +671,9 @@ int fields_read_backward(const float* raw, const float* tr, const float* ti, con
             case 3: FIELDS_BWD_SP(BwdSp3);
             case 4: FIELDS_BWD_SP(BwdSp4);
             case 5: FIELDS_BWD_SP(BwdSp5);
+            case 6: FIELDS_BWD_SP(BwdSp6);
+            case 7: FIELDS_BWD_SP(BwdSp7);
+            case 8: FIELDS_BWD_SP(BwdSp8);
             default: FIELDS_BWD_SP(BwdSp0);
         }
 #undef FIELDS_BWD_SP
