@@ -176,11 +176,12 @@ __global__ void __launch_bounds__(K::kThreads, K::kMinBlocks) stateful_entry(con
 }
 
 // Kernels that need more than the default 48 KB of dynamic shared memory opt in once per device.
+// `ready` is the caller's per-kernel, per-device record (kernels of equal signature share a
+// function-pointer type, so the record cannot live in this template).
 template <class Fn>
-static int allow_shared_memory(Fn fn, size_t bytes) {
+static int allow_shared_memory(Fn fn, size_t bytes, bool* ready) {
     if (bytes <= 48 * 1024) return FIELDS_OK;
     static std::mutex mu;
-    static bool ready[64] = {};
     int dev = 0;
     int rc = check_cuda(cudaGetDevice(&dev));
     if (rc) return rc;
@@ -200,7 +201,8 @@ static int launch_stateful(const typename K::Params& p, long long tiles, int, St
     if (tiles <= 0) return FIELDS_OK;
     if (tiles > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
     constexpr size_t bytes = K::kSmemFloats * sizeof(float);
-    const int rc = allow_shared_memory(stateful_entry<K>, bytes);
+    static bool ready[64] = {};
+    const int rc = allow_shared_memory(stateful_entry<K>, bytes, ready);
     if (rc) return rc;
     stateful_entry<K><<<(unsigned)tiles, K::kThreads, bytes, st>>>(p);
     return check_cuda(cudaGetLastError());
@@ -243,7 +245,8 @@ static int launch_walk(const typename K::Params& p, long long grid, Stream st) {
     if (grid <= 0) return FIELDS_OK;
     if (grid > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
     constexpr size_t bytes = K::kSmemFloats * sizeof(float);
-    const int rc = allow_shared_memory(walk_entry<K>, bytes);
+    static bool ready[64] = {};
+    const int rc = allow_shared_memory(walk_entry<K>, bytes, ready);
     if (rc) return rc;
     walk_entry<K><<<(unsigned)grid, K::kThreads, bytes, st>>>(p);
     return check_cuda(cudaGetLastError());
