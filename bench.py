@@ -39,7 +39,7 @@ BYTES_PER_TOKEN_FWD = (3 * C + 4 * C) * 4           # read raw, write read
 BYTES_PER_TOKEN_BWD = (3 * C + 4 * C + 3 * C) * 4   # read raw + grad_read, write grad_raw
 BYTES_PER_TOKEN = BYTES_PER_TOKEN_FWD + BYTES_PER_TOKEN_BWD
 FP32_TOL, BF16_TOL = 1e-5, 2e-2
-KERNEL_LAUNCHES_PER_STEP = 3   # chain-walk forward 1 + backward 2 (walk, parameter-gradient reduce)
+KERNEL_LAUNCHES_PER_STEP = 3   # single-pass forward 1 + backward 2 (sweeps, parameter-gradient reduce)
 FALLBACK_HBM_GBS = 6650.0
 LONG_L = 65536
 
@@ -405,7 +405,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "roofline": {
             "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
             "frac": achieved / peak, "traffic": None, "peak_source": f"of {peak_kind}",
-            "kernel": "whole step per GPU: FwdWalk + BwdWalk + BwdReduce",
+            "kernel": "whole step per GPU: FwdSinglePass + BwdSinglePass + BwdReduce (+2 workspace fills)",
             "algorithmic_bytes_per_token": BYTES_PER_TOKEN,
             "forward": {"ms": ms_fwd, "achieved": fwd_gbs, "frac": fwd_gbs / peak},
             "backward": {"ms": bwd_ms,

@@ -134,26 +134,45 @@ FL_HD void error_record(unsigned* error, unsigned code) {
 
 // Walks back from tile n-1 of a chain until a tile with a published end state is met,
 // composing the aggregates of the tiles in between, and returns the state entering tile n.
+// Four predecessors are fetched per round trip and consumed in order as far as they are ready.
 //   agg  [tile][128][4], incl [tile][128][2]: slots of this chain start at `chain_base`.
 // `thread` is the channel inside the 128-channel group. n must be > 0.
 FL_HD void look_back(const float* agg, const float* incl, long long chain_base, int n, int thread,
                      unsigned* error, float& sr, float& si) {
+    constexpr int W = 4;           // predecessors fetched per round trip
     Affine M = affine_identity();  // maps of the tiles between the one met and tile n
-    int k = n - 1;
+    int k = n - 1;                 // nearest tile not yet folded into M
     unsigned polls = 0;
     for (;;) {
-        const long long slot = (chain_base + k) * 128 + thread;
-        const Pub2 s = peek2(incl + slot * 2);
-        const Pub4 a = peek4(agg + slot * 4);
-        if (!is_unset(s.x) && !is_unset(s.y)) {
-            sr = s.x;
-            si = s.y;
-            affine_apply(M, sr, si);
-            return;
+        Pub2 s[W];
+        Pub4 a[W];
+#pragma unroll
+        for (int j = 0; j < W; ++j) {
+            if (k - j >= 0) {
+                const long long slot = (chain_base + k - j) * 128 + thread;
+                s[j] = peek2(incl + slot * 2);
+                a[j] = peek4(agg + slot * 4);
+            }
         }
-        if (k > 0 && !is_unset(a.x) && !is_unset(a.y) && !is_unset(a.z) && !is_unset(a.w)) {
-            M = affine_then(Affine{a.x, a.y, a.z, a.w}, M.ar, M.ai, M.br, M.bi);  // first a, then M
-            --k;
+        int used = 0;
+#pragma unroll
+        for (int j = 0; j < W; ++j) {
+            if (used != j || k - j < 0) continue;  // stop at the first slot that is not ready
+            if (!is_unset(s[j].x) && !is_unset(s[j].y)) {
+                sr = s[j].x;
+                si = s[j].y;
+                affine_apply(M, sr, si);
+                return;
+            }
+            if (k - j > 0 && !is_unset(a[j].x) && !is_unset(a[j].y) && !is_unset(a[j].z) &&
+                !is_unset(a[j].w)) {
+                // first a, then M
+                M = affine_then(Affine{a[j].x, a[j].y, a[j].z, a[j].w}, M.ar, M.ai, M.br, M.bi);
+                used = j + 1;
+            }
+        }
+        if (used > 0) {
+            k -= used;
             polls = 0;
             continue;
         }

@@ -350,8 +350,8 @@ static SpPlan make_sp_plan(int B, int L, int C, int tile_steps) {
 
 enum Algo { kAlgoAuto = 0, kAlgoThreePhase = 1, kAlgoSinglePass = 2, kAlgoWalk = 3 };
 
-// FIELDS_READ_ALGO = three_phase | single_pass | walk selects the kernels (default: the chain
-// walkers when there are enough chains, else single pass, whenever 16-byte accesses are possible). FIELDS_FWD_VARIANT / FIELDS_BWD_VARIANT pick a tuning alternative.
+// FIELDS_READ_ALGO = three_phase | single_pass | walk selects the kernels (default: single pass
+// whenever 16-byte accesses are possible, else three-phase). FIELDS_FWD_VARIANT / FIELDS_BWD_VARIANT pick a tuning alternative.
 static Algo algo_from_env() {
     const char* e = std::getenv("FIELDS_READ_ALGO");
     if (!e) return kAlgoAuto;
@@ -448,11 +448,12 @@ static size_t sp_backward_bytes(int B, int L, int C, int tile_steps) {
 }
 
 // ---------------------------------------------------------------------------
-// Chain walkers: used when batch x (C / 32) gives enough independent chains to fill
-// the GPU (training shapes); no workspace except one partial row per chain (backward).
+// Chain walkers: one block per (batch row, 32 channels) walks the whole sequence, no
+// inter-block communication, bitwise reproducible. Measured slower than the single-pass
+// kernels on B200 at every shape tried (few warps per SM, scalar shared-memory traffic), so
+// they run only on request (FIELDS_READ_ALGO=walk), e.g. when run-to-run identical bits
+// matter more than speed. No workspace except one partial row per chain (backward).
 // ---------------------------------------------------------------------------
-constexpr long long kWalkMinChains = 96;
-
 using FwdWalker = FwdWalk<16, 8, 3>;   // tile 128 steps, 3 x 48 KB ring, 8 warps
 using FwdWalkerB = FwdWalk<8, 16, 3>;  // same tile, 16 warps
 using BwdWalker = BwdWalk<4, 8, 4>;    // tile 32 steps, 4 x 36 KB ring, 8 warps
@@ -470,11 +471,7 @@ static WalkShape walk_shape(int B, int L, int C) {
     return WalkShape{B, L, C, (L + K::kTile - 1) / K::kTile, (C + kLane - 1) / kLane};
 }
 
-static bool walk_wanted(int B, int C, Algo algo) {
-    if (algo == kAlgoWalk) return true;
-    if (algo != kAlgoAuto) return false;
-    return (long long)B * ((C + kLane - 1) / kLane) >= kWalkMinChains;
-}
+static bool walk_wanted(int, int, Algo algo) { return algo == kAlgoWalk; }
 
 // ---------------------------------------------------------------------------
 // Built-in scratch for fields_read_forward_noalloc: one fixed buffer per GPU that
