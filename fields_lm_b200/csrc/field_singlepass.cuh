@@ -275,7 +275,7 @@ struct SpBwdParams {
     SpShape s;
 };
 
-template <int TS, int WARPS, int U1_, int U2_, int MIN_BLOCKS, bool ASYNC = false>
+template <int TS, int WARPS, int U1_, int U2_, int MIN_BLOCKS, bool ASYNC = false, int STAGES = 2>
 struct BwdSinglePass {
     using Params = SpBwdParams;
     static constexpr int kThreads = 32 * WARPS;
@@ -285,11 +285,11 @@ struct BwdSinglePass {
     static constexpr int kSplitPhase = 2;
     static constexpr int kSumFloats = WARPS * 4 * kGroup;   // warp maps, later warp partials
     static constexpr int kCarryFloats = WARPS * 2 * kGroup;
-    // ASYNC: every thread lands its next batch of inputs in a private two-slot ring in shared
+    // ASYNC: every thread lands its next batches of inputs in a private ring of STAGES slots in shared
     // memory with cp.async while it computes on the current batch, so loads stay in flight
     // without holding registers. A cell is one 16-byte vector of one thread.
     static constexpr int kCells = U1_ * 5 > U2_ * 9 ? U1_ * 5 : U2_ * 9;
-    static constexpr int kRingFloats = ASYNC ? 2 * kCells * 32 * WARPS * 4 : 0;
+    static constexpr int kRingFloats = ASYNC ? STAGES * kCells * 32 * WARPS * 4 : 0;
     static constexpr int kSmemFloats = kSumFloats + kCarryFloats + kRingFloats;
     static constexpr int kClaimAfter = 2;
     FL_HD static constexpr bool barrier_after(int ph) { return ph != 1; }
@@ -370,13 +370,16 @@ struct BwdSinglePass {
                     }
                     async_commit();
                 };
-                if constexpr (ASYNC) issue1(tend, 0);
+                if constexpr (ASYNC) {
+#pragma unroll
+                    for (int j = 0; j < STAGES - 1; ++j) issue1(tend - j * U1, j);  // empty past tbeg
+                }
                 int stage = 0;
-                for (int t0 = tend; t0 > tbeg; t0 -= U1, stage ^= 1) {
+                for (int t0 = tend; t0 > tbeg; t0 -= U1, stage = stage + 1 == STAGES ? 0 : stage + 1) {
                     Vec<4> zv[U1], ur[U1], ui[U1], gr[U1], gi[U1];
                     if constexpr (ASYNC) {
-                        if (t0 - U1 > tbeg) issue1(t0 - U1, stage ^ 1); else async_commit();
-                        async_wait_pending<1>();
+                        issue1(t0 - (STAGES - 1) * U1, stage == 0 ? STAGES - 1 : stage - 1);
+                        async_wait_pending<STAGES - 1>();
 #pragma unroll
                         for (int u = 0; u < U1; ++u) {
                             if (t0 - 1 - u >= tbeg) {
@@ -496,13 +499,16 @@ struct BwdSinglePass {
                     }
                     async_commit();
                 };
-                if constexpr (ASYNC) issue2(tend, 0);
+                if constexpr (ASYNC) {
+#pragma unroll
+                    for (int j = 0; j < STAGES - 1; ++j) issue2(tend - j * U2, j);
+                }
                 int stage = 0;
-                for (int t0 = tend; t0 > tbeg; t0 -= U2, stage ^= 1) {
+                for (int t0 = tend; t0 > tbeg; t0 -= U2, stage = stage + 1 == STAGES ? 0 : stage + 1) {
                     Vec<4> zr[U2], zi[U2], zv[U2], ur[U2], ui[U2], gr[U2], gi[U2], pr[U2], pi[U2];
                     if constexpr (ASYNC) {
-                        if (t0 - U2 > tbeg) issue2(t0 - U2, stage ^ 1); else async_commit();
-                        async_wait_pending<1>();
+                        issue2(t0 - (STAGES - 1) * U2, stage == 0 ? STAGES - 1 : stage - 1);
+                        async_wait_pending<STAGES - 1>();
 #pragma unroll
                         for (int u = 0; u < U2; ++u) {
                             const int t = t0 - 1 - u;

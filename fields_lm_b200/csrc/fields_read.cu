@@ -383,6 +383,10 @@ using BwdSp5 = BwdSinglePass<4, 8, 2, 1, 2>;    // 8 warps per block
 using BwdSp6 = BwdSinglePass<8, 4, 2, 1, 4, true>;   // cp.async rings, 40 KB + 12 KB per block
 using BwdSp7 = BwdSinglePass<8, 4, 2, 2, 3, true>;   // rings, two steps per batch in sweep 2
 using BwdSp8 = BwdSinglePass<16, 4, 2, 1, 4, true>;  // rings, tile 64
+using BwdSp9 = BwdSinglePass<8, 4, 1, 1, 3, true, 3>;   // 3-slot rings, one step per batch
+using BwdSp10 = BwdSinglePass<8, 4, 2, 1, 3, true, 3>;  // 3-slot rings
+using BwdSp11 = BwdSinglePass<8, 4, 1, 1, 4, true, 2>;  // 2-slot rings, one step per batch
+using BwdSp12 = BwdSinglePass<8, 8, 2, 1, 2, true, 2>;  // 8 warps per block
 constexpr int kSpMinTile = 32;  // smallest time tile of any instantiation above (workspace bound)
 
 static int variant_from_env(const char* name) {
@@ -674,6 +678,10 @@ int fields_read_backward(const float* raw, const float* tr, const float* ti, con
             case 6: FIELDS_BWD_SP(BwdSp6);
             case 7: FIELDS_BWD_SP(BwdSp7);
             case 8: FIELDS_BWD_SP(BwdSp8);
+            case 9: FIELDS_BWD_SP(BwdSp9);
+            case 10: FIELDS_BWD_SP(BwdSp10);
+            case 11: FIELDS_BWD_SP(BwdSp11);
+            case 12: FIELDS_BWD_SP(BwdSp12);
             default: FIELDS_BWD_SP(BwdSp0);
         }
 #undef FIELDS_BWD_SP

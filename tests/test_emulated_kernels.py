@@ -24,7 +24,9 @@ ALGOS = [("three_phase", "0", "forward"), ("single_pass", "0", "forward"),
          ("single_pass", "2", "reverse"), ("single_pass", "3", "forward"),
          ("single_pass", "4", "reverse"), ("single_pass", "5", "forward"),
          ("single_pass", "6", "reverse"), ("single_pass", "7", "forward"),
-         ("single_pass", "8", "reverse"),
+         ("single_pass", "8", "reverse"), ("single_pass", "9", "forward"),
+         ("single_pass", "10", "reverse"), ("single_pass", "11", "forward"),
+         ("single_pass", "12", "reverse"),
          ("walk", "0", "forward")]
 
 
