@@ -38,7 +38,8 @@ struct SpShape {
     int B, L, C;
     int NT;        // time tiles per chain
     int G;         // 128-channel groups
-    int prefetch;  // non-zero: blocks warm L2 with the inputs of the tile they claim next
+    int prefetch;  // non-zero: blocks warm L2 with the inputs of the tile that many positions ahead
+    unsigned max_polls;  // bound of every wait for another block's publication
 };
 
 // Prefetches `planes` consecutive 128-channel plane chunks of `steps` rows into L2:
@@ -191,7 +192,7 @@ struct FwdSinglePass {
                     sr = p.state_in ? p.state_in[(size_t)tl.b * 2 * C + ch] : 0.0f;
                     si = p.state_in ? p.state_in[(size_t)tl.b * 2 * C + C + ch] : 0.0f;
                 } else {
-                    look_back(p.agg, p.incl, tl.chain * s.NT, tl.n, thread, p.ctrl, sr, si);
+                    look_back(p.agg, p.incl, tl.chain * s.NT, tl.n, thread, p.ctrl, s.max_polls, sr, si);
                 }
 #pragma unroll
                 for (int w = 0; w < WARPS; ++w) {
@@ -448,7 +449,7 @@ struct BwdSinglePass {
                     sr = p.grad_state_out ? p.grad_state_out[(size_t)tl.b * 2 * C + ch] : 0.0f;
                     si = p.grad_state_out ? p.grad_state_out[(size_t)tl.b * 2 * C + C + ch] : 0.0f;
                 } else {
-                    look_back(p.agg, p.incl, tl.chain * s.NT, tl.n, thread, p.ctrl, sr, si);
+                    look_back(p.agg, p.incl, tl.chain * s.NT, tl.n, thread, p.ctrl, s.max_polls, sr, si);
                 }
 #pragma unroll
                 for (int w = 0; w < WARPS; ++w) {
@@ -621,6 +622,33 @@ struct BwdSinglePass {
                 }
             }
         }
+    }
+};
+
+
+// ---------------------------------------------------------------------------
+// Self-test of the bounded wait: one block looks back over a chain in which nothing was
+// ever published. Every thread must give up after `max_polls` polls, record the error
+// word and return NaN; the kernel ends normally. Used by the tests to check, without
+// hanging or faulting anything, that a lost publication turns into a status code.
+// ---------------------------------------------------------------------------
+struct WaitSelfTest {
+    struct Params {
+        const float* agg;
+        const float* incl;
+        unsigned* ctrl;
+        float* out;  // [128][2]
+        unsigned max_polls;
+    };
+    static constexpr int kThreads = kGroup;
+    static constexpr int kPhases = 1;
+    static constexpr int kSmemFloats = 0;
+
+    FL_HD static void phase0(const Params& p, int, int thread, float*) {
+        float sr, si;
+        look_back(p.agg, p.incl, 0, 3, thread, p.ctrl, p.max_polls, sr, si);
+        p.out[thread * 2] = sr;
+        p.out[thread * 2 + 1] = si;
     }
 };
 

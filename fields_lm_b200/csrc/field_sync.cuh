@@ -138,7 +138,7 @@ FL_HD void error_record(unsigned* error, unsigned code) {
 //   agg  [tile][128][4], incl [tile][128][2]: slots of this chain start at `chain_base`.
 // `thread` is the channel inside the 128-channel group. n must be > 0.
 FL_HD void look_back(const float* agg, const float* incl, long long chain_base, int n, int thread,
-                     unsigned* error, float& sr, float& si) {
+                     unsigned* error, unsigned max_polls, float& sr, float& si) {
     constexpr int W = 4;           // predecessors fetched per round trip
     Affine M = affine_identity();  // maps of the tiles between the one met and tile n
     int k = n - 1;                 // nearest tile not yet folded into M
@@ -177,10 +177,12 @@ FL_HD void look_back(const float* agg, const float* incl, long long chain_base, 
             continue;
         }
 #if FL_DEVICE_CODE
-        if (++polls < kMaxPolls) {
+        if (++polls < max_polls) {
             backoff(polls);
             continue;
         }
+#else
+        (void)max_polls;
 #endif
         error_record(error, 1u);
         sr = si = nanf("");

@@ -339,6 +339,7 @@ static SpPlan make_sp_plan(int B, int L, int C, int tile_steps) {
     pl.s.B = B; pl.s.L = L; pl.s.C = C;
     pl.s.NT = (L + tile_steps - 1) / tile_steps;
     pl.s.G = (C + kGroup - 1) / kGroup;
+    pl.s.max_polls = kMaxPolls;
     pl.tiles = (long long)B * pl.s.G * pl.s.NT;
     pl.ctrl_words = kCtrlHeader;
     pl.agg_off = pl.ctrl_words * sizeof(unsigned);
@@ -374,7 +375,7 @@ using FwdSp3 = FwdSinglePass<7, 8, 2>;   // tile 56
 using FwdSp4 = FwdSinglePass<5, 8, 2>;   // tile 40
 using FwdSp5 = FwdSinglePass<4, 8, 2>;   // tile 32, 2 blocks per SM
 //   backward <steps per warp, warps, sweep-1 unroll, sweep-2 unroll, blocks per SM>
-using BwdSp0 = BwdSinglePass<8, 4, 2, 1, 5>;    // tile 32, 96 registers, 20 warps per SM
+using BwdSp0 = BwdSinglePass<8, 4, 2, 1, 3, true, 3>;  // tile 32, 3-slot cp.async rings, 12 warps per SM
 using BwdSp1 = BwdSinglePass<8, 4, 2, 1, 4>;    // 127 registers, 16 warps per SM
 using BwdSp2 = BwdSinglePass<16, 4, 2, 1, 5>;   // tile 64
 using BwdSp3 = BwdSinglePass<8, 4, 4, 2, 2>;    // deep unroll, 8 warps per SM
@@ -384,7 +385,7 @@ using BwdSp6 = BwdSinglePass<8, 4, 2, 1, 4, true>;   // cp.async rings, 40 KB + 
 using BwdSp7 = BwdSinglePass<8, 4, 2, 2, 3, true>;   // rings, two steps per batch in sweep 2
 using BwdSp8 = BwdSinglePass<16, 4, 2, 1, 4, true>;  // rings, tile 64
 using BwdSp9 = BwdSinglePass<8, 4, 1, 1, 3, true, 3>;   // 3-slot rings, one step per batch
-using BwdSp10 = BwdSinglePass<8, 4, 2, 1, 3, true, 3>;  // 3-slot rings
+using BwdSp10 = BwdSinglePass<8, 4, 2, 1, 5>;   // direct loads, 96 registers, 20 warps per SM
 using BwdSp11 = BwdSinglePass<8, 4, 1, 1, 4, true, 2>;  // 2-slot rings, one step per batch
 using BwdSp12 = BwdSinglePass<8, 8, 2, 1, 2, true, 2>;  // 8 warps per block
 constexpr int kSpMinTile = 32;  // smallest time tile of any instantiation above (workspace bound)
@@ -790,6 +791,28 @@ int fields_read_step_bf16(const void* raw, const float* tr, const float* ti, con
                           float* state, void* read, int B, int C, void* stream) {
     return run_step<uint16_t>(static_cast<const uint16_t*>(raw), tr, ti, gamma, state,
                               static_cast<uint16_t*>(read), B, C, stream);
+}
+
+
+int fields_read_selftest_wait(void* workspace, size_t workspace_bytes, unsigned max_polls,
+                              void* stream) {
+    // layout: [ctrl 256 B | agg 4 tiles | incl 4 tiles | out 128 x 2]
+    const size_t agg_bytes = 4 * kGroup * 4 * sizeof(float), incl_bytes = 4 * kGroup * 2 * sizeof(float);
+    const size_t need = kCtrlHeader * sizeof(unsigned) + agg_bytes + incl_bytes + kGroup * 2 * sizeof(float);
+    if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return FIELDS_ERR_WORKSPACE;
+    if (max_polls == 0 || max_polls > kMaxPolls) return FIELDS_ERR_ARGUMENT;
+    Stream st = reinterpret_cast<Stream>(stream);
+    char* ws = static_cast<char*>(workspace);
+    int rc = fill_unset(ws, need, st);
+    if (rc) return rc;
+    float* agg = reinterpret_cast<float*>(ws + kCtrlHeader * sizeof(unsigned));
+    float* incl = reinterpret_cast<float*>(ws + kCtrlHeader * sizeof(unsigned) + agg_bytes);
+    float* out = reinterpret_cast<float*>(ws + kCtrlHeader * sizeof(unsigned) + agg_bytes + incl_bytes);
+    WaitSelfTest::Params p{agg, incl, reinterpret_cast<unsigned*>(ws), out, max_polls};
+    rc = launch<WaitSelfTest>(p, 1, st);
+    if (rc) return rc;
+    return fields_read_device_status(workspace, stream);
 }
 
 }  // extern "C"

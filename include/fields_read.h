@@ -138,6 +138,16 @@ const char *fields_last_cuda_error(void);
 int fields_read_device_status(const void *workspace, void *stream);
 
 /*
+ * Self-test of the bounded device-side wait: runs one block that waits for a publication
+ * nothing ever makes, with the wait limited to max_polls polls, waits for the stream and
+ * returns the resulting status - FIELDS_ERR_TIMEOUT when the wait gave up cleanly, as it
+ * must. Nothing hangs, traps or faults; the context stays usable. workspace: at least
+ * 8 KB, 256-byte aligned. (No counterpart in the reference.)
+ */
+int fields_read_selftest_wait(void *workspace, size_t workspace_bytes, unsigned max_polls,
+                              void *stream);
+
+/*
  * Forward of the fused Field read for callers that have no memory to give.
  * (No counterpart in the reference, whose operator allocates its work buffers
  * with torch.empty on every call.)

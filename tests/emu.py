@@ -54,6 +54,8 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.fields_read_step.restype = I
     lib.fields_read_step_bf16.argtypes = [P] * 6 + [I, I, P]
     lib.fields_read_step_bf16.restype = I
+    lib.fields_read_selftest_wait.argtypes = [P, SZ, ctypes.c_uint, P]
+    lib.fields_read_selftest_wait.restype = I
     lib.fields_read_device_status.argtypes = [P, P]
     lib.fields_read_device_status.restype = I
     return lib

@@ -185,3 +185,9 @@ def test_decode_step_bf16_io():
     got = torch.from_numpy(np.array(row_bits).view(np.int16)).view(torch.bfloat16).float().numpy()
     assert rel_err(new_state, ref_state) < FP32_TOL          # the state never leaves fp32
     assert rel_err(got, ref[:, 0]) < 2 ** -8                 # one bf16 rounding of the output
+
+
+def test_wait_selftest_reports_timeout():
+    ws = emu._aligned(16384)
+    assert emu.lib().fields_read_selftest_wait(ws.ctypes.data_as(emu.P), ws.size, 100, None) == 4
+    assert emu.lib().fields_read_selftest_wait(ws.ctypes.data_as(emu.P), 64, 100, None) == 2

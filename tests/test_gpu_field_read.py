@@ -285,3 +285,20 @@ def test_empty_sequence(dev):
     read, state = field_read_with_state(torch.zeros(2, 0, 12, device=dev), p, p, p, s)
     assert read.shape == (2, 0, 16)
     assert bool((state == 3.0).all())
+
+
+def test_a_wait_that_nothing_satisfies_ends_with_a_timeout_status(dev):
+    """Bounded wait: a block waiting for a publication that never comes gives up after its poll
+    limit, reports FIELDS_ERR_TIMEOUT through the error word, and the GPU stays usable."""
+    from fields_lm_b200 import _lib
+    lib = _lib.load()
+    ws = torch.empty(16384, dtype=torch.uint8, device=dev)
+    s = torch.cuda.current_stream(dev).cuda_stream
+    assert lib.fields_read_selftest_wait(ws.data_ptr(), ws.numel(), 2000, s) == 4
+    out = ws[256 + 4 * 128 * 16 + 4 * 128 * 8:][:128 * 2 * 4].view(torch.float32)
+    assert bool(torch.isnan(out).all())
+    # the context is intact: an ordinary call still works afterwards
+    p = torch.ones(4, device=dev) * 0.5
+    from fields_lm_b200 import fused_field_read
+    y = fused_field_read(torch.zeros(1, 3, 12, device=dev), p, p, p, 32, 64)
+    assert bool(torch.isfinite(y).all())
