@@ -498,11 +498,11 @@ struct BwdMaterialize {
 // ---------------------------------------------------------------------------
 // Backward, last: parameter gradients = sum of the chunk partials over batch and
 // chunks, in a fixed order (bitwise reproducible). Block = (plane, 32 channels);
-// warp w adds rows w, w + W, ... in double, then warp 0 adds the W warp sums.
+// warp w adds rows w, w + W, ... in double (W = 32), then warp 0 adds the W warp sums.
 // Stands for the three tensor.sum(dim=(0,1)) calls of the reference
 // (field_only_v4_chunked_triton_wiki100.py:1098-1105).
 // ---------------------------------------------------------------------------
-constexpr int kReduceWarps = 16;
+constexpr int kReduceWarps = 32;
 
 struct BwdReduce {
     using Params = BwdParams;
@@ -520,7 +520,16 @@ struct BwdReduce {
         if (c < s.C) {
             const int rows = s.B * s.N;
             const float* src = p.partial + (size_t)k * rows * s.C + c;
-            for (int r = w; r < rows; r += kReduceWarps) acc += (double)src[(size_t)r * s.C];
+            // rows w, w + W, w + 2W, ...; eight loads in flight, added in row order
+            int r = w;
+            for (; r + 7 * kReduceWarps < rows; r += 8 * kReduceWarps) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = src[(size_t)(r + j * kReduceWarps) * s.C];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc += (double)v[j];
+            }
+            for (; r < rows; r += kReduceWarps) acc += (double)src[(size_t)r * s.C];
         }
         reinterpret_cast<double*>(smem)[thread] = acc;
     }
@@ -539,7 +548,6 @@ struct BwdReduce {
         dst[c] = (float)acc;
     }
 };
-
 
 // ---------------------------------------------------------------------------
 // Span summary: the affine map of a whole span per (batch, channel), composed from
