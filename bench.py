@@ -355,7 +355,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         from fields_lm_b200 import seqpar
         lo, hi = seqpar.span_bounds(LONG_L, world, rank)
         long_raw = synthetic_inputs(2, 1, LONG_L)[0][:, lo:hi].contiguous().to(device)
-        long_fwd = lambda: seqpar.sequence_parallel_field_read(long_raw, tr_d, ti_d, gm_d)
+        sp_fwd = seqpar.SequenceParallelForward(1, hi - lo, C, device)
+        long_fwd = lambda: sp_fwd(long_raw, tr_d, ti_d, gm_d)
     else:
         long_op = DirectOp(device, 1, LONG_L)
         long_raw = synthetic_inputs(2, 1, LONG_L)[0].to(device)

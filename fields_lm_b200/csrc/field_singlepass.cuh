@@ -652,4 +652,96 @@ struct WaitSelfTest {
     }
 };
 
+
+// ---------------------------------------------------------------------------
+// Streaming chunk summary for sequence sharding: the affine map of every chunk of a span,
+// reading raw once at full speed. One warp owns one (batch row, chunk, 128-channel group)
+// and walks its chunk forward in batches of U steps; each thread lands the next batches in
+// a private ring of STAGES slots with cp.async (3 vectors per step) while it evaluates the
+// gates and composes the map of the current one. Output: the chunk maps in the layout of
+// the three-phase kernels, sum [4][B][N][C], which SpanCompose folds into the span's map.
+// ---------------------------------------------------------------------------
+template <int U, int STAGES, int WARPS>
+struct ChunkSummaryStream {
+    using Params = FwdParams;  // raw, tr, ti, gamma, sum, shape (ts = chunk length, N, G)
+    static constexpr int kThreads = 32 * WARPS;
+    static constexpr int kPhases = 1;
+    static constexpr int kCells = U * 3;
+    static constexpr int kSmemFloats = STAGES * kCells * kThreads * 4;
+
+    FL_HD static float* cell_at(float* smem, int stage, int idx, int thread) {
+        return smem + ((size_t)(stage * kCells + idx) * kThreads + thread) * 4;
+    }
+
+    FL_HD static void phase0(const Params& p, int block, int thread, float* smem) {
+        const Shape& s = p.s;
+        const int lane = thread & 31;
+        const long long task = (long long)block * WARPS + (thread >> 5);
+        if (task >= (long long)s.B * s.N * s.G) return;
+        const int cg = (int)(task % s.G);
+        const int n = (int)((task / s.G) % s.N);
+        const int b = (int)(task / ((long long)s.G * s.N));
+        const int C = s.C;
+        const int c0 = (cg * 32 + lane) * 4;
+        if (c0 >= C) return;
+        const int tbeg = n * s.ts;
+        const int tend = tbeg + s.ts < s.L ? tbeg + s.ts : s.L;
+        const Vec<4> lr = vec_load<4>(p.tr + c0);
+        const Vec<4> li = vec_load<4>(p.ti + c0);
+        const Vec<4> gm = vec_load<4>(p.gamma + c0);
+        const float* base = p.raw + ((size_t)b * s.L) * 3 * C + c0;
+        Affine m[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) m[k] = affine_identity();
+
+        auto issue = [&](int t0, int stage) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int t = t0 + u;
+                if (t < tend) {
+                    const float* row = base + (size_t)t * 3 * C;
+                    async_copy16(cell_at(smem, stage, u * 3 + 0, thread), row);
+                    async_copy16(cell_at(smem, stage, u * 3 + 1, thread), row + C);
+                    async_copy16(cell_at(smem, stage, u * 3 + 2, thread), row + 2 * C);
+                }
+            }
+            async_commit();
+        };
+#pragma unroll
+        for (int j = 0; j < STAGES - 1; ++j) issue(tbeg + j * U, j);
+        int stage = 0;
+        for (int t0 = tbeg; t0 < tend; t0 += U, stage = stage + 1 == STAGES ? 0 : stage + 1) {
+            issue(t0 + (STAGES - 1) * U, stage == 0 ? STAGES - 1 : stage - 1);
+            async_wait_pending<STAGES - 1>();
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (t0 + u < tend) {
+                    const Vec<4> zr = vec_load<4>(cell_at(smem, stage, u * 3 + 0, thread));
+                    const Vec<4> zi = vec_load<4>(cell_at(smem, stage, u * 3 + 1, thread));
+                    const Vec<4> zv = vec_load<4>(cell_at(smem, stage, u * 3 + 2, thread));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const Gate g = make_gate(zr.v[k], zi.v[k], zv.v[k]);
+                        const float keep = 1.0f - g.vac;
+                        const float bs = gm.v[k] * g.vac;
+                        m[k] = affine_then(m[k], keep * lr.v[k], keep * li.v[k], bs * g.inj_r,
+                                           bs * g.inj_i);
+                    }
+                }
+            }
+        }
+        const size_t plane = (size_t)s.B * s.N * C;
+        float* out = p.sum + ((size_t)b * s.N + n) * C + c0;
+        Vec<4> o0, o1, o2, o3;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            o0.v[k] = m[k].ar; o1.v[k] = m[k].ai; o2.v[k] = m[k].br; o3.v[k] = m[k].bi;
+        }
+        vec_store<4>(out, o0);
+        vec_store<4>(out + plane, o1);
+        vec_store<4>(out + 2 * plane, o2);
+        vec_store<4>(out + 3 * plane, o3);
+    }
+};
+
 }  // namespace fields

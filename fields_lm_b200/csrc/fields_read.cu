@@ -747,8 +747,14 @@ int fields_read_span_summary(const float* raw, const float* tr, const float* ti,
     float* ws = static_cast<float*>(workspace);
     FwdParams p{raw, tr, ti, gamma, nullptr, nullptr, nullptr, ws + pl.sum_off, ws + pl.carry_off,
                 pl.s};
-    int rc = vec4 ? launch<FwdSummary<4, 4>>(p, tile_blocks(pl.s), st)
-                  : launch<FwdSummary<1, 4>>(p, tile_blocks(pl.s), st);
+    int rc;
+    if (vec4) {
+        using Stream4 = ChunkSummaryStream<2, 3, 4>;  // 36 KB of rings per block
+        const long long tasks = (long long)pl.s.B * pl.s.N * pl.s.G;
+        rc = launch<Stream4>(p, (tasks + 3) / 4, st);
+    } else {
+        rc = launch<FwdSummary<1, 4>>(p, tile_blocks(pl.s), st);
+    }
     if (rc) return rc;
     SpanCompose::Params cp{p.sum, summary, pl.s};
     return launch<SpanCompose>(cp, (long long)B * ((C + 31) / 32), st);

@@ -56,6 +56,53 @@ class CudaOps:
             return field_read_with_state(raw, tr, ti, gamma, state_in)
 
 
+class SequenceParallelForward:
+    """The same four steps on preallocated buffers, for repeated calls on one span shape.
+
+    Holds the outputs (``read``, ``state_out``), the summary buffers and the workspace, so a
+    call costs three C-ABI launches and one NCCL all_gather and allocates nothing.
+    """
+
+    def __init__(self, batch: int, span_length: int, channels: int, device, group=None):
+        self.lib = _lib.load()
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.B, self.L, self.C = batch, span_length, channels
+        f32 = dict(device=device, dtype=torch.float32)
+        self.summary = torch.empty(batch, 4, channels, **f32)
+        self.gathered = torch.empty(self.world * batch, 4, channels, **f32)
+        self.state_in = torch.empty(batch, 2 * channels, **f32)
+        self.state_out = torch.empty(batch, 2 * channels, **f32)
+        self.read = torch.empty(batch, span_length, 4 * channels, **f32)
+        self.nbytes = self.lib.fields_read_workspace_bytes(batch, span_length, channels, 0)
+        self.ws = torch.empty(max(self.nbytes, 256), dtype=torch.uint8, device=device)
+        self.device = torch.device(device)
+
+    def __call__(self, raw_span, tr, ti, gamma, state0: Optional[torch.Tensor] = None):
+        lib, B, L, C = self.lib, self.B, self.L, self.C
+        if tuple(raw_span.shape) != (B, L, 3 * C) or not raw_span.is_contiguous():
+            raise ValueError(f"expected a contiguous [{B}, {L}, {3 * C}] span")
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        args = (raw_span.data_ptr(), tr.data_ptr(), ti.data_ptr(), gamma.data_ptr())
+        state_in = None if state0 is None else state0.data_ptr()
+        if self.world > 1:
+            rc = lib.fields_read_span_summary(*args, self.summary.data_ptr(), self.ws.data_ptr(),
+                                              self.nbytes, B, L, C, st)
+            _lib.check(rc, "fields_read_span_summary")
+            dist.all_gather_into_tensor(self.gathered, self.summary, group=self.group)
+            rc = lib.fields_read_fold_summaries(self.gathered.data_ptr(), state_in,
+                                                self.state_in.data_ptr(), self.rank, self.world,
+                                                B, C, st)
+            _lib.check(rc, "fields_read_fold_summaries")
+            state_in = self.state_in.data_ptr()
+        rc = lib.fields_read_forward(*args, state_in, self.read.data_ptr(),
+                                     self.state_out.data_ptr(), self.ws.data_ptr(), self.nbytes,
+                                     B, L, C, st)
+        _lib.check(rc, "fields_read_forward")
+        return self.read, self.state_out
+
+
 def span_bounds(length: int, world: int, rank: int) -> Tuple[int, int]:
     """Contiguous, near-equal spans: the first ``length % world`` ranks get one step more."""
     base, extra = divmod(length, world)

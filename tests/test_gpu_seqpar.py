@@ -29,8 +29,16 @@ def _worker(rank, world, port, L, out_dir):
         gm = torch.sqrt(1 - ring ** 2).to(dev)
         raw = (torch.randn(B, L, 3 * C, generator=gen) * 0.577)
         lo, hi = seqpar.span_bounds(L, world, rank)
-        read, state = seqpar.sequence_parallel_field_read(raw[:, lo:hi].to(dev), tr, ti, gm)
+        span = raw[:, lo:hi].contiguous().to(dev)
+        read, state = seqpar.sequence_parallel_field_read(span, tr, ti, gm)
         torch.cuda.synchronize()
+        # the preallocated form gives the same bits, call after call
+        op = seqpar.SequenceParallelForward(B, hi - lo, C, dev)
+        for _ in range(2):
+            read2, state2 = op(span, tr, ti, gm)
+        torch.cuda.synchronize()
+        assert float((read2 - read).abs().max()) <= 2e-6 * float(read.abs().max())
+        assert float((state2 - state).abs().max()) <= 2e-6 * float(state.abs().max())
         if rank == 0:
             with torch.no_grad():
                 full, full_state = field_read_with_state(raw.to(dev), tr, ti, gm, None)
