@@ -577,7 +577,19 @@ struct SpanCompose {
         const int hi = lo + per < s.N ? lo + per : s.N;
         const size_t plane = (size_t)s.B * s.N * s.C;
         Affine m = affine_identity();
-        for (int i = lo; i < hi; ++i) {
+        int i = lo;
+        for (; i + 8 <= hi; i += 8) {  // eight maps in flight, composed in order
+            float v[8][4];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const size_t idx = ((size_t)b * s.N + i + j) * s.C + c;
+                v[j][0] = p.sum[idx]; v[j][1] = p.sum[idx + plane];
+                v[j][2] = p.sum[idx + 2 * plane]; v[j][3] = p.sum[idx + 3 * plane];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) m = affine_then(m, v[j][0], v[j][1], v[j][2], v[j][3]);
+        }
+        for (; i < hi; ++i) {
             const size_t idx = ((size_t)b * s.N + i) * s.C + c;
             m = affine_then(m, p.sum[idx], p.sum[idx + plane], p.sum[idx + 2 * plane],
                             p.sum[idx + 3 * plane]);

@@ -663,11 +663,14 @@ struct WaitSelfTest {
 // ---------------------------------------------------------------------------
 template <int U, int STAGES, int WARPS>
 struct ChunkSummaryStream {
-    using Params = FwdParams;  // raw, tr, ti, gamma, sum, shape (ts = chunk length, N, G)
+    // raw, tr, ti, gamma, sum, shape: ts = steps per warp, N = maps written per sequence
+    // (one per block = WARPS consecutive warp chunks), G = 128-channel groups
+    using Params = FwdParams;
     static constexpr int kThreads = 32 * WARPS;
-    static constexpr int kPhases = 1;
+    static constexpr int kPhases = 2;
     static constexpr int kCells = U * 3;
-    static constexpr int kSmemFloats = STAGES * kCells * kThreads * 4;
+    static constexpr int kRingFloats = STAGES * kCells * kThreads * 4;
+    static constexpr int kSmemFloats = kRingFloats + WARPS * 4 * 128;  // + the warps' maps
 
     FL_HD static float* cell_at(float* smem, int stage, int idx, int thread) {
         return smem + ((size_t)(stage * kCells + idx) * kThreads + thread) * 4;
@@ -675,16 +678,17 @@ struct ChunkSummaryStream {
 
     FL_HD static void phase0(const Params& p, int block, int thread, float* smem) {
         const Shape& s = p.s;
-        const int lane = thread & 31;
-        const long long task = (long long)block * WARPS + (thread >> 5);
-        if (task >= (long long)s.B * s.N * s.G) return;
-        const int cg = (int)(task % s.G);
-        const int n = (int)((task / s.G) % s.N);
-        const int b = (int)(task / ((long long)s.G * s.N));
+        const int lane = thread & 31, warp = thread >> 5;
+        // block -> (batch row, map index, channel group); warp w takes the w-th chunk of the map
+        const int cg = block % s.G;
+        const int n = (block / s.G) % s.N;
+        const int b = block / (s.G * s.N);
         const int C = s.C;
         const int c0 = (cg * 32 + lane) * 4;
+        float* maps = smem + kRingFloats + warp * 4 * 128 + lane * 4;
         if (c0 >= C) return;
-        const int tbeg = n * s.ts;
+        const int t_first = (n * WARPS + warp) * s.ts;
+        const int tbeg = t_first < s.L ? t_first : s.L;
         const int tend = tbeg + s.ts < s.L ? tbeg + s.ts : s.L;
         const Vec<4> lr = vec_load<4>(p.tr + c0);
         const Vec<4> li = vec_load<4>(p.ti + c0);
@@ -730,17 +734,34 @@ struct ChunkSummaryStream {
                 }
             }
         }
-        const size_t plane = (size_t)s.B * s.N * C;
-        float* out = p.sum + ((size_t)b * s.N + n) * C + c0;
         Vec<4> o0, o1, o2, o3;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             o0.v[k] = m[k].ar; o1.v[k] = m[k].ai; o2.v[k] = m[k].br; o3.v[k] = m[k].bi;
         }
-        vec_store<4>(out, o0);
-        vec_store<4>(out + plane, o1);
-        vec_store<4>(out + 2 * plane, o2);
-        vec_store<4>(out + 3 * plane, o3);
+        vec_store<4>(maps, o0);
+        vec_store<4>(maps + 128, o1);
+        vec_store<4>(maps + 256, o2);
+        vec_store<4>(maps + 384, o3);
+    }
+
+    // the block's map = its warps' maps in time order; one thread per channel
+    FL_HD static void phase1(const Params& p, int block, int thread, float* smem) {
+        const Shape& s = p.s;
+        const int cg = block % s.G;
+        const int n = (block / s.G) % s.N;
+        const int b = block / (s.G * s.N);
+        const int c = cg * 128 + thread;
+        if (thread >= 128 || c >= s.C) return;
+        Affine a = affine_identity();
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float* q = smem + kRingFloats + w * 4 * 128 + thread;
+            a = affine_then(a, q[0], q[128], q[256], q[384]);
+        }
+        const size_t plane = (size_t)s.B * s.N * s.C;
+        float* out = p.sum + ((size_t)b * s.N + n) * s.C + c;
+        out[0] = a.ar; out[plane] = a.ai; out[2 * plane] = a.br; out[3 * plane] = a.bi;
     }
 };
 

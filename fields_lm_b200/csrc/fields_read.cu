@@ -740,7 +740,7 @@ int fields_read_span_summary(const float* raw, const float* tr, const float* ti,
     Stream st = reinterpret_cast<Stream>(stream);
     const bool vec4 = C % 4 == 0 && aligned16(raw) && aligned16(tr) && aligned16(ti) &&
                       aligned16(gamma) && aligned16(workspace);
-    const Plan pl = make_plan(B, L, C, vec4 ? 4 : 1);
+    Plan pl = make_plan(B, L, C, vec4 ? 4 : 1);
     if (!workspace || workspace_bytes < pl.fwd_floats * sizeof(float) ||
         (reinterpret_cast<uintptr_t>(workspace) & 255u))
         return FIELDS_ERR_WORKSPACE;
@@ -749,9 +749,14 @@ int fields_read_span_summary(const float* raw, const float* tr, const float* ti,
                 pl.s};
     int rc;
     if (vec4) {
-        using Stream4 = ChunkSummaryStream<2, 3, 4>;  // 36 KB of rings per block
-        const long long tasks = (long long)pl.s.B * pl.s.N * pl.s.G;
-        rc = launch<Stream4>(p, (tasks + 3) / 4, st);
+        // 16 steps per warp, four warps per block: one map per 64 steps (never more maps than
+        // the three-phase plan, whose workspace bound therefore still holds)
+        using Stream4 = ChunkSummaryStream<2, 3, 4>;
+        p.s.ts = 16;
+        p.s.N = (L + 63) / 64;
+        p.s.G = (C + 127) / 128;
+        pl.s = p.s;
+        rc = launch<Stream4>(p, (long long)B * p.s.N * p.s.G, st);
     } else {
         rc = launch<FwdSummary<1, 4>>(p, tile_blocks(pl.s), st);
     }
