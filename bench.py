@@ -41,6 +41,9 @@ BYTES_PER_TOKEN = BYTES_PER_TOKEN_FWD + BYTES_PER_TOKEN_BWD
 FP32_TOL, BF16_TOL = 1e-5, 2e-2
 KERNEL_LAUNCHES_PER_STEP = 3   # single-pass forward 1 + backward 2 (sweeps, parameter-gradient reduce)
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per step from the ncu capture of this workload
+# (forward 102.2 + 134.2 MB, backward 317.6 + 100.7 MB; writes still in L2 at kernel end counted in full)
+NCU_DRAM_BYTES_PER_STEP = 654.7e6
 LONG_L = 65536
 
 
@@ -405,7 +408,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "config": workload_config(world),
         "roofline": {
             "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-            "frac": achieved / peak, "traffic": None, "peak_source": f"of {peak_kind}",
+            "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_PER_STEP,
+            "traffic_source": "ncu dram__bytes_read+write of the two single-pass kernels, "
+                              "profiles/single_pass_fwd_bwd_8x2048_ncu.md",
+            "peak_source": f"of {peak_kind}",
             "kernel": "whole step per GPU: FwdSinglePass + BwdSinglePass + BwdReduce (+2 workspace fills)",
             "algorithmic_bytes_per_token": BYTES_PER_TOKEN,
             "forward": {"ms": ms_fwd, "achieved": fwd_gbs, "frac": fwd_gbs / peak},
