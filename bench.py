@@ -254,6 +254,56 @@ class DirectOp:
         return self.lib.fields_read_device_status(self.wsf.data_ptr(), self.stream)
 
 
+DECODE_BATCH, DECODE_BLOCKS = 256, 18
+DECODE_BYTES_PER_SEQ_BLOCK = 2 * (2 * C * 4) + 3 * C * 2 + 4 * C * 2   # state r+w, bf16 raw, bf16 read
+
+
+def decode_leg(device, tr, ti, gamma, peak_gbs: float, iters: int = 200):
+    from fields_lm_b200 import _lib
+    lib = _lib.load()
+    gen = torch.Generator().manual_seed(3)
+    raws = [torch.randn(DECODE_BATCH, 3 * C, generator=gen).to(device).bfloat16()
+            for _ in range(DECODE_BLOCKS)]
+    states = [torch.randn(DECODE_BATCH, 2 * C, generator=gen).to(device) for _ in range(DECODE_BLOCKS)]
+    reads = [torch.empty(DECODE_BATCH, 4 * C, device=device, dtype=torch.bfloat16)
+             for _ in range(DECODE_BLOCKS)]
+
+    def token_step():
+        st = torch.cuda.current_stream(device).cuda_stream
+        for raw, state, read in zip(raws, states, reads):
+            rc = lib.fields_read_step_bf16(raw.data_ptr(), tr.data_ptr(), ti.data_ptr(),
+                                           gamma.data_ptr(), state.data_ptr(), read.data_ptr(),
+                                           DECODE_BATCH, C, st)
+            if rc:
+                raise RuntimeError(f"fields_read_step_bf16 status {rc}")
+
+    stream = torch.cuda.current_stream(device)
+    for _ in range(5):
+        token_step()
+    ms_plain = timed_loop(token_step, iters, stream) / iters
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(device)
+    side.wait_stream(stream)
+    with torch.cuda.stream(side):
+        token_step()
+    stream.wait_stream(side)
+    with torch.cuda.graph(graph):
+        token_step()
+    for _ in range(5):
+        graph.replay()
+    ms_graph = timed_loop(graph.replay, iters, stream) / iters
+    nbytes = DECODE_BATCH * DECODE_BLOCKS * DECODE_BYTES_PER_SEQ_BLOCK
+
+    def gbs(ms):
+        return nbytes / (ms * 1e-3) / 1e9
+    return {"workload": f"one token x {DECODE_BATCH} sequences x {DECODE_BLOCKS} Field recurrences, "
+                        "bf16 rows, fp32 states",
+            "bytes_per_token_step": nbytes,
+            "plain": {"ms": ms_plain, "achieved": gbs(ms_plain), "frac": gbs(ms_plain) / peak_gbs},
+            "cuda_graph": {"ms": ms_graph, "achieved": gbs(ms_graph), "frac": gbs(ms_graph) / peak_gbs},
+            "note": "3.9 MB per launch: launch-latency scale, far below what HBM could move"}
+
+
 def timed_loop(fn, steps: int, stream) -> float:
     """Milliseconds for `steps` calls of fn, CUDA events on the launching stream."""
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -371,6 +421,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     barrier(dist_on)
     del long_raw
 
+    # decode (BASELINE config 5): one token for 256 sequences through the recurrences of 18 Field
+    # blocks, bf16 rows, fp32 carried states; plain launches and one CUDA graph of the 18 launches
+    decode = decode_leg(device, tr_d, ti_d, gm_d, peak_gbs=measured_peaks()[0]) if not dist_on else None
+
     # end to end: pinned host -> device, forward + backward, results back to pinned host
     raw_pin, grad_pin = raw_h.pin_memory(), grad_h.pin_memory()
     read_pin = torch.empty(B, L, 4 * C).pin_memory()
@@ -431,6 +485,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                         "ms": ms_long, "tokens_per_s": LONG_L / (ms_long * 1e-3),
                         "achieved": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9,
                         "frac": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9 / (peak * world)},
+        "decode_step": decode,
         "gpu_launches": KERNEL_LAUNCHES_PER_STEP * args.steps,
         "clocks": clocks.summary(),
         "parity": parity_check(device, tr.detach(), ti.detach(), gamma.detach()),
