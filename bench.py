@@ -254,6 +254,36 @@ class DirectOp:
         return self.lib.fields_read_device_status(self.wsf.data_ptr(), self.stream)
 
 
+def bf16_leg(device, raw, grad_read, tr, ti, gamma, steps, stream):
+    """Forward + backward through fields_read_*_bf16 on preallocated buffers (17,408 B/token)."""
+    from fields_lm_b200 import _lib
+    lib = _lib.load()
+    raw16, grad16 = raw.bfloat16(), grad_read.bfloat16()
+    read16 = torch.empty(B, L, 4 * C, device=device, dtype=torch.bfloat16)
+    graw16 = torch.empty(B, L, 3 * C, device=device, dtype=torch.bfloat16)
+    gpar = torch.empty(3, C, device=device)
+    nf = lib.fields_read_workspace_bytes(B, L, C, 0)
+    nb = lib.fields_read_workspace_bytes(B, L, C, 1)
+    ws = torch.empty(max(nf, nb, 256), dtype=torch.uint8, device=device)
+    st = stream.cuda_stream
+
+    def step():
+        rc = lib.fields_read_forward_bf16(raw16.data_ptr(), tr.data_ptr(), ti.data_ptr(),
+                                          gamma.data_ptr(), None, read16.data_ptr(), None,
+                                          ws.data_ptr(), nf, B, L, C, st)
+        rc = rc or lib.fields_read_backward_bf16(
+            raw16.data_ptr(), tr.data_ptr(), ti.data_ptr(), gamma.data_ptr(), None,
+            read16.data_ptr(), grad16.data_ptr(), None, graw16.data_ptr(), gpar[0].data_ptr(),
+            gpar[1].data_ptr(), gpar[2].data_ptr(), None, ws.data_ptr(), nb, B, L, C, st)
+        if rc:
+            raise RuntimeError(f"bf16 step status {rc}")
+    for _ in range(3):
+        step()
+    ms = timed_loop(step, steps, stream) / steps
+    return {"workload": "same step with bfloat16 raw/read/grad_read/grad_raw, fp32 state",
+            "ms_per_step": ms, "algorithmic_bytes_per_token": BYTES_PER_TOKEN // 2}
+
+
 DECODE_BATCH, DECODE_BLOCKS = 256, 18
 DECODE_BYTES_PER_SEQ_BLOCK = 2 * (2 * C * 4) + 3 * C * 2 + 4 * C * 2   # state r+w, bf16 raw, bf16 read
 
@@ -421,6 +451,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     barrier(dist_on)
     del long_raw
 
+    # the same step on the bfloat16 boundary (raw, read and their gradients in bf16, fp32 state)
+    bf16 = bf16_leg(device, raw_d, grad_read, tr_d, ti_d, gm_d, args.steps, stream)
+
     # decode (BASELINE config 5): one token for 256 sequences through the recurrences of 18 Field
     # blocks, bf16 rows, fp32 carried states; plain launches and one CUDA graph of the 18 launches
     decode = decode_leg(device, tr_d, ti_d, gm_d, peak_gbs=measured_peaks()[0]) if not dist_on else None
@@ -485,6 +518,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                         "ms": ms_long, "tokens_per_s": LONG_L / (ms_long * 1e-3),
                         "achieved": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9,
                         "frac": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9 / (peak * world)},
+        "bf16_io": {**bf16, "achieved": B * L * BYTES_PER_TOKEN / 2 / (bf16["ms_per_step"] * 1e-3) / 1e9,
+                    "frac": B * L * BYTES_PER_TOKEN / 2 / (bf16["ms_per_step"] * 1e-3) / 1e9 / peak,
+                    "tokens_per_s": world * B * L / (bf16["ms_per_step"] * 1e-3)},
         "decode_step": decode,
         "gpu_launches": KERNEL_LAUNCHES_PER_STEP * args.steps,
         "clocks": clocks.summary(),

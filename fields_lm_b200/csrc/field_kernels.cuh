@@ -654,30 +654,6 @@ struct FoldSummaries {
 // incremental path, its full-sequence forward over prefix + new tokens is the oracle.
 // IO = float or bf16 bits (uint16_t) for raw and read; the state is always fp32.
 // ---------------------------------------------------------------------------
-FL_HD float bf16_bits_to_float(uint16_t h) {
-    const uint32_t u = (uint32_t)h << 16;
-    float f;
-#if FL_DEVICE_CODE
-    f = __uint_as_float(u);
-#else
-    std::memcpy(&f, &u, 4);
-#endif
-    return f;
-}
-
-// round to nearest even; NaN stays NaN
-FL_HD uint16_t float_to_bf16_bits(float f) {
-    uint32_t u;
-#if FL_DEVICE_CODE
-    u = __float_as_uint(f);
-#else
-    std::memcpy(&u, &f, 4);
-#endif
-    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u);
-    u += 0x7fffu + ((u >> 16) & 1u);
-    return (uint16_t)(u >> 16);
-}
-
 FL_HD float io_load(const float* p, size_t i) { return p[i]; }
 FL_HD float io_load(const uint16_t* p, size_t i) { return bf16_bits_to_float(p[i]); }
 FL_HD void io_store(float* p, size_t i, float v) { p[i] = v; }

@@ -164,6 +164,79 @@ FL_HD void vec_store_stream(float* p, const Vec<V>& x) {
 }
 
 // ---------------------------------------------------------------------------
+// bfloat16 as raw bits (uint16_t): conversions that work on host and device alike, and
+// 4-element vector I/O for both element types (float: 16 bytes, bf16: 8 bytes per access).
+// ---------------------------------------------------------------------------
+FL_HD float bf16_bits_to_float(uint16_t h) {
+    const uint32_t u = (uint32_t)h << 16;
+    float f;
+#if FL_DEVICE_CODE
+    f = __uint_as_float(u);
+#else
+    std::memcpy(&f, &u, 4);
+#endif
+    return f;
+}
+
+// round to nearest even; NaN stays NaN
+FL_HD uint16_t float_to_bf16_bits(float f) {
+    uint32_t u;
+#if FL_DEVICE_CODE
+    u = __float_as_uint(f);
+#else
+    std::memcpy(&u, &f, 4);
+#endif
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+
+
+FL_HD Vec<4> io_load4(const float* p) { return vec_load<4>(p); }
+FL_HD Vec<4> io_load4_stream(const float* p) { return vec_load_stream<4>(p); }
+FL_HD void io_store4_stream(float* p, const Vec<4>& x) { vec_store_stream<4>(p, x); }
+
+FL_HD Vec<4> bf16x4_unpack(uint32_t lo, uint32_t hi) {
+    Vec<4> r;
+    r.v[0] = bf16_bits_to_float((uint16_t)(lo & 0xffffu));
+    r.v[1] = bf16_bits_to_float((uint16_t)(lo >> 16));
+    r.v[2] = bf16_bits_to_float((uint16_t)(hi & 0xffffu));
+    r.v[3] = bf16_bits_to_float((uint16_t)(hi >> 16));
+    return r;
+}
+
+FL_HD Vec<4> io_load4(const uint16_t* p) {
+#if FL_DEVICE_CODE
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    return bf16x4_unpack(t.x, t.y);
+#else
+    uint32_t w[2];
+    std::memcpy(w, p, 8);
+    return bf16x4_unpack(w[0], w[1]);
+#endif
+}
+
+FL_HD Vec<4> io_load4_stream(const uint16_t* p) {
+#if FL_DEVICE_CODE
+    const uint2 t = __ldcs(reinterpret_cast<const uint2*>(p));
+    return bf16x4_unpack(t.x, t.y);
+#else
+    return io_load4(p);
+#endif
+}
+
+FL_HD void io_store4_stream(uint16_t* p, const Vec<4>& x) {
+    const uint32_t lo = (uint32_t)float_to_bf16_bits(x.v[0]) | ((uint32_t)float_to_bf16_bits(x.v[1]) << 16);
+    const uint32_t hi = (uint32_t)float_to_bf16_bits(x.v[2]) | ((uint32_t)float_to_bf16_bits(x.v[3]) << 16);
+#if FL_DEVICE_CODE
+    __stcs(reinterpret_cast<uint2*>(p), make_uint2(lo, hi));
+#else
+    const uint32_t w[2] = {lo, hi};
+    std::memcpy(p, w, 8);
+#endif
+}
+
+// ---------------------------------------------------------------------------
 // Per-channel gate values of one time step.
 // ---------------------------------------------------------------------------
 struct Gate {

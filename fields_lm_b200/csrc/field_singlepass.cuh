@@ -43,32 +43,37 @@ struct SpShape {
 };
 
 // Prefetches `planes` consecutive 128-channel plane chunks of `steps` rows into L2:
-// row r, plane q is the 512 bytes at base + r * row_floats + q * plane_floats.
-FL_HD void prefetch_rows(const float* base, int steps, int valid_steps, int planes, size_t row_floats,
+// row r, plane q is the 128 elements at base + r * row_floats + q * plane_floats.
+template <typename T>
+FL_HD void prefetch_rows(const T* base, int steps, int valid_steps, int planes, size_t row_floats,
                          size_t plane_floats, int valid_floats, int thread, int threads) {
-    const int lines = steps * planes * 4;  // 4 lines of 128 bytes per chunk
+    constexpr int kPerLine = 128 / (int)sizeof(T);   // elements per 128-byte line
+    constexpr int kLines = 128 / kPerLine;           // lines per 128-channel chunk
+    const int lines = steps * planes * kLines;
     for (int q = thread; q < lines; q += threads) {
-        const int t = q / (planes * 4);
-        const int r = q % (planes * 4);
-        const int plane = r >> 2, line = r & 3;
-        if (t < valid_steps && line * 32 < valid_floats)
-            prefetch_l2(base + (size_t)t * row_floats + (size_t)plane * plane_floats + line * 32);
+        const int t = q / (planes * kLines);
+        const int r = q % (planes * kLines);
+        const int plane = r / kLines, line = r % kLines;
+        if (t < valid_steps && line * kPerLine < valid_floats)
+            prefetch_l2(base + (size_t)t * row_floats + (size_t)plane * plane_floats + line * kPerLine);
     }
 }
 
-struct SpFwdParams {
-    const float* raw;
+template <typename IO>
+struct SpFwdParamsT {
+    const IO* raw;
     const float* tr;
     const float* ti;
     const float* gamma;
     const float* state_in;  // [B, 2C] or null
-    float* read;
+    IO* read;
     float* state_out;       // [B, 2C] or null
     float* agg;             // [tiles][128][4]  tile maps (Re A, Im A, Re B, Im B)
     float* incl;            // [tiles][128][2]  state after each tile
     unsigned* ctrl;         // error word; filled with 0xFF like the slots before the launch
     SpShape s;
 };
+using SpFwdParams = SpFwdParamsT<float>;
 
 struct SpTile {
     int b, cg, n;        // batch row, channel group, position in scan order
@@ -87,9 +92,10 @@ FL_HD SpTile sp_decode(const SpShape& s, unsigned ticket) {
     return t;
 }
 
-template <int TS, int WARPS, int MIN_BLOCKS>
+// IO = float, or uint16_t for bfloat16 raw / read (the state, the maps and all arithmetic stay fp32).
+template <int TS, int WARPS, int MIN_BLOCKS, typename IO = float>
 struct FwdSinglePass {
-    using Params = SpFwdParams;
+    using Params = SpFwdParamsT<IO>;
     static constexpr int kThreads = 32 * WARPS;
     static constexpr int kMinBlocks = MIN_BLOCKS;  // blocks per SM the register budget must allow
     static constexpr int kTile = TS * WARPS;
@@ -137,14 +143,14 @@ struct FwdSinglePass {
                 const Vec<4> lr = vec_load<4>(p.tr + c0);
                 const Vec<4> li = vec_load<4>(p.ti + c0);
                 const Vec<4> gm = vec_load<4>(p.gamma + c0);
-                const float* base = p.raw + ((size_t)tl.b * s.L) * 3 * C + c0;
+                const IO* base = p.raw + ((size_t)tl.b * s.L) * 3 * C + c0;
 #pragma unroll
                 for (int u = 0; u < TS; ++u) {
                     if (tw + u < s.L) {
-                        const float* row = base + (size_t)(tw + u) * 3 * C;
-                        st.br[u] = vec_load_stream<4>(row);
-                        st.bi[u] = vec_load_stream<4>(row + C);
-                        st.vac[u] = vec_load_stream<4>(row + 2 * C);
+                        const IO* row = base + (size_t)(tw + u) * 3 * C;
+                        st.br[u] = io_load4_stream(row);
+                        st.bi[u] = io_load4_stream(row + C);
+                        st.vac[u] = io_load4_stream(row + 2 * C);
                     }
                 }
 #pragma unroll
@@ -214,7 +220,7 @@ struct FwdSinglePass {
             const Vec<4> li = vec_load<4>(p.ti + c0);
             Vec<4> sr = vec_load<4>(carry_at(smem, warp, 0) + lane * 4);
             Vec<4> si = vec_load<4>(carry_at(smem, warp, 1) + lane * 4);
-            float* obase = p.read + ((size_t)tl.b * s.L) * 4 * C + c0;
+            IO* obase = p.read + ((size_t)tl.b * s.L) * 4 * C + c0;
 #pragma unroll
             for (int u = 0; u < TS; ++u) {
                 if (tw + u < s.L) {
@@ -229,11 +235,11 @@ struct FwdSinglePass {
                         sr.v[k] = (1.0f - v) * mr + st.br[u].v[k];
                         si.v[k] = (1.0f - v) * mi + st.bi[u].v[k];
                     }
-                    float* orow = obase + (size_t)(tw + u) * 4 * C;
-                    vec_store_stream<4>(orow, sr);
-                    vec_store_stream<4>(orow + C, si);
-                    vec_store_stream<4>(orow + 2 * C, dr);
-                    vec_store_stream<4>(orow + 3 * C, di);
+                    IO* orow = obase + (size_t)(tw + u) * 4 * C;
+                    io_store4_stream(orow, sr);
+                    io_store4_stream(orow + C, si);
+                    io_store4_stream(orow + 2 * C, dr);
+                    io_store4_stream(orow + 3 * C, di);
                 }
             }
         }
@@ -258,16 +264,17 @@ struct FwdSinglePass {
 //            tile; BwdReduce adds the rows.
 // HBM traffic per channel-step: 20 B (sweep 1) + 16 B (z_r, z_i, s_{t-1}) + 12 B written.
 // ---------------------------------------------------------------------------
-struct SpBwdParams {
-    const float* raw;
+template <typename IO>
+struct SpBwdParamsT {
+    const IO* raw;
     const float* tr;
     const float* ti;
     const float* gamma;
     const float* state_in;        // [B, 2C] or null
-    const float* read;            // saved forward output
-    const float* grad_read;
+    const IO* read;               // saved forward output
+    const IO* grad_read;
     const float* grad_state_out;  // [B, 2C] or null
-    float* grad_raw;
+    IO* grad_raw;
     float* grad_state_in;         // [B, 2C] or null
     float* agg;                   // [tiles][128][4]
     float* incl;                  // [tiles][128][2]
@@ -275,10 +282,12 @@ struct SpBwdParams {
     float* partial;               // [3][B][NT][C]
     SpShape s;
 };
+using SpBwdParams = SpBwdParamsT<float>;
 
-template <int TS, int WARPS, int U1_, int U2_, int MIN_BLOCKS, bool ASYNC = false, int STAGES = 2>
+template <int TS, int WARPS, int U1_, int U2_, int MIN_BLOCKS, bool ASYNC = false, int STAGES = 2,
+          typename IO = float>
 struct BwdSinglePass {
-    using Params = SpBwdParams;
+    using Params = SpBwdParamsT<IO>;
     static constexpr int kThreads = 32 * WARPS;
     static constexpr int kMinBlocks = MIN_BLOCKS;
     static constexpr int kTile = TS * WARPS;
@@ -353,20 +362,20 @@ struct BwdSinglePass {
             if (chan_ok) {
                 const Vec<4> lr = vec_load<4>(p.tr + c0);
                 const Vec<4> li = vec_load<4>(p.ti + c0);
-                const float* zbase = p.raw + ((size_t)tl.b * s.L) * 3 * C + 2 * C + c0;
-                const float* gbase = p.grad_read + ((size_t)tl.b * s.L) * 4 * C + c0;
+                const IO* zbase = p.raw + ((size_t)tl.b * s.L) * 3 * C + 2 * C + c0;
+                const IO* gbase = p.grad_read + ((size_t)tl.b * s.L) * 4 * C + c0;
                 // batch of U1 steps ending just before t0, into ring slot `stage`
                 auto issue1 = [&](int t0, int stage) {
 #pragma unroll
                     for (int u = 0; u < U1; ++u) {
                         const int t = t0 - 1 - u;
                         if (t >= tbeg) {
-                            const float* grow = gbase + (size_t)t * 4 * C;
-                            async_copy16(cell_at(smem, stage, u * 5 + 0, thread), zbase + (size_t)t * 3 * C);
-                            async_copy16(cell_at(smem, stage, u * 5 + 1, thread), grow);
-                            async_copy16(cell_at(smem, stage, u * 5 + 2, thread), grow + C);
-                            async_copy16(cell_at(smem, stage, u * 5 + 3, thread), grow + 2 * C);
-                            async_copy16(cell_at(smem, stage, u * 5 + 4, thread), grow + 3 * C);
+                            const IO* grow = gbase + (size_t)t * 4 * C;
+                            async_copy4(cell_at(smem, stage, u * 5 + 0, thread), zbase + (size_t)t * 3 * C);
+                            async_copy4(cell_at(smem, stage, u * 5 + 1, thread), grow);
+                            async_copy4(cell_at(smem, stage, u * 5 + 2, thread), grow + C);
+                            async_copy4(cell_at(smem, stage, u * 5 + 3, thread), grow + 2 * C);
+                            async_copy4(cell_at(smem, stage, u * 5 + 4, thread), grow + 3 * C);
                         }
                     }
                     async_commit();
@@ -384,11 +393,11 @@ struct BwdSinglePass {
 #pragma unroll
                         for (int u = 0; u < U1; ++u) {
                             if (t0 - 1 - u >= tbeg) {
-                                zv[u] = vec_load<4>(cell_at(smem, stage, u * 5 + 0, thread));
-                                ur[u] = vec_load<4>(cell_at(smem, stage, u * 5 + 1, thread));
-                                ui[u] = vec_load<4>(cell_at(smem, stage, u * 5 + 2, thread));
-                                gr[u] = vec_load<4>(cell_at(smem, stage, u * 5 + 3, thread));
-                                gi[u] = vec_load<4>(cell_at(smem, stage, u * 5 + 4, thread));
+                                zv[u] = cell_load4<IO>(cell_at(smem, stage, u * 5 + 0, thread));
+                                ur[u] = cell_load4<IO>(cell_at(smem, stage, u * 5 + 1, thread));
+                                ui[u] = cell_load4<IO>(cell_at(smem, stage, u * 5 + 2, thread));
+                                gr[u] = cell_load4<IO>(cell_at(smem, stage, u * 5 + 3, thread));
+                                gi[u] = cell_load4<IO>(cell_at(smem, stage, u * 5 + 4, thread));
                             }
                         }
                     } else {
@@ -396,12 +405,12 @@ struct BwdSinglePass {
                     for (int u = 0; u < U1; ++u) {
                         const int t = t0 - 1 - u;
                         if (t >= tbeg) {
-                            zv[u] = vec_load<4>(zbase + (size_t)t * 3 * C);
-                            const float* grow = gbase + (size_t)t * 4 * C;
-                            ur[u] = vec_load<4>(grow);
-                            ui[u] = vec_load<4>(grow + C);
-                            gr[u] = vec_load<4>(grow + 2 * C);
-                            gi[u] = vec_load<4>(grow + 3 * C);
+                            zv[u] = io_load4(zbase + (size_t)t * 3 * C);
+                            const IO* grow = gbase + (size_t)t * 4 * C;
+                            ur[u] = io_load4(grow);
+                            ui[u] = io_load4(grow + C);
+                            gr[u] = io_load4(grow + 2 * C);
+                            gi[u] = io_load4(grow + 3 * C);
                         }
                     }
                     }
@@ -473,28 +482,28 @@ struct BwdSinglePass {
                 const Vec<4> gm = vec_load<4>(p.gamma + c0);
                 Vec<4> cr = vec_load<4>(carry_at(smem, slot, 0) + lane * 4);
                 Vec<4> ci = vec_load<4>(carry_at(smem, slot, 1) + lane * 4);
-                const float* zbase = p.raw + ((size_t)tl.b * s.L) * 3 * C + c0;
-                const float* gbase = p.grad_read + ((size_t)tl.b * s.L) * 4 * C + c0;
-                const float* rbase = p.read + ((size_t)tl.b * s.L) * 4 * C + c0;
-                float* obase = p.grad_raw + ((size_t)tl.b * s.L) * 3 * C + c0;
+                const IO* zbase = p.raw + ((size_t)tl.b * s.L) * 3 * C + c0;
+                const IO* gbase = p.grad_read + ((size_t)tl.b * s.L) * 4 * C + c0;
+                const IO* rbase = p.read + ((size_t)tl.b * s.L) * 4 * C + c0;
+                IO* obase = p.grad_raw + ((size_t)tl.b * s.L) * 3 * C + c0;
                 auto issue2 = [&](int t0, int stage) {
 #pragma unroll
                     for (int u = 0; u < U2; ++u) {
                         const int t = t0 - 1 - u;
                         if (t >= tbeg) {
-                            const float* zrow = zbase + (size_t)t * 3 * C;
-                            const float* grow = gbase + (size_t)t * 4 * C;
-                            async_copy16(cell_at(smem, stage, u * 9 + 0, thread), zrow);
-                            async_copy16(cell_at(smem, stage, u * 9 + 1, thread), zrow + C);
-                            async_copy16(cell_at(smem, stage, u * 9 + 2, thread), zrow + 2 * C);
-                            async_copy16(cell_at(smem, stage, u * 9 + 3, thread), grow);
-                            async_copy16(cell_at(smem, stage, u * 9 + 4, thread), grow + C);
-                            async_copy16(cell_at(smem, stage, u * 9 + 5, thread), grow + 2 * C);
-                            async_copy16(cell_at(smem, stage, u * 9 + 6, thread), grow + 3 * C);
+                            const IO* zrow = zbase + (size_t)t * 3 * C;
+                            const IO* grow = gbase + (size_t)t * 4 * C;
+                            async_copy4(cell_at(smem, stage, u * 9 + 0, thread), zrow);
+                            async_copy4(cell_at(smem, stage, u * 9 + 1, thread), zrow + C);
+                            async_copy4(cell_at(smem, stage, u * 9 + 2, thread), zrow + 2 * C);
+                            async_copy4(cell_at(smem, stage, u * 9 + 3, thread), grow);
+                            async_copy4(cell_at(smem, stage, u * 9 + 4, thread), grow + C);
+                            async_copy4(cell_at(smem, stage, u * 9 + 5, thread), grow + 2 * C);
+                            async_copy4(cell_at(smem, stage, u * 9 + 6, thread), grow + 3 * C);
                             if (t > 0) {
-                                const float* prow = rbase + (size_t)(t - 1) * 4 * C;
-                                async_copy16(cell_at(smem, stage, u * 9 + 7, thread), prow);
-                                async_copy16(cell_at(smem, stage, u * 9 + 8, thread), prow + C);
+                                const IO* prow = rbase + (size_t)(t - 1) * 4 * C;
+                                async_copy4(cell_at(smem, stage, u * 9 + 7, thread), prow);
+                                async_copy4(cell_at(smem, stage, u * 9 + 8, thread), prow + C);
                             }
                         }
                     }
@@ -514,16 +523,16 @@ struct BwdSinglePass {
                         for (int u = 0; u < U2; ++u) {
                             const int t = t0 - 1 - u;
                             if (t >= tbeg) {
-                                zr[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 0, thread));
-                                zi[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 1, thread));
-                                zv[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 2, thread));
-                                ur[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 3, thread));
-                                ui[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 4, thread));
-                                gr[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 5, thread));
-                                gi[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 6, thread));
+                                zr[u] = cell_load4<IO>(cell_at(smem, stage, u * 9 + 0, thread));
+                                zi[u] = cell_load4<IO>(cell_at(smem, stage, u * 9 + 1, thread));
+                                zv[u] = cell_load4<IO>(cell_at(smem, stage, u * 9 + 2, thread));
+                                ur[u] = cell_load4<IO>(cell_at(smem, stage, u * 9 + 3, thread));
+                                ui[u] = cell_load4<IO>(cell_at(smem, stage, u * 9 + 4, thread));
+                                gr[u] = cell_load4<IO>(cell_at(smem, stage, u * 9 + 5, thread));
+                                gi[u] = cell_load4<IO>(cell_at(smem, stage, u * 9 + 6, thread));
                                 if (t > 0) {
-                                    pr[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 7, thread));
-                                    pi[u] = vec_load<4>(cell_at(smem, stage, u * 9 + 8, thread));
+                                    pr[u] = cell_load4<IO>(cell_at(smem, stage, u * 9 + 7, thread));
+                                    pi[u] = cell_load4<IO>(cell_at(smem, stage, u * 9 + 8, thread));
                                 } else if (p.state_in) {
                                     const float* prow = p.state_in + (size_t)tl.b * 2 * C + c0;
                                     pr[u] = vec_load<4>(prow);
@@ -539,19 +548,19 @@ struct BwdSinglePass {
                     for (int u = 0; u < U2; ++u) {
                         const int t = t0 - 1 - u;
                         if (t >= tbeg) {
-                            const float* zrow = zbase + (size_t)t * 3 * C;
-                            zr[u] = vec_load_stream<4>(zrow);
-                            zi[u] = vec_load_stream<4>(zrow + C);
-                            zv[u] = vec_load_stream<4>(zrow + 2 * C);
-                            const float* grow = gbase + (size_t)t * 4 * C;
-                            ur[u] = vec_load_stream<4>(grow);
-                            ui[u] = vec_load_stream<4>(grow + C);
-                            gr[u] = vec_load_stream<4>(grow + 2 * C);
-                            gi[u] = vec_load_stream<4>(grow + 3 * C);
+                            const IO* zrow = zbase + (size_t)t * 3 * C;
+                            zr[u] = io_load4_stream(zrow);
+                            zi[u] = io_load4_stream(zrow + C);
+                            zv[u] = io_load4_stream(zrow + 2 * C);
+                            const IO* grow = gbase + (size_t)t * 4 * C;
+                            ur[u] = io_load4_stream(grow);
+                            ui[u] = io_load4_stream(grow + C);
+                            gr[u] = io_load4_stream(grow + 2 * C);
+                            gi[u] = io_load4_stream(grow + 3 * C);
                             if (t > 0) {
-                                const float* prow = rbase + (size_t)(t - 1) * 4 * C;
-                                pr[u] = vec_load_stream<4>(prow);
-                                pi[u] = vec_load_stream<4>(prow + C);
+                                const IO* prow = rbase + (size_t)(t - 1) * 4 * C;
+                                pr[u] = io_load4_stream(prow);
+                                pi[u] = io_load4_stream(prow + C);
                             } else if (p.state_in) {
                                 const float* prow = p.state_in + (size_t)tl.b * 2 * C + c0;
                                 pr[u] = vec_load<4>(prow);
@@ -596,10 +605,10 @@ struct BwdSinglePass {
                                 ozv.v[k] = dv * (g.vac - g.vac * g.sig);
                                 cmul_conj(lr.v[k], li.v[k], Hr, Hi, cr.v[k], ci.v[k]);
                             }
-                            float* orow = obase + (size_t)t * 3 * C;
-                            vec_store_stream<4>(orow, ozr);
-                            vec_store_stream<4>(orow + C, ozi);
-                            vec_store_stream<4>(orow + 2 * C, ozv);
+                            IO* orow = obase + (size_t)t * 3 * C;
+                            io_store4_stream(orow, ozr);
+                            io_store4_stream(orow + C, ozi);
+                            io_store4_stream(orow + 2 * C, ozv);
                         }
                     }
                 }

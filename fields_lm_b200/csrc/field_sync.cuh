@@ -93,6 +93,35 @@ FL_HD void async_copy16(float* smem_dst, const float* gmem_src) {
 #endif
 }
 
+// Four elements (16 bytes of float, 8 bytes of bf16) into a 16-byte shared-memory cell.
+FL_HD void async_copy4(float* cell, const float* src) { async_copy16(cell, src); }
+
+FL_HD void async_copy4(float* cell, const uint16_t* src) {
+#if FL_DEVICE_CODE
+    const unsigned saddr = (unsigned)__cvta_generic_to_shared(cell);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(saddr), "l"(src) : "memory");
+#else
+    std::memcpy(cell, src, 8);
+#endif
+}
+
+// Reads back a cell filled by async_copy4 from a source of element type IO.
+template <typename IO>
+FL_HD Vec<4> cell_load4(const float* cell) {
+    if constexpr (sizeof(IO) == 4) {
+        return vec_load<4>(cell);
+    } else {
+#if FL_DEVICE_CODE
+        const uint2 w = *reinterpret_cast<const uint2*>(cell);
+        return bf16x4_unpack(w.x, w.y);
+#else
+        uint32_t w[2];
+        std::memcpy(w, cell, 8);
+        return bf16x4_unpack(w[0], w[1]);
+#endif
+    }
+}
+
 FL_HD void async_commit() {
 #if FL_DEVICE_CODE
     asm volatile("cp.async.commit_group;" ::: "memory");

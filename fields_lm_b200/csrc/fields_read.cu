@@ -388,6 +388,9 @@ using BwdSp9 = BwdSinglePass<8, 4, 1, 1, 3, true, 3>;   // 3-slot rings, one ste
 using BwdSp10 = BwdSinglePass<8, 4, 2, 1, 5>;   // direct loads, 96 registers, 20 warps per SM
 using BwdSp11 = BwdSinglePass<8, 4, 1, 1, 4, true, 2>;  // 2-slot rings, one step per batch
 using BwdSp12 = BwdSinglePass<8, 8, 2, 1, 2, true, 2>;  // 8 warps per block
+//   bfloat16 raw / read / grad_read / grad_raw (bits as uint16_t); state and arithmetic stay fp32
+using FwdSpBf16 = FwdSinglePass<6, 8, 2, uint16_t>;
+using BwdSpBf16 = BwdSinglePass<8, 4, 2, 1, 3, true, 3, uint16_t>;
 constexpr int kSpMinTile = 32;  // smallest time tile of any instantiation above (workspace bound)
 
 static int variant_from_env(const char* name) {
@@ -404,9 +407,9 @@ static int prefetch_from_env(int resident) {
     return v == 1 ? resident : (v > 1 ? v : 0);
 }
 
-template <class K>
-static int run_forward_single_pass(const float* raw, const float* tr, const float* ti,
-                                   const float* gamma, const float* state_in, float* read,
+template <class K, typename IO = float>
+static int run_forward_single_pass(const IO* raw, const float* tr, const float* ti,
+                                   const float* gamma, const float* state_in, IO* read,
                                    float* state_out, void* workspace, int B, int L, int C,
                                    Stream st) {
     SpPlan pl = make_sp_plan(B, L, C, K::kTile);
@@ -415,17 +418,17 @@ static int run_forward_single_pass(const float* raw, const float* tr, const floa
     unsigned* ctrl = reinterpret_cast<unsigned*>(ws);
     int rc = fill_unset(ws, pl.bytes, st);  // error word and every publication slot
     if (rc) return rc;
-    SpFwdParams p{raw, tr, ti, gamma, state_in, read, state_out,
-                  reinterpret_cast<float*>(ws + pl.agg_off),
-                  reinterpret_cast<float*>(ws + pl.incl_off), ctrl, pl.s};
+    SpFwdParamsT<IO> p{raw, tr, ti, gamma, state_in, read, state_out,
+                       reinterpret_cast<float*>(ws + pl.agg_off),
+                       reinterpret_cast<float*>(ws + pl.incl_off), ctrl, pl.s};
     return launch_stateful<K>(p, pl.tiles, FIELDS_STATEFUL_ARG(K, B, pl), st);
 }
 
-template <class K>
-static int run_backward_single_pass(const float* raw, const float* tr, const float* ti,
-                                    const float* gamma, const float* state_in, const float* read,
-                                    const float* grad_read, const float* grad_state_out,
-                                    float* grad_raw, float* grad_tr, float* grad_ti,
+template <class K, typename IO = float>
+static int run_backward_single_pass(const IO* raw, const float* tr, const float* ti,
+                                    const float* gamma, const float* state_in, const IO* read,
+                                    const IO* grad_read, const float* grad_state_out,
+                                    IO* grad_raw, float* grad_tr, float* grad_ti,
                                     float* grad_gamma, float* grad_state_in, void* workspace,
                                     int B, int L, int C, Stream st) {
     SpPlan pl = make_sp_plan(B, L, C, K::kTile);
@@ -435,9 +438,9 @@ static int run_backward_single_pass(const float* raw, const float* tr, const flo
     int rc = fill_unset(ws, pl.bytes, st);
     if (rc) return rc;
     float* partial = reinterpret_cast<float*>(ws + pl.bytes);
-    SpBwdParams p{raw, tr, ti, gamma, state_in, read, grad_read, grad_state_out, grad_raw,
-                  grad_state_in, reinterpret_cast<float*>(ws + pl.agg_off),
-                  reinterpret_cast<float*>(ws + pl.incl_off), ctrl, partial, pl.s};
+    SpBwdParamsT<IO> p{raw, tr, ti, gamma, state_in, read, grad_read, grad_state_out, grad_raw,
+                       grad_state_in, reinterpret_cast<float*>(ws + pl.agg_off),
+                       reinterpret_cast<float*>(ws + pl.incl_off), ctrl, partial, pl.s};
     rc = launch_stateful<K>(p, pl.tiles, FIELDS_STATEFUL_ARG(K, B, pl), st);
     if (rc) return rc;
     BwdParams rp{};
@@ -824,6 +827,58 @@ int fields_read_selftest_wait(void* workspace, size_t workspace_bytes, unsigned 
     rc = launch<WaitSelfTest>(p, 1, st);
     if (rc) return rc;
     return fields_read_device_status(workspace, stream);
+}
+
+
+static bool aligned8(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; }
+
+int fields_read_forward_bf16(const void* raw, const float* tr, const float* ti, const float* gamma,
+                             const float* state_in, void* read, float* state_out, void* workspace,
+                             size_t workspace_bytes, int B, int L, int C, void* stream) {
+    if (B < 0 || L < 0 || C <= 0) return FIELDS_ERR_ARGUMENT;
+    if (B == 0 || L == 0) {
+        // nothing to scan: the fp32 entry point handles the state pass-through
+        return fields_read_forward(nullptr, tr, ti, gamma, state_in, nullptr, state_out, workspace,
+                                   workspace_bytes, B, 0, C, stream);
+    }
+    if (!raw || !read || !tr || !ti || !gamma) return FIELDS_ERR_ARGUMENT;
+    if (C % 4 || !aligned8(raw) || !aligned8(read) || !aligned16(tr) || !aligned16(ti) ||
+        !aligned16(gamma))
+        return FIELDS_ERR_UNSUPPORTED;  // 64-bit accesses only: C % 4 == 0, 8-byte aligned rows
+    if (!workspace || workspace_bytes < fields_read_workspace_bytes(B, L, C, FIELDS_PASS_FORWARD) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return FIELDS_ERR_WORKSPACE;
+    return run_forward_single_pass<FwdSpBf16, uint16_t>(
+        static_cast<const uint16_t*>(raw), tr, ti, gamma, state_in, static_cast<uint16_t*>(read),
+        state_out, workspace, B, L, C, reinterpret_cast<Stream>(stream));
+}
+
+int fields_read_backward_bf16(const void* raw, const float* tr, const float* ti, const float* gamma,
+                              const float* state_in, const void* read, const void* grad_read,
+                              const float* grad_state_out, void* grad_raw, float* grad_tr,
+                              float* grad_ti, float* grad_gamma, float* grad_state_in,
+                              void* workspace, size_t workspace_bytes, int B, int L, int C,
+                              void* stream) {
+    if (B < 0 || L < 0 || C <= 0) return FIELDS_ERR_ARGUMENT;
+    if (B == 0 || L == 0)
+        return fields_read_backward(nullptr, tr, ti, gamma, state_in, nullptr, nullptr, grad_state_out,
+                                    nullptr, grad_tr, grad_ti, grad_gamma, grad_state_in, workspace,
+                                    workspace_bytes, B, 0, C, stream);
+    if (!raw || !read || !grad_read || !grad_raw || !tr || !ti || !gamma || !grad_tr || !grad_ti ||
+        !grad_gamma)
+        return FIELDS_ERR_ARGUMENT;
+    if (C % 4 || !aligned8(raw) || !aligned8(read) || !aligned8(grad_read) || !aligned8(grad_raw) ||
+        !aligned16(tr) || !aligned16(ti) || !aligned16(gamma) || !aligned16(state_in))
+        return FIELDS_ERR_UNSUPPORTED;
+    if (!workspace ||
+        workspace_bytes < fields_read_workspace_bytes(B, L, C, FIELDS_PASS_BACKWARD) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return FIELDS_ERR_WORKSPACE;
+    return run_backward_single_pass<BwdSpBf16, uint16_t>(
+        static_cast<const uint16_t*>(raw), tr, ti, gamma, state_in,
+        static_cast<const uint16_t*>(read), static_cast<const uint16_t*>(grad_read), grad_state_out,
+        static_cast<uint16_t*>(grad_raw), grad_tr, grad_ti, grad_gamma, grad_state_in, workspace,
+        B, L, C, reinterpret_cast<Stream>(stream));
 }
 
 }  // extern "C"

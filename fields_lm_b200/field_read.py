@@ -98,6 +98,62 @@ class FieldReadFunction(torch.autograd.Function):
         return grad_raw, g_par[0], g_par[1], g_par[2], g_sin
 
 
+class FieldReadBf16Function(torch.autograd.Function):
+    """read = F(raw, tr, ti, gamma) with bfloat16 raw / read / gradients and an fp32 state."""
+
+    @staticmethod
+    def forward(ctx, raw, transition_r, transition_i, gamma):
+        if not raw.is_cuda:
+            raise RuntimeError("Chunked Field kernel requires CUDA")
+        if raw.dtype != torch.bfloat16:
+            raise TypeError(f"raw must be bfloat16, got {raw.dtype}")
+        if raw.dim() != 3 or raw.shape[2] % 3:
+            raise ValueError(tuple(raw.shape))
+        raw = raw.contiguous()
+        tr = transition_r.contiguous().float()
+        ti = transition_i.contiguous().float()
+        gm = gamma.contiguous().float()
+        B, L, three_c = raw.shape
+        C = three_c // 3
+        if tr.numel() != C or ti.numel() != C or gm.numel() != C:
+            raise ValueError((tuple(raw.shape), tuple(tr.shape)))
+        lib = _lib.load()
+        with torch.cuda.device(raw.device):
+            read = torch.empty((B, L, 4 * C), device=raw.device, dtype=torch.bfloat16)
+            ws, nbytes = _workspace(B, L, C, _FWD, raw.device)
+            rc = lib.fields_read_forward_bf16(_ptr(raw), _ptr(tr), _ptr(ti), _ptr(gm), None,
+                                              _ptr(read), None, _ptr(ws), nbytes, B, L, C,
+                                              _stream(raw.device))
+        _lib.check(rc, "fields_read_forward_bf16")
+        ctx.save_for_backward(raw, tr, ti, gm, read)
+        ctx.dims = (B, L, C)
+        return read
+
+    @staticmethod
+    def backward(ctx, grad_read):
+        raw, tr, ti, gm, read = ctx.saved_tensors
+        B, L, C = ctx.dims
+        lib = _lib.load()
+        with torch.cuda.device(raw.device):
+            grad_read = grad_read.contiguous().to(torch.bfloat16)
+            grad_raw = torch.empty_like(raw)
+            g_par = torch.empty((3, C), device=raw.device, dtype=torch.float32)
+            ws, nbytes = _workspace(B, L, C, _BWD, raw.device)
+            rc = lib.fields_read_backward_bf16(
+                _ptr(raw), _ptr(tr), _ptr(ti), _ptr(gm), None, _ptr(read), _ptr(grad_read), None,
+                _ptr(grad_raw), _ptr(g_par[0]), _ptr(g_par[1]), _ptr(g_par[2]), None, _ptr(ws),
+                nbytes, B, L, C, _stream(raw.device))
+        _lib.check(rc, "fields_read_backward_bf16")
+        return grad_raw, g_par[0], g_par[1], g_par[2]
+
+
+def fused_field_read_bf16(raw: torch.Tensor, transition_r: torch.Tensor,
+                          transition_i: torch.Tensor, gamma: torch.Tensor) -> torch.Tensor:
+    """The operator on a bfloat16 boundary: ``raw [B, L, 3C]`` bf16 in, ``read [B, L, 4C]`` bf16
+    out, fp32 state inside. For mixers that keep the write projection's bf16 output."""
+    return FieldReadBf16Function.apply(raw, transition_r, transition_i, gamma)
+
+
 def fused_field_read(raw: torch.Tensor, transition_r: torch.Tensor, transition_i: torch.Tensor,
                      gamma: torch.Tensor, block_c: int = 32, chunk_t: int = 64) -> torch.Tensor:
     """Drop-in for the reference's ``fused_field_read``; returns ``read [B, L, 4C]`` fp32."""

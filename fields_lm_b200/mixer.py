@@ -20,7 +20,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .decode import field_read_step
-from .field_read import field_read_with_state, fused_field_read
+from .field_read import field_read_with_state, fused_field_read, fused_field_read_bf16
 
 
 class RMSNorm(nn.Module):
@@ -82,9 +82,19 @@ class IndependentVacancyField(nn.Module):
         self.read_norm = RMSNorm(2 * dim)
         self.out_proj = nn.Linear(2 * dim, dim)
         self.gate_proj = nn.Linear(dim, dim)
+        # Not a constructor argument (the signature mirrors the reference's): set to True to keep
+        # the write projection's bf16 output under autocast and run the recurrence on a bfloat16
+        # boundary (fp32 state) instead of widening raw to fp32 first.
+        self.bf16_io = False
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        raw = self.write_proj(x).contiguous().float()
+        raw = self.write_proj(x).contiguous()
+        if self.bf16_io and raw.dtype == torch.bfloat16:
+            tr, ti, gamma = transition_parameters(self.radius_logit, self.theta)
+            read = fused_field_read_bf16(raw, tr, ti, gamma)
+            out = self.out_proj(self.read_norm(read))
+            return x + (out * torch.sigmoid(self.gate_proj(x))).to(x.dtype)
+        raw = raw.float()
         tr, ti, gamma = transition_parameters(self.radius_logit, self.theta)
         read = fused_field_read(raw, tr, ti, gamma, self.triton_block_c, self.triton_chunk_t)
         out = self.out_proj(self.read_norm(read))

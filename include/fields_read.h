@@ -92,6 +92,25 @@ int fields_read_backward(const float *raw, const float *tr, const float *ti,
                          size_t workspace_bytes, int B, int L, int C, void *stream);
 
 /*
+ * bfloat16 I/O twins of the two passes: raw, read, grad_read and grad_raw are bfloat16 (same
+ * layouts, half the bytes); parameters, states, parameter gradients and all arithmetic stay
+ * fp32. They serve a mixer that keeps the write projection's bf16 output instead of widening
+ * it as field_only_v4_chunked_triton_wiki100.py:1168 does (`.float()`), which is where the
+ * reference pays for "bf16 activations" with fp32 traffic. Need C % 4 == 0 and 8-byte aligned
+ * tensors (FIELDS_ERR_UNSUPPORTED otherwise). Same workspace sizes as the fp32 passes.
+ */
+int fields_read_forward_bf16(const void *raw, const float *tr, const float *ti,
+                             const float *gamma, const float *state_in, void *read,
+                             float *state_out, void *workspace, size_t workspace_bytes,
+                             int B, int L, int C, void *stream);
+int fields_read_backward_bf16(const void *raw, const float *tr, const float *ti,
+                              const float *gamma, const float *state_in, const void *read,
+                              const void *grad_read, const float *grad_state_out,
+                              void *grad_raw, float *grad_tr, float *grad_ti,
+                              float *grad_gamma, float *grad_state_in, void *workspace,
+                              size_t workspace_bytes, int B, int L, int C, void *stream);
+
+/*
  * Sequence sharding (no counterpart in the reference, which runs a sequence on one GPU;
  * the arithmetic is the chunk-summary composition of
  * field_only_v4_chunked_triton_wiki100.py:503-509 and :539-550 applied to a whole span).

@@ -46,6 +46,10 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.fields_read_forward.restype = I
     lib.fields_read_backward.argtypes = [P] * 14 + [SZ, I, I, I, P]
     lib.fields_read_backward.restype = I
+    lib.fields_read_forward_bf16.argtypes = [P] * 8 + [SZ, I, I, I, P]
+    lib.fields_read_forward_bf16.restype = I
+    lib.fields_read_backward_bf16.argtypes = [P] * 14 + [SZ, I, I, I, P]
+    lib.fields_read_backward_bf16.restype = I
     lib.fields_read_span_summary.argtypes = [P] * 6 + [SZ, I, I, I, P]
     lib.fields_read_span_summary.restype = I
     lib.fields_read_fold_summaries.argtypes = [P, P, P, I, I, I, I, P]
@@ -179,3 +183,43 @@ def step(raw_row, tr, ti, gamma, state, bf16=False):
     if rc:
         raise RuntimeError(lib().fields_status_string(rc).decode())
     return out, st
+
+
+def _u16(x, fill=None):
+    """Aligned uint16 copy of a bf16 bit pattern array (or an output buffer of that shape)."""
+    x = np.asarray(x, dtype=np.uint16)
+    out = _aligned(max(x.nbytes, 8)).view(np.uint16)[:x.size].reshape(x.shape)
+    out[...] = x if fill is None else fill
+    return out
+
+
+def forward_bf16(raw_bits, tr, ti, gamma):
+    B, L, C3 = raw_bits.shape
+    C = tr.size
+    r = _u16(raw_bits)
+    a = [_f32(x) for x in (tr, ti, gamma)]
+    read = _u16(np.zeros((B, L, 4 * C), np.uint16), fill=0x7fc0)
+    nbytes = lib().fields_read_workspace_bytes(B, L, C, 0)
+    ws = _aligned(max(nbytes, 256))
+    rc = lib().fields_read_forward_bf16(_ptr(r), _ptr(a[0]), _ptr(a[1]), _ptr(a[2]), None, _ptr(read),
+                                        None, _ptr(ws), nbytes, B, L, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return read
+
+
+def backward_bf16(raw_bits, tr, ti, gamma, read_bits, grad_bits):
+    B, L, C3 = raw_bits.shape
+    C = tr.size
+    r, rd, g = _u16(raw_bits), _u16(read_bits), _u16(grad_bits)
+    a = [_f32(x) for x in (tr, ti, gamma)]
+    g_raw = _u16(np.zeros((B, L, 3 * C), np.uint16), fill=0x7fc0)
+    g_tr, g_ti, g_gm = (_f32(np.full(C, np.nan)) for _ in range(3))
+    nbytes = lib().fields_read_workspace_bytes(B, L, C, 1)
+    ws = _aligned(max(nbytes, 256))
+    rc = lib().fields_read_backward_bf16(_ptr(r), _ptr(a[0]), _ptr(a[1]), _ptr(a[2]), None, _ptr(rd),
+                                         _ptr(g), None, _ptr(g_raw), _ptr(g_tr), _ptr(g_ti), _ptr(g_gm),
+                                         None, _ptr(ws), nbytes, B, L, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return g_raw, g_tr, g_ti, g_gm

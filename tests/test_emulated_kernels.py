@@ -191,3 +191,40 @@ def test_wait_selftest_reports_timeout():
     ws = emu._aligned(16384)
     assert emu.lib().fields_read_selftest_wait(ws.ctypes.data_as(emu.P), ws.size, 100, None) == 4
     assert emu.lib().fields_read_selftest_wait(ws.ctypes.data_as(emu.P), 64, 100, None) == 2
+
+
+def _bits(x):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).bfloat16().view(torch.int16).numpy().view(np.uint16)
+
+
+def _unbits(b):
+    import torch
+    return torch.from_numpy(np.array(b).view(np.int16)).view(torch.bfloat16).float().numpy()
+
+
+@pytest.mark.parametrize("B,L,C", [(2, 100, 132), (1, 37, 8), (1, 200, 512)])
+def test_bf16_boundary_forward_backward(B, L, C):
+    """bfloat16 raw / read / gradients, fp32 state: one bf16 rounding on outputs, and the
+    2e-2 bound on gradients (s_{t-1} is read back from the bf16 forward output)."""
+    from conftest import BF16_TOL
+    rng = np.random.default_rng(B + L + C)
+    tr, ti, gm = _params(C, rng)
+    raw_b = _bits(rng.standard_normal((B, L, 3 * C)))
+    grad_b = _bits(rng.standard_normal((B, L, 4 * C)))
+    raw, grad = _unbits(raw_b), _unbits(grad_b)
+    ref_read, _ = field_oracle.forward(raw, tr, ti, gm)
+    read_b = emu.forward_bf16(raw_b, tr, ti, gm)
+    assert rel_err(_unbits(read_b), ref_read) < 2 ** -7
+    ref = field_oracle.backward(raw, tr, ti, gm, grad)
+    got = emu.backward_bf16(raw_b, tr, ti, gm, read_b, grad_b)
+    assert rel_err(_unbits(got[0]), ref[0]) < BF16_TOL
+    for k in (1, 2, 3):
+        assert rel_err(got[k], ref[k]) < BF16_TOL
+
+
+def test_bf16_boundary_refuses_odd_channel_counts():
+    raw_b = np.zeros((1, 4, 21), np.uint16)
+    p = np.ones(7, np.float32)
+    with pytest.raises(RuntimeError, match="unsupported"):
+        emu.forward_bf16(raw_b, p, p, p)

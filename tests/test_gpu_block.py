@@ -139,3 +139,26 @@ def test_decode_step_bf16_matches_fp32_step():
     r16 = field_read_step(raw, tr, ti, gm, s16)
     torch.testing.assert_close(s16, s32, rtol=0, atol=0)      # same fp32 state either way
     assert rel_err(r16.float().cpu().numpy(), r32.cpu().numpy()) < BF16_TOL
+
+
+def test_bf16_boundary_mixer_matches_cpu_port():
+    """Mixer that keeps the write projection's bf16 output (bf16_io): within 2e-2 of the fp32 port."""
+    block = _block()
+    params = {k: v.detach().clone() for k, v in block.mixer.state_dict().items()}
+    gen = torch.Generator().manual_seed(2)
+    x = torch.randn(2, 384, 1024, generator=gen)
+    gy = torch.randn(2, 384, 1024, generator=gen)
+    ref_p = {k: v.clone().requires_grad_(True) for k, v in params.items()}
+    xr = x.clone().requires_grad_(True)
+    yr = torch_port.mixer_forward(ref_p, xr)
+    yr.backward(gy)
+    mixer = block.mixer.cuda().train()
+    mixer.bf16_io = True
+    xg = x.cuda().requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        yg = mixer(xg)
+    yg.backward(gy.cuda())
+    assert rel_err(yg.detach().float().cpu().numpy(), yr.detach().numpy()) < BF16_TOL
+    assert rel_err(xg.grad.float().cpu().numpy(), xr.grad.numpy()) < BF16_TOL
+    for name, p in mixer.named_parameters():
+        assert rel_err(p.grad.float().cpu().numpy(), ref_p[name].grad.numpy()) < BF16_TOL, name

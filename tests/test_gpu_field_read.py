@@ -302,3 +302,25 @@ def test_a_wait_that_nothing_satisfies_ends_with_a_timeout_status(dev):
     from fields_lm_b200 import fused_field_read
     y = fused_field_read(torch.zeros(1, 3, 12, device=dev), p, p, p, 32, 64)
     assert bool(torch.isfinite(y).all())
+
+
+def test_bf16_boundary_against_oracle(dev):
+    """bfloat16 raw / read / gradients with an fp32 state: 2e-2 relative max-abs (BF16_TOL)."""
+    from fields_lm_b200 import fused_field_read_bf16
+    gen = torch.Generator().manual_seed(31)
+    B, L, C = 4, 1024, 512
+    tr, ti, gm = _init_params(C)
+    raw = (torch.randn(B, L, 3 * C, generator=gen) * 0.577).bfloat16()
+    grad = torch.randn(B, L, 4 * C, generator=gen).bfloat16()
+    t = [_t(a, dev, True) for a in (tr, ti, gm)]
+    r = raw.to(dev).requires_grad_(True)
+    read = fused_field_read_bf16(r, *t)
+    assert read.dtype == torch.bfloat16
+    read.backward(grad.to(dev))
+    rawf, gradf = raw.float().numpy(), grad.float().numpy()
+    ref_read, _ = field_oracle.forward(rawf, tr, ti, gm)
+    ref = field_oracle.backward(rawf, tr, ti, gm, gradf)
+    assert rel_err(read.detach().float().cpu().numpy(), ref_read) < 2 ** -7
+    assert rel_err(r.grad.float().cpu().numpy(), ref[0]) < BF16_TOL
+    for k in range(3):
+        assert rel_err(t[k].grad.cpu().numpy(), ref[k + 1]) < BF16_TOL
