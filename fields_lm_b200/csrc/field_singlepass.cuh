@@ -247,6 +247,193 @@ struct FwdSinglePass {
 };
 
 // ---------------------------------------------------------------------------
+// Forward in two sweeps per tile with asynchronous rings (the shape of the backward
+// below): sweep 1 streams the tile's raw rows through per-thread cp.async rings, evaluates
+// the gates and composes the warp's map; after the look-back, sweep 2 streams the same rows
+// again (now from L2), evaluates the gates a second time and runs the recurrence, writing
+// read. Nothing of the tile lives in registers between the sweeps, so more warps fit on an
+// SM and loads are always in flight; the price is the second gate evaluation. HBM traffic
+// stays compulsory: the second read is served by L2.
+// ---------------------------------------------------------------------------
+template <int TS, int WARPS, int U_, int MIN_BLOCKS, int STAGES, typename IO = float>
+struct FwdTwoSweep {
+    using Params = SpFwdParamsT<IO>;
+    static constexpr int kThreads = 32 * WARPS;
+    static constexpr int kMinBlocks = MIN_BLOCKS;
+    static constexpr int kTile = TS * WARPS;
+    static constexpr int kPhases = 4;
+    static constexpr int kSplitPhase = 2;
+    static constexpr int kClaimAfter = 2;
+    static constexpr int U = U_;
+    static constexpr int kSumFloats = WARPS * 4 * kGroup;
+    static constexpr int kCarryFloats = WARPS * 2 * kGroup;
+    static constexpr int kCells = U * 3;
+    static constexpr int kRingFloats = STAGES * kCells * kThreads * 4;
+    static constexpr int kSmemFloats = kSumFloats + kCarryFloats + kRingFloats;
+    static_assert(kThreads >= kGroup, "one thread per channel is needed for the look-back");
+    FL_HD static constexpr bool barrier_after(int ph) { return ph != 1; }
+
+    struct State {};
+
+    FL_HD static float* sum_at(float* smem, int w, int k) { return smem + (w * 4 + k) * kGroup; }
+    FL_HD static float* carry_at(float* smem, int w, int k) {
+        return smem + kSumFloats + (w * 2 + k) * kGroup;
+    }
+    FL_HD static float* cell_at(float* smem, int stage, int idx, int thread) {
+        return smem + kSumFloats + kCarryFloats +
+               ((size_t)(stage * kCells + idx) * kThreads + thread) * 4;
+    }
+
+    FL_HD static void prefetch(const Params&, int, int) {}
+
+    template <int PH>
+    FL_HD static void phase(const Params& p, int block, int thread, float* smem, State&) {
+        const SpShape& s = p.s;
+        const SpTile tl = sp_decode(s, (unsigned)block);
+        const int lane = thread & 31, warp = thread >> 5;
+        const int C = s.C;
+        const int c0 = tl.cg * kGroup + lane * 4;
+        const bool chan_ok = c0 < C;
+        const int tfirst = tl.n * kTile + warp * TS;
+        const int tbeg = tfirst < s.L ? tfirst : s.L;
+        const int tend = tbeg + TS < s.L ? tbeg + TS : s.L;
+        const IO* base = p.raw + ((size_t)tl.b * s.L) * 3 * C + c0;
+
+        // batch of U steps starting at t0 into ring slot `stage` (nothing past tend)
+        auto issue = [&](int t0, int stage) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int t = t0 + u;
+                if (t < tend) {
+                    const IO* row = base + (size_t)t * 3 * C;
+                    async_copy4(cell_at(smem, stage, u * 3 + 0, thread), row);
+                    async_copy4(cell_at(smem, stage, u * 3 + 1, thread), row + C);
+                    async_copy4(cell_at(smem, stage, u * 3 + 2, thread), row + 2 * C);
+                }
+            }
+            async_commit();
+        };
+
+        if constexpr (PH == 0) {
+            Affine m[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) m[k] = affine_identity();
+            if (chan_ok) {
+                const Vec<4> lr = vec_load<4>(p.tr + c0);
+                const Vec<4> li = vec_load<4>(p.ti + c0);
+                const Vec<4> gm = vec_load<4>(p.gamma + c0);
+#pragma unroll
+                for (int j = 0; j < STAGES - 1; ++j) issue(tbeg + j * U, j);
+                int stage = 0;
+                for (int t0 = tbeg; t0 < tend; t0 += U, stage = stage + 1 == STAGES ? 0 : stage + 1) {
+                    issue(t0 + (STAGES - 1) * U, stage == 0 ? STAGES - 1 : stage - 1);
+                    async_wait_pending<STAGES - 1>();
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        if (t0 + u < tend) {
+                            const Vec<4> zr = cell_load4<IO>(cell_at(smem, stage, u * 3 + 0, thread));
+                            const Vec<4> zi = cell_load4<IO>(cell_at(smem, stage, u * 3 + 1, thread));
+                            const Vec<4> zv = cell_load4<IO>(cell_at(smem, stage, u * 3 + 2, thread));
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const Gate g = make_gate(zr.v[k], zi.v[k], zv.v[k]);
+                                const float keep = 1.0f - g.vac;
+                                const float bs = gm.v[k] * g.vac;
+                                m[k] = affine_then(m[k], keep * lr.v[k], keep * li.v[k],
+                                                   bs * g.inj_r, bs * g.inj_i);
+                            }
+                        }
+                    }
+                }
+                async_wait_pending<0>();  // the ring is reused by the second sweep
+            }
+            Vec<4> o0, o1, o2, o3;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                o0.v[k] = m[k].ar; o1.v[k] = m[k].ai; o2.v[k] = m[k].br; o3.v[k] = m[k].bi;
+            }
+            vec_store<4>(sum_at(smem, warp, 0) + lane * 4, o0);
+            vec_store<4>(sum_at(smem, warp, 1) + lane * 4, o1);
+            vec_store<4>(sum_at(smem, warp, 2) + lane * 4, o2);
+            vec_store<4>(sum_at(smem, warp, 3) + lane * 4, o3);
+        } else if constexpr (PH == 1) {
+            if (thread < kGroup && tl.cg * kGroup + thread < C && tl.n > 0) {
+                Affine a = affine_identity();
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w)
+                    a = affine_then(a, sum_at(smem, w, 0)[thread], sum_at(smem, w, 1)[thread],
+                                    sum_at(smem, w, 2)[thread], sum_at(smem, w, 3)[thread]);
+                publish4(p.agg + ((size_t)tl.idx * kGroup + thread) * 4, a.ar, a.ai, a.br, a.bi);
+            }
+        } else if constexpr (PH == 2) {
+            const int ch = tl.cg * kGroup + thread;
+            if (thread < kGroup && ch < C) {
+                float sr, si;
+                if (tl.n == 0) {
+                    sr = p.state_in ? p.state_in[(size_t)tl.b * 2 * C + ch] : 0.0f;
+                    si = p.state_in ? p.state_in[(size_t)tl.b * 2 * C + C + ch] : 0.0f;
+                } else {
+                    look_back(p.agg, p.incl, tl.chain * s.NT, tl.n, thread, p.ctrl, s.max_polls, sr, si);
+                }
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) {
+                    carry_at(smem, w, 0)[thread] = sr;
+                    carry_at(smem, w, 1)[thread] = si;
+                    affine_apply(Affine{sum_at(smem, w, 0)[thread], sum_at(smem, w, 1)[thread],
+                                        sum_at(smem, w, 2)[thread], sum_at(smem, w, 3)[thread]},
+                                 sr, si);
+                }
+                publish2(p.incl + ((size_t)tl.idx * kGroup + thread) * 2, sr, si);
+                if (p.state_out && tl.n == s.NT - 1) {
+                    p.state_out[(size_t)tl.b * 2 * C + ch] = sr;
+                    p.state_out[(size_t)tl.b * 2 * C + C + ch] = si;
+                }
+            }
+        } else {  // PH == 3
+            if (!chan_ok) return;
+            const Vec<4> lr = vec_load<4>(p.tr + c0);
+            const Vec<4> li = vec_load<4>(p.ti + c0);
+            const Vec<4> gm = vec_load<4>(p.gamma + c0);
+            Vec<4> sr = vec_load<4>(carry_at(smem, warp, 0) + lane * 4);
+            Vec<4> si = vec_load<4>(carry_at(smem, warp, 1) + lane * 4);
+            IO* obase = p.read + ((size_t)tl.b * s.L) * 4 * C + c0;
+#pragma unroll
+            for (int j = 0; j < STAGES - 1; ++j) issue(tbeg + j * U, j);
+            int stage = 0;
+            for (int t0 = tbeg; t0 < tend; t0 += U, stage = stage + 1 == STAGES ? 0 : stage + 1) {
+                issue(t0 + (STAGES - 1) * U, stage == 0 ? STAGES - 1 : stage - 1);
+                async_wait_pending<STAGES - 1>();
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (t0 + u < tend) {
+                        const Vec<4> zr = cell_load4<IO>(cell_at(smem, stage, u * 3 + 0, thread));
+                        const Vec<4> zi = cell_load4<IO>(cell_at(smem, stage, u * 3 + 1, thread));
+                        const Vec<4> zv = cell_load4<IO>(cell_at(smem, stage, u * 3 + 2, thread));
+                        Vec<4> dr, di;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const Gate g = make_gate(zr.v[k], zi.v[k], zv.v[k]);
+                            float mr, mi;
+                            cmul(lr.v[k], li.v[k], sr.v[k], si.v[k], mr, mi);
+                            dr.v[k] = g.vac * mr;
+                            di.v[k] = g.vac * mi;
+                            const float bs = gm.v[k] * g.vac;
+                            sr.v[k] = (1.0f - g.vac) * mr + bs * g.inj_r;
+                            si.v[k] = (1.0f - g.vac) * mi + bs * g.inj_i;
+                        }
+                        IO* orow = obase + (size_t)(t0 + u) * 4 * C;
+                        io_store4_stream(orow, sr);
+                        io_store4_stream(orow + C, si);
+                        io_store4_stream(orow + 2 * C, dr);
+                        io_store4_stream(orow + 3 * C, di);
+                    }
+                }
+            }
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------
 // Backward, single pass over HBM in two sweeps per tile.
 //
 // The dual recurrence runs from the last step to the first, so tiles are handed out

@@ -374,6 +374,11 @@ using FwdSp2 = FwdSinglePass<4, 8, 3>;   // tile 32, 3 blocks per SM
 using FwdSp3 = FwdSinglePass<7, 8, 2>;   // tile 56
 using FwdSp4 = FwdSinglePass<5, 8, 2>;   // tile 40
 using FwdSp5 = FwdSinglePass<4, 8, 2>;   // tile 32, 2 blocks per SM
+//   two-sweep forward <steps per warp, warps, unroll, blocks per SM, ring slots>
+using FwdSp6 = FwdTwoSweep<8, 4, 2, 4, 3>;    // tile 32, 16 warps per SM
+using FwdSp7 = FwdTwoSweep<16, 4, 2, 4, 3>;   // tile 64
+using FwdSp8 = FwdTwoSweep<8, 8, 2, 2, 3>;    // tile 64, 8 warps per block
+using FwdSp9 = FwdTwoSweep<8, 4, 1, 5, 4>;    // tile 32, one step per batch, 4-slot ring
 //   backward <steps per warp, warps, sweep-1 unroll, sweep-2 unroll, blocks per SM>
 using BwdSp0 = BwdSinglePass<8, 4, 2, 1, 3, true, 3>;  // tile 32, 3-slot cp.async rings, 12 warps per SM
 using BwdSp1 = BwdSinglePass<8, 4, 2, 1, 4>;    // 127 registers, 16 warps per SM
@@ -602,6 +607,10 @@ int fields_read_forward(const float* raw, const float* tr, const float* ti, cons
             case 3: FIELDS_FWD_SP(FwdSp3);
             case 4: FIELDS_FWD_SP(FwdSp4);
             case 5: FIELDS_FWD_SP(FwdSp5);
+            case 6: FIELDS_FWD_SP(FwdSp6);
+            case 7: FIELDS_FWD_SP(FwdSp7);
+            case 8: FIELDS_FWD_SP(FwdSp8);
+            case 9: FIELDS_FWD_SP(FwdSp9);
             default: FIELDS_FWD_SP(FwdSp0);
         }
 #undef FIELDS_FWD_SP
