@@ -551,20 +551,27 @@ struct BwdSinglePass {
                 const Vec<4> li = vec_load<4>(p.ti + c0);
                 const IO* zbase = p.raw + ((size_t)tl.b * s.L) * 3 * C + 2 * C + c0;
                 const IO* gbase = p.grad_read + ((size_t)tl.b * s.L) * 4 * C + c0;
-                // batch of U1 steps ending just before t0, into ring slot `stage`
-                auto issue1 = [&](int t0, int stage) {
+                // Running row pointers of the next batch to issue (rows descend; the pointers may
+                // step below the tile after the last batch and are not dereferenced then).
+                int t_issue = tend;
+                const IO* zq = zbase + (ptrdiff_t)(tend - 1) * 3 * C;
+                const IO* gq = gbase + (ptrdiff_t)(tend - 1) * 4 * C;
+                // batch of U1 steps ending just before t_issue, into ring slot `stage`
+                auto issue1 = [&](int, int stage) {
 #pragma unroll
                     for (int u = 0; u < U1; ++u) {
-                        const int t = t0 - 1 - u;
-                        if (t >= tbeg) {
-                            const IO* grow = gbase + (size_t)t * 4 * C;
-                            async_copy4(cell_at(smem, stage, u * 5 + 0, thread), zbase + (size_t)t * 3 * C);
+                        if (t_issue - 1 - u >= tbeg) {
+                            const IO* grow = gq - (ptrdiff_t)u * 4 * C;
+                            async_copy4(cell_at(smem, stage, u * 5 + 0, thread), zq - (ptrdiff_t)u * 3 * C);
                             async_copy4(cell_at(smem, stage, u * 5 + 1, thread), grow);
                             async_copy4(cell_at(smem, stage, u * 5 + 2, thread), grow + C);
                             async_copy4(cell_at(smem, stage, u * 5 + 3, thread), grow + 2 * C);
                             async_copy4(cell_at(smem, stage, u * 5 + 4, thread), grow + 3 * C);
                         }
                     }
+                    t_issue -= U1;
+                    zq -= (ptrdiff_t)U1 * 3 * C;
+                    gq -= (ptrdiff_t)U1 * 4 * C;
                     async_commit();
                 };
                 if constexpr (ASYNC) {
@@ -673,13 +680,17 @@ struct BwdSinglePass {
                 const IO* gbase = p.grad_read + ((size_t)tl.b * s.L) * 4 * C + c0;
                 const IO* rbase = p.read + ((size_t)tl.b * s.L) * 4 * C + c0;
                 IO* obase = p.grad_raw + ((size_t)tl.b * s.L) * 3 * C + c0;
-                auto issue2 = [&](int t0, int stage) {
+                int t_issue = tend;
+                const IO* zq = zbase + (ptrdiff_t)(tend - 1) * 3 * C;
+                const IO* gq = gbase + (ptrdiff_t)(tend - 1) * 4 * C;
+                const IO* rq = rbase + (ptrdiff_t)(tend - 2) * 4 * C;  // row of s_{t-1}
+                auto issue2 = [&](int, int stage) {
 #pragma unroll
                     for (int u = 0; u < U2; ++u) {
-                        const int t = t0 - 1 - u;
+                        const int t = t_issue - 1 - u;
                         if (t >= tbeg) {
-                            const IO* zrow = zbase + (size_t)t * 3 * C;
-                            const IO* grow = gbase + (size_t)t * 4 * C;
+                            const IO* zrow = zq - (ptrdiff_t)u * 3 * C;
+                            const IO* grow = gq - (ptrdiff_t)u * 4 * C;
                             async_copy4(cell_at(smem, stage, u * 9 + 0, thread), zrow);
                             async_copy4(cell_at(smem, stage, u * 9 + 1, thread), zrow + C);
                             async_copy4(cell_at(smem, stage, u * 9 + 2, thread), zrow + 2 * C);
@@ -688,12 +699,16 @@ struct BwdSinglePass {
                             async_copy4(cell_at(smem, stage, u * 9 + 5, thread), grow + 2 * C);
                             async_copy4(cell_at(smem, stage, u * 9 + 6, thread), grow + 3 * C);
                             if (t > 0) {
-                                const IO* prow = rbase + (size_t)(t - 1) * 4 * C;
+                                const IO* prow = rq - (ptrdiff_t)u * 4 * C;
                                 async_copy4(cell_at(smem, stage, u * 9 + 7, thread), prow);
                                 async_copy4(cell_at(smem, stage, u * 9 + 8, thread), prow + C);
                             }
                         }
                     }
+                    t_issue -= U2;
+                    zq -= (ptrdiff_t)U2 * 3 * C;
+                    gq -= (ptrdiff_t)U2 * 4 * C;
+                    rq -= (ptrdiff_t)U2 * 4 * C;
                     async_commit();
                 };
                 if constexpr (ASYNC) {
