@@ -465,9 +465,16 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         from fields_lm_b200 import seqpar
         lo, hi = seqpar.span_bounds(LONG_L, world, rank)
         long_raw = synthetic_inputs(2, 1, LONG_L)[0][:, lo:hi].contiguous().to(device)
-        sp_fwd = seqpar.SequenceParallelForward(1, hi - lo, C, device)
+        try:     # summaries through peer memory (NVLink stores); NCCL all_gather if that is unavailable
+            sp_fwd = seqpar.SequenceParallelForwardP2P(1, hi - lo, C, device)
+            exchange = "peer-memory stores"
+        except Exception as exc:
+            print(f"symmetric memory unavailable ({exc!r}); using NCCL all_gather", file=sys.stderr)
+            sp_fwd = seqpar.SequenceParallelForward(1, hi - lo, C, device)
+            exchange = "nccl all_gather"
         long_fwd = lambda: sp_fwd(long_raw, tr_d, ti_d, gm_d)
     else:
+        exchange = None
         long_op = DirectOp(device, 1, LONG_L)
         long_raw = synthetic_inputs(2, 1, LONG_L)[0].to(device)
         long_fwd = lambda: long_op.forward(long_raw, tr_d, ti_d, gm_d)
@@ -481,7 +488,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # the same step on the bfloat16 boundary (raw, read and their gradients in bf16, fp32 state)
     bf16 = bf16_leg(device, raw_d, grad_read, tr_d, ti_d, gm_d, args.steps, stream)
 
-    # decode (BASELINE config 5): one token for 256 sequences through the recurrences of 18 Field
+    # decode: one token for 256 sequences through the recurrences of 18 Field
     # blocks, bf16 rows, fp32 carried states; plain launches and one CUDA graph of the 18 launches
     decode = decode_leg(device, tr_d, ti_d, gm_d, peak_gbs=measured_peaks()[0]) if not dist_on else None
 
@@ -543,7 +550,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                        "row per chunk, upload / kernels / download overlapped on three streams"},
         "forward_64k": {"workload": "forward of 1 x 65,536 tokens" +
                                     (f", sequence-sharded over {world} GPUs" if dist_on else " on one GPU"),
-                        "scaling": "strong", "n_gpus": world,
+                        "scaling": "strong", "n_gpus": world, "exchange": exchange,
                         "ms": ms_long, "tokens_per_s": LONG_L / (ms_long * 1e-3),
                         "achieved": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9,
                         "frac": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9 / (peak * world)},

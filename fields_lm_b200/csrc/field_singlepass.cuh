@@ -976,4 +976,138 @@ struct ChunkSummaryStream {
     }
 };
 
+
+// ---------------------------------------------------------------------------
+// Exchange of span summaries between GPUs through peer memory (no collective library).
+//
+// Every rank owns a mailbox in memory that its peers can write:
+//   mailbox [2 parities][P ranks][B][4][C] of (value, tag) pairs, 8 bytes each.
+// PutSummary composes the span's map (as SpanCompose does) and stores it, tagged with the
+// call's epoch, into slot [epoch & 1][rank] of EVERY rank's mailbox with plain 8-byte
+// stores over NVLink: a pair is one store, so data and tag arrive together and no flag or
+// fence is needed. FoldMailbox polls its own mailbox until all P slots of that parity
+// carry the epoch (bounded wait), then folds the maps of the ranks before its own onto
+// the initial state. Waiting for all ranks, not only the earlier ones, keeps any rank at
+// most one call ahead of the slowest, so two parities are enough and nothing is ever
+// cleared. Epochs are per-call counters kept by the caller, equal on all ranks, never 0.
+// ---------------------------------------------------------------------------
+struct MailPair { float value; unsigned tag; };
+
+FL_HD void mail_store(MailPair* p, float value, unsigned tag) {
+#if FL_DEVICE_CODE
+    asm volatile("st.volatile.global.v2.b32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(value)),
+                 "r"(tag)
+                 : "memory");
+#else
+    p->value = value;
+    p->tag = tag;
+#endif
+}
+
+FL_HD MailPair mail_load(const MailPair* p) {
+    MailPair r;
+#if FL_DEVICE_CODE
+    unsigned v;
+    asm volatile("ld.volatile.global.v2.b32 {%0, %1}, [%2];" : "=r"(v), "=r"(r.tag) : "l"(p) : "memory");
+    r.value = __uint_as_float(v);
+#else
+    r = *p;
+#endif
+    return r;
+}
+
+constexpr int kMaxRanks = 16;
+
+struct PutSummary {
+    struct Params {
+        const float* sum;            // [4][B][N][C] chunk maps of this rank's span
+        MailPair* mailbox[kMaxRanks];  // every rank's mailbox (peer pointers), index = rank
+        float* summary;              // [B][4][C] local copy (may be null)
+        int rank, P;
+        unsigned epoch;
+        Shape s;
+    };
+    static constexpr int kThreads = 32 * kCarryWarps;
+    static constexpr int kPhases = 2;
+    static constexpr int kSmemFloats = 4 * kThreads;
+
+    FL_HD static void phase0(const Params& p, int block, int thread, float* smem) {
+        SpanCompose::Params q{p.sum, nullptr, p.s};
+        SpanCompose::phase0(q, block, thread, smem);
+    }
+
+    FL_HD static void phase1(const Params& p, int block, int thread, float* smem) {
+        const Shape& s = p.s;
+        if (thread >= 32) return;
+        const int cgroups = (s.C + 31) / 32;
+        const int b = block / cgroups;
+        const int c = (block % cgroups) * 32 + thread;
+        if (c >= s.C) return;
+        Affine m = affine_identity();
+        for (int w = 0; w < kCarryWarps; ++w) {
+            const float* q = smem + 4 * (w * 32 + thread);
+            m = affine_then(m, q[0], q[1], q[2], q[3]);
+        }
+        const float v[4] = {m.ar, m.ai, m.br, m.bi};
+        if (p.summary) {
+            float* o = p.summary + (size_t)b * 4 * s.C + c;
+            for (int k = 0; k < 4; ++k) o[(size_t)k * s.C] = v[k];
+        }
+        const size_t slot = (((size_t)(p.epoch & 1u) * p.P + p.rank) * s.B + b) * 4 * s.C + c;
+        for (int r = 0; r < p.P; ++r)
+            for (int k = 0; k < 4; ++k) mail_store(p.mailbox[r] + slot + (size_t)k * s.C, v[k], p.epoch);
+    }
+};
+
+struct FoldMailbox {
+    struct Params {
+        const MailPair* mailbox;  // this rank's own mailbox
+        const float* state0;      // [B, 2C] or null
+        float* state;             // [B, 2C] state entering this rank's span
+        unsigned* error;          // error word (0 = ok), set to 1 if a wait ran out
+        int rank, P, B, C;
+        unsigned epoch, max_polls;
+    };
+    static constexpr int kThreads = 128;
+    static constexpr int kPhases = 1;
+    static constexpr int kSmemFloats = 0;
+
+    FL_HD static void phase0(const Params& p, int block, int thread, float*) {
+        const long long i = (long long)block * kThreads + thread;
+        if (i >= (long long)p.B * p.C) return;
+        const int b = (int)(i / p.C), c = (int)(i % p.C);
+        float sr = p.state0 ? p.state0[(size_t)b * 2 * p.C + c] : 0.0f;
+        float si = p.state0 ? p.state0[(size_t)b * 2 * p.C + p.C + c] : 0.0f;
+        bool failed = false;
+        for (int r = 0; r < p.P; ++r) {
+            const MailPair* q =
+                p.mailbox + (((size_t)(p.epoch & 1u) * p.P + r) * p.B + b) * 4 * p.C + c;
+            float v[4];
+            for (int k = 0; k < 4; ++k) {
+                MailPair m = mail_load(q + (size_t)k * p.C);
+#if FL_DEVICE_CODE
+                unsigned polls = 0;
+                while (m.tag != p.epoch && ++polls < p.max_polls) {
+                    backoff(polls);
+                    m = mail_load(q + (size_t)k * p.C);
+                }
+#endif
+                if (m.tag != p.epoch) failed = true;
+                v[k] = m.value;
+            }
+            if (r < p.rank) affine_apply(Affine{v[0], v[1], v[2], v[3]}, sr, si);
+        }
+        if (failed) {
+#if FL_DEVICE_CODE
+            atomicExch(p.error, 1u);
+#else
+            *p.error = 1u;
+#endif
+            sr = si = nanf("");
+        }
+        p.state[(size_t)b * 2 * p.C + c] = sr;
+        p.state[(size_t)b * 2 * p.C + p.C + c] = si;
+    }
+};
+
 }  // namespace fields

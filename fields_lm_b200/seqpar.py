@@ -103,6 +103,71 @@ class SequenceParallelForward:
         return self.read, self.state_out
 
 
+class SequenceParallelForwardP2P:
+    """Sequence-sharded forward whose summary exchange goes through peer memory, not NCCL.
+
+    Each rank owns a mailbox in symmetric memory (``torch.distributed._symmetric_memory``:
+    every GPU of the node can write it over NVLink). ``fields_read_span_summary_put`` stores the
+    rank's span summary, tagged with a per-call epoch, straight into every rank's mailbox;
+    ``fields_read_fold_mailbox`` waits (bounded) for all summaries of that epoch and folds the
+    earlier ranks onto the initial state; ``fields_read_forward`` runs the span from there.
+    Three launches of this library per call, no collective, nothing to clear between calls.
+    A summary that never arrives turns into a NaN state and a non-zero status word
+    (:meth:`status`), never into a hang. The calls carry the epoch as a kernel argument, so
+    they must not be replayed from a captured CUDA graph.
+    """
+
+    def __init__(self, batch: int, span_length: int, channels: int, device, group=None):
+        import ctypes
+        import torch.distributed._symmetric_memory as symm_mem
+        self.lib = _lib.load()
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.B, self.L, self.C = batch, span_length, channels
+        self.device = torch.device(device)
+        f32 = dict(device=self.device, dtype=torch.float32)
+        nbytes = self.lib.fields_read_mailbox_bytes(self.world, batch, channels)
+        self.mail = symm_mem.empty(nbytes // 4, dtype=torch.float32, device=self.device)
+        self.mail.zero_()
+        self.handle = symm_mem.rendezvous(self.mail, self.group)
+        self.peers = (ctypes.c_void_p * self.world)(*[int(a) for a in self.handle.buffer_ptrs])
+        self.error = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.state_in = torch.empty(batch, 2 * channels, **f32)
+        self.state_out = torch.empty(batch, 2 * channels, **f32)
+        self.read = torch.empty(batch, span_length, 4 * channels, **f32)
+        self.nbytes = self.lib.fields_read_workspace_bytes(batch, span_length, channels, 0)
+        self.ws = torch.empty(max(self.nbytes, 256), dtype=torch.uint8, device=self.device)
+        self.epoch = 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)  # every mailbox is zeroed before anyone writes into it
+
+    def __call__(self, raw_span, tr, ti, gamma, state0: Optional[torch.Tensor] = None):
+        lib, B, L, C = self.lib, self.B, self.L, self.C
+        if tuple(raw_span.shape) != (B, L, 3 * C) or not raw_span.is_contiguous():
+            raise ValueError(f"expected a contiguous [{B}, {L}, {3 * C}] span")
+        self.epoch = self.epoch + 1 if self.epoch < 0xFFFFFFFE else 1
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        args = (raw_span.data_ptr(), tr.data_ptr(), ti.data_ptr(), gamma.data_ptr())
+        rc = lib.fields_read_span_summary_put(*args, self.peers, None, self.rank, self.world,
+                                              self.epoch, self.ws.data_ptr(), self.nbytes, B, L, C, st)
+        _lib.check(rc, "fields_read_span_summary_put")
+        rc = lib.fields_read_fold_mailbox(self.mail.data_ptr(),
+                                          None if state0 is None else state0.data_ptr(),
+                                          self.state_in.data_ptr(), self.error.data_ptr(),
+                                          self.rank, self.world, self.epoch, B, C, st)
+        _lib.check(rc, "fields_read_fold_mailbox")
+        rc = lib.fields_read_forward(*args, self.state_in.data_ptr(), self.read.data_ptr(),
+                                     self.state_out.data_ptr(), self.ws.data_ptr(), self.nbytes,
+                                     B, L, C, st)
+        _lib.check(rc, "fields_read_forward")
+        return self.read, self.state_out
+
+    def status(self) -> int:
+        """0, or 1 if some call since construction gave up waiting for a peer's summary (syncs)."""
+        return int(self.error.item())
+
+
 def span_bounds(length: int, world: int, rank: int) -> Tuple[int, int]:
     """Contiguous, near-equal spans: the first ``length % world`` ranks get one step more."""
     base, extra = divmod(length, world)

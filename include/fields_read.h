@@ -144,6 +144,38 @@ int fields_read_step(const float *raw, const float *tr, const float *ti, const f
 int fields_read_step_bf16(const void *raw, const float *tr, const float *ti, const float *gamma,
                           float *state, void *read, int B, int C, void *stream);
 
+/*
+ * The same exchange without a collective library: span summaries travel between the GPUs of a
+ * node through peer-writable memory (NVLink / NVSwitch). No counterpart in the reference.
+ *
+ * Every rank owns a mailbox of fields_read_mailbox_bytes(P, B, C) bytes, zeroed once when it is
+ * created, in memory its peers can write (peer access, IPC or symmetric memory); mailboxes[r] is
+ * rank r's mailbox as seen from the calling GPU (a HOST array of P device pointers, P <= 16).
+ *
+ * fields_read_span_summary_put: computes this rank's span summary and stores it, tagged with
+ * `epoch`, into its slot of every rank's mailbox (plain 8-byte peer stores; no TMA, no
+ * multicast). Also writes the summary to `summary` [B, 4, C] if that is not NULL.
+ *
+ * fields_read_fold_mailbox: waits, with a bound, until the calling rank's own mailbox holds the
+ * summaries of all P ranks for `epoch`, then writes the state entering the rank's span to
+ * `state` [B, 2C] (state0 as in fields_read_fold_summaries). If a summary does not arrive in
+ * time it sets *error_word (a device word the caller zeroed) to 1 and fills `state` with NaN.
+ *
+ * `epoch` is a per-call counter kept by the caller: the same on all ranks, never 0, increased
+ * by one for every exchange on a mailbox. Two parities alternate inside the mailbox and every
+ * rank waits for all ranks, so nothing is ever cleared and no rank can run more than one
+ * exchange ahead. The epoch is a kernel argument: a captured CUDA graph would repeat it, so
+ * these two calls must not be replayed from a graph.
+ */
+size_t fields_read_mailbox_bytes(int P, int B, int C);
+int fields_read_span_summary_put(const float *raw, const float *tr, const float *ti,
+                                 const float *gamma, void *const *mailboxes, float *summary,
+                                 int rank, int P, unsigned epoch, void *workspace,
+                                 size_t workspace_bytes, int B, int L, int C, void *stream);
+int fields_read_fold_mailbox(const void *mailbox, const float *state0, float *state,
+                             unsigned *error_word, int rank, int P, unsigned epoch, int B, int C,
+                             void *stream);
+
 /* Text of the last CUDA runtime error seen by the calling thread inside this library. */
 const char *fields_last_cuda_error(void);
 

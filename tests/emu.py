@@ -60,6 +60,12 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.fields_read_step_bf16.restype = I
     lib.fields_read_selftest_wait.argtypes = [P, SZ, ctypes.c_uint, P]
     lib.fields_read_selftest_wait.restype = I
+    lib.fields_read_mailbox_bytes.argtypes = [I, I, I]
+    lib.fields_read_mailbox_bytes.restype = SZ
+    lib.fields_read_span_summary_put.argtypes = [P] * 6 + [I, I, ctypes.c_uint, P, SZ, I, I, I, P]
+    lib.fields_read_span_summary_put.restype = I
+    lib.fields_read_fold_mailbox.argtypes = [P, P, P, P, I, I, ctypes.c_uint, I, I, P]
+    lib.fields_read_fold_mailbox.restype = I
     lib.fields_read_device_status.argtypes = [P, P]
     lib.fields_read_device_status.restype = I
     return lib
@@ -223,3 +229,36 @@ def backward_bf16(raw_bits, tr, ti, gamma, read_bits, grad_bits):
     if rc:
         raise RuntimeError(lib().fields_status_string(rc).decode())
     return g_raw, g_tr, g_ti, g_gm
+
+
+def make_mailboxes(world, B, C):
+    """One zeroed mailbox per emulated rank (all in host memory, so every 'peer' can write them)."""
+    n = lib().fields_read_mailbox_bytes(world, B, C)
+    return [_aligned(n) for _ in range(world)]
+
+
+def span_summary_put(raw, tr, ti, gamma, mailboxes, rank, epoch):
+    B, L, C3 = raw.shape
+    C = tr.size
+    a = [_f32(x) for x in (raw, tr, ti, gamma)]
+    ptrs = (ctypes.c_void_p * len(mailboxes))(*[m.ctypes.data for m in mailboxes])
+    out = _f32(np.full((B, 4, C), np.nan))
+    nbytes = lib().fields_read_workspace_bytes(B, L, C, 0)
+    ws = _aligned(max(nbytes, 256))
+    rc = lib().fields_read_span_summary_put(_ptr(a[0]), _ptr(a[1]), _ptr(a[2]), _ptr(a[3]), ptrs,
+                                            _ptr(out), rank, len(mailboxes), epoch, _ptr(ws), nbytes,
+                                            B, L, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return out
+
+
+def fold_mailbox(mailbox, rank, world, epoch, B, C, state0=None):
+    s0 = None if state0 is None else _f32(state0)
+    out = _f32(np.full((B, 2 * C), np.nan))
+    err = np.zeros(1, dtype=np.uint32)
+    rc = lib().fields_read_fold_mailbox(_ptr(mailbox), _ptr(s0), _ptr(out), _ptr(err), rank, world,
+                                        epoch, B, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return out, int(err[0])

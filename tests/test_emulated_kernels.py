@@ -228,3 +228,33 @@ def test_bf16_boundary_refuses_odd_channel_counts():
     p = np.ones(7, np.float32)
     with pytest.raises(RuntimeError, match="unsupported"):
         emu.forward_bf16(raw_b, p, p, p)
+
+
+def test_mailbox_exchange_three_ranks_two_epochs():
+    """Peer-memory exchange, emulated: every 'rank' puts its span summary into all mailboxes, then
+    folds from its own; a second exchange on the other parity does not disturb the first; a
+    mailbox that misses a summary reports the timeout."""
+    rng = np.random.default_rng(12)
+    B, L, C, world = 2, 90, 20, 3
+    tr, ti, gm = _params(C, rng)
+    boxes = emu.make_mailboxes(world, B, C)
+    for epoch in (1, 2, 3):
+        raw = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+        s0 = rng.standard_normal((B, 2 * C)).astype(np.float32)
+        cuts = [0, 31, 64, L]
+        spans = [raw[:, a:b] for a, b in zip(cuts[:-1], cuts[1:])]
+        for r, x in enumerate(spans):
+            got = emu.span_summary_put(x, tr, ti, gm, boxes, r, epoch)
+            assert rel_err(got, field_oracle.span_summary(x, tr, ti, gm)) < FP32_TOL
+        state = s0.astype(np.float64)
+        for r, x in enumerate(spans):
+            got, err = emu.fold_mailbox(boxes[r], r, world, epoch, B, C, state0=s0)
+            assert err == 0
+            assert rel_err(got, state) < FP32_TOL
+            _, state = field_oracle.forward(x, tr, ti, gm, state_in=state)
+    # an exchange in which rank 1 never puts: everyone's wait runs out (at once in the emulation)
+    fresh = emu.make_mailboxes(world, B, C)
+    for r in (0, 2):
+        emu.span_summary_put(spans[r], tr, ti, gm, fresh, r, 1)
+    got, err = emu.fold_mailbox(fresh[2], 2, world, 1, B, C)
+    assert err == 1 and np.isnan(got).all()

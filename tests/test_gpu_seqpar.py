@@ -39,6 +39,14 @@ def _worker(rank, world, port, L, out_dir):
         torch.cuda.synchronize()
         assert float((read2 - read).abs().max()) <= 2e-6 * float(read.abs().max())
         assert float((state2 - state).abs().max()) <= 2e-6 * float(state.abs().max())
+        # the same exchange through peer memory instead of NCCL; several calls alternate parities
+        p2p = seqpar.SequenceParallelForwardP2P(B, hi - lo, C, dev)
+        for _ in range(3):
+            read3, state3 = p2p(span, tr, ti, gm)
+        torch.cuda.synchronize()
+        assert p2p.status() == 0
+        assert float((read3 - read).abs().max()) <= 2e-6 * float(read.abs().max())
+        assert float((state3 - state).abs().max()) <= 2e-6 * float(state.abs().max())
         if rank == 0:
             with torch.no_grad():
                 full, full_state = field_read_with_state(raw.to(dev), tr, ti, gm, None)
