@@ -1,0 +1,30 @@
+"""The reference arm of bench.py runs without a GPU and prints one well-formed JSON line."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_reference_arm_prints_the_contract_line():
+    proc = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference",
+                           "--steps", "1", "--warmup", "0"], capture_output=True, text=True,
+                          timeout=600, cwd=str(ROOT))
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [l for l in proc.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["metric"] == "field_tokens_per_s_fwd_bwd"
+    assert d["unit"] == "tokens/s" and d["value"] > 0 and d["higher_is_better"] is True
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
+    assert d["e2e"] == {"value": d["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                        "d2h_bytes_per_step": 0}
+    assert d["config"]["workload"].startswith("field_block_recurrence_fwd_bwd")
+    assert d["vs_baseline"] is None and d["gpu_launches"] == 0
+
+
+def test_graft_entry_has_build_and_smoke():
+    sys.path.insert(0, str(ROOT))
+    import __graft_entry__ as entry
+    assert callable(entry.build) and callable(entry.smoke)
