@@ -91,8 +91,6 @@ static int fill_unset(void* p, size_t bytes, Stream) {
     return FIELDS_OK;
 }
 
-// third argument of launch_stateful: the emulation wants the number of chains
-#define FIELDS_STATEFUL_ARG(K, B, pl) ((long long)(B) * (pl).s.G)
 
 template <class K>
 static int resident_blocks() { return 4; }  // any positive distance exercises the prefetch path
@@ -196,8 +194,9 @@ static int allow_shared_memory(Fn fn, size_t bytes, bool* ready) {
     return FIELDS_OK;
 }
 
+// (the third argument, the number of chains, only matters to the host emulation)
 template <class K>
-static int launch_stateful(const typename K::Params& p, long long tiles, int, Stream st) {
+static int launch_stateful(const typename K::Params& p, long long tiles, long long, Stream st) {
     if (tiles <= 0) return FIELDS_OK;
     if (tiles > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
     constexpr size_t bytes = K::kSmemFloats * sizeof(float);
@@ -211,8 +210,6 @@ static int launch_stateful(const typename K::Params& p, long long tiles, int, St
 static int fill_unset(void* p, size_t bytes, Stream st) {
     return check_cuda(cudaMemsetAsync(p, kUnsetByte, bytes, st));
 }
-
-#define FIELDS_STATEFUL_ARG(K, B, pl) resident_blocks<K>()
 
 // Blocks of kernel K that the GPU holds at once (occupancy x SM count), asked once.
 template <class K>
@@ -363,8 +360,6 @@ static Algo algo_from_env() {
     return kAlgoAuto;
 }
 
-#define COMMA ,
-
 // Instantiations of the single-pass kernels. The first of each list is the default; the
 // others are tuning alternatives selected with FIELDS_FWD_VARIANT / FIELDS_BWD_VARIANT.
 //   forward  <steps per warp, warps, blocks per SM the registers must allow>
@@ -426,7 +421,7 @@ static int run_forward_single_pass(const IO* raw, const float* tr, const float* 
     SpFwdParamsT<IO> p{raw, tr, ti, gamma, state_in, read, state_out,
                        reinterpret_cast<float*>(ws + pl.agg_off),
                        reinterpret_cast<float*>(ws + pl.incl_off), ctrl, pl.s};
-    return launch_stateful<K>(p, pl.tiles, FIELDS_STATEFUL_ARG(K, B, pl), st);
+    return launch_stateful<K>(p, pl.tiles, (long long)B * pl.s.G, st);
 }
 
 template <class K, typename IO = float>
@@ -446,7 +441,7 @@ static int run_backward_single_pass(const IO* raw, const float* tr, const float*
     SpBwdParamsT<IO> p{raw, tr, ti, gamma, state_in, read, grad_read, grad_state_out, grad_raw,
                        grad_state_in, reinterpret_cast<float*>(ws + pl.agg_off),
                        reinterpret_cast<float*>(ws + pl.incl_off), ctrl, partial, pl.s};
-    rc = launch_stateful<K>(p, pl.tiles, FIELDS_STATEFUL_ARG(K, B, pl), st);
+    rc = launch_stateful<K>(p, pl.tiles, (long long)B * pl.s.G, st);
     if (rc) return rc;
     BwdParams rp{};
     rp.partial = partial;
