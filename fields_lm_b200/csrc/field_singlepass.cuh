@@ -838,6 +838,299 @@ struct BwdSinglePass {
 
 
 // ---------------------------------------------------------------------------
+// Backward with recomputed states. Same tiles, maps, look-back and outputs as
+// BwdSinglePass, but s_{t-1} is not read back from the saved forward output for every
+// step. Sweep 1 walks the warp's steps FORWARD in time: it reads all seven input planes
+// (z_r, z_i, z_v, grad_read), re-runs the state recurrence from the one saved row just
+// before the warp's first step, parks s_{t-1} of every step in shared memory (two 16-byte
+// cells per thread and step) and composes the dual map in the same pass. Sweep 2 walks
+// backwards as before; its seven planes come back from L2 and s_{t-1} from shared memory.
+// HBM traffic per channel-step: 28 B read + 8/TS B (the saved row) + 12 B written, which is
+// the compulsory traffic of the backward plus one row per TS steps.
+// ---------------------------------------------------------------------------
+template <int TS, int WARPS, int U_, int MIN_BLOCKS, int STAGES, typename IO = float>
+struct BwdRecompute {
+    using Params = SpBwdParamsT<IO>;
+    static constexpr int kThreads = 32 * WARPS;
+    static constexpr int kMinBlocks = MIN_BLOCKS;
+    static constexpr int kTile = TS * WARPS;
+    static constexpr int kPhases = 5;
+    static constexpr int kSplitPhase = 2;
+    static constexpr int U = U_;  // steps per ring slot
+    static constexpr int kSumFloats = WARPS * 4 * kGroup;
+    static constexpr int kCarryFloats = WARPS * 2 * kGroup;
+    static constexpr int kCells = U * 7;
+    static constexpr int kRingFloats = STAGES * kCells * kThreads * 4;
+    static constexpr int kStashFloats = TS * 2 * kThreads * 4;
+    static constexpr int kSmemFloats = kSumFloats + kCarryFloats + kRingFloats + kStashFloats;
+    static constexpr int kClaimAfter = 2;
+    FL_HD static constexpr bool barrier_after(int ph) { return ph != 1; }
+    static_assert(kThreads >= kGroup, "one thread per channel is needed for the look-back");
+    static_assert(TS % U == 0, "sub-chunk must be a multiple of the unroll");
+
+    struct State {};
+
+    FL_HD static float* sum_at(float* smem, int w, int k) { return smem + (w * 4 + k) * kGroup; }
+    FL_HD static float* carry_at(float* smem, int w, int k) {
+        return smem + kSumFloats + (w * 2 + k) * kGroup;
+    }
+    FL_HD static float* cell_at(float* smem, int stage, int idx, int thread) {
+        return smem + kSumFloats + kCarryFloats +
+               ((size_t)(stage * kCells + idx) * kThreads + thread) * 4;
+    }
+    // s_{t-1} of the warp's step j (k = 0: real parts, 1: imaginary parts)
+    FL_HD static float* stash_at(float* smem, int j, int k, int thread) {
+        return smem + kSumFloats + kCarryFloats + kRingFloats +
+               ((size_t)(j * 2 + k) * kThreads + thread) * 4;
+    }
+    FL_HD static void prefetch(const Params&, int, int) {}
+
+    // the seven planes of step row (zrow, grow) into the cells of sub-step u of a slot
+    FL_HD static void issue_step(float* smem, int stage, int u, int thread, const IO* zrow,
+                                 const IO* grow, int C) {
+        async_copy4(cell_at(smem, stage, u * 7 + 0, thread), zrow);
+        async_copy4(cell_at(smem, stage, u * 7 + 1, thread), zrow + C);
+        async_copy4(cell_at(smem, stage, u * 7 + 2, thread), zrow + 2 * C);
+        async_copy4(cell_at(smem, stage, u * 7 + 3, thread), grow);
+        async_copy4(cell_at(smem, stage, u * 7 + 4, thread), grow + C);
+        async_copy4(cell_at(smem, stage, u * 7 + 5, thread), grow + 2 * C);
+        async_copy4(cell_at(smem, stage, u * 7 + 6, thread), grow + 3 * C);
+    }
+
+    template <int PH>
+    FL_HD static void phase(const Params& p, int block, int thread, float* smem, State&) {
+        const SpShape& s = p.s;
+        const SpTile tl = sp_decode(s, (unsigned)block);
+        const int time_tile = s.NT - 1 - tl.n;
+        const int lane = thread & 31, warp = thread >> 5;
+        const int slot = WARPS - 1 - warp;  // position of this warp's steps in scan order
+        const int C = s.C;
+        const int c0 = tl.cg * kGroup + lane * 4;
+        const bool chan_ok = c0 < C;
+        const int tbeg = time_tile * kTile + warp * TS;
+        const int tend = tbeg + TS < s.L ? tbeg + TS : s.L;
+
+        if constexpr (PH == 0) {
+            Affine m[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) m[k] = affine_identity();
+            if (chan_ok && tbeg < tend) {
+                const Vec<4> lr = vec_load<4>(p.tr + c0);
+                const Vec<4> li = vec_load<4>(p.ti + c0);
+                const Vec<4> gm = vec_load<4>(p.gamma + c0);
+                const IO* zq = p.raw + ((size_t)tl.b * s.L + tbeg) * 3 * C + c0;
+                const IO* gq = p.grad_read + ((size_t)tl.b * s.L + tbeg) * 4 * C + c0;
+                int t_issue = tbeg;
+                auto issue = [&](int stage) {
+#pragma unroll
+                    for (int u = 0; u < U; ++u)
+                        if (t_issue + u < tend)
+                            issue_step(smem, stage, u, thread, zq + (size_t)u * 3 * C,
+                                       gq + (size_t)u * 4 * C, C);
+                    t_issue += U;
+                    zq += (size_t)U * 3 * C;
+                    gq += (size_t)U * 4 * C;
+                    async_commit();
+                };
+#pragma unroll
+                for (int j = 0; j < STAGES - 1; ++j) issue(j);
+                // the state just before the warp's first step
+                Vec<4> sr, si;
+                if (tbeg > 0) {
+                    const IO* prow = p.read + ((size_t)tl.b * s.L + tbeg - 1) * 4 * C + c0;
+                    sr = io_load4(prow);
+                    si = io_load4(prow + C);
+                } else if (p.state_in) {
+                    const float* prow = p.state_in + (size_t)tl.b * 2 * C + c0;
+                    sr = vec_load<4>(prow);
+                    si = vec_load<4>(prow + C);
+                } else {
+                    sr = vec_fill<4>(0.0f);
+                    si = vec_fill<4>(0.0f);
+                }
+                int stage = 0;
+                for (int t0 = tbeg; t0 < tend; t0 += U, stage = stage + 1 == STAGES ? 0 : stage + 1) {
+                    issue(stage == 0 ? STAGES - 1 : stage - 1);
+                    async_wait_pending<STAGES - 1>();
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        if (t0 + u < tend) {
+                            const Vec<4> zr = cell_load4<IO>(cell_at(smem, stage, u * 7 + 0, thread));
+                            const Vec<4> zi = cell_load4<IO>(cell_at(smem, stage, u * 7 + 1, thread));
+                            const Vec<4> zv = cell_load4<IO>(cell_at(smem, stage, u * 7 + 2, thread));
+                            const Vec<4> ur = cell_load4<IO>(cell_at(smem, stage, u * 7 + 3, thread));
+                            const Vec<4> ui = cell_load4<IO>(cell_at(smem, stage, u * 7 + 4, thread));
+                            const Vec<4> gr = cell_load4<IO>(cell_at(smem, stage, u * 7 + 5, thread));
+                            const Vec<4> gi = cell_load4<IO>(cell_at(smem, stage, u * 7 + 6, thread));
+                            vec_store<4>(stash_at(smem, t0 + u - tbeg, 0, thread), sr);
+                            vec_store<4>(stash_at(smem, t0 + u - tbeg, 1, thread), si);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const Gate g = make_gate(zr.v[k], zi.v[k], zv.v[k]);
+                                const float keep = 1.0f - g.vac;
+                                // s_t = keep lambda s_{t-1} + gamma v inj
+                                const float ar = keep * lr.v[k], ai = keep * li.v[k];
+                                const float bs = gm.v[k] * g.vac;
+                                const float nr = ar * sr.v[k] - ai * si.v[k] + bs * g.inj_r;
+                                const float ni = ar * si.v[k] + ai * sr.v[k] + bs * g.inj_i;
+                                sr.v[k] = nr;
+                                si.v[k] = ni;
+                                // dual step f_t: carry_{t-1} = conj(lambda) (keep (u + carry_t) + v gd);
+                                // the running map takes the carry after step t to the carry before tbeg
+                                const float hr = keep * ur.v[k] + g.vac * gr.v[k];
+                                const float hi = keep * ui.v[k] + g.vac * gi.v[k];
+                                float qr, qi;
+                                cmul_conj(lr.v[k], li.v[k], hr, hi, qr, qi);
+                                m[k] = affine_then(Affine{ar, -ai, qr, qi}, m[k].ar, m[k].ai, m[k].br,
+                                                   m[k].bi);
+                            }
+                        }
+                    }
+                }
+            }
+            Vec<4> o0, o1, o2, o3;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                o0.v[k] = m[k].ar; o1.v[k] = m[k].ai; o2.v[k] = m[k].br; o3.v[k] = m[k].bi;
+            }
+            vec_store<4>(sum_at(smem, slot, 0) + lane * 4, o0);
+            vec_store<4>(sum_at(smem, slot, 1) + lane * 4, o1);
+            vec_store<4>(sum_at(smem, slot, 2) + lane * 4, o2);
+            vec_store<4>(sum_at(smem, slot, 3) + lane * 4, o3);
+        } else if constexpr (PH == 1) {
+            if (thread < kGroup && tl.cg * kGroup + thread < C && tl.n > 0) {
+                Affine a = affine_identity();
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w)
+                    a = affine_then(a, sum_at(smem, w, 0)[thread], sum_at(smem, w, 1)[thread],
+                                    sum_at(smem, w, 2)[thread], sum_at(smem, w, 3)[thread]);
+                publish4(p.agg + ((size_t)tl.idx * kGroup + thread) * 4, a.ar, a.ai, a.br, a.bi);
+            }
+        } else if constexpr (PH == 2) {
+            const int ch = tl.cg * kGroup + thread;
+            if (thread < kGroup && ch < C) {
+                float sr, si;
+                if (tl.n == 0) {
+                    sr = p.grad_state_out ? p.grad_state_out[(size_t)tl.b * 2 * C + ch] : 0.0f;
+                    si = p.grad_state_out ? p.grad_state_out[(size_t)tl.b * 2 * C + C + ch] : 0.0f;
+                } else {
+                    look_back(p.agg, p.incl, tl.chain * s.NT, tl.n, thread, p.ctrl, s.max_polls, sr, si);
+                }
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) {
+                    carry_at(smem, w, 0)[thread] = sr;
+                    carry_at(smem, w, 1)[thread] = si;
+                    affine_apply(Affine{sum_at(smem, w, 0)[thread], sum_at(smem, w, 1)[thread],
+                                        sum_at(smem, w, 2)[thread], sum_at(smem, w, 3)[thread]},
+                                 sr, si);
+                }
+                publish2(p.incl + ((size_t)tl.idx * kGroup + thread) * 2, sr, si);
+                if (p.grad_state_in && tl.n == s.NT - 1) {
+                    p.grad_state_in[(size_t)tl.b * 2 * C + ch] = sr;
+                    p.grad_state_in[(size_t)tl.b * 2 * C + C + ch] = si;
+                }
+            }
+        } else if constexpr (PH == 3) {
+            Vec<4> dtr = vec_fill<4>(0.0f), dti = vec_fill<4>(0.0f), dgm = vec_fill<4>(0.0f);
+            if (chan_ok && tbeg < tend) {
+                const Vec<4> lr = vec_load<4>(p.tr + c0);
+                const Vec<4> li = vec_load<4>(p.ti + c0);
+                const Vec<4> gm = vec_load<4>(p.gamma + c0);
+                Vec<4> cr = vec_load<4>(carry_at(smem, slot, 0) + lane * 4);
+                Vec<4> ci = vec_load<4>(carry_at(smem, slot, 1) + lane * 4);
+                IO* obase = p.grad_raw + ((size_t)tl.b * s.L) * 3 * C + c0;
+                // rows descend; the pointers may step below the tile after the last batch
+                int t_issue = tend;
+                const IO* zq = p.raw + ((size_t)tl.b * s.L) * 3 * C + c0 + (ptrdiff_t)(tend - 1) * 3 * C;
+                const IO* gq = p.grad_read + ((size_t)tl.b * s.L) * 4 * C + c0 + (ptrdiff_t)(tend - 1) * 4 * C;
+                auto issue = [&](int stage) {
+#pragma unroll
+                    for (int u = 0; u < U; ++u)
+                        if (t_issue - 1 - u >= tbeg)
+                            issue_step(smem, stage, u, thread, zq - (ptrdiff_t)u * 3 * C,
+                                       gq - (ptrdiff_t)u * 4 * C, C);
+                    t_issue -= U;
+                    zq -= (ptrdiff_t)U * 3 * C;
+                    gq -= (ptrdiff_t)U * 4 * C;
+                    async_commit();
+                };
+#pragma unroll
+                for (int j = 0; j < STAGES - 1; ++j) issue(j);
+                int stage = 0;
+                for (int t0 = tend; t0 > tbeg; t0 -= U, stage = stage + 1 == STAGES ? 0 : stage + 1) {
+                    issue(stage == 0 ? STAGES - 1 : stage - 1);
+                    async_wait_pending<STAGES - 1>();
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const int t = t0 - 1 - u;
+                        if (t >= tbeg) {
+                            const Vec<4> zr = cell_load4<IO>(cell_at(smem, stage, u * 7 + 0, thread));
+                            const Vec<4> zi = cell_load4<IO>(cell_at(smem, stage, u * 7 + 1, thread));
+                            const Vec<4> zv = cell_load4<IO>(cell_at(smem, stage, u * 7 + 2, thread));
+                            const Vec<4> ur = cell_load4<IO>(cell_at(smem, stage, u * 7 + 3, thread));
+                            const Vec<4> ui = cell_load4<IO>(cell_at(smem, stage, u * 7 + 4, thread));
+                            const Vec<4> gr = cell_load4<IO>(cell_at(smem, stage, u * 7 + 5, thread));
+                            const Vec<4> gi = cell_load4<IO>(cell_at(smem, stage, u * 7 + 6, thread));
+                            const Vec<4> pr = vec_load<4>(stash_at(smem, t - tbeg, 0, thread));
+                            const Vec<4> pi = vec_load<4>(stash_at(smem, t - tbeg, 1, thread));
+                            Vec<4> ozr, ozi, ozv;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const Gate g = make_gate(zr.v[k], zi.v[k], zv.v[k]);
+                                const float keep = 1.0f - g.vac;
+                                const float Gr = ur.v[k] + cr.v[k];
+                                const float Gi = ui.v[k] + ci.v[k];
+                                const float gdr = gr.v[k], gdi = gi.v[k];
+                                const float sr = pr.v[k], si = pi.v[k];
+                                // m = lambda s_prev;  H = keep G + v gd
+                                float mr, mi, ar_, ai_;
+                                cmul(lr.v[k], li.v[k], sr, si, mr, mi);
+                                const float Hr = keep * Gr + g.vac * gdr;
+                                const float Hi = keep * Gi + g.vac * gdi;
+                                // d lambda += H conj(s_prev);  carry <- conj(lambda) H
+                                cmul_conj(sr, si, Hr, Hi, ar_, ai_);
+                                dtr.v[k] += ar_;
+                                dti.v[k] += ai_;
+                                dgm.v[k] += g.vac * (g.inj_r * Gr + g.inj_i * Gi);
+                                // dv = G . (gamma inj - m) + gd . m
+                                const float dv = Gr * (gm.v[k] * g.inj_r - mr) +
+                                                 Gi * (gm.v[k] * g.inj_i - mi) + gdr * mr + gdi * mi;
+                                const float bs = gm.v[k] * g.vac;
+                                ozr.v[k] = bs * Gr * (1.0f - g.inj_r * g.inj_r);
+                                ozi.v[k] = bs * Gi * (1.0f - g.inj_i * g.inj_i);
+                                ozv.v[k] = dv * (g.vac - g.vac * g.sig);
+                                cmul_conj(lr.v[k], li.v[k], Hr, Hi, cr.v[k], ci.v[k]);
+                            }
+                            IO* orow = obase + (size_t)t * 3 * C;
+                            io_store4_stream(orow, ozr);
+                            io_store4_stream(orow + C, ozi);
+                            io_store4_stream(orow + 2 * C, ozv);
+                        }
+                    }
+                }
+            }
+            vec_store<4>(sum_at(smem, warp, 0) + lane * 4, dtr);
+            vec_store<4>(sum_at(smem, warp, 1) + lane * 4, dti);
+            vec_store<4>(sum_at(smem, warp, 2) + lane * 4, dgm);
+        } else {  // PH == 4: one partial row per tile, warps added in a fixed order
+            const int ch = tl.cg * kGroup + thread;
+            if (thread < kGroup && ch < C) {
+                const size_t plane = (size_t)s.B * s.NT * C;
+                float* out = p.partial + ((size_t)tl.b * s.NT + time_tile) * C + ch;
+#pragma unroll
+                for (int k = 0; k < 3; ++k) {
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < WARPS; ++w) acc += sum_at(smem, w, k)[thread];
+                    out[k * plane] = acc;
+                }
+            }
+        }
+    }
+};
+
+
+// ---------------------------------------------------------------------------
 // Self-test of the bounded wait: one block looks back over a chain in which nothing was
 // ever published. Every thread must give up after `max_polls` polls, record the error
 // word and return NaN; the kernel ends normally. Used by the tests to check, without

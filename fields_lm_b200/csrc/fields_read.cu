@@ -114,9 +114,27 @@ static int launch_walk(const typename K::Params& p, long long grid, Stream) {
 using Stream = cudaStream_t;
 static thread_local const char* g_last_error = "no error";
 
+// Programmatic dependent launch. Every kernel of this library is launched with the
+// programmatic-serialization attribute and begins by waiting, before it touches any memory,
+// until the kernel before it on the stream has completed and its writes are visible. The
+// launch itself (grid set-up, block scheduling) then overlaps the end of the previous kernel
+// instead of following it. Because every kernel waits, the completion order of the stream is
+// kept along the whole chain. No kernel signals early: letting the next grid take SM slots
+// while this one still ran its last blocks was measured and was slower. The instruction does
+// nothing in a kernel launched without the attribute (FIELDS_READ_PDL=0).
+__device__ __forceinline__ void wait_for_previous_kernel() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+static bool dependent_launch_enabled() {
+    const char* e = std::getenv("FIELDS_READ_PDL");
+    return !(e && e[0] == '0');
+}
+
 template <class K>
 __global__ void __launch_bounds__(K::kThreads) kernel_entry(const typename K::Params p) {
     extern __shared__ __align__(16) float smem[];
+    wait_for_previous_kernel();
     K::phase0(p, (int)blockIdx.x, (int)threadIdx.x, smem);
     if constexpr (K::kPhases > 1) {
         __syncthreads();
@@ -130,12 +148,29 @@ static int check_cuda(cudaError_t e) {
     return FIELDS_ERR_LAUNCH;
 }
 
+// One launch, with the programmatic-serialization attribute unless FIELDS_READ_PDL=0.
+template <class P>
+static int launch_on(void (*fn)(const P), unsigned grid, unsigned threads, size_t bytes, Stream st,
+                     const P& params) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent_launch_enabled() ? 1 : 0;
+    return check_cuda(cudaLaunchKernelEx(&cfg, fn, params));
+}
+
 template <class K>
 static int launch(const typename K::Params& p, long long grid, Stream st) {
     if (grid <= 0) return FIELDS_OK;
     if (grid > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
-    kernel_entry<K><<<(unsigned)grid, K::kThreads, K::kSmemFloats * sizeof(float), st>>>(p);
-    return check_cuda(cudaGetLastError());
+    return launch_on<typename K::Params>(kernel_entry<K>, (unsigned)grid, K::kThreads,
+                                         K::kSmemFloats * sizeof(float), st, p);
 }
 
 static int fill_zero(float* p, size_t n, Stream st) {
@@ -164,6 +199,7 @@ __global__ void __launch_bounds__(K::kThreads, K::kMinBlocks) stateful_entry(con
     extern __shared__ __align__(16) float smem[];
     typename K::State st;
     const int tile = (int)blockIdx.x;
+    wait_for_previous_kernel();
     run_phases<K, 0, K::kClaimAfter>(p, tile, smem, st);
     __syncthreads();
     if (p.s.prefetch > 0) {
@@ -203,12 +239,34 @@ static int launch_stateful(const typename K::Params& p, long long tiles, long lo
     static bool ready[64] = {};
     const int rc = allow_shared_memory(stateful_entry<K>, bytes, ready);
     if (rc) return rc;
-    stateful_entry<K><<<(unsigned)tiles, K::kThreads, bytes, st>>>(p);
-    return check_cuda(cudaGetLastError());
+    return launch_on<typename K::Params>(stateful_entry<K>, (unsigned)tiles, K::kThreads, bytes, st, p);
+}
+
+// Fills with the "not yet written" pattern. A kernel rather than a memset, so that it takes part
+// in the dependent-launch chain: a memset would make the kernel after it wait for a full drain.
+struct FillParams {
+    uint4* p;
+    size_t n;  // 16-byte words
+};
+constexpr int kFillThreads = 256, kFillPerThread = 4;
+
+__global__ void __launch_bounds__(kFillThreads) fill_entry(const FillParams q) {
+    wait_for_previous_kernel();
+    const size_t base = (size_t)blockIdx.x * (kFillThreads * kFillPerThread) + threadIdx.x;
+#pragma unroll
+    for (int j = 0; j < kFillPerThread; ++j) {
+        const size_t i = base + (size_t)j * kFillThreads;
+        if (i < q.n) q.p[i] = make_uint4(kUnsetBits, kUnsetBits, kUnsetBits, kUnsetBits);
+    }
 }
 
 static int fill_unset(void* p, size_t bytes, Stream st) {
-    return check_cuda(cudaMemsetAsync(p, kUnsetByte, bytes, st));
+    if (!dependent_launch_enabled() || (reinterpret_cast<uintptr_t>(p) & 15) || (bytes & 15))
+        return check_cuda(cudaMemsetAsync(p, kUnsetByte, bytes, st));
+    const size_t n = bytes / 16, per_block = (size_t)kFillThreads * kFillPerThread;
+    if (n == 0) return FIELDS_OK;
+    return launch_on<FillParams>(fill_entry, (unsigned)((n + per_block - 1) / per_block), kFillThreads,
+                                 0, st, FillParams{static_cast<uint4*>(p), n});
 }
 
 // Blocks of kernel K that the GPU holds at once (occupancy x SM count), asked once.
@@ -230,6 +288,7 @@ template <class K>
 __global__ void __launch_bounds__(K::kThreads, K::kMinBlocks) walk_entry(const typename K::Params p) {
     extern __shared__ __align__(16) float smem[];
     typename K::State st;
+    wait_for_previous_kernel();
     const int n = K::phases(p);
     for (int ph = 0; ph < n; ++ph) {
         K::phase(ph, p, (int)blockIdx.x, (int)threadIdx.x, smem, st);
@@ -245,8 +304,7 @@ static int launch_walk(const typename K::Params& p, long long grid, Stream st) {
     static bool ready[64] = {};
     const int rc = allow_shared_memory(walk_entry<K>, bytes, ready);
     if (rc) return rc;
-    walk_entry<K><<<(unsigned)grid, K::kThreads, bytes, st>>>(p);
-    return check_cuda(cudaGetLastError());
+    return launch_on<typename K::Params>(walk_entry<K>, (unsigned)grid, K::kThreads, bytes, st, p);
 }
 
 #endif
@@ -388,6 +446,11 @@ using BwdSp9 = BwdSinglePass<8, 4, 1, 1, 3, true, 3>;   // 3-slot rings, one ste
 using BwdSp10 = BwdSinglePass<8, 4, 2, 1, 5>;   // direct loads, 96 registers, 20 warps per SM
 using BwdSp11 = BwdSinglePass<8, 4, 1, 1, 4, true, 2>;  // 2-slot rings, one step per batch
 using BwdSp12 = BwdSinglePass<8, 8, 2, 1, 2, true, 2>;  // 8 warps per block
+//   backward with recomputed states <steps per warp, warps, steps per ring slot, blocks per SM, ring slots>
+using BwdSp13 = BwdRecompute<8, 4, 1, 3, 2>;  // 73 KB per block, 12 warps per SM
+using BwdSp14 = BwdRecompute<8, 4, 1, 2, 3>;  // 3-slot rings, 8 warps per SM
+using BwdSp15 = BwdRecompute<8, 4, 2, 2, 2>;  // two steps per slot
+using BwdSp16 = BwdRecompute<4, 8, 1, 2, 2>;  // 8 warps per block, 16 warps per SM
 //   bfloat16 raw / read / grad_read / grad_raw (bits as uint16_t); state and arithmetic stay fp32
 using FwdSpBf16 = FwdSinglePass<6, 8, 2, uint16_t>;
 using BwdSpBf16 = BwdSinglePass<8, 4, 2, 1, 3, true, 3, uint16_t>;
@@ -690,6 +753,10 @@ int fields_read_backward(const float* raw, const float* tr, const float* ti, con
             case 10: FIELDS_BWD_SP(BwdSp10);
             case 11: FIELDS_BWD_SP(BwdSp11);
             case 12: FIELDS_BWD_SP(BwdSp12);
+            case 13: FIELDS_BWD_SP(BwdSp13);
+            case 14: FIELDS_BWD_SP(BwdSp14);
+            case 15: FIELDS_BWD_SP(BwdSp15);
+            case 16: FIELDS_BWD_SP(BwdSp16);
             default: FIELDS_BWD_SP(BwdSp0);
         }
 #undef FIELDS_BWD_SP
