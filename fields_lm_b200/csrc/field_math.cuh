@@ -237,6 +237,89 @@ FL_HD void io_store4_stream(uint16_t* p, const Vec<4>& x) {
 }
 
 // ---------------------------------------------------------------------------
+// F2: two adjacent channels in one 64-bit register pair. On sm_100 add, multiply and
+// fused multiply-add exist in a packed form that executes both lanes with one
+// instruction (fma.rn.f32x2 and friends), which halves the issue slots the complex
+// arithmetic needs; the hot loops are issue-limited at the occupancy their registers allow.
+// Each lane is an ordinary IEEE fp32 operation. The host forms do the same per lane.
+// ---------------------------------------------------------------------------
+struct alignas(8) F2 {
+    float x, y;
+};
+
+FL_HD F2 splat2(float s) { return F2{s, s}; }
+FL_HD F2 lo2(const Vec<4>& v) { return F2{v.v[0], v.v[1]}; }
+FL_HD F2 hi2(const Vec<4>& v) { return F2{v.v[2], v.v[3]}; }
+FL_HD Vec<4> join2(const F2& a, const F2& b) {
+    Vec<4> r;
+    r.v[0] = a.x; r.v[1] = a.y; r.v[2] = b.x; r.v[3] = b.y;
+    return r;
+}
+
+// a * b + c
+FL_HD F2 fma2(const F2& a, const F2& b, const F2& c) {
+#if FL_DEVICE_CODE
+    const float2 r = __ffma2_rn(make_float2(a.x, a.y), make_float2(b.x, b.y), make_float2(c.x, c.y));
+    return F2{r.x, r.y};
+#else
+    return F2{a.x * b.x + c.x, a.y * b.y + c.y};
+#endif
+}
+
+FL_HD F2 mul2(const F2& a, const F2& b) {
+#if FL_DEVICE_CODE
+    const float2 r = __fmul2_rn(make_float2(a.x, a.y), make_float2(b.x, b.y));
+    return F2{r.x, r.y};
+#else
+    return F2{a.x * b.x, a.y * b.y};
+#endif
+}
+
+FL_HD F2 add2(const F2& a, const F2& b) {
+#if FL_DEVICE_CODE
+    const float2 r = __fadd2_rn(make_float2(a.x, a.y), make_float2(b.x, b.y));
+    return F2{r.x, r.y};
+#else
+    return F2{a.x + b.x, a.y + b.y};
+#endif
+}
+
+FL_HD F2 exp2_2(const F2& a) { return F2{fast_exp2(a.x), fast_exp2(a.y)}; }
+FL_HD F2 rcp2(const F2& a) { return F2{fast_rcp(a.x), fast_rcp(a.y)}; }
+
+// Gates of two channels. `rr`, `ri` are the reciprocals inside the tanh form
+// (tanh = 1 - 2 r), kept because 1 - tanh^2 = (1 - 2 r)(2 r - 1) + 1 needs them.
+struct Gate2 {
+    F2 inj_r, inj_i, rr, ri, sig, vac, keep;
+};
+
+FL_HD F2 sigmoid2(const F2& z) {
+    return rcp2(add2(exp2_2(mul2(z, splat2(-kLog2e))), splat2(1.0f)));
+}
+
+FL_HD Gate2 make_gate2(const F2& zr, const F2& zi, const F2& zv) {
+    Gate2 g;
+    const F2 one = splat2(1.0f), k2 = splat2(2.0f * kLog2e), m2 = splat2(-2.0f);
+    g.rr = rcp2(add2(exp2_2(mul2(zr, k2)), one));
+    g.ri = rcp2(add2(exp2_2(mul2(zi, k2)), one));
+    g.inj_r = fma2(g.rr, m2, one);
+    g.inj_i = fma2(g.ri, m2, one);
+    g.sig = sigmoid2(zv);
+    g.vac = mul2(g.sig, splat2(kVacMax));
+    g.keep = fma2(g.sig, splat2(-kVacMax), one);
+    return g;
+}
+
+// Affine maps of two channels.
+struct Affine2 {
+    F2 ar, ai, br, bi;
+};
+
+FL_HD Affine2 affine2_identity() {
+    return Affine2{splat2(1.0f), splat2(0.0f), splat2(0.0f), splat2(0.0f)};
+}
+
+// ---------------------------------------------------------------------------
 // Per-channel gate values of one time step.
 // ---------------------------------------------------------------------------
 struct Gate {

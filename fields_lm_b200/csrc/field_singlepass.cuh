@@ -451,6 +451,98 @@ struct FwdTwoSweep {
 //            tile; BwdReduce adds the rows.
 // HBM traffic per channel-step: 20 B (sweep 1) + 16 B (z_r, z_i, s_{t-1}) + 12 B written.
 // ---------------------------------------------------------------------------
+// One step of the dual recurrence on two channels, composed onto the map of the later
+// steps: carry_{t-1} = conj(lambda) (keep (u + carry_t) + v gd)          (reference :655-705).
+// `nli` is -Im lambda.
+FL_HD void dual_step2(Affine2& m, const F2& zv, const F2& ur, const F2& ui, const F2& gr,
+                      const F2& gi, const F2& lr, const F2& li, const F2& nli) {
+    const F2 sig = sigmoid2(zv);
+    const F2 vac = mul2(sig, splat2(kVacMax));
+    const F2 keep = fma2(sig, splat2(-kVacMax), splat2(1.0f));
+    const F2 hr = fma2(keep, ur, mul2(vac, gr));
+    const F2 hi = fma2(keep, ui, mul2(vac, gi));
+    // q = conj(lambda) h;  alpha = keep conj(lambda) = (ar, na), pa = -na
+    const F2 qr = fma2(lr, hr, mul2(li, hi));
+    const F2 qi = fma2(lr, hi, mul2(nli, hr));
+    const F2 ar = mul2(keep, lr), pa = mul2(keep, li), na = mul2(keep, nli);
+    Affine2 o;
+    o.br = fma2(ar, m.br, fma2(pa, m.bi, qr));
+    o.bi = fma2(ar, m.bi, fma2(na, m.br, qi));
+    o.ar = fma2(ar, m.ar, mul2(pa, m.ai));
+    o.ai = fma2(ar, m.ai, mul2(na, m.ar));
+    m = o;
+}
+
+// dual_step2 in forward time order, together with the state recurrence it shares gates with:
+// advances (sr, si) from s_{t-1} to s_t = keep lambda s_{t-1} + gamma v inj and composes the
+// dual step BEFORE the map of the earlier steps (the map takes the carry after step t to the
+// carry before the first step).
+FL_HD void recompute_step2(Affine2& m, F2& sr, F2& si, const F2& zr, const F2& zi, const F2& zv,
+                           const F2& ur, const F2& ui, const F2& gr, const F2& gi, const F2& lr,
+                           const F2& li, const F2& nli, const F2& gm) {
+    const Gate2 g = make_gate2(zr, zi, zv);
+    const F2 ar = mul2(g.keep, lr), pa = mul2(g.keep, li), na = mul2(g.keep, nli);
+    const F2 bs = mul2(gm, g.vac);
+    const F2 nr = fma2(ar, sr, fma2(na, si, mul2(bs, g.inj_r)));
+    const F2 ni = fma2(ar, si, fma2(pa, sr, mul2(bs, g.inj_i)));
+    sr = nr;
+    si = ni;
+    const F2 hr = fma2(g.keep, ur, mul2(g.vac, gr));
+    const F2 hi = fma2(g.keep, ui, mul2(g.vac, gi));
+    const F2 qr = fma2(lr, hr, mul2(li, hi));
+    const F2 qi = fma2(lr, hi, mul2(nli, hr));
+    // first the step (alpha = (ar, na), q), then m:  A' = A alpha,  B' = A q + B
+    Affine2 o;
+    o.br = fma2(m.ar, qr, fma2(mul2(m.ai, splat2(-1.0f)), qi, m.br));
+    o.bi = fma2(m.ar, qi, fma2(m.ai, qr, m.bi));
+    o.ar = fma2(m.ar, ar, mul2(m.ai, pa));
+    o.ai = fma2(m.ar, na, mul2(m.ai, ar));
+    m = o;
+}
+
+// Parameter-gradient partial sums of two channels (Im d lambda = dtia - dtib).
+struct BwdAcc2 {
+    F2 dtr, dtia, dtib, dgm;
+};
+
+// One step of the second backward sweep on two channels (reference :794-909): from the
+// carry (cr, ci) entering step t and the saved s_{t-1} = (sr, si), the three gradients of
+// the step's raw inputs, the parameter-gradient terms, and the carry leaving the step.
+FL_HD void bwd_step2(const F2& zr, const F2& zi, const F2& zv, const F2& ur, const F2& ui,
+                     const F2& gdr, const F2& gdi, const F2& sr, const F2& si, const F2& lr,
+                     const F2& li, const F2& nli, const F2& gm, F2& cr, F2& ci, BwdAcc2& acc,
+                     F2& ozr, F2& ozi, F2& ozv) {
+    const F2 one = splat2(1.0f), mone = splat2(-1.0f), two = splat2(2.0f);
+    const Gate2 g = make_gate2(zr, zi, zv);
+    const F2 Gr = add2(ur, cr), Gi = add2(ui, ci);
+    // m = lambda s_prev;  H = keep G + v gd
+    const F2 mr = fma2(lr, sr, mul2(nli, si));
+    const F2 mi = fma2(lr, si, mul2(li, sr));
+    const F2 Hr = fma2(g.keep, Gr, mul2(g.vac, gdr));
+    const F2 Hi = fma2(g.keep, Gi, mul2(g.vac, gdi));
+    // d lambda += conj(s_prev) H
+    acc.dtr = fma2(sr, Hr, fma2(si, Hi, acc.dtr));
+    acc.dtia = fma2(sr, Hi, acc.dtia);
+    acc.dtib = fma2(si, Hr, acc.dtib);
+    // d gamma += v (inj . G)
+    const F2 common = fma2(g.inj_r, Gr, mul2(g.inj_i, Gi));
+    acc.dgm = fma2(g.vac, common, acc.dgm);
+    // dv = G . (gamma inj - m) + gd . m = gamma (inj . G) + m . (gd - G)
+    const F2 er = fma2(Gr, mone, gdr), ei = fma2(Gi, mone, gdi);
+    const F2 dv = fma2(gm, common, fma2(mr, er, mul2(mi, ei)));
+    const F2 bs = mul2(gm, g.vac);
+    // 1 - tanh^2 = tanh (-tanh) + 1 with -tanh = 2 r - 1
+    const F2 sech_r = fma2(g.inj_r, fma2(g.rr, two, mone), one);
+    const F2 sech_i = fma2(g.inj_i, fma2(g.ri, two, mone), one);
+    ozr = mul2(mul2(bs, Gr), sech_r);
+    ozi = mul2(mul2(bs, Gi), sech_i);
+    // v (1 - sig)
+    ozv = mul2(mul2(dv, g.vac), fma2(g.sig, mone, one));
+    // carry <- conj(lambda) H
+    cr = fma2(lr, Hr, mul2(li, Hi));
+    ci = fma2(lr, Hi, mul2(nli, Hr));
+}
+
 template <typename IO>
 struct SpBwdParamsT {
     const IO* raw;
@@ -543,12 +635,12 @@ struct BwdSinglePass {
                 prefetch_rows(p.read + ((size_t)tl.b * s.L + first) * 4 * C + tl.cg * kGroup, kTile,
                               s.L - 1 - first, 2, (size_t)4 * C, (size_t)C, width, thread, kThreads);
             }
-            Affine m[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) m[k] = affine_identity();
+            Affine2 m[2] = {affine2_identity(), affine2_identity()};
             if (chan_ok) {
                 const Vec<4> lr = vec_load<4>(p.tr + c0);
                 const Vec<4> li = vec_load<4>(p.ti + c0);
+                const F2 lr2[2] = {lo2(lr), hi2(lr)}, li2[2] = {lo2(li), hi2(li)};
+                const F2 nli2[2] = {mul2(li2[0], splat2(-1.0f)), mul2(li2[1], splat2(-1.0f))};
                 const IO* zbase = p.raw + ((size_t)tl.b * s.L) * 3 * C + 2 * C + c0;
                 const IO* gbase = p.grad_read + ((size_t)tl.b * s.L) * 4 * C + c0;
                 // Running row pointers of the next batch to issue (rows descend; the pointers may
@@ -611,30 +703,18 @@ struct BwdSinglePass {
 #pragma unroll
                     for (int u = 0; u < U1; ++u) {
                         if (t0 - 1 - u >= tbeg) {
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                // carry_{t-1} = conj(lambda) (keep (u + carry_t) + v gd)
-                                const float vac = kVacMax * sigmoidf_fast(zv[u].v[k]);
-                                const float keep = 1.0f - vac;
-                                const float hr = keep * ur[u].v[k] + vac * gr[u].v[k];
-                                const float hi = keep * ui[u].v[k] + vac * gi[u].v[k];
-                                float qr, qi;
-                                cmul_conj(lr.v[k], li.v[k], hr, hi, qr, qi);
-                                m[k] = affine_then(m[k], keep * lr.v[k], -keep * li.v[k], qr, qi);
-                            }
+                            dual_step2(m[0], lo2(zv[u]), lo2(ur[u]), lo2(ui[u]), lo2(gr[u]), lo2(gi[u]),
+                                       lr2[0], li2[0], nli2[0]);
+                            dual_step2(m[1], hi2(zv[u]), hi2(ur[u]), hi2(ui[u]), hi2(gr[u]), hi2(gi[u]),
+                                       lr2[1], li2[1], nli2[1]);
                         }
                     }
                 }
             }
-            Vec<4> o0, o1, o2, o3;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                o0.v[k] = m[k].ar; o1.v[k] = m[k].ai; o2.v[k] = m[k].br; o3.v[k] = m[k].bi;
-            }
-            vec_store<4>(sum_at(smem, slot, 0) + lane * 4, o0);
-            vec_store<4>(sum_at(smem, slot, 1) + lane * 4, o1);
-            vec_store<4>(sum_at(smem, slot, 2) + lane * 4, o2);
-            vec_store<4>(sum_at(smem, slot, 3) + lane * 4, o3);
+            vec_store<4>(sum_at(smem, slot, 0) + lane * 4, join2(m[0].ar, m[1].ar));
+            vec_store<4>(sum_at(smem, slot, 1) + lane * 4, join2(m[0].ai, m[1].ai));
+            vec_store<4>(sum_at(smem, slot, 2) + lane * 4, join2(m[0].br, m[1].br));
+            vec_store<4>(sum_at(smem, slot, 3) + lane * 4, join2(m[0].bi, m[1].bi));
         } else if constexpr (PH == 1) {
             if (thread < kGroup && tl.cg * kGroup + thread < C && tl.n > 0) {
                 Affine a = affine_identity();
@@ -669,13 +749,18 @@ struct BwdSinglePass {
                 }
             }
         } else if constexpr (PH == 3) {
-            Vec<4> dtr = vec_fill<4>(0.0f), dti = vec_fill<4>(0.0f), dgm = vec_fill<4>(0.0f);
+            const F2 zero2 = splat2(0.0f);
+            BwdAcc2 acc[2] = {{zero2, zero2, zero2, zero2}, {zero2, zero2, zero2, zero2}};
             if (chan_ok) {
                 const Vec<4> lr = vec_load<4>(p.tr + c0);
                 const Vec<4> li = vec_load<4>(p.ti + c0);
                 const Vec<4> gm = vec_load<4>(p.gamma + c0);
-                Vec<4> cr = vec_load<4>(carry_at(smem, slot, 0) + lane * 4);
-                Vec<4> ci = vec_load<4>(carry_at(smem, slot, 1) + lane * 4);
+                const F2 lr2[2] = {lo2(lr), hi2(lr)}, li2[2] = {lo2(li), hi2(li)};
+                const F2 nli2[2] = {mul2(li2[0], splat2(-1.0f)), mul2(li2[1], splat2(-1.0f))};
+                const F2 gm2[2] = {lo2(gm), hi2(gm)};
+                const Vec<4> cr4 = vec_load<4>(carry_at(smem, slot, 0) + lane * 4);
+                const Vec<4> ci4 = vec_load<4>(carry_at(smem, slot, 1) + lane * 4);
+                F2 cr[2] = {lo2(cr4), hi2(cr4)}, ci[2] = {lo2(ci4), hi2(ci4)};
                 const IO* zbase = p.raw + ((size_t)tl.b * s.L) * 3 * C + c0;
                 const IO* gbase = p.grad_read + ((size_t)tl.b * s.L) * 4 * C + c0;
                 const IO* rbase = p.read + ((size_t)tl.b * s.L) * 4 * C + c0;
@@ -778,47 +863,27 @@ struct BwdSinglePass {
                     for (int u = 0; u < U2; ++u) {
                         const int t = t0 - 1 - u;
                         if (t >= tbeg) {
-                            Vec<4> ozr, ozi, ozv;
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                const Gate g = make_gate(zr[u].v[k], zi[u].v[k], zv[u].v[k]);
-                                const float keep = 1.0f - g.vac;
-                                const float Gr = ur[u].v[k] + cr.v[k];
-                                const float Gi = ui[u].v[k] + ci.v[k];
-                                const float gdr = gr[u].v[k], gdi = gi[u].v[k];
-                                const float sr = pr[u].v[k], si = pi[u].v[k];
-                                // m = lambda s_prev;  H = keep G + v gd
-                                float mr, mi, ar_, ai_;
-                                cmul(lr.v[k], li.v[k], sr, si, mr, mi);
-                                const float Hr = keep * Gr + g.vac * gdr;
-                                const float Hi = keep * Gi + g.vac * gdi;
-                                // d lambda += H conj(s_prev);  carry <- conj(lambda) H
-                                cmul_conj(sr, si, Hr, Hi, ar_, ai_);
-                                dtr.v[k] += ar_;
-                                dti.v[k] += ai_;
-                                const float common_b = g.inj_r * Gr + g.inj_i * Gi;
-                                dgm.v[k] += g.vac * common_b;
-                                // dv = G . (gamma inj - m) + gd . m
-                                const float dv = Gr * (gm.v[k] * g.inj_r - mr) +
-                                                 Gi * (gm.v[k] * g.inj_i - mi) + gdr * mr + gdi * mi;
-                                const float bs = gm.v[k] * g.vac;
-                                ozr.v[k] = bs * Gr * (1.0f - g.inj_r * g.inj_r);
-                                ozi.v[k] = bs * Gi * (1.0f - g.inj_i * g.inj_i);
-                                ozv.v[k] = dv * (g.vac - g.vac * g.sig);
-                                cmul_conj(lr.v[k], li.v[k], Hr, Hi, cr.v[k], ci.v[k]);
-                            }
+                            F2 ozr[2], ozi[2], ozv[2];
+                            bwd_step2(lo2(zr[u]), lo2(zi[u]), lo2(zv[u]), lo2(ur[u]), lo2(ui[u]),
+                                      lo2(gr[u]), lo2(gi[u]), lo2(pr[u]), lo2(pi[u]), lr2[0], li2[0],
+                                      nli2[0], gm2[0], cr[0], ci[0], acc[0], ozr[0], ozi[0], ozv[0]);
+                            bwd_step2(hi2(zr[u]), hi2(zi[u]), hi2(zv[u]), hi2(ur[u]), hi2(ui[u]),
+                                      hi2(gr[u]), hi2(gi[u]), hi2(pr[u]), hi2(pi[u]), lr2[1], li2[1],
+                                      nli2[1], gm2[1], cr[1], ci[1], acc[1], ozr[1], ozi[1], ozv[1]);
                             IO* orow = obase + (size_t)t * 3 * C;
-                            io_store4_stream(orow, ozr);
-                            io_store4_stream(orow + C, ozi);
-                            io_store4_stream(orow + 2 * C, ozv);
+                            io_store4_stream(orow, join2(ozr[0], ozr[1]));
+                            io_store4_stream(orow + C, join2(ozi[0], ozi[1]));
+                            io_store4_stream(orow + 2 * C, join2(ozv[0], ozv[1]));
                         }
                     }
                 }
             }
             // warp partials into the (now free) map area: [warp][3][128]
-            vec_store<4>(sum_at(smem, warp, 0) + lane * 4, dtr);
-            vec_store<4>(sum_at(smem, warp, 1) + lane * 4, dti);
-            vec_store<4>(sum_at(smem, warp, 2) + lane * 4, dgm);
+            const F2 mone = splat2(-1.0f);
+            vec_store<4>(sum_at(smem, warp, 0) + lane * 4, join2(acc[0].dtr, acc[1].dtr));
+            vec_store<4>(sum_at(smem, warp, 1) + lane * 4,
+                         join2(fma2(acc[0].dtib, mone, acc[0].dtia), fma2(acc[1].dtib, mone, acc[1].dtia)));
+            vec_store<4>(sum_at(smem, warp, 2) + lane * 4, join2(acc[0].dgm, acc[1].dgm));
         } else {  // PH == 4: one partial row per tile, warps added in a fixed order
             const int ch = tl.cg * kGroup + thread;
             if (thread < kGroup && ch < C) {
@@ -911,13 +976,14 @@ struct BwdRecompute {
         const int tend = tbeg + TS < s.L ? tbeg + TS : s.L;
 
         if constexpr (PH == 0) {
-            Affine m[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) m[k] = affine_identity();
+            Affine2 m[2] = {affine2_identity(), affine2_identity()};
             if (chan_ok && tbeg < tend) {
                 const Vec<4> lr = vec_load<4>(p.tr + c0);
                 const Vec<4> li = vec_load<4>(p.ti + c0);
                 const Vec<4> gm = vec_load<4>(p.gamma + c0);
+                const F2 lr2[2] = {lo2(lr), hi2(lr)}, li2[2] = {lo2(li), hi2(li)};
+                const F2 nli2[2] = {mul2(li2[0], splat2(-1.0f)), mul2(li2[1], splat2(-1.0f))};
+                const F2 gm2[2] = {lo2(gm), hi2(gm)};
                 const IO* zq = p.raw + ((size_t)tl.b * s.L + tbeg) * 3 * C + c0;
                 const IO* gq = p.grad_read + ((size_t)tl.b * s.L + tbeg) * 4 * C + c0;
                 int t_issue = tbeg;
@@ -935,19 +1001,20 @@ struct BwdRecompute {
 #pragma unroll
                 for (int j = 0; j < STAGES - 1; ++j) issue(j);
                 // the state just before the warp's first step
-                Vec<4> sr, si;
+                Vec<4> sr4, si4;
                 if (tbeg > 0) {
                     const IO* prow = p.read + ((size_t)tl.b * s.L + tbeg - 1) * 4 * C + c0;
-                    sr = io_load4(prow);
-                    si = io_load4(prow + C);
+                    sr4 = io_load4(prow);
+                    si4 = io_load4(prow + C);
                 } else if (p.state_in) {
                     const float* prow = p.state_in + (size_t)tl.b * 2 * C + c0;
-                    sr = vec_load<4>(prow);
-                    si = vec_load<4>(prow + C);
+                    sr4 = vec_load<4>(prow);
+                    si4 = vec_load<4>(prow + C);
                 } else {
-                    sr = vec_fill<4>(0.0f);
-                    si = vec_fill<4>(0.0f);
+                    sr4 = vec_fill<4>(0.0f);
+                    si4 = vec_fill<4>(0.0f);
                 }
+                F2 sr[2] = {lo2(sr4), hi2(sr4)}, si[2] = {lo2(si4), hi2(si4)};
                 int stage = 0;
                 for (int t0 = tbeg; t0 < tend; t0 += U, stage = stage + 1 == STAGES ? 0 : stage + 1) {
                     issue(stage == 0 ? STAGES - 1 : stage - 1);
@@ -962,41 +1029,20 @@ struct BwdRecompute {
                             const Vec<4> ui = cell_load4<IO>(cell_at(smem, stage, u * 7 + 4, thread));
                             const Vec<4> gr = cell_load4<IO>(cell_at(smem, stage, u * 7 + 5, thread));
                             const Vec<4> gi = cell_load4<IO>(cell_at(smem, stage, u * 7 + 6, thread));
-                            vec_store<4>(stash_at(smem, t0 + u - tbeg, 0, thread), sr);
-                            vec_store<4>(stash_at(smem, t0 + u - tbeg, 1, thread), si);
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                const Gate g = make_gate(zr.v[k], zi.v[k], zv.v[k]);
-                                const float keep = 1.0f - g.vac;
-                                // s_t = keep lambda s_{t-1} + gamma v inj
-                                const float ar = keep * lr.v[k], ai = keep * li.v[k];
-                                const float bs = gm.v[k] * g.vac;
-                                const float nr = ar * sr.v[k] - ai * si.v[k] + bs * g.inj_r;
-                                const float ni = ar * si.v[k] + ai * sr.v[k] + bs * g.inj_i;
-                                sr.v[k] = nr;
-                                si.v[k] = ni;
-                                // dual step f_t: carry_{t-1} = conj(lambda) (keep (u + carry_t) + v gd);
-                                // the running map takes the carry after step t to the carry before tbeg
-                                const float hr = keep * ur.v[k] + g.vac * gr.v[k];
-                                const float hi = keep * ui.v[k] + g.vac * gi.v[k];
-                                float qr, qi;
-                                cmul_conj(lr.v[k], li.v[k], hr, hi, qr, qi);
-                                m[k] = affine_then(Affine{ar, -ai, qr, qi}, m[k].ar, m[k].ai, m[k].br,
-                                                   m[k].bi);
-                            }
+                            vec_store<4>(stash_at(smem, t0 + u - tbeg, 0, thread), join2(sr[0], sr[1]));
+                            vec_store<4>(stash_at(smem, t0 + u - tbeg, 1, thread), join2(si[0], si[1]));
+                            recompute_step2(m[0], sr[0], si[0], lo2(zr), lo2(zi), lo2(zv), lo2(ur), lo2(ui),
+                                            lo2(gr), lo2(gi), lr2[0], li2[0], nli2[0], gm2[0]);
+                            recompute_step2(m[1], sr[1], si[1], hi2(zr), hi2(zi), hi2(zv), hi2(ur), hi2(ui),
+                                            hi2(gr), hi2(gi), lr2[1], li2[1], nli2[1], gm2[1]);
                         }
                     }
                 }
             }
-            Vec<4> o0, o1, o2, o3;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                o0.v[k] = m[k].ar; o1.v[k] = m[k].ai; o2.v[k] = m[k].br; o3.v[k] = m[k].bi;
-            }
-            vec_store<4>(sum_at(smem, slot, 0) + lane * 4, o0);
-            vec_store<4>(sum_at(smem, slot, 1) + lane * 4, o1);
-            vec_store<4>(sum_at(smem, slot, 2) + lane * 4, o2);
-            vec_store<4>(sum_at(smem, slot, 3) + lane * 4, o3);
+            vec_store<4>(sum_at(smem, slot, 0) + lane * 4, join2(m[0].ar, m[1].ar));
+            vec_store<4>(sum_at(smem, slot, 1) + lane * 4, join2(m[0].ai, m[1].ai));
+            vec_store<4>(sum_at(smem, slot, 2) + lane * 4, join2(m[0].br, m[1].br));
+            vec_store<4>(sum_at(smem, slot, 3) + lane * 4, join2(m[0].bi, m[1].bi));
         } else if constexpr (PH == 1) {
             if (thread < kGroup && tl.cg * kGroup + thread < C && tl.n > 0) {
                 Affine a = affine_identity();
@@ -1031,13 +1077,18 @@ struct BwdRecompute {
                 }
             }
         } else if constexpr (PH == 3) {
-            Vec<4> dtr = vec_fill<4>(0.0f), dti = vec_fill<4>(0.0f), dgm = vec_fill<4>(0.0f);
+            const F2 zero2 = splat2(0.0f);
+            BwdAcc2 acc[2] = {{zero2, zero2, zero2, zero2}, {zero2, zero2, zero2, zero2}};
             if (chan_ok && tbeg < tend) {
                 const Vec<4> lr = vec_load<4>(p.tr + c0);
                 const Vec<4> li = vec_load<4>(p.ti + c0);
                 const Vec<4> gm = vec_load<4>(p.gamma + c0);
-                Vec<4> cr = vec_load<4>(carry_at(smem, slot, 0) + lane * 4);
-                Vec<4> ci = vec_load<4>(carry_at(smem, slot, 1) + lane * 4);
+                const F2 lr2[2] = {lo2(lr), hi2(lr)}, li2[2] = {lo2(li), hi2(li)};
+                const F2 nli2[2] = {mul2(li2[0], splat2(-1.0f)), mul2(li2[1], splat2(-1.0f))};
+                const F2 gm2[2] = {lo2(gm), hi2(gm)};
+                const Vec<4> cr4 = vec_load<4>(carry_at(smem, slot, 0) + lane * 4);
+                const Vec<4> ci4 = vec_load<4>(carry_at(smem, slot, 1) + lane * 4);
+                F2 cr[2] = {lo2(cr4), hi2(cr4)}, ci[2] = {lo2(ci4), hi2(ci4)};
                 IO* obase = p.grad_raw + ((size_t)tl.b * s.L) * 3 * C + c0;
                 // rows descend; the pointers may step below the tile after the last batch
                 int t_issue = tend;
@@ -1073,45 +1124,26 @@ struct BwdRecompute {
                             const Vec<4> gi = cell_load4<IO>(cell_at(smem, stage, u * 7 + 6, thread));
                             const Vec<4> pr = vec_load<4>(stash_at(smem, t - tbeg, 0, thread));
                             const Vec<4> pi = vec_load<4>(stash_at(smem, t - tbeg, 1, thread));
-                            Vec<4> ozr, ozi, ozv;
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                const Gate g = make_gate(zr.v[k], zi.v[k], zv.v[k]);
-                                const float keep = 1.0f - g.vac;
-                                const float Gr = ur.v[k] + cr.v[k];
-                                const float Gi = ui.v[k] + ci.v[k];
-                                const float gdr = gr.v[k], gdi = gi.v[k];
-                                const float sr = pr.v[k], si = pi.v[k];
-                                // m = lambda s_prev;  H = keep G + v gd
-                                float mr, mi, ar_, ai_;
-                                cmul(lr.v[k], li.v[k], sr, si, mr, mi);
-                                const float Hr = keep * Gr + g.vac * gdr;
-                                const float Hi = keep * Gi + g.vac * gdi;
-                                // d lambda += H conj(s_prev);  carry <- conj(lambda) H
-                                cmul_conj(sr, si, Hr, Hi, ar_, ai_);
-                                dtr.v[k] += ar_;
-                                dti.v[k] += ai_;
-                                dgm.v[k] += g.vac * (g.inj_r * Gr + g.inj_i * Gi);
-                                // dv = G . (gamma inj - m) + gd . m
-                                const float dv = Gr * (gm.v[k] * g.inj_r - mr) +
-                                                 Gi * (gm.v[k] * g.inj_i - mi) + gdr * mr + gdi * mi;
-                                const float bs = gm.v[k] * g.vac;
-                                ozr.v[k] = bs * Gr * (1.0f - g.inj_r * g.inj_r);
-                                ozi.v[k] = bs * Gi * (1.0f - g.inj_i * g.inj_i);
-                                ozv.v[k] = dv * (g.vac - g.vac * g.sig);
-                                cmul_conj(lr.v[k], li.v[k], Hr, Hi, cr.v[k], ci.v[k]);
-                            }
+                            F2 ozr[2], ozi[2], ozv[2];
+                            bwd_step2(lo2(zr), lo2(zi), lo2(zv), lo2(ur), lo2(ui), lo2(gr), lo2(gi),
+                                      lo2(pr), lo2(pi), lr2[0], li2[0], nli2[0], gm2[0], cr[0], ci[0],
+                                      acc[0], ozr[0], ozi[0], ozv[0]);
+                            bwd_step2(hi2(zr), hi2(zi), hi2(zv), hi2(ur), hi2(ui), hi2(gr), hi2(gi),
+                                      hi2(pr), hi2(pi), lr2[1], li2[1], nli2[1], gm2[1], cr[1], ci[1],
+                                      acc[1], ozr[1], ozi[1], ozv[1]);
                             IO* orow = obase + (size_t)t * 3 * C;
-                            io_store4_stream(orow, ozr);
-                            io_store4_stream(orow + C, ozi);
-                            io_store4_stream(orow + 2 * C, ozv);
+                            io_store4_stream(orow, join2(ozr[0], ozr[1]));
+                            io_store4_stream(orow + C, join2(ozi[0], ozi[1]));
+                            io_store4_stream(orow + 2 * C, join2(ozv[0], ozv[1]));
                         }
                     }
                 }
             }
-            vec_store<4>(sum_at(smem, warp, 0) + lane * 4, dtr);
-            vec_store<4>(sum_at(smem, warp, 1) + lane * 4, dti);
-            vec_store<4>(sum_at(smem, warp, 2) + lane * 4, dgm);
+            const F2 mone = splat2(-1.0f);
+            vec_store<4>(sum_at(smem, warp, 0) + lane * 4, join2(acc[0].dtr, acc[1].dtr));
+            vec_store<4>(sum_at(smem, warp, 1) + lane * 4,
+                         join2(fma2(acc[0].dtib, mone, acc[0].dtia), fma2(acc[1].dtib, mone, acc[1].dtia)));
+            vec_store<4>(sum_at(smem, warp, 2) + lane * 4, join2(acc[0].dgm, acc[1].dgm));
         } else {  // PH == 4: one partial row per tile, warps added in a fixed order
             const int ch = tl.cg * kGroup + thread;
             if (thread < kGroup && ch < C) {
