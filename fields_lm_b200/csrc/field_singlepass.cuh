@@ -1163,6 +1163,224 @@ struct BwdRecompute {
 
 
 // ---------------------------------------------------------------------------
+// Backward with the whole tile resident in shared memory and recomputed states.
+// A block issues, at its very start, the asynchronous copies of ALL seven input planes of
+// its tile (one commit group per step), so a tile costs one memory latency instead of one
+// per ring refill, and nothing is read twice: both sweeps work from shared memory.
+//   sweep 1 (forward in time)  as soon as a step has landed: gates, the state recurrence
+//            from the saved row just before the warp's first step (s_{t-1} of every step
+//            stays in registers), and the dual map;
+//   publish, look back, publish the carry (as in BwdSinglePass);
+//   sweep 2 (backward in time) from shared memory and the registers: grad_raw and the
+//            parameter-gradient partial sums.
+// HBM traffic per channel-step: 28 B read + 8/TS B (saved rows) + 12 B written.
+// Shared memory per block: TS * 7 cells of 16 B per thread (56 KB at TS = 4, 4 warps).
+// ---------------------------------------------------------------------------
+template <int TS, int WARPS, int MIN_BLOCKS, typename IO = float>
+struct BwdTileResident {
+    using Params = SpBwdParamsT<IO>;
+    static constexpr int kThreads = 32 * WARPS;
+    static constexpr int kMinBlocks = MIN_BLOCKS;
+    static constexpr int kTile = TS * WARPS;
+    static constexpr int kPhases = 5;
+    static constexpr int kSplitPhase = 2;
+    static constexpr int kSumFloats = WARPS * 4 * kGroup;
+    static constexpr int kCarryFloats = WARPS * 2 * kGroup;
+    static constexpr int kCellFloats = TS * 7 * kThreads * 4;
+    static constexpr int kSmemFloats = kSumFloats + kCarryFloats + kCellFloats;
+    static constexpr int kClaimAfter = 2;
+    FL_HD static constexpr bool barrier_after(int ph) { return ph != 1; }
+    static_assert(kThreads >= kGroup, "one thread per channel is needed for the look-back");
+    static_assert(TS <= 8, "one copy group per step, at most eight pending");
+
+    struct State {
+        F2 sr[TS][2], si[TS][2];  // s_{t-1} of the warp's steps, two channel pairs each
+    };
+
+    FL_HD static float* sum_at(float* smem, int w, int k) { return smem + (w * 4 + k) * kGroup; }
+    FL_HD static float* carry_at(float* smem, int w, int k) {
+        return smem + kSumFloats + (w * 2 + k) * kGroup;
+    }
+    // plane q (0..2 raw, 3..6 grad_read) of the warp's step j
+    FL_HD static float* cell_at(float* smem, int j, int q, int thread) {
+        return smem + kSumFloats + kCarryFloats + ((size_t)(j * 7 + q) * kThreads + thread) * 4;
+    }
+    FL_HD static void prefetch(const Params&, int, int) {}
+
+    template <int PH>
+    FL_HD static void phase(const Params& p, int block, int thread, float* smem, State& st) {
+        const SpShape& s = p.s;
+        const SpTile tl = sp_decode(s, (unsigned)block);
+        const int time_tile = s.NT - 1 - tl.n;
+        const int lane = thread & 31, warp = thread >> 5;
+        const int slot = WARPS - 1 - warp;  // position of this warp's steps in scan order
+        const int C = s.C;
+        const int c0 = tl.cg * kGroup + lane * 4;
+        const bool chan_ok = c0 < C;
+        const int tbeg = time_tile * kTile + warp * TS;
+        const int tend = tbeg + TS < s.L ? tbeg + TS : s.L;
+
+        if constexpr (PH == 0) {
+            Affine2 m[2] = {affine2_identity(), affine2_identity()};
+            if (chan_ok && tbeg < tend) {
+                const IO* zrow = p.raw + ((size_t)tl.b * s.L + tbeg) * 3 * C + c0;
+                const IO* grow = p.grad_read + ((size_t)tl.b * s.L + tbeg) * 4 * C + c0;
+#pragma unroll
+                for (int j = 0; j < TS; ++j) {
+                    if (tbeg + j < tend) {
+                        async_copy4(cell_at(smem, j, 0, thread), zrow);
+                        async_copy4(cell_at(smem, j, 1, thread), zrow + C);
+                        async_copy4(cell_at(smem, j, 2, thread), zrow + 2 * C);
+                        async_copy4(cell_at(smem, j, 3, thread), grow);
+                        async_copy4(cell_at(smem, j, 4, thread), grow + C);
+                        async_copy4(cell_at(smem, j, 5, thread), grow + 2 * C);
+                        async_copy4(cell_at(smem, j, 6, thread), grow + 3 * C);
+                    }
+                    async_commit();
+                    zrow += (size_t)3 * C;
+                    grow += (size_t)4 * C;
+                }
+                const Vec<4> lr = vec_load<4>(p.tr + c0);
+                const Vec<4> li = vec_load<4>(p.ti + c0);
+                const Vec<4> gm = vec_load<4>(p.gamma + c0);
+                const F2 lr2[2] = {lo2(lr), hi2(lr)}, li2[2] = {lo2(li), hi2(li)};
+                const F2 nli2[2] = {mul2(li2[0], splat2(-1.0f)), mul2(li2[1], splat2(-1.0f))};
+                const F2 gm2[2] = {lo2(gm), hi2(gm)};
+                // the state just before the warp's first step
+                Vec<4> sr4, si4;
+                if (tbeg > 0) {
+                    const IO* prow = p.read + ((size_t)tl.b * s.L + tbeg - 1) * 4 * C + c0;
+                    sr4 = io_load4(prow);
+                    si4 = io_load4(prow + C);
+                } else if (p.state_in) {
+                    const float* prow = p.state_in + (size_t)tl.b * 2 * C + c0;
+                    sr4 = vec_load<4>(prow);
+                    si4 = vec_load<4>(prow + C);
+                } else {
+                    sr4 = vec_fill<4>(0.0f);
+                    si4 = vec_fill<4>(0.0f);
+                }
+                F2 sr[2] = {lo2(sr4), hi2(sr4)}, si[2] = {lo2(si4), hi2(si4)};
+#pragma unroll
+                for (int j = 0; j < TS; ++j) {
+                    if (tbeg + j < tend) {
+                        async_wait_pending_dyn(TS - 1 - j);
+                        const Vec<4> zr = cell_load4<IO>(cell_at(smem, j, 0, thread));
+                        const Vec<4> zi = cell_load4<IO>(cell_at(smem, j, 1, thread));
+                        const Vec<4> zv = cell_load4<IO>(cell_at(smem, j, 2, thread));
+                        const Vec<4> ur = cell_load4<IO>(cell_at(smem, j, 3, thread));
+                        const Vec<4> ui = cell_load4<IO>(cell_at(smem, j, 4, thread));
+                        const Vec<4> gr = cell_load4<IO>(cell_at(smem, j, 5, thread));
+                        const Vec<4> gi = cell_load4<IO>(cell_at(smem, j, 6, thread));
+                        st.sr[j][0] = sr[0]; st.sr[j][1] = sr[1];
+                        st.si[j][0] = si[0]; st.si[j][1] = si[1];
+                        recompute_step2(m[0], sr[0], si[0], lo2(zr), lo2(zi), lo2(zv), lo2(ur), lo2(ui),
+                                        lo2(gr), lo2(gi), lr2[0], li2[0], nli2[0], gm2[0]);
+                        recompute_step2(m[1], sr[1], si[1], hi2(zr), hi2(zi), hi2(zv), hi2(ur), hi2(ui),
+                                        hi2(gr), hi2(gi), lr2[1], li2[1], nli2[1], gm2[1]);
+                    }
+                }
+            }
+            vec_store<4>(sum_at(smem, slot, 0) + lane * 4, join2(m[0].ar, m[1].ar));
+            vec_store<4>(sum_at(smem, slot, 1) + lane * 4, join2(m[0].ai, m[1].ai));
+            vec_store<4>(sum_at(smem, slot, 2) + lane * 4, join2(m[0].br, m[1].br));
+            vec_store<4>(sum_at(smem, slot, 3) + lane * 4, join2(m[0].bi, m[1].bi));
+        } else if constexpr (PH == 1) {
+            if (thread < kGroup && tl.cg * kGroup + thread < C && tl.n > 0) {
+                Affine a = affine_identity();
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w)
+                    a = affine_then(a, sum_at(smem, w, 0)[thread], sum_at(smem, w, 1)[thread],
+                                    sum_at(smem, w, 2)[thread], sum_at(smem, w, 3)[thread]);
+                publish4(p.agg + ((size_t)tl.idx * kGroup + thread) * 4, a.ar, a.ai, a.br, a.bi);
+            }
+        } else if constexpr (PH == 2) {
+            const int ch = tl.cg * kGroup + thread;
+            if (thread < kGroup && ch < C) {
+                float sr, si;
+                if (tl.n == 0) {
+                    sr = p.grad_state_out ? p.grad_state_out[(size_t)tl.b * 2 * C + ch] : 0.0f;
+                    si = p.grad_state_out ? p.grad_state_out[(size_t)tl.b * 2 * C + C + ch] : 0.0f;
+                } else {
+                    look_back(p.agg, p.incl, tl.chain * s.NT, tl.n, thread, p.ctrl, s.max_polls, sr, si);
+                }
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) {
+                    carry_at(smem, w, 0)[thread] = sr;
+                    carry_at(smem, w, 1)[thread] = si;
+                    affine_apply(Affine{sum_at(smem, w, 0)[thread], sum_at(smem, w, 1)[thread],
+                                        sum_at(smem, w, 2)[thread], sum_at(smem, w, 3)[thread]},
+                                 sr, si);
+                }
+                publish2(p.incl + ((size_t)tl.idx * kGroup + thread) * 2, sr, si);
+                if (p.grad_state_in && tl.n == s.NT - 1) {
+                    p.grad_state_in[(size_t)tl.b * 2 * C + ch] = sr;
+                    p.grad_state_in[(size_t)tl.b * 2 * C + C + ch] = si;
+                }
+            }
+        } else if constexpr (PH == 3) {
+            const F2 zero2 = splat2(0.0f);
+            BwdAcc2 acc[2] = {{zero2, zero2, zero2, zero2}, {zero2, zero2, zero2, zero2}};
+            if (chan_ok && tbeg < tend) {
+                const Vec<4> lr = vec_load<4>(p.tr + c0);
+                const Vec<4> li = vec_load<4>(p.ti + c0);
+                const Vec<4> gm = vec_load<4>(p.gamma + c0);
+                const F2 lr2[2] = {lo2(lr), hi2(lr)}, li2[2] = {lo2(li), hi2(li)};
+                const F2 nli2[2] = {mul2(li2[0], splat2(-1.0f)), mul2(li2[1], splat2(-1.0f))};
+                const F2 gm2[2] = {lo2(gm), hi2(gm)};
+                const Vec<4> cr4 = vec_load<4>(carry_at(smem, slot, 0) + lane * 4);
+                const Vec<4> ci4 = vec_load<4>(carry_at(smem, slot, 1) + lane * 4);
+                F2 cr[2] = {lo2(cr4), hi2(cr4)}, ci[2] = {lo2(ci4), hi2(ci4)};
+                IO* obase = p.grad_raw + ((size_t)tl.b * s.L) * 3 * C + c0;
+#pragma unroll
+                for (int j = TS - 1; j >= 0; --j) {
+                    const int t = tbeg + j;
+                    if (t < tend) {
+                        const Vec<4> zr = cell_load4<IO>(cell_at(smem, j, 0, thread));
+                        const Vec<4> zi = cell_load4<IO>(cell_at(smem, j, 1, thread));
+                        const Vec<4> zv = cell_load4<IO>(cell_at(smem, j, 2, thread));
+                        const Vec<4> ur = cell_load4<IO>(cell_at(smem, j, 3, thread));
+                        const Vec<4> ui = cell_load4<IO>(cell_at(smem, j, 4, thread));
+                        const Vec<4> gr = cell_load4<IO>(cell_at(smem, j, 5, thread));
+                        const Vec<4> gi = cell_load4<IO>(cell_at(smem, j, 6, thread));
+                        F2 ozr[2], ozi[2], ozv[2];
+                        bwd_step2(lo2(zr), lo2(zi), lo2(zv), lo2(ur), lo2(ui), lo2(gr), lo2(gi),
+                                  st.sr[j][0], st.si[j][0], lr2[0], li2[0], nli2[0], gm2[0], cr[0], ci[0],
+                                  acc[0], ozr[0], ozi[0], ozv[0]);
+                        bwd_step2(hi2(zr), hi2(zi), hi2(zv), hi2(ur), hi2(ui), hi2(gr), hi2(gi),
+                                  st.sr[j][1], st.si[j][1], lr2[1], li2[1], nli2[1], gm2[1], cr[1], ci[1],
+                                  acc[1], ozr[1], ozi[1], ozv[1]);
+                        IO* orow = obase + (size_t)t * 3 * C;
+                        io_store4_stream(orow, join2(ozr[0], ozr[1]));
+                        io_store4_stream(orow + C, join2(ozi[0], ozi[1]));
+                        io_store4_stream(orow + 2 * C, join2(ozv[0], ozv[1]));
+                    }
+                }
+            }
+            const F2 mone = splat2(-1.0f);
+            vec_store<4>(sum_at(smem, warp, 0) + lane * 4, join2(acc[0].dtr, acc[1].dtr));
+            vec_store<4>(sum_at(smem, warp, 1) + lane * 4,
+                         join2(fma2(acc[0].dtib, mone, acc[0].dtia), fma2(acc[1].dtib, mone, acc[1].dtia)));
+            vec_store<4>(sum_at(smem, warp, 2) + lane * 4, join2(acc[0].dgm, acc[1].dgm));
+        } else {  // PH == 4: one partial row per tile, warps added in a fixed order
+            const int ch = tl.cg * kGroup + thread;
+            if (thread < kGroup && ch < C) {
+                const size_t plane = (size_t)s.B * s.NT * C;
+                float* out = p.partial + ((size_t)tl.b * s.NT + time_tile) * C + ch;
+#pragma unroll
+                for (int k = 0; k < 3; ++k) {
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < WARPS; ++w) acc += sum_at(smem, w, k)[thread];
+                    out[k * plane] = acc;
+                }
+            }
+        }
+    }
+};
+
+
+// ---------------------------------------------------------------------------
 // Self-test of the bounded wait: one block looks back over a chain in which nothing was
 // ever published. Every thread must give up after `max_polls` polls, record the error
 // word and return NaN; the kernel ends normally. Used by the tests to check, without

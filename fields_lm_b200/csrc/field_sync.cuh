@@ -135,6 +135,25 @@ FL_HD void async_wait_pending() {
 #endif
 }
 
+// Waits until at most `n` of this thread's copy groups are still pending (n known only at
+// run time; the instruction wants an immediate).
+FL_HD void async_wait_pending_dyn(int n) {
+#if FL_DEVICE_CODE
+    switch (n) {
+        case 0: async_wait_pending<0>(); break;
+        case 1: async_wait_pending<1>(); break;
+        case 2: async_wait_pending<2>(); break;
+        case 3: async_wait_pending<3>(); break;
+        case 4: async_wait_pending<4>(); break;
+        case 5: async_wait_pending<5>(); break;
+        case 6: async_wait_pending<6>(); break;
+        default: async_wait_pending<7>(); break;
+    }
+#else
+    (void)n;
+#endif
+}
+
 // Asks the memory system to bring one 128-byte line into L2 (no register, no wait).
 FL_HD void prefetch_l2(const void* p) {
 #if FL_DEVICE_CODE

@@ -421,40 +421,22 @@ static Algo algo_from_env() {
 // Instantiations of the single-pass kernels. The first of each list is the default; the
 // others are tuning alternatives selected with FIELDS_FWD_VARIANT / FIELDS_BWD_VARIANT.
 //   forward  <steps per warp, warps, blocks per SM the registers must allow>
-using FwdSp0 = FwdSinglePass<6, 8, 2>;   // tile 48 steps, 128 registers, no spills
-using FwdSp1 = FwdSinglePass<8, 8, 2>;   // tile 64
-using FwdSp2 = FwdSinglePass<4, 8, 3>;   // tile 32, 3 blocks per SM
-using FwdSp3 = FwdSinglePass<7, 8, 2>;   // tile 56
-using FwdSp4 = FwdSinglePass<5, 8, 2>;   // tile 40
-using FwdSp5 = FwdSinglePass<4, 8, 2>;   // tile 32, 2 blocks per SM
+using FwdSp0 = FwdSinglePass<6, 8, 2>;        // tile 48 steps, 128 registers, no spills
+using FwdSp1 = FwdSinglePass<4, 8, 2>;        // tile 32
 //   two-sweep forward <steps per warp, warps, unroll, blocks per SM, ring slots>
-using FwdSp6 = FwdTwoSweep<8, 4, 2, 4, 3>;    // tile 32, 16 warps per SM
-using FwdSp7 = FwdTwoSweep<16, 4, 2, 4, 3>;   // tile 64
-using FwdSp8 = FwdTwoSweep<8, 8, 2, 2, 3>;    // tile 64, 8 warps per block
-using FwdSp9 = FwdTwoSweep<8, 4, 1, 5, 4>;    // tile 32, one step per batch, 4-slot ring
-//   backward <steps per warp, warps, sweep-1 unroll, sweep-2 unroll, blocks per SM>
+using FwdSp2 = FwdTwoSweep<8, 4, 2, 4, 3>;    // tile 32, 16 warps per SM
+//   backward <steps per warp, warps, sweep-1 unroll, sweep-2 unroll, blocks per SM, rings, ring slots>
 using BwdSp0 = BwdSinglePass<8, 4, 2, 1, 3, true, 3>;  // tile 32, 3-slot cp.async rings, 12 warps per SM
-using BwdSp1 = BwdSinglePass<8, 4, 2, 1, 4>;    // 127 registers, 16 warps per SM
-using BwdSp2 = BwdSinglePass<16, 4, 2, 1, 5>;   // tile 64
-using BwdSp3 = BwdSinglePass<8, 4, 4, 2, 2>;    // deep unroll, 8 warps per SM
-using BwdSp4 = BwdSinglePass<8, 4, 1, 1, 6>;    // shallow unroll, 24 warps per SM
-using BwdSp5 = BwdSinglePass<4, 8, 2, 1, 2>;    // 8 warps per block
-using BwdSp6 = BwdSinglePass<8, 4, 2, 1, 4, true>;   // cp.async rings, 40 KB + 12 KB per block
-using BwdSp7 = BwdSinglePass<8, 4, 2, 2, 3, true>;   // rings, two steps per batch in sweep 2
-using BwdSp8 = BwdSinglePass<16, 4, 2, 1, 4, true>;  // rings, tile 64
-using BwdSp9 = BwdSinglePass<8, 4, 1, 1, 3, true, 3>;   // 3-slot rings, one step per batch
-using BwdSp10 = BwdSinglePass<8, 4, 2, 1, 5>;   // direct loads, 96 registers, 20 warps per SM
-using BwdSp11 = BwdSinglePass<8, 4, 1, 1, 4, true, 2>;  // 2-slot rings, one step per batch
-using BwdSp12 = BwdSinglePass<8, 8, 2, 1, 2, true, 2>;  // 8 warps per block
+using BwdSp1 = BwdSinglePass<8, 4, 2, 1, 4>;           // direct loads, 16 warps per SM
 //   backward with recomputed states <steps per warp, warps, steps per ring slot, blocks per SM, ring slots>
-using BwdSp13 = BwdRecompute<8, 4, 1, 3, 2>;  // 73 KB per block, 12 warps per SM
-using BwdSp14 = BwdRecompute<8, 4, 1, 2, 3>;  // 3-slot rings, 8 warps per SM
-using BwdSp15 = BwdRecompute<8, 4, 2, 2, 2>;  // two steps per slot
-using BwdSp16 = BwdRecompute<4, 8, 1, 2, 2>;  // 8 warps per block, 16 warps per SM
+using BwdSp2 = BwdRecompute<8, 4, 1, 3, 2>;   // 73 KB per block, 12 warps per SM
+//   tile resident in shared memory, recomputed states <steps per warp, warps, blocks per SM>
+using BwdSp3 = BwdTileResident<4, 4, 3>;      // tile 16, 68 KB per block, 12 warps per SM
 //   bfloat16 raw / read / grad_read / grad_raw (bits as uint16_t); state and arithmetic stay fp32
 using FwdSpBf16 = FwdSinglePass<6, 8, 2, uint16_t>;
 using BwdSpBf16 = BwdSinglePass<8, 4, 2, 1, 3, true, 3, uint16_t>;
-constexpr int kSpMinTile = 32;  // smallest time tile of any instantiation above (workspace bound)
+constexpr int kSpMinTile = 32;     // smallest time tile of any forward instantiation above (workspace bound)
+constexpr int kSpMinTileBwd = 16;  // same for the backward
 
 static int variant_from_env(const char* name) {
     const char* e = std::getenv(name);
@@ -526,16 +508,7 @@ static size_t sp_backward_bytes(int B, int L, int C, int tile_steps) {
 // matter more than speed. No workspace except one partial row per chain (backward).
 // ---------------------------------------------------------------------------
 using FwdWalker = FwdWalk<16, 8, 3>;   // tile 128 steps, 3 x 48 KB ring, 8 warps
-using FwdWalkerB = FwdWalk<8, 16, 3>;  // same tile, 16 warps
 using BwdWalker = BwdWalk<4, 8, 4>;    // tile 32 steps, 4 x 36 KB ring, 8 warps
-using BwdWalkerB = BwdWalk<8, 8, 3>;   // tile 64 steps, 3 x 72 KB ring
-using BwdWalkerC = BwdWalk<4, 16, 3>;  // tile 64 steps, 16 warps
-
-// FIELDS_WALK_VARIANT = 0 | 1 | 2 picks among the instantiations above (tuning aid).
-static int walk_variant_from_env() {
-    const char* e = std::getenv("FIELDS_WALK_VARIANT");
-    return e ? std::atoi(e) : 0;
-}
 
 template <class K>
 static WalkShape walk_shape(int B, int L, int C) {
@@ -613,7 +586,7 @@ size_t fields_read_workspace_bytes(int B, int L, int C, int pass) {
     const Plan pl = make_plan(B, L, C, 1);
     const size_t floats = pass == FIELDS_PASS_BACKWARD ? pl.bwd_floats : pl.fwd_floats;
     size_t bytes = floats * sizeof(float);
-    const size_t sp = pass == FIELDS_PASS_BACKWARD ? sp_backward_bytes(B, L, C, kSpMinTile)
+    const size_t sp = pass == FIELDS_PASS_BACKWARD ? sp_backward_bytes(B, L, C, kSpMinTileBwd)
                                                    : make_sp_plan(B, L, C, kSpMinTile).bytes;
     return sp > bytes ? sp : bytes;
 }
@@ -649,10 +622,7 @@ int fields_read_forward(const float* raw, const float* tr, const float* ti, cons
     const Algo algo = algo_from_env();
     if (vec4 && walk_wanted(B, C, algo)) {
         WalkFwdParams wp{raw, tr, ti, gamma, state_in, read, state_out,
-                         walk_shape<FwdWalker>(B, L, C)};  // both variants share the tile length
-        static_assert(FwdWalker::kTile == FwdWalkerB::kTile, "variants must share the tile");
-        if (walk_variant_from_env() == 1)
-            return launch_walk<FwdWalkerB>(wp, (long long)B * wp.s.G, st);
+                         walk_shape<FwdWalker>(B, L, C)};
         return launch_walk<FwdWalker>(wp, (long long)B * wp.s.G, st);
     }
     if (vec4 && algo != kAlgoThreePhase) {
@@ -662,13 +632,6 @@ int fields_read_forward(const float* raw, const float* tr, const float* ti, cons
         switch (variant_from_env("FIELDS_FWD_VARIANT")) {
             case 1: FIELDS_FWD_SP(FwdSp1);
             case 2: FIELDS_FWD_SP(FwdSp2);
-            case 3: FIELDS_FWD_SP(FwdSp3);
-            case 4: FIELDS_FWD_SP(FwdSp4);
-            case 5: FIELDS_FWD_SP(FwdSp5);
-            case 6: FIELDS_FWD_SP(FwdSp6);
-            case 7: FIELDS_FWD_SP(FwdSp7);
-            case 8: FIELDS_FWD_SP(FwdSp8);
-            case 9: FIELDS_FWD_SP(FwdSp9);
             default: FIELDS_FWD_SP(FwdSp0);
         }
 #undef FIELDS_FWD_SP
@@ -719,15 +682,9 @@ int fields_read_backward(const float* raw, const float* tr, const float* ti, con
         return FIELDS_ERR_WORKSPACE;
     if (vec4 && walk_wanted(B, C, algo_from_env())) {
         float* partial = static_cast<float*>(workspace);
-        const int variant = walk_variant_from_env();
         WalkBwdParams wp{raw, tr, ti, gamma, state_in, read, grad_read, grad_state_out, grad_raw,
-                         grad_state_in, partial,
-                         variant == 0 ? walk_shape<BwdWalker>(B, L, C)
-                                      : walk_shape<BwdWalkerB>(B, L, C)};
-        static_assert(BwdWalkerB::kTile == BwdWalkerC::kTile, "variants must share the tile");
-        int rc = variant == 1   ? launch_walk<BwdWalkerB>(wp, (long long)B * wp.s.G, st)
-                 : variant == 2 ? launch_walk<BwdWalkerC>(wp, (long long)B * wp.s.G, st)
-                                : launch_walk<BwdWalker>(wp, (long long)B * wp.s.G, st);
+                         grad_state_in, partial, walk_shape<BwdWalker>(B, L, C)};
+        int rc = launch_walk<BwdWalker>(wp, (long long)B * wp.s.G, st);
         if (rc) return rc;
         BwdParams rp{};
         rp.partial = partial;
@@ -744,19 +701,6 @@ int fields_read_backward(const float* raw, const float* tr, const float* ti, con
             case 1: FIELDS_BWD_SP(BwdSp1);
             case 2: FIELDS_BWD_SP(BwdSp2);
             case 3: FIELDS_BWD_SP(BwdSp3);
-            case 4: FIELDS_BWD_SP(BwdSp4);
-            case 5: FIELDS_BWD_SP(BwdSp5);
-            case 6: FIELDS_BWD_SP(BwdSp6);
-            case 7: FIELDS_BWD_SP(BwdSp7);
-            case 8: FIELDS_BWD_SP(BwdSp8);
-            case 9: FIELDS_BWD_SP(BwdSp9);
-            case 10: FIELDS_BWD_SP(BwdSp10);
-            case 11: FIELDS_BWD_SP(BwdSp11);
-            case 12: FIELDS_BWD_SP(BwdSp12);
-            case 13: FIELDS_BWD_SP(BwdSp13);
-            case 14: FIELDS_BWD_SP(BwdSp14);
-            case 15: FIELDS_BWD_SP(BwdSp15);
-            case 16: FIELDS_BWD_SP(BwdSp16);
             default: FIELDS_BWD_SP(BwdSp0);
         }
 #undef FIELDS_BWD_SP

@@ -20,15 +20,10 @@ def _params(C, rng):
 
 
 ALGOS = [("three_phase", "0", "forward"), ("single_pass", "0", "forward"),
-         ("single_pass", "0", "reverse"), ("single_pass", "1", "reverse"),
+         ("single_pass", "0", "reverse"), ("single_pass", "1", "forward"),
+         ("single_pass", "1", "reverse"), ("single_pass", "2", "forward"),
          ("single_pass", "2", "reverse"), ("single_pass", "3", "forward"),
-         ("single_pass", "4", "reverse"), ("single_pass", "5", "forward"),
-         ("single_pass", "6", "reverse"), ("single_pass", "7", "forward"),
-         ("single_pass", "8", "reverse"), ("single_pass", "9", "forward"),
-         ("single_pass", "10", "reverse"), ("single_pass", "11", "forward"),
-         ("single_pass", "12", "reverse"), ("single_pass", "13", "forward"),
-         ("single_pass", "13", "reverse"), ("single_pass", "14", "reverse"),
-         ("single_pass", "15", "forward"), ("single_pass", "16", "reverse"),
+         ("single_pass", "3", "reverse"),
          ("walk", "0", "forward")]
 
 
