@@ -42,8 +42,8 @@ FP32_TOL, BF16_TOL = 1e-5, 2e-2
 KERNEL_LAUNCHES_PER_STEP = 5   # forward: fill + kernel; backward: fill + kernel + parameter-gradient reduce
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per step from the ncu capture of this workload
-# (forward 102.2 + 134.2 MB, backward 317.6 + 100.7 MB; writes still in L2 at kernel end counted in full)
-NCU_DRAM_BYTES_PER_STEP = 654.7e6
+# (forward 102.2 + 134.2 MB, backward 323.3 + 100.7 MB; writes still in L2 at kernel end counted in full)
+NCU_DRAM_BYTES_PER_STEP = 660.4e6
 LONG_L = 65536
 
 
