@@ -30,6 +30,8 @@ SYMBOLS = {
     "fields_read_step_bf16": (_I, [_P] * 6 + [_I, _I, _P]),
     "fields_read_span_summary": (_I, [_P] * 6 + [_SZ, _I, _I, _I, _P]),
     "fields_read_fold_summaries": (_I, [_P, _P, _P, _I, _I, _I, _I, _P]),
+    "fields_read_span_summary_backward": (_I, [_P] * 6 + [_SZ, _I, _I, _I, _P]),
+    "fields_read_fold_summaries_backward": (_I, [_P, _P, _P, _I, _I, _I, _I, _P]),
     "fields_read_mailbox_bytes": (_SZ, [_I, _I, _I]),
     "fields_read_span_summary_put": (_I, [_P] * 6 + [_I, _I, ctypes.c_uint, _P, _SZ, _I, _I, _I, _P]),
     "fields_read_fold_mailbox": (_I, [_P, _P, _P, _P, _I, _I, ctypes.c_uint, _I, _I, _P]),

@@ -560,6 +560,7 @@ struct SpanCompose {
         const float* sum;  // [4][B][N][C]
         float* summary;    // [B][4][C]  Re A | Im A | Re B | Im B
         Shape s;
+        int reverse;       // non-zero: compose from the last chunk to the first (dual maps)
     };
     static constexpr int kThreads = 32 * kCarryWarps;
     static constexpr int kPhases = 2;
@@ -576,13 +577,15 @@ struct SpanCompose {
         const int lo = w * per < s.N ? w * per : s.N;
         const int hi = lo + per < s.N ? lo + per : s.N;
         const size_t plane = (size_t)s.B * s.N * s.C;
+        // position i in composition order is chunk i, or chunk N-1-i when composing backwards
+        const int first = p.reverse ? s.N - 1 : 0, step = p.reverse ? -1 : 1;
         Affine m = affine_identity();
         int i = lo;
         for (; i + 8 <= hi; i += 8) {  // eight maps in flight, composed in order
             float v[8][4];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const size_t idx = ((size_t)b * s.N + i + j) * s.C + c;
+                const size_t idx = ((size_t)b * s.N + first + step * (i + j)) * s.C + c;
                 v[j][0] = p.sum[idx]; v[j][1] = p.sum[idx + plane];
                 v[j][2] = p.sum[idx + 2 * plane]; v[j][3] = p.sum[idx + 3 * plane];
             }
@@ -590,7 +593,7 @@ struct SpanCompose {
             for (int j = 0; j < 8; ++j) m = affine_then(m, v[j][0], v[j][1], v[j][2], v[j][3]);
         }
         for (; i < hi; ++i) {
-            const size_t idx = ((size_t)b * s.N + i) * s.C + c;
+            const size_t idx = ((size_t)b * s.N + first + step * i) * s.C + c;
             m = affine_then(m, p.sum[idx], p.sum[idx + plane], p.sum[idx + 2 * plane],
                             p.sum[idx + 3 * plane]);
         }
@@ -625,6 +628,7 @@ struct FoldSummaries {
         const float* state0;     // [B, 2C] or null: state before the first span
         float* state;            // [B, 2C]
         int rank, P, B, C;
+        int reverse;  // non-zero: fold the ranks AFTER `rank`, last first (gradient carry)
     };
     static constexpr int kThreads = 128;
     static constexpr int kPhases = 1;
@@ -636,7 +640,9 @@ struct FoldSummaries {
         const int b = (int)(i / p.C), c = (int)(i % p.C);
         float sr = p.state0 ? p.state0[(size_t)b * 2 * p.C + c] : 0.0f;
         float si = p.state0 ? p.state0[(size_t)b * 2 * p.C + p.C + c] : 0.0f;
-        for (int r = 0; r < p.rank; ++r) {
+        const int count = p.reverse ? p.P - 1 - p.rank : p.rank;
+        for (int k = 0; k < count; ++k) {
+            const int r = p.reverse ? p.P - 1 - k : k;
             const float* m = p.summaries + (((size_t)r * p.B + b) * 4) * p.C + c;
             affine_apply(Affine{m[0], m[p.C], m[2 * (size_t)p.C], m[3 * (size_t)p.C]}, sr, si);
         }

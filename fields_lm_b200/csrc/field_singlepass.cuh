@@ -1575,7 +1575,7 @@ struct PutSummary {
     static constexpr int kSmemFloats = 4 * kThreads;
 
     FL_HD static void phase0(const Params& p, int block, int thread, float* smem) {
-        SpanCompose::Params q{p.sum, nullptr, p.s};
+        SpanCompose::Params q{p.sum, nullptr, p.s, 0};
         SpanCompose::phase0(q, block, thread, smem);
     }
 

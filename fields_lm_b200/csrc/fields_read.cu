@@ -779,7 +779,33 @@ int fields_read_span_summary(const float* raw, const float* tr, const float* ti,
         rc = launch<FwdSummary<1, 4>>(p, tile_blocks(pl.s), st);
     }
     if (rc) return rc;
-    SpanCompose::Params cp{p.sum, summary, pl.s};
+    SpanCompose::Params cp{p.sum, summary, pl.s, 0};
+    return launch<SpanCompose>(cp, (long long)B * ((C + 31) / 32), st);
+}
+
+int fields_read_span_summary_backward(const float* raw, const float* tr, const float* ti,
+                                      const float* grad_read, float* summary, void* workspace,
+                                      size_t workspace_bytes, int B, int L, int C, void* stream) {
+    if (B < 0 || L < 0 || C <= 0) return FIELDS_ERR_ARGUMENT;
+    if (B == 0) return FIELDS_OK;
+    if (!raw || !tr || !ti || !grad_read || !summary) return FIELDS_ERR_ARGUMENT;
+    if (L == 0) return FIELDS_ERR_ARGUMENT;
+    Stream st = reinterpret_cast<Stream>(stream);
+    const bool vec4 = C % 4 == 0 && aligned16(raw) && aligned16(tr) && aligned16(ti) &&
+                      aligned16(grad_read) && aligned16(workspace);
+    const Plan pl = make_plan(B, L, C, vec4 ? 4 : 1);
+    if (!workspace || workspace_bytes < pl.bwd_floats * sizeof(float) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return FIELDS_ERR_WORKSPACE;
+    float* ws = static_cast<float*>(workspace);
+    BwdParams p{};
+    p.raw = raw; p.tr = tr; p.ti = ti; p.grad_read = grad_read;
+    p.sum = ws + pl.sum_off;
+    p.s = pl.s;
+    const int rc = vec4 ? launch<BwdSummary<4, 4>>(p, tile_blocks(pl.s), st)
+                        : launch<BwdSummary<1, 4>>(p, tile_blocks(pl.s), st);
+    if (rc) return rc;
+    SpanCompose::Params cp{p.sum, summary, pl.s, 1};
     return launch<SpanCompose>(cp, (long long)B * ((C + 31) / 32), st);
 }
 
@@ -788,7 +814,18 @@ int fields_read_fold_summaries(const float* summaries, const float* state0, floa
     if (B < 0 || C <= 0 || P <= 0 || rank < 0 || rank >= P) return FIELDS_ERR_ARGUMENT;
     if (B == 0) return FIELDS_OK;
     if (!summaries || !state) return FIELDS_ERR_ARGUMENT;
-    FoldSummaries::Params p{summaries, state0, state, rank, P, B, C};
+    FoldSummaries::Params p{summaries, state0, state, rank, P, B, C, 0};
+    const long long n = (long long)B * C;
+    return launch<FoldSummaries>(p, (n + FoldSummaries::kThreads - 1) / FoldSummaries::kThreads,
+                                 reinterpret_cast<Stream>(stream));
+}
+
+int fields_read_fold_summaries_backward(const float* summaries, const float* carry_end, float* carry,
+                                        int rank, int P, int B, int C, void* stream) {
+    if (B < 0 || C <= 0 || P <= 0 || rank < 0 || rank >= P) return FIELDS_ERR_ARGUMENT;
+    if (B == 0) return FIELDS_OK;
+    if (!summaries || !carry) return FIELDS_ERR_ARGUMENT;
+    FoldSummaries::Params p{summaries, carry_end, carry, rank, P, B, C, 1};
     const long long n = (long long)B * C;
     return launch<FoldSummaries>(p, (n + FoldSummaries::kThreads - 1) / FoldSummaries::kThreads,
                                  reinterpret_cast<Stream>(stream));

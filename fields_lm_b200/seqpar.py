@@ -1,4 +1,4 @@
-"""Sequence-sharded forward of the Field read across the GPUs of one node.
+"""Sequence-sharded Field read (forward, and backward for training) across the GPUs of one node.
 
 A long sequence is cut into P contiguous spans, one per rank. The recurrence is an
 affine map per (batch, channel), so a span is summarised by one complex pair
@@ -13,6 +13,12 @@ Steps on rank r (all on the current CUDA stream):
   2. ``all_gather`` of the summaries over NCCL (NVLink/NVSwitch);
   3. ``fields_read_fold_summaries`` - state entering span r;
   4. ``fields_read_forward`` with that state.
+
+The backward pass mirrors this in reverse rank order (``sequence_parallel_field_read_autograd``):
+the gradient carry is an affine map per span as well (``carry_in = P carry_out + Q``), so ranks
+exchange dual summaries, every rank folds the spans AFTER it, last first, and runs
+``fields_read_backward`` on its span with that carry; the three parameter gradients are sums
+over spans (one all-reduce of 3 C floats).
 """
 from __future__ import annotations
 
@@ -54,6 +60,50 @@ class CudaOps:
         from .field_read import field_read_with_state
         with torch.no_grad():
             return field_read_with_state(raw, tr, ti, gamma, state_in)
+
+    def span_summary_backward(self, raw, tr, ti, grad_read):
+        lib = _lib.load()
+        B, L, C3 = raw.shape
+        C = C3 // 3
+        out = torch.empty((B, 4, C), device=raw.device, dtype=torch.float32)
+        n = lib.fields_read_workspace_bytes(B, L, C, 1)
+        ws = torch.empty(max(n, 256), dtype=torch.uint8, device=raw.device)
+        rc = lib.fields_read_span_summary_backward(
+            raw.data_ptr(), tr.data_ptr(), ti.data_ptr(), grad_read.data_ptr(), out.data_ptr(),
+            ws.data_ptr(), n, B, L, C, torch.cuda.current_stream(raw.device).cuda_stream)
+        _lib.check(rc, "fields_read_span_summary_backward")
+        return out
+
+    def fold_backward(self, summaries, rank, carry_end):
+        lib = _lib.load()
+        P, B, _, C = summaries.shape
+        out = torch.empty((B, 2 * C), device=summaries.device, dtype=torch.float32)
+        rc = lib.fields_read_fold_summaries_backward(
+            summaries.data_ptr(), None if carry_end is None else carry_end.data_ptr(),
+            out.data_ptr(), rank, P, B, C,
+            torch.cuda.current_stream(summaries.device).cuda_stream)
+        _lib.check(rc, "fields_read_fold_summaries_backward")
+        return out
+
+    def backward(self, raw, tr, ti, gamma, read, grad_read, state_in, grad_state_out):
+        """Returns ``(grad_raw, grad_params [3, C], grad_state_in [B, 2C])`` of one span."""
+        lib = _lib.load()
+        B, L, C3 = raw.shape
+        C = C3 // 3
+        grad_raw = torch.empty_like(raw)
+        g_par = torch.empty((3, C), device=raw.device, dtype=torch.float32)
+        g_sin = torch.empty((B, 2 * C), device=raw.device, dtype=torch.float32)
+        n = lib.fields_read_workspace_bytes(B, L, C, 1)
+        ws = torch.empty(max(n, 256), dtype=torch.uint8, device=raw.device)
+        rc = lib.fields_read_backward(
+            raw.data_ptr(), tr.data_ptr(), ti.data_ptr(), gamma.data_ptr(),
+            None if state_in is None else state_in.data_ptr(), read.data_ptr(),
+            grad_read.data_ptr(), None if grad_state_out is None else grad_state_out.data_ptr(),
+            grad_raw.data_ptr(), g_par[0].data_ptr(), g_par[1].data_ptr(), g_par[2].data_ptr(),
+            g_sin.data_ptr(), ws.data_ptr(), n, B, L, C,
+            torch.cuda.current_stream(raw.device).cuda_stream)
+        _lib.check(rc, "fields_read_backward")
+        return grad_raw, g_par, g_sin
 
 
 class SequenceParallelForward:
@@ -199,3 +249,66 @@ def sequence_parallel_field_read(raw_span: torch.Tensor, tr: torch.Tensor, ti: t
     dist.all_gather_into_tensor(gathered, summary, group=group)  # rank-major along dim 0
     state_in = ops.fold(gathered.view(world, B, *summary.shape[1:]), rank, state0)
     return ops.forward(raw_span, tr, ti, gamma, state_in)
+
+
+def _gather_summaries(summary: torch.Tensor, world: int, group) -> torch.Tensor:
+    B = summary.shape[0]
+    gathered = torch.empty((world * B,) + tuple(summary.shape[1:]), device=summary.device,
+                           dtype=summary.dtype)
+    dist.all_gather_into_tensor(gathered, summary.contiguous(), group=group)  # rank-major
+    return gathered.view(world, B, *summary.shape[1:])
+
+
+class _SequenceParallelFieldRead(torch.autograd.Function):
+    """read_span = F(raw_span, tr, ti, gamma) for one rank's span, differentiable across ranks."""
+
+    @staticmethod
+    def forward(ctx, raw_span, tr, ti, gamma, state0, group, ops, reduce_parameter_grads):
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        raw_span = raw_span.contiguous().float()
+        tr, ti, gamma = (t.contiguous().float() for t in (tr, ti, gamma))
+        state_in = state0
+        if world > 1:
+            gathered = _gather_summaries(ops.span_summary(raw_span, tr, ti, gamma), world, group)
+            state_in = ops.fold(gathered, rank, state0)
+        read, _ = ops.forward(raw_span, tr, ti, gamma, state_in)
+        ctx.save_for_backward(raw_span, tr, ti, gamma, read,
+                              state_in if state_in is not None else torch.empty(0))
+        ctx.group, ctx.ops, ctx.reduce = group, ops, reduce_parameter_grads
+        return read
+
+    @staticmethod
+    def backward(ctx, grad_read):
+        raw_span, tr, ti, gamma, read, state_in = ctx.saved_tensors
+        state_in = state_in if state_in.numel() else None
+        group, ops = ctx.group, ctx.ops
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        grad_read = grad_read.contiguous().float()
+        carry = None
+        if world > 1:
+            dual = ops.span_summary_backward(raw_span, tr, ti, grad_read)
+            carry = ops.fold_backward(_gather_summaries(dual, world, group), rank, None)
+        grad_raw, g_par, _ = ops.backward(raw_span, tr, ti, gamma, read, grad_read, state_in, carry)
+        if world > 1 and ctx.reduce:
+            dist.all_reduce(g_par, group=group)
+        return grad_raw, g_par[0], g_par[1], g_par[2], None, None, None, None
+
+
+def sequence_parallel_field_read_autograd(raw_span: torch.Tensor, tr: torch.Tensor,
+                                          ti: torch.Tensor, gamma: torch.Tensor, group=None,
+                                          state0: Optional[torch.Tensor] = None, ops=None,
+                                          reduce_parameter_grads: bool = True) -> torch.Tensor:
+    """Differentiable forward of this rank's span of a sequence sharded over ``group``.
+
+    ``loss.backward()`` on every rank exchanges the dual span summaries (one all_gather of
+    ``[B, 4, C]`` per rank), so ``raw_span.grad`` equals the corresponding slice of the
+    single-device gradient. The gradients of ``tr``, ``ti`` and ``gamma`` are sums over the
+    spans: with ``reduce_parameter_grads`` they are all-reduced here and every rank gets the
+    full gradient; without it each rank keeps its span's share (for callers whose data-parallel
+    wrapper already sums replicated parameters over this group). ``state0`` (the state before
+    the first span) is treated as a constant.
+    """
+    if raw_span.dim() != 3 or raw_span.shape[1] == 0:
+        raise ValueError(f"every rank needs a non-empty span, got {tuple(raw_span.shape)}")
+    return _SequenceParallelFieldRead.apply(raw_span, tr, ti, gamma, state0, group,
+                                            ops or CudaOps(), reduce_parameter_grads)

@@ -131,6 +131,29 @@ int fields_read_fold_summaries(const float *summaries, const float *state0, floa
                                int rank, int P, int B, int C, void *stream);
 
 /*
+ * The same for the backward pass of a sharded sequence (the reverse-order composition of
+ * field_only_v4_chunked_triton_wiki100.py:655-705 and :725-745 applied to a whole span).
+ *
+ * fields_read_span_summary_backward: the dual map  carry_in = P carry_out + Q  of a span per
+ * (batch, channel): carry_out is the gradient carry arriving from the steps after the span,
+ * carry_in the one leaving towards the steps before it. summary [B, 4, C] = Re P | Im P |
+ * Re Q | Im Q. Reads z_v of raw and grad_read. Workspace as for the backward pass.
+ *
+ * fields_read_fold_summaries_backward: given the dual summaries of all P spans, [P, B, 4, C]
+ * in span order, and the carry after the last span (carry_end [B, 2C] or NULL = zero), writes
+ * the carry arriving at the end of span `rank` into carry [B, 2C] (the spans after `rank` are
+ * applied last first). That carry is the grad_state_out of fields_read_backward for the span;
+ * its state_in is the state fields_read_fold_summaries gave the forward pass. The three
+ * parameter gradients of the spans add up (an all-reduce the caller owns).
+ */
+int fields_read_span_summary_backward(const float *raw, const float *tr, const float *ti,
+                                      const float *grad_read, float *summary, void *workspace,
+                                      size_t workspace_bytes, int B, int L, int C, void *stream);
+int fields_read_fold_summaries_backward(const float *summaries, const float *carry_end,
+                                        float *carry, int rank, int P, int B, int C,
+                                        void *stream);
+
+/*
  * One recurrent step for incremental decoding (no counterpart in the reference, whose
  * inference is always a full-sequence pass; the arithmetic is one iteration of
  * field_only_v4_chunked_triton_wiki100.py:599-622).

@@ -54,6 +54,10 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.fields_read_span_summary.restype = I
     lib.fields_read_fold_summaries.argtypes = [P, P, P, I, I, I, I, P]
     lib.fields_read_fold_summaries.restype = I
+    lib.fields_read_span_summary_backward.argtypes = [P] * 6 + [SZ, I, I, I, P]
+    lib.fields_read_span_summary_backward.restype = I
+    lib.fields_read_fold_summaries_backward.argtypes = [P, P, P, I, I, I, I, P]
+    lib.fields_read_fold_summaries_backward.restype = I
     lib.fields_read_step.argtypes = [P] * 6 + [I, I, P]
     lib.fields_read_step.restype = I
     lib.fields_read_step_bf16.argtypes = [P] * 6 + [I, I, P]
@@ -164,6 +168,32 @@ def fold_summaries(summaries, rank, state0=None):
     s0 = None if state0 is None else _f32(state0)
     out = _f32(np.full((B, 2 * C), np.nan))
     rc = lib().fields_read_fold_summaries(_ptr(s), _ptr(s0), _ptr(out), rank, P_, B, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return out
+
+
+def span_summary_backward(raw, tr, ti, grad_read):
+    B, L, C3 = raw.shape
+    C = tr.size
+    a = [_f32(x) for x in (raw, tr, ti, grad_read)]
+    out = _f32(np.full((B, 4, C), np.nan))
+    nbytes = lib().fields_read_workspace_bytes(B, L, C, 1)
+    ws = _aligned(max(nbytes, 256))
+    ws[...] = 0xFF
+    rc = lib().fields_read_span_summary_backward(_ptr(a[0]), _ptr(a[1]), _ptr(a[2]), _ptr(a[3]),
+                                                 _ptr(out), _ptr(ws), nbytes, B, L, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return out
+
+
+def fold_summaries_backward(summaries, rank, carry_end=None):
+    P_, B, four, C = summaries.shape
+    s = _f32(summaries)
+    c0 = None if carry_end is None else _f32(carry_end)
+    out = _f32(np.full((B, 2 * C), np.nan))
+    rc = lib().fields_read_fold_summaries_backward(_ptr(s), _ptr(c0), _ptr(out), rank, P_, B, C, None)
     if rc:
         raise RuntimeError(lib().fields_status_string(rc).decode())
     return out

@@ -155,6 +155,43 @@ def test_span_summary_and_fold(B, L, C):
     np.testing.assert_array_equal(emu.fold_summaries(summaries, 0), 0.0)
 
 
+@pytest.mark.parametrize("B,L,C", [(2, 333, 20), (1, 64, 512), (3, 17, 7)])
+def test_backward_over_spans_equals_one_backward_pass(B, L, C):
+    """Dual summaries folded in reverse span order give every span the gradient carry a single
+    backward pass would hand it; span backward passes then add up to the full one."""
+    rng = np.random.default_rng(3 * L + C)
+    tr, ti, gm = _params(C, rng)
+    raw = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+    grad = rng.standard_normal((B, L, 4 * C)).astype(np.float32)
+    s0 = rng.standard_normal((B, 2 * C)).astype(np.float32)
+    g_end = rng.standard_normal((B, 2 * C)).astype(np.float32)
+    want = field_oracle.backward(raw, tr, ti, gm, grad, state_in=s0, grad_state_out=g_end)
+    cuts = [0, L // 3, L // 3 + 1, L]
+    spans = [(a, b) for a, b in zip(cuts[:-1], cuts[1:]) if b > a]
+    fwd = np.stack([emu.span_summary(raw[:, a:b], tr, ti, gm) for a, b in spans])
+    dual = np.stack([emu.span_summary_backward(raw[:, a:b], tr, ti, grad[:, a:b]) for a, b in spans])
+    g_raw = np.zeros((B, L, 3 * C), np.float32)
+    g_par = [np.zeros(C, np.float64) for _ in range(3)]
+    g_in = None
+    for r, (a, b) in enumerate(spans):
+        state_in = emu.fold_summaries(fwd, r, state0=s0)
+        carry = emu.fold_summaries_backward(dual, r, carry_end=g_end)
+        read, _ = emu.forward(raw[:, a:b], tr, ti, gm, state_in=state_in)
+        out = emu.backward(raw[:, a:b], tr, ti, gm, read, grad[:, a:b], state_in=state_in,
+                           grad_state_out=carry)
+        g_raw[:, a:b] = out[0]
+        for k in range(3):
+            g_par[k] += out[1 + k]
+        if r == 0:
+            g_in = out[4]
+    assert rel_err(g_raw, want[0]) < FP32_TOL
+    for k in range(3):
+        assert rel_err(g_par[k], want[1 + k]) < FP32_TOL
+    assert rel_err(g_in, want[4]) < FP32_TOL
+    # the last span's carry is the caller's; no carry and no later span gives zero
+    np.testing.assert_array_equal(emu.fold_summaries_backward(dual, len(spans) - 1), 0.0)
+
+
 def test_decode_steps_continue_a_prefix():
     """Prefix in one pass, then token-by-token steps == one pass over prefix + tokens (causality)."""
     rng = np.random.default_rng(8)

@@ -150,6 +150,39 @@ def test_spans_chain_exactly_like_one_pass(dev):
     assert rel_err(prefix["read"], full["read"][:, :517]) < 2e-6
 
 
+@pytest.mark.parametrize("C", [512, 20, 7])
+def test_backward_over_spans_equals_one_backward_pass(dev, C):
+    """The device operations of the sequence-sharded backward, spans taken one after another on
+    one GPU: dual summaries folded in reverse order hand every span the carry of a single pass."""
+    from fields_lm_b200.seqpar import CudaOps
+    ops = CudaOps()
+    rng = np.random.default_rng(17 + C)
+    B, L = 2, 700
+    tr, ti, gm = _init_params(C)
+    raw = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+    grad = rng.standard_normal((B, L, 4 * C)).astype(np.float32)
+    want = field_oracle.backward(raw, tr, ti, gm, grad)
+    t = lambda a: _t(np.ascontiguousarray(a), dev)
+    tr_t, ti_t, gm_t = t(tr), t(ti), t(gm)
+    spans = [(0, 233), (233, 234), (234, 700)]
+    fwd = torch.stack([ops.span_summary(t(raw[:, a:b]), tr_t, ti_t, gm_t) for a, b in spans])
+    dual = torch.stack([ops.span_summary_backward(t(raw[:, a:b]), tr_t, ti_t, t(grad[:, a:b]))
+                        for a, b in spans])
+    g_raw = np.zeros_like(raw)
+    g_par = np.zeros((3, C))
+    for r, (a, b) in enumerate(spans):
+        state_in = ops.fold(fwd, r, None)
+        carry = ops.fold_backward(dual, r, None)
+        read, _ = ops.forward(t(raw[:, a:b]), tr_t, ti_t, gm_t, state_in)
+        gr, gp, _ = ops.backward(t(raw[:, a:b]), tr_t, ti_t, gm_t, read, t(grad[:, a:b]), state_in,
+                                 carry)
+        g_raw[:, a:b] = gr.cpu().numpy()
+        g_par += gp.double().cpu().numpy()
+    assert rel_err(g_raw, want[0]) < FP32_TOL
+    for k in range(3):
+        assert rel_err(g_par[k], want[1 + k]) < FP32_TOL
+
+
 def _config2_inputs(B=8, L=2048, C=512):
     """bf16-rounded activations held in fp32, as autocast hands them to the operator."""
     gen = torch.Generator().manual_seed(1)

@@ -75,3 +75,57 @@ def test_sequence_sharded_forward_matches_single_gpu_and_oracle(tmp_path, L):
     ref, ref_state = field_oracle.forward(full["raw"], full["tr"], full["ti"], full["gm"])
     assert rel_err(got, ref) < FP32_TOL
     assert rel_err(parts[-1]["state"], ref_state) < FP32_TOL
+
+
+def _train_worker(rank, world, port, L, out_dir):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from fields_lm_b200 import seqpar
+        gen = torch.Generator().manual_seed(321)
+        B, C = 2, 512
+        ring = torch.linspace(0.85, 0.999, C)
+        theta = torch.linspace(0.03, torch.pi * 0.97, C)
+        tr = (ring * torch.cos(theta)).to(dev).requires_grad_(True)
+        ti = (ring * torch.sin(theta)).to(dev).requires_grad_(True)
+        gm = torch.sqrt(1 - ring ** 2).to(dev).requires_grad_(True)
+        raw = torch.randn(B, L, 3 * C, generator=gen) * 0.577
+        grad = torch.randn(B, L, 4 * C, generator=gen)
+        lo, hi = seqpar.span_bounds(L, world, rank)
+        span = raw[:, lo:hi].contiguous().to(dev).requires_grad_(True)
+        read = seqpar.sequence_parallel_field_read_autograd(span, tr, ti, gm)
+        read.backward(grad[:, lo:hi].contiguous().to(dev))
+        torch.cuda.synchronize()
+        if rank == 0:
+            np.savez(os.path.join(out_dir, "inputs.npz"), raw=raw.numpy(), grad=grad.numpy(),
+                     tr=tr.detach().cpu().numpy(), ti=ti.detach().cpu().numpy(),
+                     gm=gm.detach().cpu().numpy())
+        np.savez(os.path.join(out_dir, f"rank{rank}.npz"), lo=lo, hi=hi,
+                 grad_raw=span.grad.cpu().numpy(), grad_tr=tr.grad.cpu().numpy(),
+                 grad_ti=ti.grad.cpu().numpy(), grad_gamma=gm.grad.cpu().numpy())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+def test_sequence_sharded_training_step_matches_the_oracle(tmp_path):
+    """Forward + backward of a sequence sharded over the GPUs: gradients of every span and the
+    all-reduced parameter gradients equal the single-device ones."""
+    import torch.multiprocessing as mp
+    from conftest import FP32_TOL, rel_err
+    from oracle import field_oracle
+    L = 2048 + 11
+    world = min(torch.cuda.device_count(), 4)
+    port = 30600 + (os.getpid() % 2000)
+    mp.spawn(_train_worker, args=(world, port, L, str(tmp_path)), nprocs=world, join=True)
+    x = np.load(tmp_path / "inputs.npz")
+    parts = [np.load(tmp_path / f"rank{r}.npz") for r in range(world)]
+    want = field_oracle.backward(x["raw"], x["tr"], x["ti"], x["gm"], x["grad"])
+    assert rel_err(np.concatenate([p["grad_raw"] for p in parts], axis=1), want[0]) < FP32_TOL
+    for k, name in enumerate(("grad_tr", "grad_ti", "grad_gamma")):
+        for p in parts:
+            assert rel_err(p[name], want[1 + k]) < FP32_TOL

@@ -1,7 +1,9 @@
-"""Sequence-sharded forward on CPU: two gloo ranks, the device operations emulated on the host.
+"""Sequence-sharded forward and backward on CPU: gloo ranks, the device operations emulated on
+the host.
 
-Checks the host logic of fields_lm_b200.seqpar (span bounds, gather, fold order, state hand-over)
-against a single full-sequence pass of the oracle.
+Checks the host logic of fields_lm_b200.seqpar (span bounds, gather, fold order in both
+directions, state and gradient-carry hand-over, parameter-gradient reduction) against a single
+full-sequence pass of the oracle.
 """
 import os
 import sys
@@ -33,6 +35,87 @@ class EmuOps:
         s_in = None if state_in is None else state_in.numpy()
         read, state = emu.forward(raw.numpy(), tr.numpy(), ti.numpy(), gamma.numpy(), state_in=s_in)
         return torch.from_numpy(np.array(read)), torch.from_numpy(np.array(state))
+
+
+    def span_summary_backward(self, raw, tr, ti, grad_read):
+        import emu
+        return torch.from_numpy(np.array(emu.span_summary_backward(raw.numpy(), tr.numpy(),
+                                                                   ti.numpy(), grad_read.numpy())))
+
+    def fold_backward(self, summaries, rank, carry_end):
+        import emu
+        c = None if carry_end is None else carry_end.numpy()
+        return torch.from_numpy(np.array(emu.fold_summaries_backward(summaries.numpy(), rank, c)))
+
+    def backward(self, raw, tr, ti, gamma, read, grad_read, state_in, grad_state_out):
+        import emu
+        s_in = None if state_in is None else state_in.numpy()
+        g_out = None if grad_state_out is None else grad_state_out.numpy()
+        g_raw, g_tr, g_ti, g_gm, g_sin = emu.backward(raw.numpy(), tr.numpy(), ti.numpy(),
+                                                      gamma.numpy(), read.numpy(), grad_read.numpy(),
+                                                      state_in=s_in, grad_state_out=g_out)
+        return (torch.from_numpy(np.array(g_raw)),
+                torch.from_numpy(np.stack([np.array(g_tr), np.array(g_ti), np.array(g_gm)])),
+                torch.from_numpy(np.array(g_sin)))
+
+
+def _problem(L, with_state0):
+    gen = torch.Generator().manual_seed(99)
+    B, C = 2, 20
+    radius = torch.rand(C, generator=gen) * 0.49 + 0.5
+    theta = (torch.rand(C, generator=gen) * 2 - 1) * torch.pi
+    tr, ti = radius * torch.cos(theta), radius * torch.sin(theta)
+    gamma = torch.sqrt(1 - radius ** 2)
+    raw = torch.randn(B, L, 3 * C, generator=gen)
+    state0 = torch.randn(B, 2 * C, generator=gen) if with_state0 else None
+    grad = torch.randn(B, L, 4 * C, generator=gen)
+    return tr, ti, gamma, raw, state0, grad
+
+
+def _train_worker(rank, world, port, L, with_state0, reduce, out_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from fields_lm_b200 import seqpar
+        tr, ti, gamma, raw, state0, grad = _problem(L, with_state0)
+        lo, hi = seqpar.span_bounds(L, world, rank)
+        span = raw[:, lo:hi].clone().requires_grad_(True)
+        tr, ti, gamma = (t.clone().requires_grad_(True) for t in (tr, ti, gamma))
+        read = seqpar.sequence_parallel_field_read_autograd(span, tr, ti, gamma, state0=state0,
+                                                            ops=EmuOps(),
+                                                            reduce_parameter_grads=reduce)
+        (read * grad[:, lo:hi]).sum().backward()
+        np.savez(os.path.join(out_dir, f"rank{rank}.npz"), lo=lo, hi=hi, read=read.detach().numpy(),
+                 grad_raw=span.grad.numpy(), grad_tr=tr.grad.numpy(), grad_ti=ti.grad.numpy(),
+                 grad_gamma=gamma.grad.numpy())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,L,with_state0,reduce", [(2, 101, False, True), (3, 50, True, True),
+                                                        (2, 64, True, False)])
+def test_sharded_training_step_matches_one_device(tmp_path, world, L, with_state0, reduce):
+    from conftest import FP32_TOL, rel_err
+    from oracle import field_oracle
+    port = 31500 + (os.getpid() % 2000)
+    mp.spawn(_train_worker, args=(world, port, L, with_state0, reduce, str(tmp_path)), nprocs=world,
+             join=True)
+    parts = [np.load(tmp_path / f"rank{r}.npz") for r in range(world)]
+    tr, ti, gamma, raw, state0, grad = _problem(L, with_state0)
+    s0 = None if state0 is None else state0.numpy()
+    want = field_oracle.backward(raw.numpy(), tr.numpy(), ti.numpy(), gamma.numpy(), grad.numpy(),
+                                 state_in=s0)
+    ref_read, _ = field_oracle.forward(raw.numpy(), tr.numpy(), ti.numpy(), gamma.numpy(), state_in=s0)
+    assert rel_err(np.concatenate([p["read"] for p in parts], axis=1), ref_read) < FP32_TOL
+    assert rel_err(np.concatenate([p["grad_raw"] for p in parts], axis=1), want[0]) < FP32_TOL
+    for k, name in enumerate(("grad_tr", "grad_ti", "grad_gamma")):
+        if reduce:  # every rank holds the full gradient
+            for p in parts:
+                assert rel_err(p[name], want[1 + k]) < FP32_TOL
+        else:       # each rank holds its span's share
+            assert rel_err(sum(p[name].astype(np.float64) for p in parts), want[1 + k]) < FP32_TOL
 
 
 def _worker(rank, world, port, L, with_state0, out_dir):
