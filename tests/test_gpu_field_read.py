@@ -183,6 +183,18 @@ def test_backward_over_spans_equals_one_backward_pass(dev, C):
         assert rel_err(g_par[k], want[1 + k]) < FP32_TOL
 
 
+def test_ordinary_launches_give_the_same_results(dev, monkeypatch):
+    """FIELDS_READ_PDL=0: plain launches and a memset instead of dependent launches and the fill
+    kernel."""
+    monkeypatch.setenv("FIELDS_READ_PDL", "0")
+    rng = np.random.default_rng(77)
+    B, L, C = 2, 300, 512
+    tr, ti, gm = _init_params(C)
+    raw = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+    grad = rng.standard_normal((B, L, 4 * C)).astype(np.float32)
+    check_against_oracle(dev, raw, tr, ti, gm, grad)
+
+
 def _config2_inputs(B=8, L=2048, C=512):
     """bf16-rounded activations held in fp32, as autocast hands them to the operator."""
     gen = torch.Generator().manual_seed(1)
