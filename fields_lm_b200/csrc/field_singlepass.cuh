@@ -560,8 +560,13 @@ struct SpBwdParamsT {
     unsigned* ctrl;               // error word
     float* partial;               // [3][B][NT][C]
     SpShape s;
+    // Optional replacement for `read` in the kernels that recompute the states: row j holds the
+    // state after step kStateRowEvery * (j + 1) - 1, [B, state_rows, 2C] fp32. Null: use `read`.
+    const float* states = nullptr;
+    int state_rows = 0;
 };
 using SpBwdParams = SpBwdParamsT<float>;
+constexpr int kStateRowEvery = 8;
 
 template <int TS, int WARPS, int U1_, int U2_, int MIN_BLOCKS, bool ASYNC = false, int STAGES = 2,
           typename IO = float>
@@ -1002,7 +1007,13 @@ struct BwdRecompute {
                 for (int j = 0; j < STAGES - 1; ++j) issue(j);
                 // the state just before the warp's first step
                 Vec<4> sr4, si4;
-                if (tbeg > 0) {
+                if (tbeg > 0 && p.states) {
+                    static_assert(TS == kStateRowEvery, "one saved row per warp sub-chunk");
+                    const float* prow =
+                        p.states + ((size_t)tl.b * p.state_rows + tbeg / TS - 1) * 2 * C + c0;
+                    sr4 = vec_load<4>(prow);
+                    si4 = vec_load<4>(prow + C);
+                } else if (tbeg > 0) {
                     const IO* prow = p.read + ((size_t)tl.b * s.L + tbeg - 1) * 4 * C + c0;
                     sr4 = io_load4(prow);
                     si4 = io_load4(prow + C);

@@ -475,7 +475,8 @@ static int run_backward_single_pass(const IO* raw, const float* tr, const float*
                                     const IO* grad_read, const float* grad_state_out,
                                     IO* grad_raw, float* grad_tr, float* grad_ti,
                                     float* grad_gamma, float* grad_state_in, void* workspace,
-                                    int B, int L, int C, Stream st) {
+                                    int B, int L, int C, Stream st,
+                                    const float* states = nullptr) {
     SpPlan pl = make_sp_plan(B, L, C, K::kTile);
     pl.s.prefetch = prefetch_from_env(resident_blocks<K>());
     char* ws = static_cast<char*>(workspace);
@@ -486,6 +487,8 @@ static int run_backward_single_pass(const IO* raw, const float* tr, const float*
     SpBwdParamsT<IO> p{raw, tr, ti, gamma, state_in, read, grad_read, grad_state_out, grad_raw,
                        grad_state_in, reinterpret_cast<float*>(ws + pl.agg_off),
                        reinterpret_cast<float*>(ws + pl.incl_off), ctrl, partial, pl.s};
+    p.states = states;
+    p.state_rows = L / kStateRowEvery;
     rc = launch_stateful<K>(p, pl.tiles, (long long)B * pl.s.G, st);
     if (rc) return rc;
     BwdParams rp{};
@@ -712,6 +715,35 @@ int fields_read_backward(const float* raw, const float* tr, const float* ti, con
     return vec4 ? run_backward<4>(p, st) : run_backward<1>(p, st);
 }
 
+
+int fields_read_state_rows(int L) { return L > 0 ? L / kStateRowEvery : 0; }
+
+int fields_read_backward_from_states(const float* raw, const float* tr, const float* ti,
+                                     const float* gamma, const float* state_in,
+                                     const float* states, const float* grad_read,
+                                     const float* grad_state_out, float* grad_raw, float* grad_tr,
+                                     float* grad_ti, float* grad_gamma, float* grad_state_in,
+                                     void* workspace, size_t workspace_bytes, int B, int L, int C,
+                                     void* stream) {
+    if (B <= 0 || L <= 0 || C <= 0) return FIELDS_ERR_ARGUMENT;
+    if (!raw || !tr || !ti || !gamma || !grad_read || !grad_raw || !grad_tr || !grad_ti ||
+        !grad_gamma)
+        return FIELDS_ERR_ARGUMENT;
+    if (!states && L > kStateRowEvery) return FIELDS_ERR_ARGUMENT;
+    if (C % 4 != 0 || !aligned16(raw) || !aligned16(grad_read) || !aligned16(grad_raw) ||
+        !aligned16(tr) || !aligned16(ti) || !aligned16(gamma) || !aligned16(state_in) ||
+        !aligned16(states))
+        return FIELDS_ERR_UNSUPPORTED;
+    if (!workspace ||
+        workspace_bytes < fields_read_workspace_bytes(B, L, C, FIELDS_PASS_BACKWARD) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return FIELDS_ERR_WORKSPACE;
+    // `read` is never dereferenced when the rows are given; a sequence of up to 8 steps needs no row
+    return run_backward_single_pass<BwdSp2>(raw, tr, ti, gamma, state_in, (const float*)nullptr,
+                                            grad_read, grad_state_out, grad_raw, grad_tr, grad_ti,
+                                            grad_gamma, grad_state_in, workspace, B, L, C,
+                                            reinterpret_cast<Stream>(stream), states);
+}
 
 size_t fields_read_static_scratch_bytes(void) { return kStaticScratchBytes; }
 

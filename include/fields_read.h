@@ -92,6 +92,27 @@ int fields_read_backward(const float *raw, const float *tr, const float *ti,
                          size_t workspace_bytes, int B, int L, int C, void *stream);
 
 /*
+ * Backward pass without the saved forward output (no counterpart in the reference, whose
+ * backward reads s_{t-1} of every step from the saved `read`,
+ * field_only_v4_chunked_triton_wiki100.py:1008-1014 and :840-853).
+ *
+ * The kernel re-runs the state recurrence inside its first sweep and needs only the state at
+ * every eighth step: states [B, fields_read_state_rows(L), 2C] fp32, row j = Re s | Im s
+ * after step 8 (j + 1) - 1, i.e. read[:, 8 (j + 1) - 1, 0:2C]. A caller keeps those rows
+ * (1/16 of `read`) and may free `read` itself. Other arguments, workspace and results as
+ * fields_read_backward. Needs C % 4 == 0 and 16-byte aligned tensors
+ * (FIELDS_ERR_UNSUPPORTED otherwise); states may be NULL when L <= 8.
+ */
+int fields_read_state_rows(int L);
+int fields_read_backward_from_states(const float *raw, const float *tr, const float *ti,
+                                     const float *gamma, const float *state_in,
+                                     const float *states, const float *grad_read,
+                                     const float *grad_state_out, float *grad_raw,
+                                     float *grad_tr, float *grad_ti, float *grad_gamma,
+                                     float *grad_state_in, void *workspace,
+                                     size_t workspace_bytes, int B, int L, int C, void *stream);
+
+/*
  * bfloat16 I/O twins of the two passes: raw, read, grad_read and grad_raw are bfloat16 (same
  * layouts, half the bytes); parameters, states, parameter gradients and all arithmetic stay
  * fp32. They serve a mixer that keeps the write projection's bf16 output instead of widening

@@ -46,6 +46,10 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.fields_read_forward.restype = I
     lib.fields_read_backward.argtypes = [P] * 14 + [SZ, I, I, I, P]
     lib.fields_read_backward.restype = I
+    lib.fields_read_state_rows.argtypes = [I]
+    lib.fields_read_state_rows.restype = I
+    lib.fields_read_backward_from_states.argtypes = [P] * 14 + [SZ, I, I, I, P]
+    lib.fields_read_backward_from_states.restype = I
     lib.fields_read_forward_bf16.argtypes = [P] * 8 + [SZ, I, I, I, P]
     lib.fields_read_forward_bf16.restype = I
     lib.fields_read_backward_bf16.argtypes = [P] * 14 + [SZ, I, I, I, P]
@@ -142,6 +146,31 @@ def backward(raw, tr, ti, gamma, read, grad_read, state_in=None, grad_state_out=
                                     _ptr(read_a), _ptr(gr_a), _ptr(gso_a), _ptr(g_raw), _ptr(g_tr),
                                     _ptr(g_ti), _ptr(g_gm), _ptr(g_sin), _ptr(ws), nbytes,
                                     B, L, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return g_raw, g_tr, g_ti, g_gm, g_sin
+
+
+def backward_from_states(raw, tr, ti, gamma, read, grad_read, state_in=None, grad_state_out=None):
+    """Backward that is given only every eighth state row of `read` (taken from it here)."""
+    B, L, C3 = raw.shape
+    C = tr.size
+    rows = lib().fields_read_state_rows(L)
+    states = _f32(np.ascontiguousarray(np.asarray(read)[:, 7::8, :2 * C][:, :rows])) if rows else None
+    a = [_f32(x) for x in (raw, tr, ti, gamma)]
+    sin_a = None if state_in is None else _f32(state_in)
+    gso_a = None if grad_state_out is None else _f32(grad_state_out)
+    gr_a = _f32(grad_read)
+    g_raw = _f32(np.full((B, L, 3 * C), np.nan))
+    g_tr, g_ti, g_gm = (_f32(np.full(C, np.nan)) for _ in range(3))
+    g_sin = _f32(np.full((B, 2 * C), np.nan))
+    nbytes = lib().fields_read_workspace_bytes(B, L, C, 1)
+    ws = _aligned(max(nbytes, 256))
+    ws[...] = 0xFF
+    rc = lib().fields_read_backward_from_states(
+        _ptr(a[0]), _ptr(a[1]), _ptr(a[2]), _ptr(a[3]), _ptr(sin_a), _ptr(states), _ptr(gr_a),
+        _ptr(gso_a), _ptr(g_raw), _ptr(g_tr), _ptr(g_ti), _ptr(g_gm), _ptr(g_sin), _ptr(ws), nbytes,
+        B, L, C, None)
     if rc:
         raise RuntimeError(lib().fields_status_string(rc).decode())
     return g_raw, g_tr, g_ti, g_gm, g_sin

@@ -192,6 +192,37 @@ def test_backward_over_spans_equals_one_backward_pass(B, L, C):
     np.testing.assert_array_equal(emu.fold_summaries_backward(dual, len(spans) - 1), 0.0)
 
 
+@pytest.mark.parametrize("B,L,C", [(2, 130, 20), (1, 300, 132), (2, 8, 4), (3, 9, 512), (1, 64, 4)])
+@pytest.mark.parametrize("with_state", [False, True])
+@pytest.mark.parametrize("order", ["forward", "reverse"])
+def test_backward_from_saved_state_rows(monkeypatch, B, L, C, with_state, order):
+    """Backward that sees every eighth state only equals the backward that reads all of `read`."""
+    monkeypatch.setenv("FIELDS_EMU_ORDER", order)
+    rng = np.random.default_rng(B * L + C)
+    tr, ti, gm = _params(C, rng)
+    raw = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+    grad = rng.standard_normal((B, L, 4 * C)).astype(np.float32)
+    s0 = rng.standard_normal((B, 2 * C)).astype(np.float32) if with_state else None
+    g_end = rng.standard_normal((B, 2 * C)).astype(np.float32) if with_state else None
+    read, _ = emu.forward(raw, tr, ti, gm, state_in=s0)
+    got = emu.backward_from_states(raw, tr, ti, gm, read, grad, state_in=s0, grad_state_out=g_end)
+    want = field_oracle.backward(raw, tr, ti, gm, grad, state_in=s0, grad_state_out=g_end)
+    for g, w in zip(got[:4], want[:4]):
+        assert rel_err(g, w) < FP32_TOL
+    if with_state:
+        assert rel_err(got[4], want[4]) < FP32_TOL
+
+
+def test_backward_from_saved_state_rows_refuses_what_it_cannot_do():
+    rng = np.random.default_rng(0)
+    tr, ti, gm = _params(7, rng)
+    raw = rng.standard_normal((1, 20, 21)).astype(np.float32)
+    grad = rng.standard_normal((1, 20, 28)).astype(np.float32)
+    read, _ = emu.forward(raw, tr, ti, gm)
+    with pytest.raises(RuntimeError):  # channel count not a multiple of four
+        emu.backward_from_states(raw, tr, ti, gm, read, grad)
+
+
 def test_decode_steps_continue_a_prefix():
     """Prefix in one pass, then token-by-token steps == one pass over prefix + tokens (causality)."""
     rng = np.random.default_rng(8)

@@ -120,6 +120,46 @@ def test_shape_sweep(dev, L, C):
     check_against_oracle(dev, raw, tr, ti, gm, grad_read)
 
 
+@pytest.mark.parametrize("variant", ["1", "2", "3"])
+def test_single_pass_alternatives(dev, algo, monkeypatch, variant):
+    """The selectable alternatives of the single-pass kernels (tile shapes, two-sweep forward,
+    backward with recomputed states, tile-resident backward) against the oracle."""
+    if algo != "single_pass":
+        pytest.skip("variants exist for the single-pass kernels only")
+    monkeypatch.setenv("FIELDS_FWD_VARIANT", variant)
+    monkeypatch.setenv("FIELDS_BWD_VARIANT", variant)
+    rng = np.random.default_rng(int(variant))
+    for B, L, C, with_state in ((2, 300, 512, False), (1, 2053, 132, True), (3, 17, 20, True)):
+        tr, ti, gm = _params(C, rng)
+        raw = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+        grad_read = rng.standard_normal((B, L, 4 * C)).astype(np.float32)
+        s_in = rng.standard_normal((B, 2 * C)).astype(np.float32) if with_state else None
+        g_out = rng.standard_normal((B, 2 * C)).astype(np.float32) if with_state else None
+        check_against_oracle(dev, raw, tr, ti, gm, grad_read, s_in, g_out)
+
+
+@pytest.mark.parametrize("B,L,C", [(2, 300, 512), (1, 2053, 132), (2, 8, 20), (3, 9, 4)])
+def test_lean_backward_keeps_state_rows_only(dev, B, L, C):
+    """lean=True: the autograd function keeps every eighth state row instead of `read`; gradients
+    equal the oracle's and the ordinary backward's."""
+    from fields_lm_b200 import field_read_with_state
+    rng = np.random.default_rng(L + C)
+    tr, ti, gm = _params(C, rng)
+    raw = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+    grad = rng.standard_normal((B, L, 4 * C)).astype(np.float32)
+    s_in = rng.standard_normal((B, 2 * C)).astype(np.float32)
+    g_out = rng.standard_normal((B, 2 * C)).astype(np.float32)
+    raw_t, tr_t, ti_t, gm_t, sin_t = (_t(a, dev, True) for a in (raw, tr, ti, gm, s_in))
+    read, state = field_read_with_state(raw_t, tr_t, ti_t, gm_t, sin_t, lean=True)
+    saved = read.grad_fn.saved_tensors if hasattr(read.grad_fn, "saved_tensors") else ()
+    assert all(t.numel() < read.numel() or t.shape[-1] == 3 * C for t in saved)
+    torch.autograd.backward([read, state], [_t(grad, dev), _t(g_out, dev)])
+    want = field_oracle.backward(raw, tr, ti, gm, grad, state_in=s_in, grad_state_out=g_out)
+    got = (raw_t.grad, tr_t.grad, ti_t.grad, gm_t.grad, sin_t.grad)
+    for g, w in zip(got, want):
+        assert rel_err(g.cpu().numpy(), w) < FP32_TOL
+
+
 def test_state_in_and_out(dev):
     rng = np.random.default_rng(77)
     B, L, C = 3, 200, 132
