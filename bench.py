@@ -288,6 +288,40 @@ DECODE_BATCH, DECODE_BLOCKS = 256, 18
 DECODE_BYTES_PER_SEQ_BLOCK = 2 * (2 * C * 4) + 3 * C * 2 + 4 * C * 2   # state r+w, bf16 raw, bf16 read
 
 
+def block_leg(device, stream, iters: int = 10):
+    """Forward + backward of one whole Field block (mixer + SwiGLU, d_model 1,024, 8 x 2,048
+    tokens, autocast bf16) around the operator: on the reference's fp32 operator boundary, and on
+    the bfloat16 boundary with the norm statistics taken from the recurrence kernel. The GEMMs,
+    norms and the feed-forward are PyTorch library calls in both."""
+    from fields_lm_b200.mixer import FieldBlock
+    torch.manual_seed(0)
+    block = FieldBlock(D_MODEL, "triton", 32, 32, 64, 2528).to(device).train()
+    gen = torch.Generator(device=device).manual_seed(5)
+    x = torch.randn(B, L, D_MODEL, device=device, generator=gen)
+    gy = torch.randn(B, L, D_MODEL, device=device, generator=gen)
+
+    def step():
+        block.zero_grad(set_to_none=True)
+        xg = x.clone().requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = block(xg)
+        y.backward(gy)
+
+    out = {"workload": f"one FieldBlock forward + backward, {B} x {L} tokens, d_model {D_MODEL}, "
+                       "autocast bf16, random-init weights"}
+    for name, bf16_io, fused in (("fp32_operator_boundary", False, False),
+                                 ("bf16_boundary_fused_norm", True, True)):
+        block.mixer.bf16_io, block.mixer.fused_norm = bf16_io, fused
+        for _ in range(3):
+            step()
+        torch.cuda.reset_peak_memory_stats(device)
+        ms = timed_loop(step, iters, stream) / iters
+        out[name] = {"ms": ms, "tokens_per_s": B * L / (ms * 1e-3),
+                     "peak_mib": torch.cuda.max_memory_allocated(device) / 2 ** 20}
+    del block, x, gy
+    return out
+
+
 def decode_leg(device, tr, ti, gamma, peak_gbs: float, iters: int = 200):
     from fields_lm_b200 import _lib
     lib = _lib.load()
@@ -483,7 +517,34 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     barrier(dist_on)
     ms_long = max_over_ranks(timed_loop(long_fwd, long_steps, stream) / long_steps, dist_on, device)
     barrier(dist_on)
-    del long_raw
+
+    # the training step of the same sequence: forward + backward, on one GPU through the C ABI on
+    # preallocated buffers, on several sharded over the sequence through the autograd function
+    # (dual summaries all-gathered in the backward pass, parameter gradients all-reduced)
+    long_grad = torch.randn(1, long_raw.shape[1], 4 * C, device=device,
+                            generator=torch.Generator(device=device).manual_seed(3 + rank))
+    if dist_on:
+        span = long_raw.clone().requires_grad_(True)
+        par = [t.detach().clone().requires_grad_(True) for t in (tr_d, ti_d, gm_d)]
+
+        def long_train():
+            span.grad = None
+            for t in par:
+                t.grad = None
+            seqpar.sequence_parallel_field_read_autograd(span, *par).backward(long_grad)
+        train_api = "seqpar.sequence_parallel_field_read_autograd (NCCL all_gather x2, all_reduce)"
+    else:
+        def long_train():
+            long_op.forward(long_raw, tr_d, ti_d, gm_d)
+            long_op.backward(long_raw, tr_d, ti_d, gm_d, long_grad)
+        train_api = "fields_read_forward + fields_read_backward on preallocated buffers"
+    for _ in range(3):
+        long_train()
+    barrier(dist_on)
+    train_steps = max(5, min(args.steps, 20))
+    ms_train = max_over_ranks(timed_loop(long_train, train_steps, stream) / train_steps, dist_on, device)
+    barrier(dist_on)
+    del long_raw, long_grad
 
     # the same step on the bfloat16 boundary (raw, read and their gradients in bf16, fp32 state)
     bf16 = bf16_leg(device, raw_d, grad_read, tr_d, ti_d, gm_d, args.steps, stream)
@@ -491,6 +552,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # decode: one token for 256 sequences through the recurrences of 18 Field
     # blocks, bf16 rows, fp32 carried states; plain launches and one CUDA graph of the 18 launches
     decode = decode_leg(device, tr_d, ti_d, gm_d, peak_gbs=measured_peaks()[0]) if not dist_on else None
+    block = block_leg(device, stream) if not dist_on else None
 
     # end to end: pinned host -> device, forward + backward, results back to pinned host
     raw_pin, grad_pin = raw_h.pin_memory(), grad_h.pin_memory()
@@ -554,10 +616,17 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                         "ms": ms_long, "tokens_per_s": LONG_L / (ms_long * 1e-3),
                         "achieved": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9,
                         "frac": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9 / (peak * world)},
+        "train_64k": {"workload": "forward + backward of 1 x 65,536 tokens" +
+                                  (f", sequence-sharded over {world} GPUs" if dist_on else " on one GPU"),
+                      "scaling": "strong", "n_gpus": world, "api": train_api, "ms": ms_train,
+                      "tokens_per_s": LONG_L / (ms_train * 1e-3),
+                      "achieved": LONG_L * BYTES_PER_TOKEN / (ms_train * 1e-3) / 1e9,
+                      "frac": LONG_L * BYTES_PER_TOKEN / (ms_train * 1e-3) / 1e9 / (peak * world)},
         "bf16_io": {**bf16, "achieved": B * L * BYTES_PER_TOKEN / 2 / (bf16["ms_per_step"] * 1e-3) / 1e9,
                     "frac": B * L * BYTES_PER_TOKEN / 2 / (bf16["ms_per_step"] * 1e-3) / 1e9 / peak,
                     "tokens_per_s": world * B * L / (bf16["ms_per_step"] * 1e-3)},
         "decode_step": decode,
+        "field_block": block,
         "gpu_launches": KERNEL_LAUNCHES_PER_STEP * args.steps,
         "clocks": clocks.summary(),
         "parity": parity_check(device, tr.detach(), ti.detach(), gamma.detach()),

@@ -4,6 +4,7 @@ Public surface:
 
 * :func:`fused_field_read` - drop-in for the reference operator of the same name;
 * :func:`fused_field_read_bf16` - the operator on a bfloat16 boundary (fp32 state);
+* :func:`fused_field_read_bf16_stats` - the same plus the per-token sum of squares an RMS norm needs;
 * :func:`field_read_with_state` - the operator with carried state in and out;
 * :func:`field_read_step` - one recurrent step for incremental decoding;
 * :func:`fields_lm_b200.seqpar.sequence_parallel_field_read` - sequence-sharded forward;
@@ -15,8 +16,8 @@ The CUDA library is required: nothing here falls back to a CPU or PyTorch path.
 """
 from .decode import field_read_step
 from .field_read import (FieldReadFunction, field_read_with_state, fused_field_read,
-                         fused_field_read_bf16)
+                         fused_field_read_bf16, fused_field_read_bf16_stats)
 from .install import install, uninstall
 
-__all__ = ["FieldReadFunction", "field_read_step", "field_read_with_state", "fused_field_read", "fused_field_read_bf16", "install",
+__all__ = ["FieldReadFunction", "field_read_step", "field_read_with_state", "fused_field_read", "fused_field_read_bf16", "fused_field_read_bf16_stats", "install",
            "uninstall"]

@@ -72,6 +72,9 @@ struct SpFwdParamsT {
     float* incl;            // [tiles][128][2]  state after each tile
     unsigned* ctrl;         // error word; filled with 0xFF like the slots before the launch
     SpShape s;
+    // Kernels built with STATS also write, per token and 128-channel group, the sum of squares of
+    // the four output planes (fp32 values, before any rounding of `read`): [B, L, G].
+    float* sumsq = nullptr;
 };
 using SpFwdParams = SpFwdParamsT<float>;
 
@@ -93,13 +96,15 @@ FL_HD SpTile sp_decode(const SpShape& s, unsigned ticket) {
 }
 
 // IO = float, or uint16_t for bfloat16 raw / read (the state, the maps and all arithmetic stay fp32).
-template <int TS, int WARPS, int MIN_BLOCKS, typename IO = float>
+template <int TS, int WARPS, int MIN_BLOCKS, typename IO = float, bool STATS = false>
 struct FwdSinglePass {
     using Params = SpFwdParamsT<IO>;
     static constexpr int kThreads = 32 * WARPS;
     static constexpr int kMinBlocks = MIN_BLOCKS;  // blocks per SM the register budget must allow
     static constexpr int kTile = TS * WARPS;
-    static constexpr int kPhases = 4;
+    static constexpr int kPhases = STATS ? 5 : 4;
+    static constexpr int kStatRow = 33;  // lane partials of one (warp, step), padded against bank conflicts
+    static_assert(!STATS || kTile * kStatRow <= WARPS * 4 * kGroup, "lane partials reuse the map area");
     static constexpr int kSplitPhase = 2;  // host emulation: phases < 2 of all blocks run first
     static constexpr int kSumFloats = WARPS * 4 * kGroup;
     static constexpr int kCarryFloats = WARPS * 2 * kGroup;
@@ -214,8 +219,14 @@ struct FwdSinglePass {
                     p.state_out[(size_t)tl.b * 2 * C + C + ch] = si;
                 }
             }
-        } else {  // PH == 3
-            if (!chan_ok) return;
+        } else if constexpr (PH == 3) {
+            if (!chan_ok) {
+                if constexpr (STATS) {
+#pragma unroll
+                    for (int u = 0; u < TS; ++u) smem[(warp * TS + u) * kStatRow + lane] = 0.0f;
+                }
+                return;
+            }
             const Vec<4> lr = vec_load<4>(p.tr + c0);
             const Vec<4> li = vec_load<4>(p.ti + c0);
             Vec<4> sr = vec_load<4>(carry_at(smem, warp, 0) + lane * 4);
@@ -225,6 +236,7 @@ struct FwdSinglePass {
             for (int u = 0; u < TS; ++u) {
                 if (tw + u < s.L) {
                     Vec<4> dr, di;
+                    float sq = 0.0f;
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         float mr, mi;
@@ -234,12 +246,27 @@ struct FwdSinglePass {
                         di.v[k] = v * mi;
                         sr.v[k] = (1.0f - v) * mr + st.br[u].v[k];
                         si.v[k] = (1.0f - v) * mi + st.bi[u].v[k];
+                        if constexpr (STATS)
+                            sq += sr.v[k] * sr.v[k] + si.v[k] * si.v[k] + dr.v[k] * dr.v[k] +
+                                  di.v[k] * di.v[k];
                     }
                     IO* orow = obase + (size_t)(tw + u) * 4 * C;
                     io_store4_stream(orow, sr);
                     io_store4_stream(orow + C, si);
                     io_store4_stream(orow + 2 * C, dr);
                     io_store4_stream(orow + 3 * C, di);
+                    // the map area is free after the look-back: one partial per lane and step
+                    if constexpr (STATS) smem[(warp * TS + u) * kStatRow + lane] = sq;
+                }
+            }
+        } else {  // PH == 4 (STATS): one sum per step of the tile, lanes added in order
+            if (thread < kTile) {
+                const int t = tl.n * kTile + thread;  // thread = warp * TS + step
+                if (t < s.L) {
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int l = 0; l < 32; ++l) acc += smem[thread * kStatRow + l];
+                    p.sumsq[((size_t)tl.b * s.L + t) * s.G + tl.cg] = acc;
                 }
             }
         }

@@ -434,6 +434,7 @@ using BwdSp2 = BwdRecompute<8, 4, 1, 3, 2>;   // 73 KB per block, 12 warps per S
 using BwdSp3 = BwdTileResident<4, 4, 3>;      // tile 16, 68 KB per block, 12 warps per SM
 //   bfloat16 raw / read / grad_read / grad_raw (bits as uint16_t); state and arithmetic stay fp32
 using FwdSpBf16 = FwdSinglePass<6, 8, 2, uint16_t>;
+using FwdSpBf16Stats = FwdSinglePass<6, 8, 2, uint16_t, true>;  // also writes per-token sums of squares
 using BwdSpBf16 = BwdSinglePass<8, 4, 2, 1, 3, true, 3, uint16_t>;
 constexpr int kSpMinTile = 32;     // smallest time tile of any forward instantiation above (workspace bound)
 constexpr int kSpMinTileBwd = 16;  // same for the backward
@@ -456,7 +457,7 @@ template <class K, typename IO = float>
 static int run_forward_single_pass(const IO* raw, const float* tr, const float* ti,
                                    const float* gamma, const float* state_in, IO* read,
                                    float* state_out, void* workspace, int B, int L, int C,
-                                   Stream st) {
+                                   Stream st, float* sumsq = nullptr) {
     SpPlan pl = make_sp_plan(B, L, C, K::kTile);
     pl.s.prefetch = prefetch_from_env(resident_blocks<K>());
     char* ws = static_cast<char*>(workspace);
@@ -466,6 +467,7 @@ static int run_forward_single_pass(const IO* raw, const float* tr, const float* 
     SpFwdParamsT<IO> p{raw, tr, ti, gamma, state_in, read, state_out,
                        reinterpret_cast<float*>(ws + pl.agg_off),
                        reinterpret_cast<float*>(ws + pl.incl_off), ctrl, pl.s};
+    p.sumsq = sumsq;
     return launch_stateful<K>(p, pl.tiles, (long long)B * pl.s.G, st);
 }
 
@@ -935,6 +937,23 @@ int fields_read_forward_bf16(const void* raw, const float* tr, const float* ti, 
     return run_forward_single_pass<FwdSpBf16, uint16_t>(
         static_cast<const uint16_t*>(raw), tr, ti, gamma, state_in, static_cast<uint16_t*>(read),
         state_out, workspace, B, L, C, reinterpret_cast<Stream>(stream));
+}
+
+int fields_read_forward_bf16_stats(const void* raw, const float* tr, const float* ti,
+                                   const float* gamma, const float* state_in, void* read,
+                                   float* sumsq, float* state_out, void* workspace,
+                                   size_t workspace_bytes, int B, int L, int C, void* stream) {
+    if (B <= 0 || L <= 0 || C <= 0) return FIELDS_ERR_ARGUMENT;
+    if (!raw || !read || !sumsq || !tr || !ti || !gamma) return FIELDS_ERR_ARGUMENT;
+    if (C % 4 || !aligned8(raw) || !aligned8(read) || !aligned16(tr) || !aligned16(ti) ||
+        !aligned16(gamma))
+        return FIELDS_ERR_UNSUPPORTED;
+    if (!workspace || workspace_bytes < fields_read_workspace_bytes(B, L, C, FIELDS_PASS_FORWARD) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return FIELDS_ERR_WORKSPACE;
+    return run_forward_single_pass<FwdSpBf16Stats, uint16_t>(
+        static_cast<const uint16_t*>(raw), tr, ti, gamma, state_in, static_cast<uint16_t*>(read),
+        state_out, workspace, B, L, C, reinterpret_cast<Stream>(stream), sumsq);
 }
 
 int fields_read_backward_bf16(const void* raw, const float* tr, const float* ti, const float* gamma,

@@ -160,6 +160,75 @@ class FieldReadBf16Function(torch.autograd.Function):
         return grad_raw, g_par[0], g_par[1], g_par[2]
 
 
+class FieldReadBf16StatsFunction(torch.autograd.Function):
+    """read, sumsq = F(raw, tr, ti, gamma): the bfloat16 operator plus, per token, the sum of the
+    squares of its 4C outputs (``sumsq [B, L]`` fp32, from the fp32 values before rounding)."""
+
+    @staticmethod
+    def forward(ctx, raw, transition_r, transition_i, gamma):
+        if not raw.is_cuda:
+            raise RuntimeError("Chunked Field kernel requires CUDA")
+        if raw.dtype != torch.bfloat16:
+            raise TypeError(f"raw must be bfloat16, got {raw.dtype}")
+        if raw.dim() != 3 or raw.shape[2] % 3 or raw.shape[0] == 0 or raw.shape[1] == 0:
+            raise ValueError(tuple(raw.shape))
+        raw = raw.contiguous()
+        tr = transition_r.contiguous().float()
+        ti = transition_i.contiguous().float()
+        gm = gamma.contiguous().float()
+        B, L, three_c = raw.shape
+        C = three_c // 3
+        if tr.numel() != C or ti.numel() != C or gm.numel() != C:
+            raise ValueError((tuple(raw.shape), tuple(tr.shape)))
+        lib = _lib.load()
+        with torch.cuda.device(raw.device):
+            read = torch.empty((B, L, 4 * C), device=raw.device, dtype=torch.bfloat16)
+            groups = torch.empty((B, L, (C + 127) // 128), device=raw.device, dtype=torch.float32)
+            ws, nbytes = _workspace(B, L, C, _FWD, raw.device)
+            rc = lib.fields_read_forward_bf16_stats(_ptr(raw), _ptr(tr), _ptr(ti), _ptr(gm), None,
+                                                    _ptr(read), _ptr(groups), None, _ptr(ws), nbytes,
+                                                    B, L, C, _stream(raw.device))
+            _lib.check(rc, "fields_read_forward_bf16_stats")
+            sumsq = groups.sum(dim=-1)
+        ctx.set_materialize_grads(False)
+        ctx.save_for_backward(raw, tr, ti, gm, read)
+        ctx.dims = (B, L, C)
+        return read, sumsq
+
+    @staticmethod
+    def backward(ctx, grad_read, grad_sumsq):
+        raw, tr, ti, gm, read = ctx.saved_tensors
+        B, L, C = ctx.dims
+        lib = _lib.load()
+        with torch.cuda.device(raw.device):
+            # d sumsq / d read = 2 read: folded into the gradient the recurrence receives
+            if grad_sumsq is not None:
+                extra = read.float() * (2.0 * grad_sumsq.float()).unsqueeze(-1)
+                total = extra if grad_read is None else extra + grad_read.float()
+            elif grad_read is not None:
+                total = grad_read
+            else:
+                total = torch.zeros_like(read)
+            total = total.contiguous().to(torch.bfloat16)
+            grad_raw = torch.empty_like(raw)
+            g_par = torch.empty((3, C), device=raw.device, dtype=torch.float32)
+            ws, nbytes = _workspace(B, L, C, _BWD, raw.device)
+            rc = lib.fields_read_backward_bf16(
+                _ptr(raw), _ptr(tr), _ptr(ti), _ptr(gm), None, _ptr(read), _ptr(total), None,
+                _ptr(grad_raw), _ptr(g_par[0]), _ptr(g_par[1]), _ptr(g_par[2]), None, _ptr(ws),
+                nbytes, B, L, C, _stream(raw.device))
+        _lib.check(rc, "fields_read_backward_bf16")
+        return grad_raw, g_par[0], g_par[1], g_par[2]
+
+
+def fused_field_read_bf16_stats(raw: torch.Tensor, transition_r: torch.Tensor,
+                                transition_i: torch.Tensor, gamma: torch.Tensor):
+    """``fused_field_read_bf16`` that also returns ``sumsq [B, L]`` (fp32): the sum of squares of
+    each token's 4C outputs, which is all an RMS norm over ``read`` needs from it. Both outputs
+    are differentiable."""
+    return FieldReadBf16StatsFunction.apply(raw, transition_r, transition_i, gamma)
+
+
 def fused_field_read_bf16(raw: torch.Tensor, transition_r: torch.Tensor,
                           transition_i: torch.Tensor, gamma: torch.Tensor) -> torch.Tensor:
     """The operator on a bfloat16 boundary: ``raw [B, L, 3C]`` bf16 in, ``read [B, L, 4C]`` bf16

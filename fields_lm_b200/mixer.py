@@ -20,7 +20,8 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .decode import field_read_step
-from .field_read import field_read_with_state, fused_field_read, fused_field_read_bf16
+from .field_read import (field_read_with_state, fused_field_read, fused_field_read_bf16,
+                         fused_field_read_bf16_stats)
 
 
 class RMSNorm(nn.Module):
@@ -86,11 +87,26 @@ class IndependentVacancyField(nn.Module):
         # the write projection's bf16 output under autocast and run the recurrence on a bfloat16
         # boundary (fp32 state) instead of widening raw to fp32 first.
         self.bf16_io = False
+        # With bf16_io: take the norm's statistics from the recurrence kernel and apply the norm
+        # after the output projection (a per-token scale commutes with the projection), so that
+        # `read` is neither reduced nor rewritten between the recurrence and the GEMM:
+        #   out_proj(read_norm(read)) = rstd * (read @ (W diag(w))^T) + b
+        self.fused_norm = False
+
+    def _readout_fused_norm(self, x, raw, tr, ti, gamma):
+        read, sumsq = fused_field_read_bf16_stats(raw, tr, ti, gamma)
+        rstd = torch.rsqrt(sumsq / read.shape[-1] + self.read_norm.eps)
+        w_eff = self.out_proj.weight.float() * self.read_norm.weight.float().unsqueeze(0)
+        acc = F.linear(read, w_eff.to(read.dtype))
+        out = acc.float() * rstd.unsqueeze(-1) + self.out_proj.bias.float()
+        return x + (out * torch.sigmoid(self.gate_proj(x))).to(x.dtype)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raw = self.write_proj(x).contiguous()
         if self.bf16_io and raw.dtype == torch.bfloat16:
             tr, ti, gamma = transition_parameters(self.radius_logit, self.theta)
+            if self.fused_norm and self.channels % 4 == 0:
+                return self._readout_fused_norm(x, raw, tr, ti, gamma)
             read = fused_field_read_bf16(raw, tr, ti, gamma)
             out = self.out_proj(self.read_norm(read))
             return x + (out * torch.sigmoid(self.gate_proj(x))).to(x.dtype)

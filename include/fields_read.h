@@ -124,6 +124,19 @@ int fields_read_forward_bf16(const void *raw, const float *tr, const float *ti,
                              const float *gamma, const float *state_in, void *read,
                              float *state_out, void *workspace, size_t workspace_bytes,
                              int B, int L, int C, void *stream);
+/*
+ * fields_read_forward_bf16 that also returns what the RMS norm after the recurrence
+ * (read_norm, field_only_v4_chunked_triton_wiki100.py:1177 and :300-309) needs from `read`:
+ * sumsq [B, L, G] fp32, G = ceil(C / 128), the sum over the four output planes of the squares
+ * of the 128 channels of group g at token t, taken from the fp32 values before they are
+ * rounded to bfloat16. mean(read^2) over the 4C features of a token is the sum over g divided
+ * by 4C, so the norm's reduction pass over `read` is not needed; a caller can apply
+ * rsqrt(mean + eps) after the output projection instead of before it. B, L > 0.
+ */
+int fields_read_forward_bf16_stats(const void *raw, const float *tr, const float *ti,
+                                   const float *gamma, const float *state_in, void *read,
+                                   float *sumsq, float *state_out, void *workspace,
+                                   size_t workspace_bytes, int B, int L, int C, void *stream);
 int fields_read_backward_bf16(const void *raw, const float *tr, const float *ti,
                               const float *gamma, const float *state_in, const void *read,
                               const void *grad_read, const float *grad_state_out,

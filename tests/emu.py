@@ -52,6 +52,8 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.fields_read_backward_from_states.restype = I
     lib.fields_read_forward_bf16.argtypes = [P] * 8 + [SZ, I, I, I, P]
     lib.fields_read_forward_bf16.restype = I
+    lib.fields_read_forward_bf16_stats.argtypes = [P] * 9 + [SZ, I, I, I, P]
+    lib.fields_read_forward_bf16_stats.restype = I
     lib.fields_read_backward_bf16.argtypes = [P] * 14 + [SZ, I, I, I, P]
     lib.fields_read_backward_bf16.restype = I
     lib.fields_read_span_summary.argtypes = [P] * 6 + [SZ, I, I, I, P]
@@ -271,6 +273,25 @@ def forward_bf16(raw_bits, tr, ti, gamma):
     if rc:
         raise RuntimeError(lib().fields_status_string(rc).decode())
     return read
+
+
+def forward_bf16_stats(raw_bits, tr, ti, gamma):
+    """Returns (read bits, sumsq [B, L, G])."""
+    B, L, C3 = raw_bits.shape
+    C = tr.size
+    G = (C + 127) // 128
+    r = _u16(raw_bits)
+    a = [_f32(x) for x in (tr, ti, gamma)]
+    read = _u16(np.zeros((B, L, 4 * C), np.uint16), fill=0x7fc0)
+    sumsq = _f32(np.full((B, L, G), np.nan))
+    nbytes = lib().fields_read_workspace_bytes(B, L, C, 0)
+    ws = _aligned(max(nbytes, 256))
+    rc = lib().fields_read_forward_bf16_stats(_ptr(r), _ptr(a[0]), _ptr(a[1]), _ptr(a[2]), None,
+                                              _ptr(read), _ptr(sumsq), None, _ptr(ws), nbytes,
+                                              B, L, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return read, sumsq
 
 
 def backward_bf16(raw_bits, tr, ti, gamma, read_bits, grad_bits):

@@ -288,6 +288,25 @@ def test_bf16_boundary_forward_backward(B, L, C):
         assert rel_err(got[k], ref[k]) < BF16_TOL
 
 
+@pytest.mark.parametrize("B,L,C", [(2, 130, 20), (1, 50, 512), (2, 7, 132)])
+@pytest.mark.parametrize("order", ["forward", "reverse"])
+def test_forward_with_norm_statistics(monkeypatch, B, L, C, order):
+    """The per-token sums of squares that come with the bf16 forward equal those of the fp32
+    oracle output, group by group, and `read` is the plain bf16 forward's."""
+    monkeypatch.setenv("FIELDS_EMU_ORDER", order)
+    rng = np.random.default_rng(B + L + C)
+    tr, ti, gm = _params(C, rng)
+    raw_b = _bits(rng.standard_normal((B, L, 3 * C)))
+    ref_read, _ = field_oracle.forward(_unbits(raw_b), tr, ti, gm)
+    read_b, sumsq = emu.forward_bf16_stats(raw_b, tr, ti, gm)
+    np.testing.assert_array_equal(np.array(read_b), np.array(emu.forward_bf16(raw_b, tr, ti, gm)))
+    G = (C + 127) // 128
+    planes = ref_read.reshape(B, L, 4, C)
+    want = np.stack([(planes[..., g * 128:(g + 1) * 128] ** 2).sum(axis=(2, 3)) for g in range(G)], -1)
+    assert sumsq.shape == (B, L, G)
+    assert rel_err(sumsq, want) < FP32_TOL
+
+
 def test_bf16_boundary_refuses_odd_channel_counts():
     raw_b = np.zeros((1, 4, 21), np.uint16)
     p = np.ones(7, np.float32)

@@ -1,5 +1,6 @@
 """Sequence-sharded forward on real GPUs (needs at least two): every rank's span must equal the
 corresponding slice of a single-GPU full-sequence pass and of the CPU oracle."""
+import datetime
 import os
 import sys
 
@@ -18,7 +19,8 @@ def _worker(rank, world, port, L, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=90))
     try:
         from fields_lm_b200 import field_read_with_state, seqpar
         gen = torch.Generator().manual_seed(123)
@@ -83,7 +85,8 @@ def _train_worker(rank, world, port, L, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=90))
     try:
         from fields_lm_b200 import seqpar
         gen = torch.Generator().manual_seed(321)
