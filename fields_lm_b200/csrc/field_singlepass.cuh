@@ -1559,6 +1559,109 @@ struct ChunkSummaryStream {
 
 
 // ---------------------------------------------------------------------------
+// The same for the backward pass of a sharded sequence: the dual map of every chunk of a
+// span (carry before the chunk = P * carry after it + Q), reading z_v and grad_read once.
+// One warp walks its chunk from its last step to its first, five vectors per step through
+// the same kind of ring; the block's map composes its warps' maps, later chunks first.
+// Output layout as BwdSummary: sum [4][B][N][C] = Re P | Im P | Re Q | Im Q per chunk.
+// ---------------------------------------------------------------------------
+template <int U, int STAGES, int WARPS>
+struct ChunkDualSummaryStream {
+    using Params = BwdParams;  // raw, tr, ti, grad_read, sum, s (ts, N, G as ChunkSummaryStream)
+    static constexpr int kThreads = 32 * WARPS;
+    static constexpr int kPhases = 2;
+    static constexpr int kCells = U * 5;
+    static constexpr int kRingFloats = STAGES * kCells * kThreads * 4;
+    static constexpr int kSmemFloats = kRingFloats + WARPS * 4 * 128;
+
+    FL_HD static float* cell_at(float* smem, int stage, int idx, int thread) {
+        return smem + ((size_t)(stage * kCells + idx) * kThreads + thread) * 4;
+    }
+
+    FL_HD static void phase0(const Params& p, int block, int thread, float* smem) {
+        const Shape& s = p.s;
+        const int lane = thread & 31, warp = thread >> 5;
+        const int cg = block % s.G;
+        const int n = (block / s.G) % s.N;
+        const int b = block / (s.G * s.N);
+        const int C = s.C;
+        const int c0 = (cg * 32 + lane) * 4;
+        float* maps = smem + kRingFloats + warp * 4 * 128 + lane * 4;
+        if (c0 >= C) return;
+        const int t_first = (n * WARPS + warp) * s.ts;
+        const int tbeg = t_first < s.L ? t_first : s.L;
+        const int tend = tbeg + s.ts < s.L ? tbeg + s.ts : s.L;
+        const Vec<4> lr = vec_load<4>(p.tr + c0);
+        const Vec<4> li = vec_load<4>(p.ti + c0);
+        const F2 lr2[2] = {lo2(lr), hi2(lr)}, li2[2] = {lo2(li), hi2(li)};
+        const F2 nli2[2] = {mul2(li2[0], splat2(-1.0f)), mul2(li2[1], splat2(-1.0f))};
+        const float* zbase = p.raw + ((size_t)b * s.L) * 3 * C + 2 * C + c0;
+        const float* gbase = p.grad_read + ((size_t)b * s.L) * 4 * C + c0;
+        Affine2 m[2] = {affine2_identity(), affine2_identity()};
+
+        // batch of U steps ending just before t1 (rows descend), into ring slot `stage`
+        auto issue = [&](int t1, int stage) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int t = t1 - 1 - u;
+                if (t >= tbeg) {
+                    const float* grow = gbase + (size_t)t * 4 * C;
+                    async_copy16(cell_at(smem, stage, u * 5 + 0, thread), zbase + (size_t)t * 3 * C);
+                    async_copy16(cell_at(smem, stage, u * 5 + 1, thread), grow);
+                    async_copy16(cell_at(smem, stage, u * 5 + 2, thread), grow + C);
+                    async_copy16(cell_at(smem, stage, u * 5 + 3, thread), grow + 2 * C);
+                    async_copy16(cell_at(smem, stage, u * 5 + 4, thread), grow + 3 * C);
+                }
+            }
+            async_commit();
+        };
+#pragma unroll
+        for (int j = 0; j < STAGES - 1; ++j) issue(tend - j * U, j);
+        int stage = 0;
+        for (int t1 = tend; t1 > tbeg; t1 -= U, stage = stage + 1 == STAGES ? 0 : stage + 1) {
+            issue(t1 - (STAGES - 1) * U, stage == 0 ? STAGES - 1 : stage - 1);
+            async_wait_pending<STAGES - 1>();
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (t1 - 1 - u >= tbeg) {
+                    const Vec<4> zv = vec_load<4>(cell_at(smem, stage, u * 5 + 0, thread));
+                    const Vec<4> ur = vec_load<4>(cell_at(smem, stage, u * 5 + 1, thread));
+                    const Vec<4> ui = vec_load<4>(cell_at(smem, stage, u * 5 + 2, thread));
+                    const Vec<4> gr = vec_load<4>(cell_at(smem, stage, u * 5 + 3, thread));
+                    const Vec<4> gi = vec_load<4>(cell_at(smem, stage, u * 5 + 4, thread));
+                    dual_step2(m[0], lo2(zv), lo2(ur), lo2(ui), lo2(gr), lo2(gi), lr2[0], li2[0], nli2[0]);
+                    dual_step2(m[1], hi2(zv), hi2(ur), hi2(ui), hi2(gr), hi2(gi), lr2[1], li2[1], nli2[1]);
+                }
+            }
+        }
+        vec_store<4>(maps, join2(m[0].ar, m[1].ar));
+        vec_store<4>(maps + 128, join2(m[0].ai, m[1].ai));
+        vec_store<4>(maps + 256, join2(m[0].br, m[1].br));
+        vec_store<4>(maps + 384, join2(m[0].bi, m[1].bi));
+    }
+
+    // the block's map = its warps' maps, the later chunk first; one thread per channel
+    FL_HD static void phase1(const Params& p, int block, int thread, float* smem) {
+        const Shape& s = p.s;
+        const int cg = block % s.G;
+        const int n = (block / s.G) % s.N;
+        const int b = block / (s.G * s.N);
+        const int c = cg * 128 + thread;
+        if (thread >= 128 || c >= s.C) return;
+        Affine a = affine_identity();
+#pragma unroll
+        for (int w = WARPS - 1; w >= 0; --w) {
+            const float* q = smem + kRingFloats + w * 4 * 128 + thread;
+            a = affine_then(a, q[0], q[128], q[256], q[384]);
+        }
+        const size_t plane = (size_t)s.B * s.N * s.C;
+        float* out = p.sum + ((size_t)b * s.N + n) * s.C + c;
+        out[0] = a.ar; out[plane] = a.ai; out[2 * plane] = a.br; out[3 * plane] = a.bi;
+    }
+};
+
+
+// ---------------------------------------------------------------------------
 // Exchange of span summaries between GPUs through peer memory (no collective library).
 //
 // Every rank owns a mailbox in memory that its peers can write:

@@ -836,10 +836,21 @@ int fields_read_span_summary_backward(const float* raw, const float* tr, const f
     p.raw = raw; p.tr = tr; p.ti = ti; p.grad_read = grad_read;
     p.sum = ws + pl.sum_off;
     p.s = pl.s;
-    const int rc = vec4 ? launch<BwdSummary<4, 4>>(p, tile_blocks(pl.s), st)
-                        : launch<BwdSummary<1, 4>>(p, tile_blocks(pl.s), st);
+    Shape cs = pl.s;
+    int rc;
+    if (vec4) {
+        // as in fields_read_span_summary: 16 steps per warp, one map per 64 steps
+        using Stream4 = ChunkDualSummaryStream<1, 3, 4>;  // 38 KB of shared memory per block
+        p.s.ts = 16;
+        p.s.N = (L + 63) / 64;
+        p.s.G = (C + 127) / 128;
+        cs = p.s;
+        rc = launch<Stream4>(p, (long long)B * p.s.N * p.s.G, st);
+    } else {
+        rc = launch<BwdSummary<1, 4>>(p, tile_blocks(pl.s), st);
+    }
     if (rc) return rc;
-    SpanCompose::Params cp{p.sum, summary, pl.s, 1};
+    SpanCompose::Params cp{p.sum, summary, cs, 1};
     return launch<SpanCompose>(cp, (long long)B * ((C + 31) / 32), st);
 }
 

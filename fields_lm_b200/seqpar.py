@@ -153,6 +153,68 @@ class SequenceParallelForward:
         return self.read, self.state_out
 
 
+class SequenceParallelTrainStep:
+    """Forward and backward of one rank's span on preallocated buffers (NCCL exchanges).
+
+    ``forward`` is :class:`SequenceParallelForward`; ``backward`` mirrors it in reverse rank
+    order: dual span summary, all_gather, reverse fold, ``fields_read_backward`` with the folded
+    carry, all_reduce of the three parameter gradients. Seven C-ABI launches and three NCCL calls
+    per step, no allocation.
+    """
+
+    def __init__(self, batch: int, span_length: int, channels: int, device, group=None):
+        self.fwd = SequenceParallelForward(batch, span_length, channels, device, group)
+        f = self.fwd
+        f32 = dict(device=device, dtype=torch.float32)
+        self.dual = torch.empty(batch, 4, channels, **f32)
+        self.gathered_dual = torch.empty(f.world * batch, 4, channels, **f32)
+        self.carry = torch.empty(batch, 2 * channels, **f32)
+        self.grad_raw = torch.empty(batch, span_length, 3 * channels, **f32)
+        self.grad_par = torch.empty(3, channels, **f32)
+        self.nbytes_bwd = f.lib.fields_read_workspace_bytes(batch, span_length, channels, 1)
+        self.ws_bwd = torch.empty(max(self.nbytes_bwd, 256), dtype=torch.uint8, device=device)
+        self.had_state0 = False
+
+    def forward(self, raw_span, tr, ti, gamma, state0: Optional[torch.Tensor] = None):
+        self.had_state0 = state0 is not None
+        self.state0 = state0
+        return self.fwd(raw_span, tr, ti, gamma, state0)
+
+    def backward(self, raw_span, tr, ti, gamma, grad_read_span):
+        """Gradients of the last ``forward``: ``(grad_raw_span, grad_params [3, C])``; the
+        parameter gradients are summed over the ranks."""
+        f = self.fwd
+        lib, B, L, C = f.lib, f.B, f.L, f.C
+        if tuple(grad_read_span.shape) != (B, L, 4 * C) or not grad_read_span.is_contiguous():
+            raise ValueError(f"expected a contiguous [{B}, {L}, {4 * C}] gradient")
+        st = torch.cuda.current_stream(f.device).cuda_stream
+        args = (raw_span.data_ptr(), tr.data_ptr(), ti.data_ptr())
+        carry = None
+        if f.world > 1:
+            rc = lib.fields_read_span_summary_backward(*args, grad_read_span.data_ptr(),
+                                                       self.dual.data_ptr(), self.ws_bwd.data_ptr(),
+                                                       self.nbytes_bwd, B, L, C, st)
+            _lib.check(rc, "fields_read_span_summary_backward")
+            dist.all_gather_into_tensor(self.gathered_dual, self.dual, group=f.group)
+            rc = lib.fields_read_fold_summaries_backward(self.gathered_dual.data_ptr(), None,
+                                                         self.carry.data_ptr(), f.rank, f.world,
+                                                         B, C, st)
+            _lib.check(rc, "fields_read_fold_summaries_backward")
+            carry = self.carry.data_ptr()
+            state_in = f.state_in.data_ptr()
+        else:
+            state_in = self.state0.data_ptr() if self.had_state0 else None
+        g = self.grad_par
+        rc = lib.fields_read_backward(*args, gamma.data_ptr(), state_in, f.read.data_ptr(),
+                                      grad_read_span.data_ptr(), carry, self.grad_raw.data_ptr(),
+                                      g[0].data_ptr(), g[1].data_ptr(), g[2].data_ptr(), None,
+                                      self.ws_bwd.data_ptr(), self.nbytes_bwd, B, L, C, st)
+        _lib.check(rc, "fields_read_backward")
+        if f.world > 1:
+            dist.all_reduce(g, group=f.group)
+        return self.grad_raw, g
+
+
 class SequenceParallelForwardP2P:
     """Sequence-sharded forward whose summary exchange goes through peer memory, not NCCL.
 

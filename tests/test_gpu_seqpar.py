@@ -103,6 +103,16 @@ def _train_worker(rank, world, port, L, out_dir):
         read = seqpar.sequence_parallel_field_read_autograd(span, tr, ti, gm)
         read.backward(grad[:, lo:hi].contiguous().to(dev))
         torch.cuda.synchronize()
+        # the same step on preallocated buffers
+        step = seqpar.SequenceParallelTrainStep(B, hi - lo, C, dev)
+        g_span = grad[:, lo:hi].contiguous().to(dev)
+        for _ in range(2):
+            step.forward(span.detach(), tr.detach(), ti.detach(), gm.detach())
+            g_raw, g_par = step.backward(span.detach(), tr.detach(), ti.detach(), gm.detach(), g_span)
+        torch.cuda.synchronize()
+        assert float((g_raw - span.grad).abs().max()) <= 1e-5 * float(span.grad.abs().max())
+        for k, t in enumerate((tr, ti, gm)):
+            assert float((g_par[k] - t.grad).abs().max()) <= 1e-5 * float(t.grad.abs().max())
         if rank == 0:
             np.savez(os.path.join(out_dir, "inputs.npz"), raw=raw.numpy(), grad=grad.numpy(),
                      tr=tr.detach().cpu().numpy(), ti=ti.detach().cpu().numpy(),
