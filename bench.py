@@ -541,12 +541,16 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                             generator=torch.Generator(device=device).manual_seed(3 + rank))
     if dist_on:
         del sp_fwd  # its buffers; the training step holds its own
-        trainer = seqpar.SequenceParallelTrainStep(1, hi - lo, C, device)
+        if healthy:
+            trainer = seqpar.SequenceParallelTrainStepP2P(1, hi - lo, C, device)
+            train_api = "seqpar.SequenceParallelTrainStepP2P (peer-memory exchanges, one all_reduce)"
+        else:
+            trainer = seqpar.SequenceParallelTrainStep(1, hi - lo, C, device)
+            train_api = "seqpar.SequenceParallelTrainStep (NCCL all_gather x2, all_reduce)"
 
         def long_train():
             trainer.forward(long_raw, tr_d, ti_d, gm_d)
             trainer.backward(long_raw, tr_d, ti_d, gm_d, long_grad)
-        train_api = "seqpar.SequenceParallelTrainStep (NCCL all_gather x2, all_reduce)"
     else:
         def long_train():
             long_op.forward(long_raw, tr_d, ti_d, gm_d)

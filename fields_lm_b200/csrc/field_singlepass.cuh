@@ -1710,13 +1710,14 @@ struct PutSummary {
         int rank, P;
         unsigned epoch;
         Shape s;
+        int reverse;                 // non-zero: the chunk maps are dual maps, composed last first
     };
     static constexpr int kThreads = 32 * kCarryWarps;
     static constexpr int kPhases = 2;
     static constexpr int kSmemFloats = 4 * kThreads;
 
     FL_HD static void phase0(const Params& p, int block, int thread, float* smem) {
-        SpanCompose::Params q{p.sum, nullptr, p.s, 0};
+        SpanCompose::Params q{p.sum, nullptr, p.s, p.reverse};
         SpanCompose::phase0(q, block, thread, smem);
     }
 
@@ -1751,6 +1752,7 @@ struct FoldMailbox {
         unsigned* error;          // error word (0 = ok), set to 1 if a wait ran out
         int rank, P, B, C;
         unsigned epoch, max_polls;
+        int reverse;  // non-zero: fold the ranks after `rank`, last first (gradient carry)
     };
     static constexpr int kThreads = 128;
     static constexpr int kPhases = 1;
@@ -1763,7 +1765,8 @@ struct FoldMailbox {
         float sr = p.state0 ? p.state0[(size_t)b * 2 * p.C + c] : 0.0f;
         float si = p.state0 ? p.state0[(size_t)b * 2 * p.C + p.C + c] : 0.0f;
         bool failed = false;
-        for (int r = 0; r < p.P; ++r) {
+        for (int j = 0; j < p.P; ++j) {
+            const int r = p.reverse ? p.P - 1 - j : j;
             const MailPair* q =
                 p.mailbox + (((size_t)(p.epoch & 1u) * p.P + r) * p.B + b) * 4 * p.C + c;
             float v[4];
@@ -1779,7 +1782,7 @@ struct FoldMailbox {
                 if (m.tag != p.epoch) failed = true;
                 v[k] = m.value;
             }
-            if (r < p.rank) affine_apply(Affine{v[0], v[1], v[2], v[3]}, sr, si);
+            if (p.reverse ? r > p.rank : r < p.rank) affine_apply(Affine{v[0], v[1], v[2], v[3]}, sr, si);
         }
         if (failed) {
 #if FL_DEVICE_CODE

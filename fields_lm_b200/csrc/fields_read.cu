@@ -1038,6 +1038,51 @@ int fields_read_span_summary_put(const float* raw, const float* tr, const float*
     pp.summary = summary;
     pp.rank = rank; pp.P = P; pp.epoch = epoch;
     pp.s = p.s;
+    pp.reverse = 0;
+    return launch<PutSummary>(pp, (long long)B * ((C + 31) / 32), st);
+}
+
+int fields_read_span_summary_backward_put(const float* raw, const float* tr, const float* ti,
+                                          const float* grad_read, void* const* mailboxes,
+                                          float* summary, int rank, int P, unsigned epoch,
+                                          void* workspace, size_t workspace_bytes, int B, int L,
+                                          int C, void* stream) {
+    if (B < 0 || L <= 0 || C <= 0 || P <= 0 || P > kMaxRanks || rank < 0 || rank >= P || epoch == 0)
+        return FIELDS_ERR_ARGUMENT;
+    if (B == 0) return FIELDS_OK;
+    if (!raw || !tr || !ti || !grad_read || !mailboxes) return FIELDS_ERR_ARGUMENT;
+    for (int r = 0; r < P; ++r)
+        if (!mailboxes[r] || (reinterpret_cast<uintptr_t>(mailboxes[r]) & 7u)) return FIELDS_ERR_ARGUMENT;
+    Stream st = reinterpret_cast<Stream>(stream);
+    const bool vec4 = C % 4 == 0 && aligned16(raw) && aligned16(tr) && aligned16(ti) &&
+                      aligned16(grad_read) && aligned16(workspace);
+    const Plan pl = make_plan(B, L, C, vec4 ? 4 : 1);
+    if (!workspace || workspace_bytes < pl.bwd_floats * sizeof(float) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return FIELDS_ERR_WORKSPACE;
+    float* ws = static_cast<float*>(workspace);
+    BwdParams p{};
+    p.raw = raw; p.tr = tr; p.ti = ti; p.grad_read = grad_read;
+    p.sum = ws + pl.sum_off;
+    p.s = pl.s;
+    int rc;
+    if (vec4) {
+        using Stream4 = ChunkDualSummaryStream<1, 3, 4>;
+        p.s.ts = 16;
+        p.s.N = (L + 63) / 64;
+        p.s.G = (C + 127) / 128;
+        rc = launch<Stream4>(p, (long long)B * p.s.N * p.s.G, st);
+    } else {
+        rc = launch<BwdSummary<1, 4>>(p, tile_blocks(pl.s), st);
+    }
+    if (rc) return rc;
+    PutSummary::Params pp{};
+    pp.sum = p.sum;
+    for (int r = 0; r < P; ++r) pp.mailbox[r] = static_cast<MailPair*>(mailboxes[r]);
+    pp.summary = summary;
+    pp.rank = rank; pp.P = P; pp.epoch = epoch;
+    pp.s = p.s;
+    pp.reverse = 1;
     return launch<PutSummary>(pp, (long long)B * ((C + 31) / 32), st);
 }
 
@@ -1049,7 +1094,21 @@ int fields_read_fold_mailbox(const void* mailbox, const float* state0, float* st
     if (B == 0) return FIELDS_OK;
     if (!mailbox || !state || !error_word) return FIELDS_ERR_ARGUMENT;
     FoldMailbox::Params p{static_cast<const MailPair*>(mailbox), state0, state, error_word,
-                          rank, P, B, C, epoch, kMaxPolls};
+                          rank, P, B, C, epoch, kMaxPolls, 0};
+    const long long n = (long long)B * C;
+    return launch<FoldMailbox>(p, (n + FoldMailbox::kThreads - 1) / FoldMailbox::kThreads,
+                               reinterpret_cast<Stream>(stream));
+}
+
+int fields_read_fold_mailbox_backward(const void* mailbox, const float* carry_end, float* carry,
+                                      unsigned* error_word, int rank, int P, unsigned epoch, int B,
+                                      int C, void* stream) {
+    if (B < 0 || C <= 0 || P <= 0 || P > kMaxRanks || rank < 0 || rank >= P || epoch == 0)
+        return FIELDS_ERR_ARGUMENT;
+    if (B == 0) return FIELDS_OK;
+    if (!mailbox || !carry || !error_word) return FIELDS_ERR_ARGUMENT;
+    FoldMailbox::Params p{static_cast<const MailPair*>(mailbox), carry_end, carry, error_word,
+                          rank, P, B, C, epoch, kMaxPolls, 1};
     const long long n = (long long)B * C;
     return launch<FoldMailbox>(p, (n + FoldMailbox::kThreads - 1) / FoldMailbox::kThreads,
                                reinterpret_cast<Stream>(stream));

@@ -280,6 +280,59 @@ class SequenceParallelForwardP2P:
         return int(self.error.item())
 
 
+class SequenceParallelTrainStepP2P(SequenceParallelForwardP2P):
+    """Forward and backward of one rank's span with both exchanges through peer memory.
+
+    Calling the object runs the forward (as :class:`SequenceParallelForwardP2P`); ``backward``
+    puts the span's dual summary into every mailbox under the next epoch
+    (``fields_read_span_summary_backward_put``), waits with a bound for all of them and folds
+    the later spans, last first (``fields_read_fold_mailbox_backward``), and runs
+    ``fields_read_backward`` with that carry. Only the 3 C parameter-gradient floats go through
+    NCCL (one all_reduce). Like the forward, not for replay from a captured CUDA graph.
+    """
+
+    def __init__(self, batch: int, span_length: int, channels: int, device, group=None):
+        super().__init__(batch, span_length, channels, device, group)
+        f32 = dict(device=self.device, dtype=torch.float32)
+        self.carry = torch.empty(batch, 2 * channels, **f32)
+        self.grad_raw = torch.empty(batch, span_length, 3 * channels, **f32)
+        self.grad_par = torch.empty(3, channels, **f32)
+        self.nbytes_bwd = self.lib.fields_read_workspace_bytes(batch, span_length, channels, 1)
+        self.ws_bwd = torch.empty(max(self.nbytes_bwd, 256), dtype=torch.uint8, device=self.device)
+
+    def forward(self, raw_span, tr, ti, gamma, state0: Optional[torch.Tensor] = None):
+        return self(raw_span, tr, ti, gamma, state0)
+
+    def backward(self, raw_span, tr, ti, gamma, grad_read_span):
+        """Gradients of the last forward: ``(grad_raw_span, grad_params [3, C])``, the parameter
+        gradients summed over the ranks."""
+        lib, B, L, C = self.lib, self.B, self.L, self.C
+        if tuple(grad_read_span.shape) != (B, L, 4 * C) or not grad_read_span.is_contiguous():
+            raise ValueError(f"expected a contiguous [{B}, {L}, {4 * C}] gradient")
+        self.epoch = self.epoch + 1 if self.epoch < 0xFFFFFFFE else 1
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        args = (raw_span.data_ptr(), tr.data_ptr(), ti.data_ptr())
+        rc = lib.fields_read_span_summary_backward_put(*args, grad_read_span.data_ptr(), self.peers,
+                                                       None, self.rank, self.world, self.epoch,
+                                                       self.ws_bwd.data_ptr(), self.nbytes_bwd,
+                                                       B, L, C, st)
+        _lib.check(rc, "fields_read_span_summary_backward_put")
+        rc = lib.fields_read_fold_mailbox_backward(self.mail.data_ptr(), None, self.carry.data_ptr(),
+                                                   self.error.data_ptr(), self.rank, self.world,
+                                                   self.epoch, B, C, st)
+        _lib.check(rc, "fields_read_fold_mailbox_backward")
+        g = self.grad_par
+        rc = lib.fields_read_backward(*args, gamma.data_ptr(), self.state_in.data_ptr(),
+                                      self.read.data_ptr(), grad_read_span.data_ptr(),
+                                      self.carry.data_ptr(), self.grad_raw.data_ptr(),
+                                      g[0].data_ptr(), g[1].data_ptr(), g[2].data_ptr(), None,
+                                      self.ws_bwd.data_ptr(), self.nbytes_bwd, B, L, C, st)
+        _lib.check(rc, "fields_read_backward")
+        if self.world > 1:
+            dist.all_reduce(g, group=self.group)
+        return self.grad_raw, g
+
+
 def span_bounds(length: int, world: int, rank: int) -> Tuple[int, int]:
     """Contiguous, near-equal spans: the first ``length % world`` ranks get one step more."""
     base, extra = divmod(length, world)

@@ -233,6 +233,24 @@ int fields_read_fold_mailbox(const void *mailbox, const float *state0, float *st
                              unsigned *error_word, int rank, int P, unsigned epoch, int B, int C,
                              void *stream);
 
+/*
+ * The backward exchange through the same mailboxes (they and the epoch sequence are shared
+ * with the forward exchange: every exchange, in either direction, takes the next epoch).
+ * fields_read_span_summary_backward_put stores the span's dual summary (see
+ * fields_read_span_summary_backward) into every rank's mailbox;
+ * fields_read_fold_mailbox_backward waits, with the same bound, for all P dual summaries of
+ * `epoch` and writes the gradient carry arriving at the end of the rank's span (carry_end as
+ * in fields_read_fold_summaries_backward).
+ */
+int fields_read_span_summary_backward_put(const float *raw, const float *tr, const float *ti,
+                                          const float *grad_read, void *const *mailboxes,
+                                          float *summary, int rank, int P, unsigned epoch,
+                                          void *workspace, size_t workspace_bytes, int B, int L,
+                                          int C, void *stream);
+int fields_read_fold_mailbox_backward(const void *mailbox, const float *carry_end, float *carry,
+                                      unsigned *error_word, int rank, int P, unsigned epoch,
+                                      int B, int C, void *stream);
+
 /* Text of the last CUDA runtime error seen by the calling thread inside this library. */
 const char *fields_last_cuda_error(void);
 

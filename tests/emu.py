@@ -76,6 +76,10 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.fields_read_span_summary_put.restype = I
     lib.fields_read_fold_mailbox.argtypes = [P, P, P, P, I, I, ctypes.c_uint, I, I, P]
     lib.fields_read_fold_mailbox.restype = I
+    lib.fields_read_span_summary_backward_put.argtypes = [P] * 6 + [I, I, ctypes.c_uint, P, SZ, I, I, I, P]
+    lib.fields_read_span_summary_backward_put.restype = I
+    lib.fields_read_fold_mailbox_backward.argtypes = [P, P, P, P, I, I, ctypes.c_uint, I, I, P]
+    lib.fields_read_fold_mailbox_backward.restype = I
     lib.fields_read_device_status.argtypes = [P, P]
     lib.fields_read_device_status.restype = I
     return lib
@@ -331,6 +335,33 @@ def span_summary_put(raw, tr, ti, gamma, mailboxes, rank, epoch):
     if rc:
         raise RuntimeError(lib().fields_status_string(rc).decode())
     return out
+
+
+def span_summary_backward_put(raw, tr, ti, grad_read, mailboxes, rank, epoch):
+    B, L, C3 = raw.shape
+    C = tr.size
+    a = [_f32(x) for x in (raw, tr, ti, grad_read)]
+    ptrs = (ctypes.c_void_p * len(mailboxes))(*[m.ctypes.data for m in mailboxes])
+    out = _f32(np.full((B, 4, C), np.nan))
+    nbytes = lib().fields_read_workspace_bytes(B, L, C, 1)
+    ws = _aligned(max(nbytes, 256))
+    rc = lib().fields_read_span_summary_backward_put(_ptr(a[0]), _ptr(a[1]), _ptr(a[2]), _ptr(a[3]),
+                                                     ptrs, _ptr(out), rank, len(mailboxes), epoch,
+                                                     _ptr(ws), nbytes, B, L, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return out
+
+
+def fold_mailbox_backward(mailbox, rank, world, epoch, B, C, carry_end=None):
+    c0 = None if carry_end is None else _f32(carry_end)
+    out = _f32(np.full((B, 2 * C), np.nan))
+    err = np.zeros(1, dtype=np.uint32)
+    rc = lib().fields_read_fold_mailbox_backward(_ptr(mailbox), _ptr(c0), _ptr(out), _ptr(err), rank,
+                                                 world, epoch, B, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return out, int(err[0])
 
 
 def fold_mailbox(mailbox, rank, world, epoch, B, C, state0=None):

@@ -342,3 +342,36 @@ def test_mailbox_exchange_three_ranks_two_epochs():
         emu.span_summary_put(spans[r], tr, ti, gm, fresh, r, 1)
     got, err = emu.fold_mailbox(fresh[2], 2, world, 1, B, C)
     assert err == 1 and np.isnan(got).all()
+
+
+def test_mailbox_exchange_carries_the_backward_too():
+    """Forward and backward exchanges alternate on the same mailboxes (epochs 1, 2, 3, 4): the
+    carries folded from the mailboxes equal those folded from gathered dual summaries."""
+    rng = np.random.default_rng(21)
+    B, L, C, world = 2, 90, 20, 3
+    tr, ti, gm = _params(C, rng)
+    boxes = emu.make_mailboxes(world, B, C)
+    cuts = [0, 31, 64, L]
+    epoch = 0
+    for _ in range(2):
+        raw = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+        grad = rng.standard_normal((B, L, 4 * C)).astype(np.float32)
+        g_end = rng.standard_normal((B, 2 * C)).astype(np.float32)
+        spans = list(zip(cuts[:-1], cuts[1:]))
+        epoch += 1
+        for r, (a, b) in enumerate(spans):
+            emu.span_summary_put(raw[:, a:b], tr, ti, gm, boxes, r, epoch)
+        states = [emu.fold_mailbox(boxes[r], r, world, epoch, B, C)[0] for r in range(world)]
+        epoch += 1
+        dual = np.stack([emu.span_summary_backward_put(raw[:, a:b], tr, ti, grad[:, a:b], boxes, r, epoch)
+                         for r, (a, b) in enumerate(spans)])
+        for r in range(world):
+            got, err = emu.fold_mailbox_backward(boxes[r], r, world, epoch, B, C, carry_end=g_end)
+            assert err == 0
+            np.testing.assert_allclose(got, emu.fold_summaries_backward(dual, r, carry_end=g_end),
+                                       rtol=1e-6, atol=1e-7)
+        # the forward states of this round are untouched by the backward exchange on the other parity
+        want = np.zeros((B, 2 * C))
+        for r, (a, b) in enumerate(spans):
+            assert rel_err(states[r], want) < FP32_TOL or r == 0
+            _, want = field_oracle.forward(raw[:, a:b], tr, ti, gm, state_in=want)

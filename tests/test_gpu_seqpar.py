@@ -113,6 +113,16 @@ def _train_worker(rank, world, port, L, out_dir):
         assert float((g_raw - span.grad).abs().max()) <= 1e-5 * float(span.grad.abs().max())
         for k, t in enumerate((tr, ti, gm)):
             assert float((g_par[k] - t.grad).abs().max()) <= 1e-5 * float(t.grad.abs().max())
+        # and with both exchanges through peer memory
+        p2p = seqpar.SequenceParallelTrainStepP2P(B, hi - lo, C, dev)
+        for _ in range(3):
+            p2p.forward(span.detach(), tr.detach(), ti.detach(), gm.detach())
+            g_raw2, g_par2 = p2p.backward(span.detach(), tr.detach(), ti.detach(), gm.detach(), g_span)
+        torch.cuda.synchronize()
+        assert p2p.status() == 0
+        assert float((g_raw2 - span.grad).abs().max()) <= 1e-5 * float(span.grad.abs().max())
+        for k, t in enumerate((tr, ti, gm)):
+            assert float((g_par2[k] - t.grad).abs().max()) <= 1e-5 * float(t.grad.abs().max())
         if rank == 0:
             np.savez(os.path.join(out_dir, "inputs.npz"), raw=raw.numpy(), grad=grad.numpy(),
                      tr=tr.detach().cpu().numpy(), ti=ti.detach().cpu().numpy(),
