@@ -165,10 +165,10 @@ def run_reference_arm(args, rank: int):
     raw, grad_read = synthetic_inputs(1, B, L)
     # bound the whole run to a few minutes: use fewer batch rows per step if the full batch is too slow
     t_full = cpu_step(raw, grad_read, tr, ti, gamma)
-    budget_s = 150.0
+    time_limit_s = 150.0
     sample_batch = B
-    if (args.steps + args.warmup) * t_full > budget_s:
-        sample_batch = max(1, min(B, int(B * budget_s / ((args.steps + args.warmup) * t_full))))
+    if (args.steps + args.warmup) * t_full > time_limit_s:
+        sample_batch = max(1, min(B, int(B * time_limit_s / ((args.steps + args.warmup) * t_full))))
         raw, grad_read = raw[:sample_batch].contiguous(), grad_read[:sample_batch].contiguous()
     for _ in range(args.warmup):
         cpu_step(raw, grad_read, tr, ti, gamma)

@@ -100,7 +100,7 @@ template <int TS, int WARPS, int MIN_BLOCKS, typename IO = float, bool STATS = f
 struct FwdSinglePass {
     using Params = SpFwdParamsT<IO>;
     static constexpr int kThreads = 32 * WARPS;
-    static constexpr int kMinBlocks = MIN_BLOCKS;  // blocks per SM the register budget must allow
+    static constexpr int kMinBlocks = MIN_BLOCKS;  // blocks per SM that the register count must allow
     static constexpr int kTile = TS * WARPS;
     static constexpr int kPhases = STATS ? 5 : 4;
     static constexpr int kStatRow = 33;  // lane partials of one (warp, step), padded against bank conflicts
