@@ -231,6 +231,7 @@ FL_HD void look_back(const float* agg, const float* incl, long long chain_base, 
         }
 #else
         (void)max_polls;
+        (void)polls;
 #endif
         error_record(error, 1u);
         sr = si = nanf("");

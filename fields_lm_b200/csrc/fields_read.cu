@@ -10,6 +10,7 @@
 #include "field_kernels.cuh"
 #include "field_singlepass.cuh"
 #include "field_walk.cuh"
+#include "field_epilogue.cuh"
 
 #include "../../include/fields_read.h"
 
@@ -1113,5 +1114,51 @@ int fields_read_fold_mailbox_backward(const void* mailbox, const float* carry_en
     return launch<FoldMailbox>(p, (n + FoldMailbox::kThreads - 1) / FoldMailbox::kThreads,
                                reinterpret_cast<Stream>(stream));
 }
+
+#ifndef FIELDS_HOST_EMU
+size_t fields_mixer_epilogue_bias_rows(long long N) {
+    return N > 0 ? (size_t)((N + kEpiRows - 1) / kEpiRows) : 0;
+}
+
+int fields_mixer_epilogue_forward(const float* x, const void* acc, const void* gate,
+                                  const float* sumsq, const float* bias, float* y, float eps,
+                                  int features, long long N, int D, void* stream) {
+    if (N < 0 || D <= 0 || features <= 0) return FIELDS_ERR_ARGUMENT;
+    if (N == 0) return FIELDS_OK;
+    if (!x || !acc || !gate || !sumsq || !bias || !y) return FIELDS_ERR_ARGUMENT;
+    if (D % 4 || !aligned16(x) || !aligned16(y) || !aligned16(bias) || !aligned8(acc) ||
+        !aligned8(gate))
+        return FIELDS_ERR_UNSUPPORTED;
+    const long long blocks = (N + kEpiRows - 1) / kEpiRows;
+    if (blocks > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
+    EpilogueParams p{x, static_cast<const uint16_t*>(acc), static_cast<const uint16_t*>(gate), sumsq,
+                     bias, y, eps, 1.0f / (float)features, N, D};
+    return launch_on<EpilogueParams>(epilogue_forward, (unsigned)blocks, kEpiThreads, 0,
+                                     reinterpret_cast<Stream>(stream), p);
+}
+
+int fields_mixer_epilogue_backward(const float* grad_y, const void* acc, const void* gate,
+                                   const float* sumsq, const float* bias, void* grad_acc,
+                                   void* grad_gate, float* grad_sumsq, float* grad_bias_rows,
+                                   float eps, int features, long long N, int D, void* stream) {
+    if (N < 0 || D <= 0 || features <= 0) return FIELDS_ERR_ARGUMENT;
+    if (N == 0) return FIELDS_OK;
+    if (!grad_y || !acc || !gate || !sumsq || !bias || !grad_acc || !grad_gate || !grad_sumsq ||
+        !grad_bias_rows)
+        return FIELDS_ERR_ARGUMENT;
+    if (D % 4 || D > kEpiMaxD || !aligned16(grad_y) || !aligned16(bias) ||
+        !aligned16(grad_bias_rows) || !aligned8(acc) || !aligned8(gate) || !aligned8(grad_acc) ||
+        !aligned8(grad_gate))
+        return FIELDS_ERR_UNSUPPORTED;
+    const long long blocks = (N + kEpiRows - 1) / kEpiRows;
+    if (blocks > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
+    EpilogueGradParams p{grad_y, static_cast<const uint16_t*>(acc),
+                         static_cast<const uint16_t*>(gate), sumsq, bias,
+                         static_cast<uint16_t*>(grad_acc), static_cast<uint16_t*>(grad_gate),
+                         grad_sumsq, grad_bias_rows, eps, 1.0f / (float)features, N, D};
+    return launch_on<EpilogueGradParams>(epilogue_backward, (unsigned)blocks, kEpiThreads, 0,
+                                         reinterpret_cast<Stream>(stream), p);
+}
+#endif  // FIELDS_HOST_EMU
 
 }  // extern "C"

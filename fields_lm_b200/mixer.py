@@ -21,7 +21,7 @@ import torch.nn.functional as F
 
 from .decode import field_read_step
 from .field_read import (field_read_with_state, fused_field_read, fused_field_read_bf16,
-                         fused_field_read_bf16_stats)
+                         fused_field_read_bf16_stats, mixer_epilogue)
 
 
 class RMSNorm(nn.Module):
@@ -95,11 +95,17 @@ class IndependentVacancyField(nn.Module):
 
     def _readout_fused_norm(self, x, raw, tr, ti, gamma):
         read, sumsq = fused_field_read_bf16_stats(raw, tr, ti, gamma)
-        rstd = torch.rsqrt(sumsq / read.shape[-1] + self.read_norm.eps)
         w_eff = self.out_proj.weight.float() * self.read_norm.weight.float().unsqueeze(0)
         acc = F.linear(read, w_eff.to(read.dtype))
+        gate = self.gate_proj(x)
+        if (x.dtype == torch.float32 and acc.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16
+                and self.dim % 4 == 0 and self.dim <= 4096):
+            # one kernel for scale, bias, gate and residual (and one for their gradients)
+            return mixer_epilogue(x, acc, gate, sumsq, self.out_proj.bias, self.read_norm.eps,
+                                  read.shape[-1])
+        rstd = torch.rsqrt(sumsq / read.shape[-1] + self.read_norm.eps)
         out = acc.float() * rstd.unsqueeze(-1) + self.out_proj.bias.float()
-        return x + (out * torch.sigmoid(self.gate_proj(x))).to(x.dtype)
+        return x + (out * torch.sigmoid(gate)).to(x.dtype)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raw = self.write_proj(x).contiguous()

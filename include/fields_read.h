@@ -310,6 +310,29 @@ int fields_read_forward_noalloc(const float *raw, const float *tr, const float *
                                 float *read, float *state_out, int B, int L, int C,
                                 void *stream);
 
+/*
+ * Readout epilogue of the Field mixer with the RMS norm moved behind the output projection
+ * (the reference computes, field_only_v4_chunked_triton_wiki100.py:1177-1179,
+ *   y = x + out_proj(read_norm(read)) * sigmoid(gate_proj(x)) ).
+ * Given acc = read @ (W diag(w))^T and gate = gate_proj(x), both [N, D] bfloat16, x [N, D] and
+ * bias [D] fp32, and sumsq [N] = the sum of squares of each token's `features` read values
+ * (fields_read_forward_bf16_stats, summed over the groups):
+ *   y = x + (acc * rsqrt(sumsq / features + eps) + bias) * sigmoid(gate)          fp32 [N, D]
+ * in one pass; the backward entry returns, in one pass, grad_acc and grad_gate (bfloat16),
+ * grad_sumsq [N], and the bias gradient as fields_mixer_epilogue_bias_rows(N) partial rows
+ * [rows, D] for the caller to add up (grad_x is grad_y itself). D % 4 == 0, D <= 4096 for the
+ * backward, 16-byte aligned fp32 and 8-byte aligned bfloat16 tensors
+ * (FIELDS_ERR_UNSUPPORTED otherwise).
+ */
+size_t fields_mixer_epilogue_bias_rows(long long N);
+int fields_mixer_epilogue_forward(const float *x, const void *acc, const void *gate,
+                                  const float *sumsq, const float *bias, float *y, float eps,
+                                  int features, long long N, int D, void *stream);
+int fields_mixer_epilogue_backward(const float *grad_y, const void *acc, const void *gate,
+                                   const float *sumsq, const float *bias, void *grad_acc,
+                                   void *grad_gate, float *grad_sumsq, float *grad_bias_rows,
+                                   float eps, int features, long long N, int D, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -213,3 +213,31 @@ def test_norm_statistics_equal_the_sum_of_squares_of_read():
     from fields_lm_b200 import fused_field_read
     ref = fused_field_read(raw.float(), tr, ti, gm).double().pow(2).sum(-1)
     assert float(((sumsq.double() - ref).abs() / ref.clamp_min(1e-12)).max()) < 1e-5
+
+
+@pytest.mark.parametrize("N,D", [(37, 1024), (4096, 1024), (5, 8), (33, 4096)])
+def test_mixer_epilogue_matches_the_formula(N, D):
+    """One-kernel epilogue and its one-kernel backward against the same formula in fp32 PyTorch
+    ops on the same bfloat16 inputs."""
+    from fields_lm_b200.field_read import mixer_epilogue
+    gen = torch.Generator().manual_seed(N + D)
+    x = torch.randn(N, D, generator=gen).cuda().requires_grad_(True)
+    acc = torch.randn(N, D, generator=gen).cuda().bfloat16().requires_grad_(True)
+    gate = torch.randn(N, D, generator=gen).cuda().bfloat16().requires_grad_(True)
+    sumsq = (torch.rand(N, generator=gen) * 100 + 1).cuda().requires_grad_(True)
+    bias = torch.randn(D, generator=gen).cuda().requires_grad_(True)
+    gy = torch.randn(N, D, generator=gen).cuda()
+    eps, features = 1e-6, 2048
+    y = mixer_epilogue(x, acc, gate, sumsq, bias, eps, features)
+    y.backward(gy)
+    got = [y.detach()] + [t.grad.float().clone() for t in (x, acc, gate, sumsq, bias)]
+    for t in (x, acc, gate, sumsq, bias):
+        t.grad = None
+    rstd = torch.rsqrt(sumsq / features + eps)
+    ref = x + (acc.float() * rstd[:, None] + bias) * torch.sigmoid(gate.float())
+    ref.backward(gy)
+    want = [ref.detach()] + [t.grad.float() for t in (x, acc, gate, sumsq, bias)]
+    names = ("y", "grad_x", "grad_acc", "grad_gate", "grad_sumsq", "grad_bias")
+    tols = (1e-5, 1e-6, 2 ** -7, 2 ** -7, 1e-4, 1e-4)   # bf16 outputs carry one rounding
+    for name, g, w, tol in zip(names, got, want, tols):
+        assert rel_err(g.cpu().numpy(), w.cpu().numpy()) < tol, name
