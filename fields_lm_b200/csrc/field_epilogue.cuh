@@ -145,6 +145,42 @@ __global__ void __launch_bounds__(kEpiThreads) epilogue_backward(const EpilogueG
     }
 }
 
+// Gradient entering the recurrence when the norm statistics are an output too:
+//   total = grad_read + 2 * grad_sumsq[token] * read          (all [N, F] bfloat16, fp32 arithmetic)
+// d sumsq / d read = 2 read. grad_read may be null (then total = 2 grad_sumsq read). One pass.
+struct NormGradParams {
+    const uint16_t* grad_read;  // [N, F] bf16 or null
+    const uint16_t* read;       // [N, F] bf16
+    const float* grad_sumsq;    // [N]
+    uint16_t* total;            // [N, F] bf16
+    long long N;
+    int F;
+};
+
+__global__ void __launch_bounds__(kEpiThreads) norm_grad_combine(const NormGradParams p) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const long long row0 = (long long)blockIdx.x * kEpiRows;
+    for (int r = 0; r < kEpiRows; ++r) {
+        const long long n = row0 + r;
+        if (n >= p.N) return;
+        const float two_gs = 2.0f * p.grad_sumsq[n];
+        const size_t base = (size_t)n * p.F;
+        for (int c = (int)threadIdx.x * 4; c < p.F; c += kEpiThreads * 4) {
+            const Vec<4> rd = io_load4_stream(p.read + base + c);
+            Vec<4> out;
+            if (p.grad_read) {
+                const Vec<4> g = io_load4_stream(p.grad_read + base + c);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) out.v[k] = g.v[k] + two_gs * rd.v[k];
+            } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) out.v[k] = two_gs * rd.v[k];
+            }
+            io_store4_stream(p.total + base + c, out);
+        }
+    }
+}
+
 constexpr int kEpiMaxD = 4 * kEpiThreads * 4;  // 4,096 columns: four column groups per thread
 
 }  // namespace fields

@@ -1159,6 +1159,21 @@ int fields_mixer_epilogue_backward(const float* grad_y, const void* acc, const v
     return launch_on<EpilogueGradParams>(epilogue_backward, (unsigned)blocks, kEpiThreads, 0,
                                          reinterpret_cast<Stream>(stream), p);
 }
+
+int fields_read_norm_grad_combine(const void* grad_read, const void* read, const float* grad_sumsq,
+                                  void* total, long long N, int F, void* stream) {
+    if (N < 0 || F <= 0) return FIELDS_ERR_ARGUMENT;
+    if (N == 0) return FIELDS_OK;
+    if (!read || !grad_sumsq || !total) return FIELDS_ERR_ARGUMENT;
+    if (F % 4 || !aligned8(grad_read) || !aligned8(read) || !aligned8(total))
+        return FIELDS_ERR_UNSUPPORTED;
+    const long long blocks = (N + kEpiRows - 1) / kEpiRows;
+    if (blocks > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
+    NormGradParams p{static_cast<const uint16_t*>(grad_read), static_cast<const uint16_t*>(read),
+                     grad_sumsq, static_cast<uint16_t*>(total), N, F};
+    return launch_on<NormGradParams>(norm_grad_combine, (unsigned)blocks, kEpiThreads, 0,
+                                     reinterpret_cast<Stream>(stream), p);
+}
 #endif  // FIELDS_HOST_EMU
 
 }  // extern "C"

@@ -203,13 +203,18 @@ class FieldReadBf16StatsFunction(torch.autograd.Function):
         with torch.cuda.device(raw.device):
             # d sumsq / d read = 2 read: folded into the gradient the recurrence receives
             if grad_sumsq is not None:
-                extra = read.float() * (2.0 * grad_sumsq.float()).unsqueeze(-1)
-                total = extra if grad_read is None else extra + grad_read.float()
+                if grad_read is not None:
+                    grad_read = grad_read.contiguous().to(torch.bfloat16)
+                total = torch.empty_like(read)
+                rc = lib.fields_read_norm_grad_combine(_ptr(grad_read), _ptr(read),
+                                                       _ptr(grad_sumsq.contiguous().float()),
+                                                       _ptr(total), B * L, 4 * C,
+                                                       _stream(raw.device))
+                _lib.check(rc, "fields_read_norm_grad_combine")
             elif grad_read is not None:
-                total = grad_read
+                total = grad_read.contiguous().to(torch.bfloat16)
             else:
                 total = torch.zeros_like(read)
-            total = total.contiguous().to(torch.bfloat16)
             grad_raw = torch.empty_like(raw)
             g_par = torch.empty((3, C), device=raw.device, dtype=torch.float32)
             ws, nbytes = _workspace(B, L, C, _BWD, raw.device)

@@ -323,7 +323,15 @@ int fields_read_forward_noalloc(const float *raw, const float *tr, const float *
  * [rows, D] for the caller to add up (grad_x is grad_y itself). D % 4 == 0, D <= 4096 for the
  * backward, 16-byte aligned fp32 and 8-byte aligned bfloat16 tensors
  * (FIELDS_ERR_UNSUPPORTED otherwise).
+ *
+ * fields_read_norm_grad_combine: the gradient that fields_read_backward_bf16 must receive when
+ * sumsq of fields_read_forward_bf16_stats has a gradient of its own:
+ *   total = grad_read + 2 * grad_sumsq[token] * read        ([N, F] bfloat16, F = 4C, F % 4 == 0)
+ * in one pass; grad_read may be NULL.
  */
+int fields_read_norm_grad_combine(const void *grad_read, const void *read,
+                                  const float *grad_sumsq, void *total, long long N, int F,
+                                  void *stream);
 size_t fields_mixer_epilogue_bias_rows(long long N);
 int fields_mixer_epilogue_forward(const float *x, const void *acc, const void *gate,
                                   const float *sumsq, const float *bias, float *y, float eps,
