@@ -226,11 +226,15 @@ FL_HD Vec<4> io_load4_stream(const uint16_t* p) {
 }
 
 FL_HD void io_store4_stream(uint16_t* p, const Vec<4>& x) {
-    const uint32_t lo = (uint32_t)float_to_bf16_bits(x.v[0]) | ((uint32_t)float_to_bf16_bits(x.v[1]) << 16);
-    const uint32_t hi = (uint32_t)float_to_bf16_bits(x.v[2]) | ((uint32_t)float_to_bf16_bits(x.v[3]) << 16);
 #if FL_DEVICE_CODE
+    // one conversion instruction per pair (round to nearest even; the upper half is the first operand)
+    uint32_t lo, hi;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"(x.v[1]), "f"(x.v[0]));
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(x.v[3]), "f"(x.v[2]));
     __stcs(reinterpret_cast<uint2*>(p), make_uint2(lo, hi));
 #else
+    const uint32_t lo = (uint32_t)float_to_bf16_bits(x.v[0]) | ((uint32_t)float_to_bf16_bits(x.v[1]) << 16);
+    const uint32_t hi = (uint32_t)float_to_bf16_bits(x.v[2]) | ((uint32_t)float_to_bf16_bits(x.v[3]) << 16);
     const uint32_t w[2] = {lo, hi};
     std::memcpy(p, w, 8);
 #endif

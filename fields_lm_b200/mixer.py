@@ -93,11 +93,11 @@ class IndependentVacancyField(nn.Module):
         #   out_proj(read_norm(read)) = rstd * (read @ (W diag(w))^T) + b
         self.fused_norm = False
 
-    def _readout_fused_norm(self, x, raw, tr, ti, gamma):
+    def _readout_fused_norm(self, x, x_in, raw, tr, ti, gamma):
         read, sumsq = fused_field_read_bf16_stats(raw, tr, ti, gamma)
         w_eff = self.out_proj.weight.float() * self.read_norm.weight.float().unsqueeze(0)
         acc = F.linear(read, w_eff.to(read.dtype))
-        gate = self.gate_proj(x)
+        gate = self.gate_proj(x_in)
         if (x.dtype == torch.float32 and acc.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16
                 and self.dim % 4 == 0 and self.dim <= 4096):
             # one kernel for scale, bias, gate and residual (and one for their gradients)
@@ -108,11 +108,15 @@ class IndependentVacancyField(nn.Module):
         return x + (out * torch.sigmoid(gate)).to(x.dtype)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        raw = self.write_proj(x).contiguous()
+        fused = (self.bf16_io and self.fused_norm and self.channels % 4 == 0 and x.is_cuda
+                 and torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16)
+        # both projections of x take the same bf16 copy (autocast would make one each)
+        x_in = x.to(torch.bfloat16) if fused and x.dtype == torch.float32 else x
+        raw = self.write_proj(x_in).contiguous()
         if self.bf16_io and raw.dtype == torch.bfloat16:
             tr, ti, gamma = transition_parameters(self.radius_logit, self.theta)
-            if self.fused_norm and self.channels % 4 == 0:
-                return self._readout_fused_norm(x, raw, tr, ti, gamma)
+            if fused:
+                return self._readout_fused_norm(x, x_in, raw, tr, ti, gamma)
             read = fused_field_read_bf16(raw, tr, ti, gamma)
             out = self.out_proj(self.read_norm(read))
             return x + (out * torch.sigmoid(self.gate_proj(x))).to(x.dtype)
