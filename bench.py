@@ -322,6 +322,38 @@ def block_leg(device, stream, iters: int = 10):
     return out
 
 
+def block_breakdown(device, iters: int = 5):
+    """Kernel-time table of the mixer's forward + backward on the fused bfloat16 boundary (torch
+    profiler): where the time of a Field block goes around the operator. Not part of the JSON line."""
+    from torch.profiler import ProfilerActivity, profile
+    from fields_lm_b200.mixer import FieldBlock
+    torch.manual_seed(0)
+    block = FieldBlock(D_MODEL, "triton", 32, 32, 64, 2528).to(device).train()
+    block.mixer.bf16_io = block.mixer.fused_norm = True
+    gen = torch.Generator(device=device).manual_seed(5)
+    x = torch.randn(B, L, D_MODEL, device=device, generator=gen)
+    gy = torch.randn(B, L, D_MODEL, device=device, generator=gen)
+
+    def step():
+        block.zero_grad(set_to_none=True)
+        xg = x.requires_grad_(True)
+        xg.grad = None
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = block.mixer(xg)
+        y.backward(gy)
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize(device)
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(iters):
+            step()
+        torch.cuda.synchronize(device)
+    print(f"mixer forward + backward, {B} x {L} tokens, d_model {D_MODEL}, {iters} iterations")
+    print(prof.key_averages().table(sort_by="self_cuda_time_total", row_limit=24,
+                                    max_name_column_width=64))
+
+
 def decode_leg(device, tr, ti, gamma, peak_gbs: float, iters: int = 200):
     from fields_lm_b200 import _lib
     lib = _lib.load()
@@ -672,6 +704,8 @@ def main():
                     help="skip the CPU baseline leg (used for profiler runs)")
     ap.add_argument("--no-graph", action="store_true",
                     help="time plain launches instead of a CUDA graph of the step")
+    ap.add_argument("--block-breakdown", action="store_true",
+                    help="print the kernel-time table of one fused mixer step and exit")
     ap.add_argument("--profile", action="store_true",
                     help="run warm-up + steps only (for ncu captures); prints no bench line")
     args = ap.parse_args()
@@ -680,6 +714,12 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.block_breakdown:
+        if not torch.cuda.is_available():
+            raise SystemExit("--block-breakdown needs a CUDA device")
+        torch.cuda.set_device(0)
+        block_breakdown(torch.device("cuda", 0))
         return
     run_ours(args, rank, world, local_rank)
 

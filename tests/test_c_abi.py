@@ -55,3 +55,28 @@ def test_emulation_and_library_agree_on_workspace(library):
         for which in (0, 1):
             assert lib.fields_read_workspace_bytes(*dims, which) == \
                 emu.lib().fields_read_workspace_bytes(*dims, which)
+
+
+def test_argument_checks_need_no_device(library):
+    """Bad arguments are refused with a status code before anything is launched."""
+    from fields_lm_b200 import _lib
+    lib = _lib.load()
+    ARG, UNSUPPORTED = 1, 5
+    assert lib.fields_read_state_rows(2048) == 256 and lib.fields_read_state_rows(7) == 0
+    assert lib.fields_mixer_epilogue_bias_rows(16384) == 1024
+    assert lib.fields_mixer_epilogue_forward(None, None, None, None, None, None, 1e-6, 2048, 4, 8,
+                                             None) == ARG
+    assert lib.fields_mixer_epilogue_backward(None, None, None, None, None, None, None, None, None,
+                                              1e-6, 2048, 4, 8, None) == ARG
+    assert lib.fields_read_norm_grad_combine(None, None, None, None, 4, 8, None) == ARG
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    # a feature count that is not a multiple of four
+    assert lib.fields_read_norm_grad_combine(p, p, p, p, 4, 6, None) == UNSUPPORTED
+    assert lib.fields_read_backward_from_states(None, None, None, None, None, None, None, None,
+                                                None, None, None, None, None, None, 0, 1, 8, 4,
+                                                None) == ARG
+    assert lib.fields_read_forward_bf16_stats(None, None, None, None, None, None, None, None, None,
+                                              0, 1, 8, 4, None) == ARG
+    assert lib.fields_read_span_summary_backward(None, None, None, None, None, None, 0, 1, 8, 4,
+                                                 None) == ARG
