@@ -42,8 +42,8 @@ SYMBOLS = {
     "fields_read_fold_mailbox_backward": (_I, [_P, _P, _P, _P, _I, _I, ctypes.c_uint, _I, _I, _P]),
     "fields_read_norm_grad_combine": (_I, [_P, _P, _P, _P, ctypes.c_longlong, _I, _P]),
     "fields_mixer_epilogue_bias_rows": (_SZ, [ctypes.c_longlong]),
-    "fields_mixer_epilogue_forward": (_I, [_P] * 6 + [ctypes.c_float, _I, ctypes.c_longlong, _I, _P]),
-    "fields_mixer_epilogue_backward": (_I, [_P] * 9 + [ctypes.c_float, _I, ctypes.c_longlong, _I, _P]),
+    "fields_mixer_epilogue_forward": (_I, [_P] * 7 + [ctypes.c_float, _I, ctypes.c_longlong, _I, _P]),
+    "fields_mixer_epilogue_backward": (_I, [_P] * 11 + [ctypes.c_float, _I, ctypes.c_longlong, _I, _P]),
     "fields_read_static_scratch_bytes": (_SZ, []),
     "fields_read_forward_noalloc": (_I, [_P] * 7 + [_I, _I, _I, _P]),
 }

@@ -1121,41 +1121,44 @@ size_t fields_mixer_epilogue_bias_rows(long long N) {
 }
 
 int fields_mixer_epilogue_forward(const float* x, const void* acc, const void* gate,
-                                  const float* sumsq, const float* bias, float* y, float eps,
-                                  int features, long long N, int D, void* stream) {
+                                  const float* sumsq, const float* bias, const float* gate_bias,
+                                  float* y, float eps, int features, long long N, int D,
+                                  void* stream) {
     if (N < 0 || D <= 0 || features <= 0) return FIELDS_ERR_ARGUMENT;
     if (N == 0) return FIELDS_OK;
     if (!x || !acc || !gate || !sumsq || !bias || !y) return FIELDS_ERR_ARGUMENT;
-    if (D % 4 || !aligned16(x) || !aligned16(y) || !aligned16(bias) || !aligned8(acc) ||
-        !aligned8(gate))
+    if (D % 4 || !aligned16(x) || !aligned16(y) || !aligned16(bias) || !aligned16(gate_bias) ||
+        !aligned8(acc) || !aligned8(gate))
         return FIELDS_ERR_UNSUPPORTED;
     const long long blocks = (N + kEpiRows - 1) / kEpiRows;
     if (blocks > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
     EpilogueParams p{x, static_cast<const uint16_t*>(acc), static_cast<const uint16_t*>(gate), sumsq,
-                     bias, y, eps, 1.0f / (float)features, N, D};
+                     bias, gate_bias, y, eps, 1.0f / (float)features, N, D};
     return launch_on<EpilogueParams>(epilogue_forward, (unsigned)blocks, kEpiThreads, 0,
                                      reinterpret_cast<Stream>(stream), p);
 }
 
 int fields_mixer_epilogue_backward(const float* grad_y, const void* acc, const void* gate,
-                                   const float* sumsq, const float* bias, void* grad_acc,
-                                   void* grad_gate, float* grad_sumsq, float* grad_bias_rows,
-                                   float eps, int features, long long N, int D, void* stream) {
+                                   const float* sumsq, const float* bias, const float* gate_bias,
+                                   void* grad_acc, void* grad_gate, float* grad_sumsq,
+                                   float* grad_bias_rows, float* grad_gate_bias_rows, float eps,
+                                   int features, long long N, int D, void* stream) {
     if (N < 0 || D <= 0 || features <= 0) return FIELDS_ERR_ARGUMENT;
     if (N == 0) return FIELDS_OK;
     if (!grad_y || !acc || !gate || !sumsq || !bias || !grad_acc || !grad_gate || !grad_sumsq ||
-        !grad_bias_rows)
+        !grad_bias_rows || (gate_bias && !grad_gate_bias_rows))
         return FIELDS_ERR_ARGUMENT;
-    if (D % 4 || D > kEpiMaxD || !aligned16(grad_y) || !aligned16(bias) ||
-        !aligned16(grad_bias_rows) || !aligned8(acc) || !aligned8(gate) || !aligned8(grad_acc) ||
-        !aligned8(grad_gate))
+    if (D % 4 || D > kEpiMaxD || !aligned16(grad_y) || !aligned16(bias) || !aligned16(gate_bias) ||
+        !aligned16(grad_bias_rows) || !aligned16(grad_gate_bias_rows) || !aligned8(acc) ||
+        !aligned8(gate) || !aligned8(grad_acc) || !aligned8(grad_gate))
         return FIELDS_ERR_UNSUPPORTED;
     const long long blocks = (N + kEpiRows - 1) / kEpiRows;
     if (blocks > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
     EpilogueGradParams p{grad_y, static_cast<const uint16_t*>(acc),
-                         static_cast<const uint16_t*>(gate), sumsq, bias,
+                         static_cast<const uint16_t*>(gate), sumsq, bias, gate_bias,
                          static_cast<uint16_t*>(grad_acc), static_cast<uint16_t*>(grad_gate),
-                         grad_sumsq, grad_bias_rows, eps, 1.0f / (float)features, N, D};
+                         grad_sumsq, grad_bias_rows, grad_gate_bias_rows, eps,
+                         1.0f / (float)features, N, D};
     return launch_on<EpilogueGradParams>(epilogue_backward, (unsigned)blocks, kEpiThreads, 0,
                                          reinterpret_cast<Stream>(stream), p);
 }

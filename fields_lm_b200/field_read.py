@@ -235,28 +235,31 @@ def fused_field_read_bf16_stats(raw: torch.Tensor, transition_r: torch.Tensor,
 
 
 class MixerEpilogueFunction(torch.autograd.Function):
-    """y = x + (acc * rsqrt(sumsq / features + eps) + bias) * sigmoid(gate), one kernel each way."""
+    """y = x + (acc * rsqrt(sumsq / features + eps) + bias) * sigmoid(gate + gate_bias), one
+    kernel each way."""
 
     @staticmethod
-    def forward(ctx, x, acc, gate, sumsq, bias, eps, features):
+    def forward(ctx, x, acc, gate, sumsq, bias, gate_bias, eps, features):
         lib = _lib.load()
         D = x.shape[-1]
         x, acc, gate = x.contiguous(), acc.contiguous(), gate.contiguous()
         sumsq, bias = sumsq.contiguous().float(), bias.contiguous().float()
+        if gate_bias is not None:
+            gate_bias = gate_bias.contiguous().float()
         N = x.numel() // D
         y = torch.empty_like(x)
         with torch.cuda.device(x.device):
             rc = lib.fields_mixer_epilogue_forward(_ptr(x), _ptr(acc), _ptr(gate), _ptr(sumsq),
-                                                   _ptr(bias), _ptr(y), float(eps), int(features),
-                                                   N, D, _stream(x.device))
+                                                   _ptr(bias), _ptr(gate_bias), _ptr(y), float(eps),
+                                                   int(features), N, D, _stream(x.device))
         _lib.check(rc, "fields_mixer_epilogue_forward")
-        ctx.save_for_backward(acc, gate, sumsq, bias)
+        ctx.save_for_backward(acc, gate, sumsq, bias, gate_bias)
         ctx.consts = (float(eps), int(features), N, D)
         return y
 
     @staticmethod
     def backward(ctx, grad_y):
-        acc, gate, sumsq, bias = ctx.saved_tensors
+        acc, gate, sumsq, bias, gate_bias = ctx.saved_tensors
         eps, features, N, D = ctx.consts
         lib = _lib.load()
         grad_y = grad_y.contiguous().float()
@@ -264,24 +267,29 @@ class MixerEpilogueFunction(torch.autograd.Function):
             grad_acc, grad_gate = torch.empty_like(acc), torch.empty_like(gate)
             grad_sumsq = torch.empty_like(sumsq)
             rows = lib.fields_mixer_epilogue_bias_rows(N)
-            bias_rows = torch.empty((rows, D), device=grad_y.device, dtype=torch.float32)
-            rc = lib.fields_mixer_epilogue_backward(_ptr(grad_y), _ptr(acc), _ptr(gate), _ptr(sumsq),
-                                                    _ptr(bias), _ptr(grad_acc), _ptr(grad_gate),
-                                                    _ptr(grad_sumsq), _ptr(bias_rows), eps, features,
-                                                    N, D, _stream(grad_y.device))
+            bias_rows = torch.empty((2 if gate_bias is not None else 1, rows, D),
+                                    device=grad_y.device, dtype=torch.float32)
+            rc = lib.fields_mixer_epilogue_backward(
+                _ptr(grad_y), _ptr(acc), _ptr(gate), _ptr(sumsq), _ptr(bias), _ptr(gate_bias),
+                _ptr(grad_acc), _ptr(grad_gate), _ptr(grad_sumsq), _ptr(bias_rows[0]),
+                _ptr(bias_rows[1]) if gate_bias is not None else None, eps, features, N, D,
+                _stream(grad_y.device))
             _lib.check(rc, "fields_mixer_epilogue_backward")
-            grad_bias = bias_rows.sum(dim=0)
-        return grad_y, grad_acc, grad_gate, grad_sumsq, grad_bias, None, None
+            sums = bias_rows.sum(dim=1)
+        return (grad_y, grad_acc, grad_gate, grad_sumsq, sums[0],
+                sums[1] if gate_bias is not None else None, None, None)
 
 
 def mixer_epilogue(x: torch.Tensor, acc: torch.Tensor, gate: torch.Tensor, sumsq: torch.Tensor,
-                   bias: torch.Tensor, eps: float, features: int) -> torch.Tensor:
-    """``x + (acc * rsqrt(sumsq / features + eps) + bias) * sigmoid(gate)`` in one CUDA kernel
-    (and one for all gradients): ``x [..., D]`` fp32, ``acc`` and ``gate`` ``[..., D]`` bfloat16,
-    ``sumsq [...]`` fp32 (per token), ``bias [D]``; ``D`` a multiple of 4, at most 4096."""
+                   bias: torch.Tensor, eps: float, features: int,
+                   gate_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x + (acc * rsqrt(sumsq / features + eps) + bias) * sigmoid(gate + gate_bias)`` in one CUDA
+    kernel (and one for all gradients): ``x [..., D]`` fp32, ``acc`` and ``gate`` ``[..., D]``
+    bfloat16, ``sumsq [...]`` fp32 (per token), ``bias``, ``gate_bias`` ``[D]`` (the latter
+    optional); ``D`` a multiple of 4, at most 4096."""
     if x.dtype != torch.float32 or acc.dtype != torch.bfloat16 or gate.dtype != torch.bfloat16:
         raise TypeError((x.dtype, acc.dtype, gate.dtype))
-    return MixerEpilogueFunction.apply(x, acc, gate, sumsq, bias, eps, features)
+    return MixerEpilogueFunction.apply(x, acc, gate, sumsq, bias, gate_bias, eps, features)
 
 
 def fused_field_read_bf16(raw: torch.Tensor, transition_r: torch.Tensor,

@@ -1,5 +1,13 @@
 """Re-points a built fields-lm model at the CUDA library, without touching its source.
 
+Two boundaries. The operator (always): the reference's Field mixer calls
+``fused_field_read`` through a module global, which ``install`` rebinds. The mixer
+(``fused_mixer=True``): ``IndependentVacancyField.forward`` of the model's own class is
+replaced by a wrapper that runs ``fields_lm_b200.mixer.fused_mixer_forward`` - the same
+function of the same parameters on the bfloat16 boundary, with the norm statistics taken
+from the recurrence kernel - whenever it applies (CUDA, bfloat16 autocast, fp32 input), and
+the class's original forward otherwise.
+
 The reference's Field mixer looks ``fused_field_read`` up as a global of its own
 module at call time (``field_only_v4_chunked_triton_wiki100.py:1175-1183``).
 Every model build executes that file into a fresh module object, so the patch is
@@ -18,6 +26,15 @@ from .field_read import fused_field_read
 _NAME = "fused_field_read"
 _MIXER_CLASS = "IndependentVacancyField"
 _saved: Dict[int, object] = {}
+_saved_forward: Dict[type, object] = {}
+
+
+def _mixer_classes(model: torch.nn.Module) -> List[type]:
+    out: List[type] = []
+    for module in model.modules():
+        if type(module).__name__ == _MIXER_CLASS and type(module) not in out:
+            out.append(type(module))
+    return out
 
 
 def _namespaces(model: torch.nn.Module) -> List[dict]:
@@ -25,15 +42,17 @@ def _namespaces(model: torch.nn.Module) -> List[dict]:
     for module in model.modules():
         if type(module).__name__ != _MIXER_CLASS:
             continue
-        ns = type(module).forward.__globals__
+        # the class's own forward (not the wrapper install(fused_mixer=True) may have put there)
+        ns = _saved_forward.get(type(module), type(module).forward).__globals__
         if id(ns) not in seen and _NAME in ns:
             seen.add(id(ns))
             out.append(ns)
     return out
 
 
-def install(model: torch.nn.Module, fn=fused_field_read) -> int:
-    """Rebinds ``fused_field_read`` for every Field mixer in ``model``.
+def install(model: torch.nn.Module, fn=fused_field_read, fused_mixer: bool = False) -> int:
+    """Rebinds ``fused_field_read`` for every Field mixer in ``model``; with ``fused_mixer`` also
+    routes the mixers' ``forward`` through ``fused_mixer_forward`` where that applies.
 
     Returns the number of module namespaces patched (one per model build).
     Raises if the model holds no Field mixer with the Triton backend boundary.
@@ -44,12 +63,28 @@ def install(model: torch.nn.Module, fn=fused_field_read) -> int:
     for ns in spaces:
         _saved.setdefault(id(ns), ns[_NAME])
         ns[_NAME] = fn
+    if fused_mixer:
+        from .mixer import fused_mixer_forward
+        for cls in _mixer_classes(model):
+            if cls in _saved_forward:
+                continue
+            original = cls.forward
+            _saved_forward[cls] = original
+
+            def forward(self, x, _original=original):
+                y = fused_mixer_forward(self, x)
+                return y if y is not None else _original(self, x)
+
+            cls.forward = forward
     return len(spaces)
 
 
 def uninstall(model: torch.nn.Module) -> int:
     """Restores the original operator in every namespace ``install`` changed."""
     n = 0
+    for cls in _mixer_classes(model):
+        if cls in _saved_forward:
+            cls.forward = _saved_forward.pop(cls)
     for ns in _namespaces(model):
         if id(ns) in _saved:
             ns[_NAME] = _saved.pop(id(ns))

@@ -60,6 +60,38 @@ def transition_parameters(radius_logit: torch.Tensor, theta: torch.Tensor):
             torch.sqrt((1.0 - radius.square()).clamp_min(1e-4)))
 
 
+def fused_mixer_forward(m: nn.Module, x: torch.Tensor) -> Optional[torch.Tensor]:
+    """The Field mixer's forward on the bfloat16 boundary with the norm behind the projection.
+
+    Works on any module with the reference mixer's attributes (``write_proj``, ``radius_logit``,
+    ``theta``, ``read_norm``, ``out_proj``, ``gate_proj``, ``channels``, ``dim``): the mirror below
+    and the reference's own ``IndependentVacancyField`` (``fields_lm_b200.install(...,
+    fused_mixer=True)``). Same function of the same parameters as reference :1167-1195:
+
+        out_proj(read_norm(read)) = rstd * (read @ (W diag(w))^T) + b
+
+    with ``rstd`` from the sums of squares that the recurrence kernel returns, so ``read`` goes
+    from the recurrence to the GEMM in bfloat16 with no reduction pass and no normalised copy;
+    scale, both biases, sigmoid gate and residual are one kernel. Returns None when it does not
+    apply (not CUDA, no bfloat16 autocast, fp32 input expected, channel count not a multiple of
+    four): the caller then runs the ordinary forward.
+    """
+    if not (x.is_cuda and x.dtype == torch.float32 and torch.is_autocast_enabled()
+            and torch.get_autocast_dtype("cuda") == torch.bfloat16
+            and m.channels % 4 == 0 and m.dim % 4 == 0 and m.dim <= 4096):
+        return None
+    x_in = x.to(torch.bfloat16)  # both projections of x take the same copy
+    raw = m.write_proj(x_in).contiguous()
+    tr, ti, gamma = transition_parameters(m.radius_logit, m.theta)
+    read, sumsq = fused_field_read_bf16_stats(raw, tr, ti, gamma)
+    w_eff = m.out_proj.weight.float() * m.read_norm.weight.float().unsqueeze(0)
+    acc = F.linear(read, w_eff.to(read.dtype))
+    gate = F.linear(x_in, m.gate_proj.weight)
+    # the gate projection's bias is added, and its gradient summed, inside the epilogue kernels
+    return mixer_epilogue(x, acc, gate, sumsq, m.out_proj.bias, m.read_norm.eps, read.shape[-1],
+                          gate_bias=m.gate_proj.bias)
+
+
 class IndependentVacancyField(nn.Module):
     """Field mixer: write projection -> recurrence -> norm, output projection, gate, residual."""
 
@@ -87,36 +119,18 @@ class IndependentVacancyField(nn.Module):
         # the write projection's bf16 output under autocast and run the recurrence on a bfloat16
         # boundary (fp32 state) instead of widening raw to fp32 first.
         self.bf16_io = False
-        # With bf16_io: take the norm's statistics from the recurrence kernel and apply the norm
-        # after the output projection (a per-token scale commutes with the projection), so that
-        # `read` is neither reduced nor rewritten between the recurrence and the GEMM:
-        #   out_proj(read_norm(read)) = rstd * (read @ (W diag(w))^T) + b
+        # With bf16_io: run fused_mixer_forward (norm statistics from the recurrence kernel, norm
+        # applied after the output projection, one epilogue kernel) whenever it applies.
         self.fused_norm = False
 
-    def _readout_fused_norm(self, x, x_in, raw, tr, ti, gamma):
-        read, sumsq = fused_field_read_bf16_stats(raw, tr, ti, gamma)
-        w_eff = self.out_proj.weight.float() * self.read_norm.weight.float().unsqueeze(0)
-        acc = F.linear(read, w_eff.to(read.dtype))
-        gate = self.gate_proj(x_in)
-        if (x.dtype == torch.float32 and acc.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16
-                and self.dim % 4 == 0 and self.dim <= 4096):
-            # one kernel for scale, bias, gate and residual (and one for their gradients)
-            return mixer_epilogue(x, acc, gate, sumsq, self.out_proj.bias, self.read_norm.eps,
-                                  read.shape[-1])
-        rstd = torch.rsqrt(sumsq / read.shape[-1] + self.read_norm.eps)
-        out = acc.float() * rstd.unsqueeze(-1) + self.out_proj.bias.float()
-        return x + (out * torch.sigmoid(gate)).to(x.dtype)
-
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        fused = (self.bf16_io and self.fused_norm and self.channels % 4 == 0 and x.is_cuda
-                 and torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16)
-        # both projections of x take the same bf16 copy (autocast would make one each)
-        x_in = x.to(torch.bfloat16) if fused and x.dtype == torch.float32 else x
-        raw = self.write_proj(x_in).contiguous()
+        if self.bf16_io and self.fused_norm:
+            y = fused_mixer_forward(self, x)
+            if y is not None:
+                return y
+        raw = self.write_proj(x).contiguous()
         if self.bf16_io and raw.dtype == torch.bfloat16:
             tr, ti, gamma = transition_parameters(self.radius_logit, self.theta)
-            if fused:
-                return self._readout_fused_norm(x, x_in, raw, tr, ti, gamma)
             read = fused_field_read_bf16(raw, tr, ti, gamma)
             out = self.out_proj(self.read_norm(read))
             return x + (out * torch.sigmoid(self.gate_proj(x))).to(x.dtype)

@@ -317,10 +317,11 @@ int fields_read_forward_noalloc(const float *raw, const float *tr, const float *
  * Given acc = read @ (W diag(w))^T and gate = gate_proj(x), both [N, D] bfloat16, x [N, D] and
  * bias [D] fp32, and sumsq [N] = the sum of squares of each token's `features` read values
  * (fields_read_forward_bf16_stats, summed over the groups):
- *   y = x + (acc * rsqrt(sumsq / features + eps) + bias) * sigmoid(gate)          fp32 [N, D]
- * in one pass; the backward entry returns, in one pass, grad_acc and grad_gate (bfloat16),
- * grad_sumsq [N], and the bias gradient as fields_mixer_epilogue_bias_rows(N) partial rows
- * [rows, D] for the caller to add up (grad_x is grad_y itself). D % 4 == 0, D <= 4096 for the
+ *   y = x + (acc * rsqrt(sumsq / features + eps) + bias) * sigmoid(gate + gate_bias)   [N, D]
+ * in one pass (gate_bias [D] may be NULL: then `gate` already contains it); the backward entry
+ * returns, in one pass, grad_acc and grad_gate (bfloat16), grad_sumsq [N], and the gradients of
+ * bias and, if given, gate_bias as fields_mixer_epilogue_bias_rows(N) partial rows [rows, D]
+ * each for the caller to add up (grad_x is grad_y itself). D % 4 == 0, D <= 4096 for the
  * backward, 16-byte aligned fp32 and 8-byte aligned bfloat16 tensors
  * (FIELDS_ERR_UNSUPPORTED otherwise).
  *
@@ -334,12 +335,14 @@ int fields_read_norm_grad_combine(const void *grad_read, const void *read,
                                   void *stream);
 size_t fields_mixer_epilogue_bias_rows(long long N);
 int fields_mixer_epilogue_forward(const float *x, const void *acc, const void *gate,
-                                  const float *sumsq, const float *bias, float *y, float eps,
-                                  int features, long long N, int D, void *stream);
+                                  const float *sumsq, const float *bias, const float *gate_bias,
+                                  float *y, float eps, int features, long long N, int D,
+                                  void *stream);
 int fields_mixer_epilogue_backward(const float *grad_y, const void *acc, const void *gate,
-                                   const float *sumsq, const float *bias, void *grad_acc,
-                                   void *grad_gate, float *grad_sumsq, float *grad_bias_rows,
-                                   float eps, int features, long long N, int D, void *stream);
+                                   const float *sumsq, const float *bias, const float *gate_bias,
+                                   void *grad_acc, void *grad_gate, float *grad_sumsq,
+                                   float *grad_bias_rows, float *grad_gate_bias_rows, float eps,
+                                   int features, long long N, int D, void *stream);
 
 #ifdef __cplusplus
 }

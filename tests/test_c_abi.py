@@ -64,10 +64,10 @@ def test_argument_checks_need_no_device(library):
     ARG, UNSUPPORTED = 1, 5
     assert lib.fields_read_state_rows(2048) == 256 and lib.fields_read_state_rows(7) == 0
     assert lib.fields_mixer_epilogue_bias_rows(16384) == 1024
-    assert lib.fields_mixer_epilogue_forward(None, None, None, None, None, None, 1e-6, 2048, 4, 8,
-                                             None) == ARG
+    assert lib.fields_mixer_epilogue_forward(None, None, None, None, None, None, None, 1e-6, 2048,
+                                             4, 8, None) == ARG
     assert lib.fields_mixer_epilogue_backward(None, None, None, None, None, None, None, None, None,
-                                              1e-6, 2048, 4, 8, None) == ARG
+                                              None, None, 1e-6, 2048, 4, 8, None) == ARG
     assert lib.fields_read_norm_grad_combine(None, None, None, None, 4, 8, None) == ARG
     buf = ctypes.create_string_buffer(4096)
     p = ctypes.cast(buf, ctypes.c_void_p)

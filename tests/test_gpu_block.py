@@ -215,8 +215,9 @@ def test_norm_statistics_equal_the_sum_of_squares_of_read():
     assert float(((sumsq.double() - ref).abs() / ref.clamp_min(1e-12)).max()) < 1e-5
 
 
+@pytest.mark.parametrize("with_gate_bias", [False, True])
 @pytest.mark.parametrize("N,D", [(37, 1024), (4096, 1024), (5, 8), (33, 4096)])
-def test_mixer_epilogue_matches_the_formula(N, D):
+def test_mixer_epilogue_matches_the_formula(N, D, with_gate_bias):
     """One-kernel epilogue and its one-kernel backward against the same formula in fp32 PyTorch
     ops on the same bfloat16 inputs."""
     from fields_lm_b200.field_read import mixer_epilogue
@@ -226,18 +227,45 @@ def test_mixer_epilogue_matches_the_formula(N, D):
     gate = torch.randn(N, D, generator=gen).cuda().bfloat16().requires_grad_(True)
     sumsq = (torch.rand(N, generator=gen) * 100 + 1).cuda().requires_grad_(True)
     bias = torch.randn(D, generator=gen).cuda().requires_grad_(True)
+    gbias = torch.randn(D, generator=gen).cuda().requires_grad_(True) if with_gate_bias else None
     gy = torch.randn(N, D, generator=gen).cuda()
     eps, features = 1e-6, 2048
-    y = mixer_epilogue(x, acc, gate, sumsq, bias, eps, features)
+    leaves = [x, acc, gate, sumsq, bias] + ([gbias] if with_gate_bias else [])
+    y = mixer_epilogue(x, acc, gate, sumsq, bias, eps, features, gate_bias=gbias)
     y.backward(gy)
-    got = [y.detach()] + [t.grad.float().clone() for t in (x, acc, gate, sumsq, bias)]
-    for t in (x, acc, gate, sumsq, bias):
+    got = [y.detach()] + [t.grad.float().clone() for t in leaves]
+    for t in leaves:
         t.grad = None
     rstd = torch.rsqrt(sumsq / features + eps)
-    ref = x + (acc.float() * rstd[:, None] + bias) * torch.sigmoid(gate.float())
+    g = gate.float() + (gbias if with_gate_bias else 0.0)
+    ref = x + (acc.float() * rstd[:, None] + bias) * torch.sigmoid(g)
     ref.backward(gy)
-    want = [ref.detach()] + [t.grad.float() for t in (x, acc, gate, sumsq, bias)]
-    names = ("y", "grad_x", "grad_acc", "grad_gate", "grad_sumsq", "grad_bias")
-    tols = (1e-5, 1e-6, 2 ** -7, 2 ** -7, 1e-4, 1e-4)   # bf16 outputs carry one rounding
-    for name, g, w, tol in zip(names, got, want, tols):
-        assert rel_err(g.cpu().numpy(), w.cpu().numpy()) < tol, name
+    want = [ref.detach()] + [t.grad.float() for t in leaves]
+    names = ("y", "grad_x", "grad_acc", "grad_gate", "grad_sumsq", "grad_bias", "grad_gate_bias")
+    tols = (1e-5, 1e-6, 2 ** -7, 2 ** -7, 1e-4, 1e-4, 1e-4)   # bf16 outputs carry one rounding
+    for name, a, w, tol in zip(names, got, want, tols):
+        assert rel_err(a.cpu().numpy(), w.cpu().numpy()) < tol, name
+
+
+def test_install_fused_mixer_runs_the_fused_path():
+    """install(..., fused_mixer=True) on a block whose flags are off gives the fused mixer's result."""
+    import fields_lm_b200
+    block = _block().cuda().train()
+    gen = torch.Generator().manual_seed(8)
+    x = torch.randn(2, 256, 1024, generator=gen).cuda()
+    block.mixer.bf16_io = block.mixer.fused_norm = True
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        want = block.mixer(x)
+    block.mixer.bf16_io = block.mixer.fused_norm = False
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        plain = block.mixer(x)
+    try:
+        fields_lm_b200.install(block, fused_mixer=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            got = block.mixer(x)
+        without_autocast = block.mixer(x)      # no autocast: the wrapper uses the original forward
+    finally:
+        fields_lm_b200.uninstall(block)
+    torch.testing.assert_close(got, want, rtol=0, atol=0)
+    assert rel_err(got.detach().float().cpu().numpy(), plain.detach().float().cpu().numpy()) < BF16_TOL
+    assert without_autocast.dtype == torch.float32

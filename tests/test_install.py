@@ -70,3 +70,28 @@ def test_install_on_the_reference_modules():
         block(torch.randn(1, 6, 16))
     assert fields_lm_b200.uninstall(block) == 1
     assert canon.fused_field_read is original
+
+
+def test_install_fused_mixer_wraps_and_restores_the_class_forward():
+    """fused_mixer=True replaces the mixer class's forward by a wrapper that falls back to the
+    original one where the fused path does not apply (here: CPU), and uninstall restores it."""
+    block = mirror.FieldBlock(16, "triton", 8, 8, 16, 32)
+    cls = type(block.mixer)
+    original = cls.forward
+    calls = []
+
+    def probe(raw, tr, ti, gamma, block_c, chunk_t):
+        calls.append(tuple(raw.shape))
+        return raw.new_zeros(raw.shape[0], raw.shape[1], 4 * tr.numel())
+
+    x = torch.randn(2, 5, 16)
+    try:
+        assert fields_lm_b200.install(block, probe, fused_mixer=True) == 1
+        assert cls.forward is not original
+        y = block(x)                      # CPU: the wrapper hands over to the original forward
+        assert calls == [(2, 5, 24)] and y.shape == x.shape
+        assert fields_lm_b200.install(block, probe, fused_mixer=True) == 1   # idempotent
+    finally:
+        assert fields_lm_b200.uninstall(block) == 1
+    assert cls.forward is original
+    assert mirror.fused_field_read is fields_lm_b200.fused_field_read
