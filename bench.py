@@ -664,7 +664,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                 "d2h_bytes_per_step": (read_pin.numel() + graw_pin.numel() + gpar_pin.numel()) * 4,
                 "ms_per_step": ms_e2e,
                 "api": "fields_lm_b200.host.HostFieldRead.fwd_bwd: pinned host in/out, one batch "
-                       "row per chunk, upload / kernels / download overlapped on three streams"},
+                       "row per chunk, uploads / kernels / downloads overlapped on three streams "
+                       "(read leaves after the forward while grad_read still arrives)"},
         "forward_64k": {"workload": "forward of 1 x 65,536 tokens" +
                                     (f", sequence-sharded over {world} GPUs" if dist_on else " on one GPU"),
                         "scaling": "strong", "n_gpus": world, "exchange": exchange,

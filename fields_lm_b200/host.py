@@ -14,7 +14,8 @@ from . import _lib
 
 
 class HostFieldRead:
-    def __init__(self, device, batch: int, length: int, channels: int, rows_per_chunk: int = 1):
+    def __init__(self, device, batch: int, length: int, channels: int, rows_per_chunk: int = 1,
+                 slots: int = 2):
         self.lib = _lib.load()
         self.device = torch.device(device)
         self.B, self.L, self.C = batch, length, channels
@@ -22,12 +23,14 @@ class HostFieldRead:
         r, L, C = self.rows, length, channels
         f32 = dict(device=self.device, dtype=torch.float32)
         self.slots = []
-        for _ in range(2):
+        for _ in range(max(2, slots)):
             self.slots.append(dict(
                 raw=torch.empty(r, L, 3 * C, **f32), grad=torch.empty(r, L, 4 * C, **f32),
                 read=torch.empty(r, L, 4 * C, **f32), graw=torch.empty(r, L, 3 * C, **f32),
                 gpar=torch.empty(3, C, **f32),
-                loaded=torch.cuda.Event(), computed=torch.cuda.Event(), stored=torch.cuda.Event()))
+                raw_loaded=torch.cuda.Event(), loaded=torch.cuda.Event(),
+                forward_done=torch.cuda.Event(), computed=torch.cuda.Event(),
+                stored=torch.cuda.Event()))
         self.nf = self.lib.fields_read_workspace_bytes(r, L, C, 0)
         self.nb = self.lib.fields_read_workspace_bytes(r, L, C, 1)
         self.ws = torch.empty(max(self.nf, self.nb, 256), dtype=torch.uint8, device=self.device)
@@ -48,20 +51,26 @@ class HostFieldRead:
         for i, lo in enumerate(range(0, self.B, self.rows)):
             hi = min(lo + self.rows, self.B)
             n = hi - lo
-            s = self.slots[i % 2]
+            s = self.slots[i % len(self.slots)]
+            # Finer than one event per chunk: the forward needs only `raw`, and `read` can leave as
+            # soon as the forward is done, while `grad_read` is still arriving; `grad_raw` follows
+            # the backward. That shortens the phases in which only one copy direction is busy.
             with torch.cuda.stream(self.s_in):
                 self.s_in.wait_event(s["computed"])      # kernels of the slot's last use are done
                 s["raw"][:n].copy_(raw_host[lo:hi], non_blocking=True)
+                s["raw_loaded"].record(self.s_in)
                 s["grad"][:n].copy_(grad_host[lo:hi], non_blocking=True)
                 s["loaded"].record(self.s_in)
             with torch.cuda.stream(self.s_run):
-                self.s_run.wait_event(s["loaded"])
+                self.s_run.wait_event(s["raw_loaded"])
                 self.s_run.wait_event(s["stored"])       # the slot's last results have left
                 q = self.s_run.cuda_stream
                 rc = lib.fields_read_forward(s["raw"].data_ptr(), trp, tip, gmp, None,
                                              s["read"].data_ptr(), None, self.ws.data_ptr(),
                                              self.nf, n, L, C, q)
                 _lib.check(rc, "fields_read_forward")
+                s["forward_done"].record(self.s_run)
+                self.s_run.wait_event(s["loaded"])
                 g = s["gpar"]
                 rc = lib.fields_read_backward(s["raw"].data_ptr(), trp, tip, gmp, None,
                                               s["read"].data_ptr(), s["grad"].data_ptr(), None,
@@ -72,8 +81,9 @@ class HostFieldRead:
                 self.gpar_total.add_(g)
                 s["computed"].record(self.s_run)
             with torch.cuda.stream(self.s_out):
-                self.s_out.wait_event(s["computed"])
+                self.s_out.wait_event(s["forward_done"])
                 read_host[lo:hi].copy_(s["read"][:n], non_blocking=True)
+                self.s_out.wait_event(s["computed"])
                 graw_host[lo:hi].copy_(s["graw"][:n], non_blocking=True)
                 s["stored"].record(self.s_out)
         for st in (self.s_in, self.s_run, self.s_out):
