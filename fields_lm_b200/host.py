@@ -35,18 +35,33 @@ class HostFieldRead:
         self.nb = self.lib.fields_read_workspace_bytes(r, L, C, 1)
         self.ws = torch.empty(max(self.nf, self.nb, 256), dtype=torch.uint8, device=self.device)
         self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
-        self.gpar_total = torch.zeros(3, C, **f32)
+        # two accumulators for the parameter gradients, used by alternate calls, so that a call may
+        # start while the previous call's result is still on its way to the host
+        self.gpar = [torch.zeros(3, C, **f32) for _ in range(2)]
+        self.gpar_free = [torch.cuda.Event() for _ in range(2)]
+        self.calls = 0
 
-    def fwd_bwd(self, raw_host, grad_host, tr, ti, gamma, read_host, graw_host) -> torch.Tensor:
+    def fwd_bwd(self, raw_host, grad_host, tr, ti, gamma, read_host, graw_host, gpar_host=None,
+                wait: bool = True) -> torch.Tensor:
         """All host tensors pinned: raw [B,L,3C], grad_read [B,L,4C] in; read, grad_raw out.
-        Returns the parameter gradients ``[3, C]`` (d lambda_r, d lambda_i, d gamma) on the device.
-        The caller's current stream waits for everything before this returns control to it."""
+        Returns the parameter gradients ``[3, C]`` (d lambda_r, d lambda_i, d gamma) on the device
+        and, if ``gpar_host`` (pinned ``[3, C]``) is given, also copies them there.
+
+        With ``wait`` the caller's current stream waits for everything before control returns to
+        it. With ``wait=False`` it does not: the next call may then start uploading while this
+        call's results are still being downloaded (the two PCIe directions overlap across calls
+        too); call :meth:`join` before touching the host outputs, and pass ``gpar_host`` - the
+        returned device tensor is reused by the call after next."""
         lib, L, C = self.lib, self.L, self.C
         main = torch.cuda.current_stream(self.device)
         for st in (self.s_in, self.s_run, self.s_out):
             st.wait_stream(main)
+        which = self.calls % 2
+        self.calls += 1
+        gpar_total = self.gpar[which]
         with torch.cuda.stream(self.s_run):
-            self.gpar_total.zero_()
+            self.s_run.wait_event(self.gpar_free[which])   # its last result has left
+            gpar_total.zero_()
         trp, tip, gmp = tr.data_ptr(), ti.data_ptr(), gamma.data_ptr()
         for i, lo in enumerate(range(0, self.B, self.rows)):
             hi = min(lo + self.rows, self.B)
@@ -78,7 +93,7 @@ class HostFieldRead:
                                               g[2].data_ptr(), None, self.ws.data_ptr(), self.nb,
                                               n, L, C, q)
                 _lib.check(rc, "fields_read_backward")
-                self.gpar_total.add_(g)
+                gpar_total.add_(g)
                 s["computed"].record(self.s_run)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(s["forward_done"])
@@ -86,6 +101,17 @@ class HostFieldRead:
                 self.s_out.wait_event(s["computed"])
                 graw_host[lo:hi].copy_(s["graw"][:n], non_blocking=True)
                 s["stored"].record(self.s_out)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_stream(self.s_run)
+            if gpar_host is not None:
+                gpar_host.copy_(gpar_total, non_blocking=True)
+            self.gpar_free[which].record(self.s_out)
+        if wait:
+            self.join()
+        return gpar_total
+
+    def join(self):
+        """Makes the caller's current stream wait for every call issued so far."""
+        main = torch.cuda.current_stream(self.device)
         for st in (self.s_in, self.s_run, self.s_out):
             main.wait_stream(st)
-        return self.gpar_total
