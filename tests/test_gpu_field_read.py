@@ -160,6 +160,23 @@ def test_lean_backward_keeps_state_rows_only(dev, B, L, C):
         assert rel_err(g.cpu().numpy(), w) < FP32_TOL
 
 
+def test_saturated_gates_and_slowest_decay(dev):
+    """Inputs that drive tanh and sigmoid into saturation, zero inputs, and every channel at the
+    largest radius the mixer allows (0.99995, 4,096 steps of accumulation), against the oracle."""
+    rng = np.random.default_rng(99)
+    B, L, C = 2, 4096, 128
+    radius = np.full(C, 0.99995, np.float32)
+    theta = np.linspace(0.03, np.pi * 0.97, C).astype(np.float32)
+    tr, ti = radius * np.cos(theta), radius * np.sin(theta)
+    gm = np.sqrt(np.maximum(1 - radius ** 2, 1e-4)).astype(np.float32)
+    raw = (rng.standard_normal((B, L, 3 * C)) * 8.0).astype(np.float32)
+    raw[:, 100:200] = 0.0          # a stretch of exact zeros
+    raw[:, 300:400, 2 * C:] = -60  # vacancy 0: pure decay; then +60: vacancy at its maximum
+    raw[:, 400:500, 2 * C:] = 60
+    grad_read = rng.standard_normal((B, L, 4 * C)).astype(np.float32)
+    check_against_oracle(dev, raw, tr, ti, gm, grad_read)
+
+
 def test_state_in_and_out(dev):
     rng = np.random.default_rng(77)
     B, L, C = 3, 200, 132
