@@ -2,9 +2,12 @@
 
 ``HostFieldRead`` streams a batch from pinned host tensors through the GPU and back in
 row chunks on three CUDA streams, so the upload of chunk i+1, the kernels of chunk i and
-the download of chunk i-1 overlap and both PCIe directions stay busy. Results are the same
-as one call of the operator on the whole batch: the recurrence never mixes batch rows, and
-the parameter gradients are sums over rows, accumulated chunk by chunk in a fixed order.
+the download of chunk i-1 overlap and both PCIe directions stay busy. Dependencies are
+tracked per tensor, not per chunk: the forward starts when ``raw`` has landed, ``read``
+leaves while ``grad_read`` is still arriving, ``grad_raw`` follows the backward; with
+``wait=False`` consecutive calls overlap as well. Results are the same as one call of the
+operator on the whole batch: the recurrence never mixes batch rows, and the parameter
+gradients are sums over rows, accumulated chunk by chunk in a fixed order.
 """
 from __future__ import annotations
 
