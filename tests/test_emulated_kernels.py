@@ -223,6 +223,30 @@ def test_backward_from_saved_state_rows_refuses_what_it_cannot_do():
         emu.backward_from_states(raw, tr, ti, gm, read, grad)
 
 
+def test_saturated_gates_and_slowest_decay(algo):
+    """Saturating inputs, exact zeros, vacancy pinned at both ends, every channel at the largest
+    radius: forward and backward of every kernel family and variant against the oracle."""
+    rng = np.random.default_rng(99)
+    B, L, C = 2, 300, 20
+    radius = np.full(C, 0.99995, np.float32)
+    theta = np.linspace(0.03, np.pi * 0.97, C).astype(np.float32)
+    tr, ti = radius * np.cos(theta), radius * np.sin(theta)
+    gm = np.sqrt(np.maximum(1 - radius ** 2, 1e-4)).astype(np.float32)
+    raw = (rng.standard_normal((B, L, 3 * C)) * 8.0).astype(np.float32)
+    raw[:, 40:80] = 0.0
+    raw[:, 100:140, 2 * C:] = -60
+    raw[:, 140:180, 2 * C:] = 60
+    grad = rng.standard_normal((B, L, 4 * C)).astype(np.float32)
+    read, state = emu.forward(raw, tr, ti, gm)
+    want_read, want_state = field_oracle.forward(raw, tr, ti, gm)
+    assert rel_err(read, want_read) < FP32_TOL
+    assert rel_err(state, want_state) < FP32_TOL
+    got = emu.backward(raw, tr, ti, gm, read, grad)
+    want = field_oracle.backward(raw, tr, ti, gm, grad)
+    for g, w in zip(got[:4], want[:4]):
+        assert rel_err(g, w) < FP32_TOL
+
+
 def test_decode_steps_continue_a_prefix():
     """Prefix in one pass, then token-by-token steps == one pass over prefix + tokens (causality)."""
     rng = np.random.default_rng(8)
