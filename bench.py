@@ -12,9 +12,10 @@ no collective on the data path; weak scaling); rank 0 prints ONE JSON line.
 `value` is tokens/s with inputs resident in HBM, through the C ABI on preallocated
 buffers, timed with CUDA events on the launching stream; `e2e` is the same metric from pinned host buffers through the
 public Python call and back to the host; `roofline` relates the step to the
-measured HBM copy bandwidth; `cpu_baseline` times the CPU port of the reference's
-complex64 PyTorch path on the host cores (a reported baseline, not the target).
-`--impl reference` times only that CPU path, as the reference arm.
+measured HBM copy bandwidth; `cpu_baseline` times the reference's own CPU implementation
+(`reference_field_read` + autograd, from the staged copy under oracle/_ref) on the host cores
+(a reported baseline, not the target); `triton_reference` times the reference's Triton kernels
+on the same GPU. `--impl reference` times only the CPU path, as the reference arm.
 """
 from __future__ import annotations
 
@@ -128,15 +129,30 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------
-# CPU side: the port of the reference's complex64 PyTorch path, on the host cores
+# CPU side: the reference's own complex64 PyTorch path on the host cores
 # ---------------------------------------------------------------------------
-def cpu_step(raw, grad_read, tr, ti, gamma):
-    """One forward + backward of the CPU port; returns seconds."""
+def cpu_reference():
+    """(function, kind, description): the reference's `reference_field_read`
+    (field_only_v4_chunked_triton_wiki100.py:392-416) from the staged copy, kind "reference";
+    where that copy is absent, the pinned port of it, kind "port"."""
+    from oracle import ref
+    if ref.available():
+        canon = ref.load_canon()
+        return (lambda raw, tr, ti, gamma: canon.reference_field_read(raw, tr, ti, gamma, 32),
+                "reference", "the reference's reference_field_read (complex64 hierarchical scan, "
+                             "chunk 32) + PyTorch autograd, staged copy of the reference")
     from oracle import torch_port
+    return (lambda raw, tr, ti, gamma: torch_port.field_read(raw, tr, ti, gamma, 32), "port",
+            "complex64 PyTorch port of the reference's reference_field_read + autograd "
+            f"({ref.why_unavailable()})")
+
+
+def cpu_step(fn, raw, grad_read, tr, ti, gamma):
+    """One forward + backward on the CPU; returns seconds."""
     raw = raw.clone().requires_grad_(True)
     tr, ti, gamma = (p.clone().requires_grad_(True) for p in (tr, ti, gamma))
     t0 = time.perf_counter()
-    read = torch_port.field_read(raw, tr, ti, gamma, 32)
+    read = fn(raw, tr, ti, gamma)
     read.backward(grad_read)
     return time.perf_counter() - t0
 
@@ -144,15 +160,15 @@ def cpu_step(raw, grad_read, tr, ti, gamma):
 def cpu_baseline(sample_batch: int = B, iters: int = 3):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
+    fn, kind, what = cpu_reference()
     tr, ti, gamma = init_parameters("cpu")
     raw, grad_read = synthetic_inputs(1, sample_batch, L)
-    cpu_step(raw, grad_read, tr, ti, gamma)  # warm-up
-    secs = [cpu_step(raw, grad_read, tr, ti, gamma) for _ in range(iters)]
+    cpu_step(fn, raw, grad_read, tr, ti, gamma)  # warm-up
+    secs = [cpu_step(fn, raw, grad_read, tr, ti, gamma) for _ in range(iters)]
     return {"value": sample_batch * L / statistics.median(secs), "unit": "tokens/s",
-            "cores": torch.get_num_threads(), "kind": "port",
+            "cores": torch.get_num_threads(), "kind": kind,
             "sample": f"forward+backward of {sample_batch} x {L} tokens (of the {B} x {L} "
-                      f"workload), median of {iters} after 1 warm-up, complex64 PyTorch port of "
-                      "the reference's reference_field_read + autograd"}
+                      f"workload), median of {iters} after 1 warm-up; {what}"}
 
 
 def run_reference_arm(args, rank: int):
@@ -161,24 +177,25 @@ def run_reference_arm(args, rank: int):
         return
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
+    fn, kind, what = cpu_reference()
     tr, ti, gamma = init_parameters("cpu")
     raw, grad_read = synthetic_inputs(1, B, L)
     # bound the whole run to a few minutes: use fewer batch rows per step if the full batch is too slow
-    t_full = cpu_step(raw, grad_read, tr, ti, gamma)
+    t_full = cpu_step(fn, raw, grad_read, tr, ti, gamma)
     time_limit_s = 150.0
     sample_batch = B
     if (args.steps + args.warmup) * t_full > time_limit_s:
         sample_batch = max(1, min(B, int(B * time_limit_s / ((args.steps + args.warmup) * t_full))))
         raw, grad_read = raw[:sample_batch].contiguous(), grad_read[:sample_batch].contiguous()
     for _ in range(args.warmup):
-        cpu_step(raw, grad_read, tr, ti, gamma)
+        cpu_step(fn, raw, grad_read, tr, ti, gamma)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_step(raw, grad_read, tr, ti, gamma)
+        cpu_step(fn, raw, grad_read, tr, ti, gamma)
     total = time.perf_counter() - t0
     value = sample_batch * L * args.steps / total
     sample = (f"each step = forward+backward of {sample_batch} x {L} tokens (of the {B} x {L} "
-              "workload), complex64 PyTorch port of the reference's CPU path")
+              f"workload); {what}")
     line = {
         "impl": "reference", "metric": "field_tokens_per_s_fwd_bwd", "value": value,
         "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -186,7 +203,7 @@ def run_reference_arm(args, rank: int):
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args.gpus),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(),
-                         "kind": "port", "sample": sample},
+                         "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -288,14 +305,26 @@ DECODE_BATCH, DECODE_BLOCKS = 256, 18
 DECODE_BYTES_PER_SEQ_BLOCK = 2 * (2 * C * 4) + 3 * C * 2 + 4 * C * 2   # state r+w, bf16 raw, bf16 read
 
 
-def block_leg(device, stream, iters: int = 10):
-    """Forward + backward of one whole Field block (mixer + SwiGLU, d_model 1,024, 8 x 2,048
-    tokens, autocast bf16) around the operator: on the reference's fp32 operator boundary, and on
-    the bfloat16 boundary with the norm statistics taken from the recurrence kernel. The GEMMs,
-    norms and the feed-forward are PyTorch library calls in both."""
-    from fields_lm_b200.mixer import FieldBlock
+def reference_field_block(device):
+    """The reference's own `FieldBlock(1024, "triton", 32, 32, 64, 2528)` from the staged copy,
+    seed-0 weights, on the GPU, and the module it lives in."""
+    from oracle import ref
+    canon = ref.load_canon()
     torch.manual_seed(0)
-    block = FieldBlock(D_MODEL, "triton", 32, 32, 64, 2528).to(device).train()
+    return canon, canon.FieldBlock(D_MODEL, "triton", 32, 32, 64, 2528).to(device).train()
+
+
+def block_leg(device, stream, iters: int = 10):
+    """Forward + backward of one whole Field block of the reference (mixer + SwiGLU, d_model
+    1,024, 8 x 2,048 tokens, autocast bf16), three ways: with the reference's Triton kernels, with
+    this library installed at the operator boundary, and with `install(fused_mixer=True)`
+    (bfloat16 boundary, norm statistics from the recurrence kernel). The GEMMs, norms and the
+    feed-forward are PyTorch library calls in all three."""
+    import fields_lm_b200
+    from oracle import ref
+    if not ref.available():
+        return {"unavailable": ref.why_unavailable()}
+    canon, block = reference_field_block(device)
     gen = torch.Generator(device=device).manual_seed(5)
     x = torch.randn(B, L, D_MODEL, device=device, generator=gen)
     gy = torch.randn(B, L, D_MODEL, device=device, generator=gen)
@@ -306,30 +335,47 @@ def block_leg(device, stream, iters: int = 10):
         with torch.autocast("cuda", dtype=torch.bfloat16):
             y = block(xg)
         y.backward(gy)
+        return y, xg.grad
 
-    out = {"workload": f"one FieldBlock forward + backward, {B} x {L} tokens, d_model {D_MODEL}, "
-                       "autocast bf16, random-init weights"}
-    for name, bf16_io, fused in (("fp32_operator_boundary", False, False),
-                                 ("bf16_boundary_fused_norm", True, True)):
-        block.mixer.bf16_io, block.mixer.fused_norm = bf16_io, fused
-        for _ in range(3):
-            step()
-        torch.cuda.reset_peak_memory_stats(device)
-        ms = timed_loop(step, iters, stream) / iters
-        out[name] = {"ms": ms, "tokens_per_s": B * L / (ms * 1e-3),
-                     "peak_mib": torch.cuda.max_memory_allocated(device) / 2 ** 20}
+    def rel(a, b):
+        return float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-6))
+
+    out = {"workload": f"one reference FieldBlock forward + backward, {B} x {L} tokens, d_model "
+                       f"{D_MODEL}, autocast bf16, seed-0 weights"}
+    base = None
+    for name, mode in (("reference_triton_kernels", None), ("operator_installed", False),
+                       ("fused_mixer_installed", True)):
+        try:
+            if mode is not None:
+                fields_lm_b200.install(block, fused_mixer=mode)
+            for _ in range(3):
+                y, gx = step()
+            torch.cuda.reset_peak_memory_stats(device)
+            ms = timed_loop(step, iters, stream) / iters
+            out[name] = {"ms": ms, "tokens_per_s": B * L / (ms * 1e-3),
+                         "peak_mib": torch.cuda.max_memory_allocated(device) / 2 ** 20}
+            if base is None:
+                base = (y.detach().clone(), gx.clone())
+            else:
+                out[name]["rel_vs_triton"] = {"y": rel(y.detach(), base[0]), "grad_x": rel(gx, base[1]),
+                                              "tolerance": BF16_TOL}
+        except Exception as exc:
+            out[name] = {"error": repr(exc)[:300]}
+        finally:
+            if mode is not None:
+                fields_lm_b200.uninstall(block)
     del block, x, gy
     return out
 
 
 def block_breakdown(device, iters: int = 5):
-    """Kernel-time table of the mixer's forward + backward on the fused bfloat16 boundary (torch
-    profiler): where the time of a Field block goes around the operator. Not part of the JSON line."""
+    """Kernel-time table of the reference mixer's forward + backward with
+    `install(fused_mixer=True)` (torch profiler): where the time of a Field block goes around the
+    operator. Not part of the JSON line."""
+    import fields_lm_b200
     from torch.profiler import ProfilerActivity, profile
-    from fields_lm_b200.mixer import FieldBlock
-    torch.manual_seed(0)
-    block = FieldBlock(D_MODEL, "triton", 32, 32, 64, 2528).to(device).train()
-    block.mixer.bf16_io = block.mixer.fused_norm = True
+    canon, block = reference_field_block(device)
+    fields_lm_b200.install(block, fused_mixer=True)
     gen = torch.Generator(device=device).manual_seed(5)
     x = torch.randn(B, L, D_MODEL, device=device, generator=gen)
     gy = torch.randn(B, L, D_MODEL, device=device, generator=gen)
@@ -352,6 +398,149 @@ def block_breakdown(device, iters: int = 5):
     print(f"mixer forward + backward, {B} x {L} tokens, d_model {D_MODEL}, {iters} iterations")
     print(prof.key_averages().table(sort_by="self_cuda_time_total", row_limit=24,
                                     max_name_column_width=64))
+
+
+def triton_reference_leg(device, stream, raw, grad_read, tr, ti, gamma, steps, ours_read,
+                         ours_grad_raw):
+    """The comparator this library displaces: the reference's six Triton kernels behind
+    `fused_field_read` (field_only_v4_chunked_triton_wiki100.py:443-1123, geometry BLOCK_C 32 /
+    CHUNK_T 64), JIT-compiled for this GPU, timed with CUDA events on the same tensors: forward
+    + backward of 8 x 2,048 through its autograd function (as its callers run it), the same
+    through this library's autograd function, and the forward of 1 x 65,536."""
+    from oracle import ref
+    from fields_lm_b200 import fused_field_read as ours
+    if not ref.available():
+        return {"unavailable": ref.why_unavailable()}
+    peak = measured_peaks()[0]
+    try:
+        canon = ref.load_canon()
+        theirs = canon.fused_field_read
+        raw_g = raw.detach().clone().requires_grad_(True)
+        par = [p.detach().clone().requires_grad_(True) for p in (tr, ti, gamma)]
+        box = {}
+
+        def make_step(fn):
+            def step():
+                raw_g.grad = None
+                for q in par:
+                    q.grad = None
+                read = fn(raw_g, *par, 32, 64)
+                read.backward(grad_read)
+                box["read"] = read
+            return step
+
+        def rel(a, b):
+            return float((a - b).abs().max() / b.abs().max().clamp_min(1e-6))
+
+        out = {"what": "reference Triton kernels (BLOCK_C 32, CHUNK_T 64) on this GPU, through the "
+                       "reference's autograd function; `ours_autograd_ms` is this library through "
+                       "its autograd function on the same tensors"}
+        timings = {}
+        for name, fn in (("triton", theirs), ("ours", ours)):
+            step = make_step(fn)
+            for _ in range(3):
+                step()
+            timings[name] = timed_loop(step, steps, stream) / steps
+            if name == "triton":
+                out["parity_vs_triton"] = {
+                    "read_rel": rel(ours_read, box["read"].detach()),
+                    "grad_raw_rel": rel(ours_grad_raw, raw_g.grad), "tolerance": FP32_TOL}
+        ms = timings["triton"]
+        out["fwd_bwd_8x2048"] = {
+            "ms": ms, "tokens_per_s": B * L / (ms * 1e-3),
+            "achieved": B * L * BYTES_PER_TOKEN / (ms * 1e-3) / 1e9,
+            "frac": B * L * BYTES_PER_TOKEN / (ms * 1e-3) / 1e9 / peak,
+            "ours_autograd_ms": timings["ours"]}
+        box.clear()
+        raw_g.grad = None
+        long_raw = synthetic_inputs(2, 1, LONG_L)[0].to(device)
+        tr_d, ti_d, gm_d = tr.detach(), ti.detach(), gamma.detach()
+
+        def long_fwd():
+            with torch.no_grad():
+                theirs(long_raw, tr_d, ti_d, gm_d, 32, 64)
+        for _ in range(3):
+            long_fwd()
+        n = max(5, min(steps, 30))
+        ms = timed_loop(long_fwd, n, stream) / n
+        out["fwd_1x65536"] = {
+            "ms": ms, "tokens_per_s": LONG_L / (ms * 1e-3),
+            "achieved": LONG_L * BYTES_PER_TOKEN_FWD / (ms * 1e-3) / 1e9,
+            "frac": LONG_L * BYTES_PER_TOKEN_FWD / (ms * 1e-3) / 1e9 / peak}
+        del long_raw
+        return out
+    except Exception as exc:  # Triton could not compile or run here: say why, keep the line
+        return {"unavailable": f"reference Triton path failed on this box: {exc!r}"[:600]}
+
+
+def recurrence_kernel_share(step, device):
+    """Share of one step's GPU kernel time spent in Field-recurrence kernels (torch profiler)."""
+    from torch.profiler import ProfilerActivity, profile
+    torch.cuda.synchronize(device)
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step()
+        torch.cuda.synchronize(device)
+    total = field = 0.0
+    for ev in prof.key_averages():
+        t = float(getattr(ev, "self_device_time_total", 0.0) or 0.0)
+        total += t
+        key = ev.key
+        if ("_field_" in key or "fields::" in key or "fill_entry" in key):
+            field += t
+    return field / total if total > 0 else None
+
+
+def full_model_leg(device, stream, iters: int = 3):
+    """One training step of the reference's full 24-layer model (18 Field / 2 Mamba-2 / 4 refresh
+    blocks + PCAF, about 300 M parameters, seed 0) on token ids uniform in [0, 16384) of shape
+    [8, 2048] under bf16 autocast, through the reference's public API: once with the reference's
+    Triton Field kernels, once with this library installed; same model object, same weights."""
+    import fields_lm_b200
+    from oracle import full_model, mamba_standin, ref
+    if not ref.available():
+        return {"unavailable": ref.why_unavailable()}
+    try:
+        model, standin = full_model.build(device, model_seed=0)
+        model.train()
+        ids, labels = full_model.token_batch(B, L, 11, device)
+
+        def step():
+            return full_model.training_step(model, ids, labels)
+
+        out = {"workload": f"FieldsForCausalLM(ids [{B}, {L}], labels) forward + backward, bf16 "
+                           "autocast, fp32 weights from model_seed 0, checkpoint policy field_half",
+               "parameters": sum(q.numel() for q in model.parameters()),
+               "field_blocks": full_model.field_block_count(model),
+               "mamba2": mamba_standin.STANDIN_LABEL if standin else "mamba-ssm package"}
+        runs = {}
+        for name in ("reference_triton_kernels", "operator_installed"):
+            if name == "operator_installed":
+                fields_lm_b200.install(model)
+            for _ in range(2):
+                step()
+            ms = timed_loop(step, iters, stream) / iters
+            loss = float(step())
+            runs[name] = (loss, full_model.gradients(model))
+            out[name] = {"ms": ms, "tokens_per_s": B * L / (ms * 1e-3), "loss": loss,
+                         "recurrence_kernel_share": recurrence_kernel_share(step, device)}
+            if name == "reference_triton_kernels":
+                # the reference against itself: what its own atomics and bf16 GEMMs leave undetermined
+                step()
+                out[name]["rerun_grad_rel"] = full_model.compare_gradients(
+                    full_model.gradients(model), runs[name][1])[0]
+        fields_lm_b200.uninstall(model)
+        worst, where = full_model.compare_gradients(runs["operator_installed"][1],
+                                                    runs["reference_triton_kernels"][1])
+        out["parity"] = {"loss_abs": abs(runs["operator_installed"][0] -
+                                         runs["reference_triton_kernels"][0]),
+                         "grad_rel_worst": worst, "grad_worst_parameter": where,
+                         "tolerance": BF16_TOL}
+        out["speedup"] = out["reference_triton_kernels"]["ms"] / out["operator_installed"]["ms"]
+        del model, runs
+        torch.cuda.empty_cache()
+        return out
+    except Exception as exc:
+        return {"unavailable": f"full model step failed: {exc!r}"[:600]}
 
 
 def decode_leg(device, tr, ti, gamma, peak_gbs: float, iters: int = 200):
@@ -443,6 +632,54 @@ def parity_check(device, tr, ti, gamma):
     return {"read_rel": rel(read.detach().cpu().numpy().astype(np.float64), ref_read),
             "grad_raw_rel": rel(grad_raw.cpu().numpy().astype(np.float64), ref_grad),
             "tolerance": FP32_TOL}
+
+
+def pin_to_gpu_numa_node(index: int):
+    """Moves this process onto the CPUs NVML names as closest to GPU `index` (a process
+    setting: nothing of the GPU changes). Returns what was done, for the JSON line."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        cpus &= set(os.sched_getaffinity(0))
+        if not cpus:
+            return {"pinned": False, "why": "NVML's ideal CPUs are outside this process's cpuset"}
+        os.sched_setaffinity(0, cpus)
+        return {"pinned": True, "cpus": len(cpus), "of": os.cpu_count()}
+    except Exception as exc:
+        return {"pinned": False, "why": repr(exc)[:200]}
+
+
+def pcie_rates(device, stream, host_pinned, device_like):
+    """Plain pinned copies of one input tensor each way and both ways at once: the rate the box's
+    host link gives, which bounds the end-to-end figure."""
+    dev = torch.empty_like(device_like)
+    back = torch.empty_like(host_pinned)
+    nbytes = host_pinned.numel() * host_pinned.element_size()
+    side = torch.cuda.Stream(device)
+
+    def h2d():
+        dev.copy_(host_pinned, non_blocking=True)
+
+    def d2h():
+        back.copy_(device_like, non_blocking=True)
+
+    def both():
+        side.wait_stream(stream)
+        with torch.cuda.stream(side):
+            back.copy_(device_like, non_blocking=True)
+        dev.copy_(host_pinned, non_blocking=True)
+        stream.wait_stream(side)
+    out = {"bytes_each_way": nbytes}
+    for name, fn in (("h2d", h2d), ("d2h", d2h), ("both_ways", both)):
+        fn()
+        torch.cuda.synchronize(device)
+        ms = timed_loop(fn, 3, stream) / 3
+        out[name + "_ms"] = ms
+        out[name + "_gbs"] = nbytes * (2 if name == "both_ways" else 1) / (ms * 1e-3) / 1e9
+    return out
 
 
 def run_ours(args, rank: int, world: int, local_rank: int):
@@ -566,11 +803,28 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     ms_long = max_over_ranks(timed_loop(long_fwd, long_steps, stream) / long_steps, dist_on, device)
     barrier(dist_on)
 
+    # Sharded runs prove their output, outside the timed region: every rank also runs the whole
+    # sequence on its own GPU (the single-GPU path that the parity tests hold to the oracle) and
+    # compares its span of `read` with that slice; the worst rank's figure goes into the line.
+    long_parity = None
+    full_long = None
+    if dist_on:
+        full_long = {"raw": synthetic_inputs(2, 1, LONG_L)[0].to(device)}
+        full_op = DirectOp(device, 1, LONG_L)
+        full_op.forward(full_long["raw"], tr_d, ti_d, gm_d)
+        span_read, _ = long_fwd()
+        want = full_op.read[:, lo:hi]
+        err = float((span_read - want).abs().max() / full_op.read.abs().max().clamp_min(1e-6))
+        long_parity = {"read_rel_vs_single_gpu": max_over_ranks(err, dist_on, device),
+                       "tolerance": FP32_TOL, "ranks": world}
+        full_long["op"] = full_op
+
     # the training step of the same sequence: forward + backward, on one GPU through the C ABI on
     # preallocated buffers, on several sharded over the sequence through the autograd function
     # (dual summaries all-gathered in the backward pass, parameter gradients all-reduced)
-    long_grad = torch.randn(1, long_raw.shape[1], 4 * C, device=device,
-                            generator=torch.Generator(device=device).manual_seed(3 + rank))
+    full_grad = torch.randn(1, LONG_L, 4 * C, device=device,
+                            generator=torch.Generator(device=device).manual_seed(3))
+    long_grad = full_grad[:, lo:hi].contiguous() if dist_on else full_grad
     if dist_on:
         del sp_fwd  # its buffers; the training step holds its own
         if healthy:
@@ -599,7 +853,20 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     except Exception as exc:  # the headline line must still be printed
         print(f"train_64k leg failed: {exc!r}", file=sys.stderr)
         ms_train = None
-    del long_raw, long_grad
+    train_parity = None
+    if dist_on and ms_train is not None:
+        full_op = full_long["op"]
+        full_op.backward(full_long["raw"], tr_d, ti_d, gm_d, full_grad)
+        trainer.forward(long_raw, tr_d, ti_d, gm_d)
+        span_graw, span_gpar = trainer.backward(long_raw, tr_d, ti_d, gm_d, long_grad)
+        want = full_op.grad_raw[:, lo:hi]
+        e1 = float((span_graw - want).abs().max() / full_op.grad_raw.abs().max().clamp_min(1e-6))
+        e2 = float((span_gpar - full_op.grad_par).abs().max() /
+                   full_op.grad_par.abs().max().clamp_min(1e-6))
+        train_parity = {"grad_raw_rel_vs_single_gpu": max_over_ranks(e1, dist_on, device),
+                        "grad_params_rel_vs_single_gpu": max_over_ranks(e2, dist_on, device),
+                        "tolerance": FP32_TOL, "ranks": world}
+    del long_raw, long_grad, full_grad, full_long
 
     # the same step on the bfloat16 boundary (raw, read and their gradients in bf16, fp32 state)
     bf16 = bf16_leg(device, raw_d, grad_read, tr_d, ti_d, gm_d, args.steps, stream)
@@ -608,8 +875,20 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # blocks, bf16 rows, fp32 carried states; plain launches and one CUDA graph of the 18 launches
     decode = decode_leg(device, tr_d, ti_d, gm_d, peak_gbs=measured_peaks()[0]) if not dist_on else None
     block = block_leg(device, stream) if not dist_on else None
+    # the reference's Triton kernels on this GPU, same tensors (rank 0's GPU only)
+    triton = None
+    if rank == 0 and not args.no_triton:
+        read0, graw0 = gpu_step(raw, grad_read, tr, ti, gamma)
+        triton = triton_reference_leg(device, stream, raw, grad_read, tr, ti, gamma,
+                                      max(5, min(args.steps, 30)), read0.detach(), graw0)
+        del read0, graw0
+    full_model = full_model_leg(device, stream) if (not dist_on and not args.no_full_model) else None
 
-    # end to end: pinned host -> device, forward + backward, results back to pinned host
+    # end to end: pinned host -> device, forward + backward, results back to pinned host.
+    # The process first moves onto the CPUs next to its GPU (NVML's ideal affinity for the device),
+    # so that the pinned buffers it allocates from here on sit on that NUMA node.
+    all_cpus = os.sched_getaffinity(0)
+    placement = pin_to_gpu_numa_node(local_rank)
     raw_pin, grad_pin = raw_h.pin_memory(), grad_h.pin_memory()
     read_pin = torch.empty(B, L, 4 * C).pin_memory()
     graw_pin = torch.empty(B, L, 3 * C).pin_memory()
@@ -629,11 +908,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         pipe.join()
     e2e_steps_then_join(2)
     torch.cuda.synchronize(device)
+    pcie = pcie_rates(device, stream, raw_pin, raw_d)
     e2e_steps = max(3, min(args.steps, 10))
     barrier(dist_on)
     ms_e2e = max_over_ranks(timed_loop(lambda: e2e_steps_then_join(e2e_steps), 1, stream) / e2e_steps,
                             dist_on, device)
     barrier(dist_on)
+    os.sched_setaffinity(0, all_cpus)  # the CPU baseline below uses every host core again
 
     if rank != 0:
         if dist_on:
@@ -673,25 +954,32 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                 "api": "fields_lm_b200.host.HostFieldRead.fwd_bwd: pinned host in/out, one batch "
                        "row per chunk, uploads / kernels / downloads overlapped on three streams "
                        "(read leaves after the forward while grad_read still arrives; steps issued "
-                       "back to back, the timed region ends when the last result is on the host)"},
+                       "back to back, the timed region ends when the last result is on the host)",
+                "host_placement": placement, "pcie": pcie,
+                "bound": "PCIe: every step moves h2d + d2h bytes through the host link; "
+                         "pcie.both_ways_ms is what plain copies of the same bytes take"},
         "forward_64k": {"workload": "forward of 1 x 65,536 tokens" +
                                     (f", sequence-sharded over {world} GPUs" if dist_on else " on one GPU"),
                         "scaling": "strong", "n_gpus": world, "exchange": exchange,
                         "ms": ms_long, "tokens_per_s": LONG_L / (ms_long * 1e-3),
                         "achieved": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9,
-                        "frac": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9 / (peak * world)},
+                        "frac": LONG_L * BYTES_PER_TOKEN_FWD / (ms_long * 1e-3) / 1e9 / (peak * world),
+                        "parity": long_parity},
         "train_64k": None if ms_train is None else {
             "workload": "forward + backward of 1 x 65,536 tokens" +
                         (f", sequence-sharded over {world} GPUs" if dist_on else " on one GPU"),
             "scaling": "strong", "n_gpus": world, "api": train_api, "ms": ms_train,
             "tokens_per_s": LONG_L / (ms_train * 1e-3),
             "achieved": LONG_L * BYTES_PER_TOKEN / (ms_train * 1e-3) / 1e9,
-            "frac": LONG_L * BYTES_PER_TOKEN / (ms_train * 1e-3) / 1e9 / (peak * world)},
+            "frac": LONG_L * BYTES_PER_TOKEN / (ms_train * 1e-3) / 1e9 / (peak * world),
+            "parity": train_parity},
         "bf16_io": {**bf16, "achieved": B * L * BYTES_PER_TOKEN / 2 / (bf16["ms_per_step"] * 1e-3) / 1e9,
                     "frac": B * L * BYTES_PER_TOKEN / 2 / (bf16["ms_per_step"] * 1e-3) / 1e9 / peak,
                     "tokens_per_s": world * B * L / (bf16["ms_per_step"] * 1e-3)},
         "decode_step": decode,
         "field_block": block,
+        "triton_reference": triton,
+        "full_model": full_model,
         "gpu_launches": KERNEL_LAUNCHES_PER_STEP * args.steps,
         "clocks": clocks.summary(),
         "parity": parity_check(device, tr.detach(), ti.detach(), gamma.detach()),
@@ -711,6 +999,10 @@ def main():
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true",
                     help="skip the CPU baseline leg (used for profiler runs)")
+    ap.add_argument("--no-triton", action="store_true",
+                    help="skip the leg that times the reference's Triton kernels on this GPU")
+    ap.add_argument("--no-full-model", action="store_true",
+                    help="skip the full 24-layer model leg")
     ap.add_argument("--no-graph", action="store_true",
                     help="time plain launches instead of a CUDA graph of the step")
     ap.add_argument("--block-breakdown", action="store_true",

@@ -13,8 +13,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libfields_read.so"
 SOURCES = [CSRC / "fields_read.cu"]
-HEADERS = [CSRC / "field_math.cuh", CSRC / "field_kernels.cuh",
-           PKG.parent / "include" / "fields_read.h"]
+HEADERS = sorted(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "fields_read.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

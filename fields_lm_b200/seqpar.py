@@ -231,6 +231,10 @@ class SequenceParallelForwardP2P:
 
     def __init__(self, batch: int, span_length: int, channels: int, device, group=None):
         import ctypes
+        import os
+        # The mailboxes are written with plain peer stores only; binding them to an NVLink
+        # multicast object buys nothing and ties every rank's memory to the others' lifetime.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         self.lib = _lib.load()
         self.group = group if group is not None else dist.group.WORLD

@@ -16,7 +16,7 @@ BLOCK_FP32_TOL = 5e-5
 
 
 def _block(seed=0):
-    from fields_lm_b200.mixer import FieldBlock
+    from mirror import FieldBlock
     torch.manual_seed(seed)
     return FieldBlock(1024, "triton", 32, 32, 64, 2528)
 
@@ -102,7 +102,7 @@ def test_state_dict_keys_match_the_reference_block():
 def test_prefill_then_decode_steps_equal_one_full_pass():
     """Three stacked blocks: a prefix pass that returns states, then single-token steps, must
     reproduce the full pass over prefix + tokens (the model is causal)."""
-    from fields_lm_b200.mixer import FieldBlock
+    from mirror import FieldBlock
     torch.manual_seed(5)
     blocks = [FieldBlock(256, "triton", 32, 32, 64, 512).cuda().eval() for _ in range(3)]
     gen = torch.Generator().manual_seed(6)

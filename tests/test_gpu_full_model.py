@@ -1,0 +1,45 @@
+"""The reference's full 24-layer model with the CUDA library swapped in (GPU).
+
+``build_official_fields`` of the staged reference builds the promoted 18 Field / 2 Mamba-2 /
+4 refresh model; one training step under bf16 autocast runs first with the reference's Triton
+Field kernels, then with ``fields_lm_b200.install(model)`` on the same object. The Mamba-2
+editors are the labelled stand-in of ``oracle/mamba_standin.py`` on both sides where
+``mamba-ssm`` is not installed. Smaller batch than the benchmark's [8, 2048] to keep the test
+short; the benchmark's ``full_model`` leg runs the full shape.
+"""
+import pytest
+import torch
+
+import fields_lm_b200
+from conftest import BF16_TOL
+from oracle import full_model, ref
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(not ref.available(), reason="staged reference absent")]
+
+
+def test_training_step_matches_the_reference_triton_path():
+    device = torch.device("cuda", 0)
+    model, _ = full_model.build(device, model_seed=0)
+    model.train()
+    audit = model.topology_audit
+    assert (audit["native_field_count"], audit["mamba_count"], audit["refresh_count"]) == (18, 2, 4)
+    ids, labels = full_model.token_batch(2, 1024, 11, device)
+
+    loss_ref = float(full_model.training_step(model, ids, labels))
+    grads_ref = full_model.gradients(model)
+    full_model.training_step(model, ids, labels)
+    noise, _ = full_model.compare_gradients(full_model.gradients(model), grads_ref)
+
+    assert fields_lm_b200.install(model) == 1     # one module namespace for all 18 blocks
+    try:
+        loss_new = float(full_model.training_step(model, ids, labels))
+        grads_new = full_model.gradients(model)
+    finally:
+        fields_lm_b200.uninstall(model)
+    assert set(grads_new) == set(grads_ref)
+    assert all(torch.isfinite(g).all() for g in grads_new.values())
+    assert abs(loss_new - loss_ref) <= BF16_TOL * abs(loss_ref)
+    worst, where = full_model.compare_gradients(grads_new, grads_ref)
+    # the reference re-run against itself differs by `noise` (atomics, bf16 GEMM splits)
+    assert worst <= max(BF16_TOL, 2 * noise), (worst, where, noise)

@@ -67,7 +67,7 @@ def test_sequence_sharded_forward_matches_single_gpu_and_oracle(tmp_path, L):
     import torch.multiprocessing as mp
     from conftest import FP32_TOL, rel_err
     from oracle import field_oracle
-    world = min(torch.cuda.device_count(), 4)
+    world = torch.cuda.device_count()
     port = 29600 + (os.getpid() % 2000)
     mp.spawn(_worker, args=(world, port, L, str(tmp_path)), nprocs=world, join=True)
     full = np.load(tmp_path / "full.npz")
@@ -142,7 +142,7 @@ def test_sequence_sharded_training_step_matches_the_oracle(tmp_path):
     from conftest import FP32_TOL, rel_err
     from oracle import field_oracle
     L = 2048 + 11
-    world = min(torch.cuda.device_count(), 4)
+    world = torch.cuda.device_count()
     port = 30600 + (os.getpid() % 2000)
     mp.spawn(_train_worker, args=(world, port, L, str(tmp_path)), nprocs=world, join=True)
     x = np.load(tmp_path / "inputs.npz")

@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import fields_lm_b200
-from fields_lm_b200 import mixer as mirror
+import mirror
 
 CANON_REL = "src/fields_official/reference/field_only_v4_chunked_triton_wiki100.py"
 
@@ -37,22 +37,28 @@ def test_operator_rejects_cpu_and_wrong_dtype_like_the_reference():
         fields_lm_b200.fused_field_read(raw, p, p, p, 32, 64)
 
 
-def _reference_root():
-    """FIELDS_LM_REFERENCE, or a checkout named ``reference`` beside this repository."""
+def _load_canon():
+    """The reference's canonical module: the staged copy, else FIELDS_LM_REFERENCE, else a
+    checkout named ``reference`` beside this repository. None if there is none."""
+    from oracle import ref
+    if ref.available():
+        return ref.load_canon()
     sibling = Path(__file__).resolve().parent.parent.parent / "reference"
     for cand in (os.environ.get("FIELDS_LM_REFERENCE", ""), str(sibling)):
         if cand and (Path(cand) / CANON_REL).exists():
-            return Path(cand)
+            spec = importlib.util.spec_from_file_location("canon_for_install_test",
+                                                          Path(cand) / CANON_REL)
+            canon = importlib.util.module_from_spec(spec)
+            sys.modules[spec.name] = canon
+            spec.loader.exec_module(canon)
+            return canon
     return None
 
 
-@pytest.mark.skipif(_reference_root() is None, reason="reference checkout not present")
 def test_install_on_the_reference_modules():
-    path = _reference_root() / CANON_REL
-    spec = importlib.util.spec_from_file_location("canon_for_install_test", path)
-    canon = importlib.util.module_from_spec(spec)
-    sys.modules[spec.name] = canon
-    spec.loader.exec_module(canon)
+    canon = _load_canon()
+    if canon is None:
+        pytest.skip("neither the staged reference nor a checkout is present")
     block = canon.FieldBlock(16, "triton", 8, 8, 16, 32)
     original = canon.fused_field_read
     seen = []
