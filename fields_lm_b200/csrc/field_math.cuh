@@ -130,6 +130,24 @@ FL_HD Vec<V> vec_load_stream(const float* p) {
     return r;
 }
 
+// Load cached in L2 only (data that another pass reads again, no use for L1).
+template <int V>
+FL_HD Vec<V> vec_load_l2(const float* p) {
+    Vec<V> r;
+#if FL_DEVICE_CODE
+    if constexpr (V == 4) {
+        const float4 t = __ldcg(reinterpret_cast<const float4*>(p));
+        r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
+    } else {
+#pragma unroll
+        for (int k = 0; k < V; ++k) r.v[k] = __ldcg(p + k);
+    }
+#else
+    std::memcpy(r.v, p, sizeof(float) * V);
+#endif
+    return r;
+}
+
 template <int V>
 FL_HD void vec_store(float* p, const Vec<V>& x) {
 #if FL_DEVICE_CODE

@@ -1,0 +1,625 @@
+// Sequence-sharded forward in ONE launch per rank: span summary, exchange over peer memory
+// and the span's forward pass, with the span read from HBM once.
+//
+// A sequence is cut into P contiguous spans, one per GPU. A rank needs the state entering
+// its span, which is the fold of the affine maps of all earlier spans onto the initial
+// state; every rank's own map needs one pass over its span. This kernel makes that pass
+// and the forward pass two sweeps of the same persistent blocks:
+//
+//   sweep 1   the span is cut into runs (chain = batch row x 128 channels; a run = a
+//             contiguous stretch of steps of one chain, one run per block when the grid
+//             allows); a block walks its run from the last tile to the first, evaluates the
+//             gates and composes the run's affine map (reference :493-509). Loads are
+//             ordinary (cached) loads: what was read last stays in L2.
+//   scan      two levels, no counters and no flags: a block stores its run's map on the
+//             rank's board as (value, epoch) pairs. Runs are grouped by eight; the block that
+//             owns a group's last run composes the group's map from the board and stores it
+//             the same way. A block's prefix - the map from the span's start to the start of
+//             its run - is then at most seven run maps of its own group after at most
+//             (runs / 8) group maps, fetched in two round trips. While a block waits, one
+//             warp polls one channel of what is missing, a lane per map (bounded); the others
+//             sit at the barrier and then fetch their own channels, re-reading the rare cell
+//             whose tag is not there yet. The block that owns the chain's last run thereby holds the
+//             span's own map and stores it into every rank's mailbox over NVLink (8-byte
+//             value+tag peer stores, as PutSummary does).
+//   wait      the block waits (bounded) for the summaries of all P ranks in its own mailbox,
+//             folds the earlier ranks onto the initial state and applies its prefix map: the
+//             state entering its run. The first tile of sweep 2 is loaded and its gates are
+//             evaluated BEFORE any of this, so that work hides the scan for every block but
+//             the last to finish sweep 1.
+//   sweep 2   the block walks its run forward - first tile first, i.e. the rows it read
+//             most recently, which a 126 MB L2 still holds when the span's raw fits
+//             (8,192 tokens x 6 KB = 50 MB at 8 ranks) - and runs the recurrence, writing
+//             `read` with streaming stores (reference :599-622).
+//
+// Blocks wait for one another (scan) and for peers (mailbox), so all blocks of the grid must
+// be resident: the launch is cooperative and the grid is sized from the occupancy query.
+// The board lives behind the mailbox's slots (memory zeroed once that only this rank's
+// kernels touch), and tags are the mailbox's epochs, which never repeat: nothing is cleared.
+// Every wait is bounded; on expiry the block records the error word, poisons its state with
+// NaN and finishes. Peer memory is touched by plain stores only (no TMA, no multicast).
+//
+// The reference has no counterpart: it runs a sequence on one GPU, and its serial carry
+// kernel (:519-550) is what the scan replaces.
+#pragma once
+
+#include "field_singlepass.cuh"
+
+namespace fields {
+
+struct SpanShape {
+    int B, L, C;
+    int G;          // 128-channel groups
+    int chains;     // B * G
+    int run_steps;  // steps per run (a multiple of the tile length)
+    int R;          // runs per chain
+    int items;      // chains * R; item = run * chains + chain
+};
+
+struct SpanFwdParams {
+    const float* raw;
+    const float* tr;
+    const float* ti;
+    const float* gamma;
+    const float* state0;     // [B, 2C] or null: state before the FIRST span (same on every rank)
+    float* read;             // [B, L, 4C]
+    float* state_out;        // [B, 2C] or null: state after this rank's span
+    float* summary;          // [B, 4, C] or null: this span's own map
+    MailPair* board;         // [items][2][128][2] run maps as (value, epoch) pairs, rank-local
+    MailPair* gboard;        // [groups][chains][2][128][2] maps of groups of eight runs
+    int emu_round;           // host emulation: only the block's item of this round (-1: all)
+    unsigned* error;         // error word (0 = ok)
+    MailPair* mailbox[kMaxRanks];  // every rank's mailbox slots as seen from this GPU
+    const MailPair* own;     // this rank's own slots
+    int rank, P;
+    unsigned epoch, max_polls;
+    int stages;              // bit 0: sweep 1, bit 1: prefix, exchange and sweep 2; bit 2 (host emulation,
+                             // which runs the ranks in turn): prefix and the sending half of the exchange only
+    SpanShape s;
+};
+
+template <int TS, int WARPS, int MIN_BLOCKS>
+struct FwdSpanSweep {
+    using Params = SpanFwdParams;
+    static constexpr int kThreads = 32 * WARPS;
+    static constexpr int kMinBlocks = MIN_BLOCKS;
+    static constexpr int kTile = TS * WARPS;
+    static constexpr int kSumFloats = WARPS * 4 * kGroup;    // warp maps; scan: segment maps
+    static constexpr int kCarryFloats = WARPS * 2 * kGroup;  // state entering each warp's steps
+    static constexpr int kRunFloats = 2 * kGroup;            // running state of the run
+    static constexpr int kFlagFloats = 4;                    // the wait flag
+    static constexpr int kStashFloats = 3 * TS * 4 * kThreads;  // the first tile of sweep 2, parked
+    static constexpr int kSmemFloats = kSumFloats + kCarryFloats + kRunFloats + kFlagFloats + kStashFloats;
+    static_assert(kThreads >= kGroup, "one thread per channel is needed for the carries");
+
+    struct State {
+        Vec<4> br[TS], bi[TS], vac[TS];  // sweep 2: gamma*v*inj and vacancy of the warp's steps
+        Affine run;                      // sweep 1: map of the run so far (channel threads)
+    };
+
+    FL_HD static float* sum_at(float* smem, int w, int k) { return smem + (w * 4 + k) * kGroup; }
+    FL_HD static float* carry_at(float* smem, int w, int k) {
+        return smem + kSumFloats + (w * 2 + k) * kGroup;
+    }
+    FL_HD static float* run_at(float* smem, int k) { return smem + kSumFloats + kCarryFloats + k * kGroup; }
+
+    struct Item {
+        int chain, run, b, cg;
+        int lo, hi;   // steps of the run
+        int tiles;
+    };
+    FL_HD static Item decode(const SpanShape& s, int item) {
+        Item it;
+        it.chain = item % s.chains;
+        it.run = item / s.chains;
+        it.b = it.chain / s.G;
+        it.cg = it.chain % s.G;
+        it.lo = it.run * s.run_steps;
+        it.hi = it.lo + s.run_steps < s.L ? it.lo + s.run_steps : s.L;
+        it.tiles = (it.hi - it.lo + kTile - 1) / kTile;
+        return it;
+    }
+
+    // Issues the loads of the warp's TS steps of one tile into the state's registers (nothing
+    // waits for them here). STREAM: the rows are not needed again (evict first).
+    template <bool STREAM>
+    FL_HD static void tile_load(const Params& p, const Item& it, int q, int thread, State& st) {
+        const SpanShape& s = p.s;
+        const int lane = thread & 31, warp = thread >> 5;
+        const int C = s.C;
+        const int c0 = it.cg * kGroup + lane * 4;
+        const int tw = it.lo + q * kTile + warp * TS;
+        if (c0 >= C) return;
+        const float* base = p.raw + ((size_t)it.b * s.L) * 3 * C + c0;
+#pragma unroll
+        for (int u = 0; u < TS; ++u) {
+            if (tw + u < it.hi) {
+                const float* row = base + (size_t)(tw + u) * 3 * C;
+                if constexpr (STREAM) {
+                    st.br[u] = vec_load_stream<4>(row);
+                    st.bi[u] = vec_load_stream<4>(row + C);
+                    st.vac[u] = vec_load_stream<4>(row + 2 * C);
+                } else {  // stays in L2 for sweep 2, bypasses L1
+                    st.br[u] = vec_load_l2<4>(row);
+                    st.bi[u] = vec_load_l2<4>(row + C);
+                    st.vac[u] = vec_load_l2<4>(row + 2 * C);
+                }
+            }
+        }
+    }
+
+    // Turns the loaded rows into (b_r, b_i, vacancy) in place - they stay in `st` for the
+    // recurrence of sweep 2 - and composes the warp's map into shared memory.
+    FL_HD static void tile_compose(const Params& p, const Item& it, int q, int thread, float* smem,
+                                   State& st) {
+        const SpanShape& s = p.s;
+        const int lane = thread & 31, warp = thread >> 5;
+        const int c0 = it.cg * kGroup + lane * 4;
+        const int tw = it.lo + q * kTile + warp * TS;
+        Affine m[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) m[k] = affine_identity();
+        if (c0 < s.C) {
+            const Vec<4> lr = vec_load<4>(p.tr + c0);
+            const Vec<4> li = vec_load<4>(p.ti + c0);
+            const Vec<4> gm = vec_load<4>(p.gamma + c0);
+#pragma unroll
+            for (int u = 0; u < TS; ++u) {
+                if (tw + u < it.hi) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const Gate g = make_gate(st.br[u].v[k], st.bi[u].v[k], st.vac[u].v[k]);
+                        const float keep = 1.0f - g.vac;
+                        const float bs = gm.v[k] * g.vac;
+                        st.br[u].v[k] = bs * g.inj_r;
+                        st.bi[u].v[k] = bs * g.inj_i;
+                        st.vac[u].v[k] = g.vac;
+                        m[k] = affine_then(m[k], keep * lr.v[k], keep * li.v[k], st.br[u].v[k],
+                                           st.bi[u].v[k]);
+                    }
+                }
+            }
+        }
+        Vec<4> o0, o1, o2, o3;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            o0.v[k] = m[k].ar; o1.v[k] = m[k].ai; o2.v[k] = m[k].br; o3.v[k] = m[k].bi;
+        }
+        vec_store<4>(sum_at(smem, warp, 0) + lane * 4, o0);
+        vec_store<4>(sum_at(smem, warp, 1) + lane * 4, o1);
+        vec_store<4>(sum_at(smem, warp, 2) + lane * 4, o2);
+        vec_store<4>(sum_at(smem, warp, 3) + lane * 4, o3);
+    }
+
+    // The first tile of sweep 2 is computed before the scan; its (b_r, b_i, vacancy) wait in
+    // shared memory meanwhile, so the scan has the registers to itself.
+    FL_HD static float* stash_at(float* smem, int k, int thread) {
+        return smem + kSumFloats + kCarryFloats + kRunFloats + kFlagFloats + ((size_t)k * kThreads + thread) * 4;
+    }
+    FL_HD static void stash(float* smem, int thread, const State& st) {
+#pragma unroll
+        for (int u = 0; u < TS; ++u) {
+            vec_store<4>(stash_at(smem, 3 * u + 0, thread), st.br[u]);
+            vec_store<4>(stash_at(smem, 3 * u + 1, thread), st.bi[u]);
+            vec_store<4>(stash_at(smem, 3 * u + 2, thread), st.vac[u]);
+        }
+    }
+    FL_HD static void unstash(float* smem, int thread, State& st) {
+#pragma unroll
+        for (int u = 0; u < TS; ++u) {
+            st.br[u] = vec_load<4>(stash_at(smem, 3 * u + 0, thread));
+            st.bi[u] = vec_load<4>(stash_at(smem, 3 * u + 1, thread));
+            st.vac[u] = vec_load<4>(stash_at(smem, 3 * u + 2, thread));
+        }
+    }
+
+    // sweep 1, channel threads: the tile's map goes in front of the run's map so far
+    FL_HD static void fold_tile(const Params& p, const Item& it, int thread, float* smem, State& st) {
+        if (thread >= kGroup || it.cg * kGroup + thread >= p.s.C) return;
+        Affine a = affine_identity();
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w)
+            a = affine_then(a, sum_at(smem, w, 0)[thread], sum_at(smem, w, 1)[thread],
+                            sum_at(smem, w, 2)[thread], sum_at(smem, w, 3)[thread]);
+        st.run = affine_then(a, st.run.ar, st.run.ai, st.run.br, st.run.bi);
+    }
+
+    // Board cell of (item, half, channel): 16 bytes = two (value, epoch) pairs,
+    // half 0 = (Re A, Im A), half 1 = (Re B, Im B).
+    FL_HD static MailPair* board_at(const Params& p, size_t item, int half, int ch) {
+        return p.board + ((item * 2 + half) * kGroup + ch) * 2;
+    }
+    struct Cell { float a, b; unsigned ta, tb; };
+    FL_HD static void cell_store(MailPair* q, float a, float b, unsigned tag) {
+#if FL_DEVICE_CODE
+        asm volatile("st.volatile.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(q),
+                     "r"(__float_as_uint(a)), "r"(tag), "r"(__float_as_uint(b)), "r"(tag)
+                     : "memory");
+#else
+        q[0].value = a; q[0].tag = tag; q[1].value = b; q[1].tag = tag;
+#endif
+    }
+    // (a 16-byte access may be performed as two 8-byte ones: each pair carries its own tag)
+    FL_HD static Cell cell_load(const MailPair* q) {
+        Cell c;
+#if FL_DEVICE_CODE
+        unsigned a, b;
+        asm volatile("ld.volatile.global.v4.b32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(a), "=r"(c.ta), "=r"(b), "=r"(c.tb) : "l"(q) : "memory");
+        c.a = __uint_as_float(a);
+        c.b = __uint_as_float(b);
+#else
+        c.a = q[0].value; c.ta = q[0].tag; c.b = q[1].value; c.tb = q[1].tag;
+#endif
+        return c;
+    }
+
+    // end of sweep 1, channel threads: the run's map goes on the board, tagged with the epoch
+    FL_HD static void publish_run(const Params& p, int item, int thread, State& st) {
+        if (thread >= kGroup) return;
+        cell_store(board_at(p, (size_t)item, 0, thread), st.run.ar, st.run.ai, p.epoch);
+        cell_store(board_at(p, (size_t)item, 1, thread), st.run.br, st.run.bi, p.epoch);
+    }
+
+    static constexpr int kGroupRuns = 8;   // runs per group of the two-level scan
+    FL_HD static MailPair* gboard_at(const Params& p, int g, int chain, int half, int ch) {
+        return p.gboard + ((((size_t)g * p.s.chains + chain) * 2 + half) * kGroup + ch) * 2;
+    }
+    // the two cells of a map on either board
+    struct MapRef { const MailPair* c0; const MailPair* c1; };
+    FL_HD static MapRef run_ref(const Params& p, const Item& it, int run, int ch) {
+        const size_t item = (size_t)run * p.s.chains + it.chain;
+        return MapRef{board_at(p, item, 0, ch), board_at(p, item, 1, ch)};
+    }
+    FL_HD static MapRef group_ref(const Params& p, const Item& it, int g, int ch) {
+        return MapRef{gboard_at(p, g, it.chain, 0, ch), gboard_at(p, g, it.chain, 1, ch)};
+    }
+    FL_HD static bool map_there(const Cell& a, const Cell& b, unsigned epoch) {
+        return a.ta == epoch && a.tb == epoch && b.ta == epoch && b.tb == epoch;
+    }
+    FL_HD static unsigned* wait_flag(float* smem) {
+        return reinterpret_cast<unsigned*>(smem + kSumFloats + kCarryFloats + kRunFloats);
+    }
+
+    // Warp 0 waits (bounded) until channel 0 of maps [lo, hi) of one board carries the epoch,
+    // a lane per map, so a check of all of them is one round trip. GROUPS: the group board,
+    // else the run board. Clears the block's wait flag on expiry.
+    template <bool GROUPS>
+    FL_HD static void wait_maps(const Params& p, const Item& it, int lo, int hi, int thread,
+                                float* smem) {
+        if (thread >= 32) return;
+        bool ok = true;
+        for (int k = lo + thread; k < hi && ok; k += 32) {
+            const MapRef r = GROUPS ? group_ref(p, it, k, 0) : run_ref(p, it, k, 0);
+            bool there = map_there(cell_load(r.c0), cell_load(r.c1), p.epoch);
+#if FL_DEVICE_CODE
+            unsigned polls = 0;
+            while (!there && ++polls < p.max_polls) {
+                __nanosleep(polls < 4096 ? 40 : 256);
+                there = map_there(cell_load(r.c0), cell_load(r.c1), p.epoch);
+            }
+#endif
+            ok = there;
+        }
+        if (!ok) wait_flag(smem)[0] = 0u;
+    }
+
+    // Composes, in order, maps [lo, hi) of one board for this thread's channel. kThreads / 128
+    // threads share a channel and split the range; four maps are in flight per thread. A cell
+    // whose tag is not there yet (thread 0 saw channel 0 only) is read again, bounded.
+    static constexpr int kShares = kThreads / kGroup;
+    static constexpr int kWindow = 4;
+    FL_HD static float* share_at(float* smem, int h, int ch) {
+        return smem + kSumFloats + ((size_t)h * kGroup + ch) * 4;   // the carry area, free here
+    }
+    FL_HD static float* prefix_at(float* smem, int k) {
+        return smem + kSumFloats + kShares * kGroup * 4 + k * kGroup;
+    }
+    static_assert((kShares + 1) * kGroup * 4 <= kCarryFloats, "shares and prefix fit the carry area");
+
+    template <bool GROUPS>
+    FL_HD static void compose_shares(const Params& p, const Item& it, int lo, int hi, int thread,
+                                     float* smem) {
+        const int ch = thread % kGroup, h = thread / kGroup;
+        if (h >= kShares) return;
+        const int n = hi - lo;
+        const int per = (n + kShares - 1) / kShares;
+        const int a = lo + (h * per < n ? h * per : n);
+        const int b = a + per < hi ? a + per : hi;
+        Affine m = affine_identity();
+        bool ok = wait_flag(smem)[0] != 0u;
+        if (it.cg * kGroup + ch < p.s.C && ok) {
+            int j = a;
+            unsigned polls = 0;
+            while (j < b && ok) {
+                float va[kWindow], vb[kWindow], vc[kWindow], vd[kWindow];
+                bool all = true;
+#pragma unroll
+                for (int u = 0; u < kWindow; ++u) {
+                    if (j + u < b) {
+                        const MapRef r = GROUPS ? group_ref(p, it, j + u, ch) : run_ref(p, it, j + u, ch);
+                        const Cell c0 = cell_load(r.c0), c1 = cell_load(r.c1);
+                        all = all && map_there(c0, c1, p.epoch);
+                        va[u] = c0.a; vb[u] = c0.b; vc[u] = c1.a; vd[u] = c1.b;
+                    }
+                }
+                if (all) {
+#pragma unroll
+                    for (int u = 0; u < kWindow; ++u)
+                        if (j + u < b) m = affine_then(m, va[u], vb[u], vc[u], vd[u]);
+                    j += kWindow;
+                    polls = 0;
+                    continue;
+                }
+                // rare: a tag is not there yet (thread 0 saw channel 0 only): the window again
+#if FL_DEVICE_CODE
+                if (++polls < p.max_polls) {
+                    __nanosleep(40);
+                    continue;
+                }
+#endif
+                ok = false;
+            }
+        }
+        if (!ok) {  // a map never came: the error word, and NaN from here on
+#if FL_DEVICE_CODE
+            atomicExch(p.error, 1u);
+#else
+            *p.error = 1u;
+#endif
+            m.ar = m.ai = m.br = m.bi = nanf("");
+        }
+        float* o = share_at(smem, h, ch);
+        o[0] = m.ar; o[1] = m.ai; o[2] = m.br; o[3] = m.bi;
+    }
+
+    FL_HD static Affine join_shares(float* smem, int thread) {
+        Affine m = affine_identity();
+#pragma unroll
+        for (int h = 0; h < kShares; ++h) {
+            const float* q = share_at(smem, h, thread);
+            m = affine_then(m, q[0], q[1], q[2], q[3]);
+        }
+        return m;
+    }
+
+    // channel threads, after the in-group shares: the map from the group's start to this run
+    // is kept; the owner of the group's last run appends its own map and stores the group's map
+    FL_HD static void group_join(const Params& p, int item, const Item& it, int thread, float* smem) {
+        const SpanShape& s = p.s;
+        if (thread >= kGroup || it.cg * kGroup + thread >= s.C) return;
+        const Affine m = join_shares(smem, thread);
+        const int g = it.run / kGroupRuns;
+        const int last = (g + 1) * kGroupRuns - 1 < s.R - 1 ? (g + 1) * kGroupRuns - 1 : s.R - 1;
+        if (it.run == last) {
+            const Cell o0 = cell_load(board_at(p, (size_t)item, 0, thread));  // this block's own stores
+            const Cell o1 = cell_load(board_at(p, (size_t)item, 1, thread));
+            const Affine t = affine_then(m, o0.a, o0.b, o1.a, o1.b);
+            cell_store(gboard_at(p, g, it.chain, 0, thread), t.ar, t.ai, p.epoch);
+            cell_store(gboard_at(p, g, it.chain, 1, thread), t.br, t.bi, p.epoch);
+        }
+        prefix_at(smem, 0)[thread] = m.ar;
+        prefix_at(smem, 1)[thread] = m.ai;
+        prefix_at(smem, 2)[thread] = m.br;
+        prefix_at(smem, 3)[thread] = m.bi;
+    }
+
+    // channel threads, after the shares over the earlier groups: prefix = (earlier groups) then
+    // (earlier runs of the own group); the owner of the chain's last run appends its own map,
+    // which gives the span's map, and sends it to every rank
+    FL_HD static void prefix_join(const Params& p, int item, const Item& it, int thread, float* smem) {
+        const SpanShape& s = p.s;
+        const int c = it.cg * kGroup + thread;
+        if (thread >= kGroup || c >= s.C) return;
+        const Affine groups = join_shares(smem, thread);
+        const Affine m = affine_then(groups, prefix_at(smem, 0)[thread], prefix_at(smem, 1)[thread],
+                                     prefix_at(smem, 2)[thread], prefix_at(smem, 3)[thread]);
+        if (it.run == s.R - 1) {
+            const Cell o0 = cell_load(board_at(p, (size_t)item, 0, thread));
+            const Cell o1 = cell_load(board_at(p, (size_t)item, 1, thread));
+            const Affine t = affine_then(m, o0.a, o0.b, o1.a, o1.b);
+            if (p.summary) {
+                float* o = p.summary + (size_t)it.b * 4 * s.C + c;
+                o[0] = t.ar; o[s.C] = t.ai; o[2 * (size_t)s.C] = t.br; o[3 * (size_t)s.C] = t.bi;
+            }
+            if (p.P > 1) {
+                const size_t slot =
+                    (((size_t)(p.epoch & 1u) * p.P + p.rank) * s.B + it.b) * 4 * s.C + c;
+                // (a fixed trip count keeps the pointer table in the kernel's parameter space)
+#pragma unroll
+                for (int r = 0; r < kMaxRanks; ++r) {
+                    if (r < p.P) {
+                        MailPair* q = p.mailbox[r] + slot;
+                        mail_store(q, t.ar, p.epoch);
+                        mail_store(q + s.C, t.ai, p.epoch);
+                        mail_store(q + 2 * (size_t)s.C, t.br, p.epoch);
+                        mail_store(q + 3 * (size_t)s.C, t.bi, p.epoch);
+                    }
+                }
+            }
+        }
+        prefix_at(smem, 0)[thread] = m.ar;
+        prefix_at(smem, 1)[thread] = m.ai;
+        prefix_at(smem, 2)[thread] = m.br;
+        prefix_at(smem, 3)[thread] = m.bi;
+    }
+
+    // channel threads: state entering the run = prefix map of (earlier ranks folded onto state0)
+    FL_HD static void enter_run(const Params& p, const Item& it, int thread, float* smem) {
+        const SpanShape& s = p.s;
+        const int c = it.cg * kGroup + thread;
+        if (thread >= kGroup || c >= s.C) return;
+        float sr = p.state0 ? p.state0[(size_t)it.b * 2 * s.C + c] : 0.0f;
+        float si = p.state0 ? p.state0[(size_t)it.b * 2 * s.C + s.C + c] : 0.0f;
+        bool failed = false;
+        if (p.P > 1) {
+            for (int r = 0; r < p.P && !failed; ++r) {
+                const MailPair* q =
+                    p.own + (((size_t)(p.epoch & 1u) * p.P + r) * s.B + it.b) * 4 * s.C + c;
+                float v[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    MailPair m = mail_load(q + (size_t)k * s.C);
+#if FL_DEVICE_CODE
+                    unsigned polls = 0;
+                    // a summary that is late ends the waiting for all that follow it
+                    while (m.tag != p.epoch && !failed && ++polls < p.max_polls) {
+                        backoff(polls);
+                        m = mail_load(q + (size_t)k * s.C);
+                    }
+#endif
+                    if (m.tag != p.epoch) failed = true;
+                    v[k] = m.value;
+                }
+                if (!failed && r < p.rank) affine_apply(Affine{v[0], v[1], v[2], v[3]}, sr, si);
+            }
+        }
+        if (failed) {
+#if FL_DEVICE_CODE
+            atomicExch(p.error, 1u);
+#else
+            *p.error = 1u;
+#endif
+            sr = si = nanf("");
+        } else {
+            affine_apply(Affine{prefix_at(smem, 0)[thread], prefix_at(smem, 1)[thread],
+                                prefix_at(smem, 2)[thread], prefix_at(smem, 3)[thread]},
+                         sr, si);
+        }
+        run_at(smem, 0)[thread] = sr;
+        run_at(smem, 1)[thread] = si;
+    }
+
+    // sweep 2, channel threads: state entering each warp's steps, running state moves on
+    FL_HD static void carries(const Params& p, const Item& it, int q, int thread, float* smem) {
+        const SpanShape& s = p.s;
+        const int c = it.cg * kGroup + thread;
+        if (thread >= kGroup || c >= s.C) return;
+        float sr = run_at(smem, 0)[thread], si = run_at(smem, 1)[thread];
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            carry_at(smem, w, 0)[thread] = sr;
+            carry_at(smem, w, 1)[thread] = si;
+            affine_apply(Affine{sum_at(smem, w, 0)[thread], sum_at(smem, w, 1)[thread],
+                                sum_at(smem, w, 2)[thread], sum_at(smem, w, 3)[thread]},
+                         sr, si);
+        }
+        run_at(smem, 0)[thread] = sr;
+        run_at(smem, 1)[thread] = si;
+        if (p.state_out && it.run == s.R - 1 && q == it.tiles - 1) {
+            p.state_out[(size_t)it.b * 2 * s.C + c] = sr;
+            p.state_out[(size_t)it.b * 2 * s.C + s.C + c] = si;
+        }
+    }
+
+    // sweep 2: recurrence over the warp's steps from its carry, streaming stores
+    FL_HD static void emit(const Params& p, const Item& it, int q, int thread, float* smem, State& st) {
+        const SpanShape& s = p.s;
+        const int lane = thread & 31, warp = thread >> 5;
+        const int C = s.C;
+        const int c0 = it.cg * kGroup + lane * 4;
+        if (c0 >= C) return;
+        const int tw = it.lo + q * kTile + warp * TS;
+        const Vec<4> lr = vec_load<4>(p.tr + c0);
+        const Vec<4> li = vec_load<4>(p.ti + c0);
+        Vec<4> sr = vec_load<4>(carry_at(smem, warp, 0) + lane * 4);
+        Vec<4> si = vec_load<4>(carry_at(smem, warp, 1) + lane * 4);
+        float* obase = p.read + ((size_t)it.b * s.L) * 4 * C + c0;
+#pragma unroll
+        for (int u = 0; u < TS; ++u) {
+            if (tw + u < it.hi) {
+                Vec<4> dr, di;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    float mr, mi;
+                    cmul(lr.v[k], li.v[k], sr.v[k], si.v[k], mr, mi);
+                    const float v = st.vac[u].v[k];
+                    dr.v[k] = v * mr;
+                    di.v[k] = v * mi;
+                    sr.v[k] = (1.0f - v) * mr + st.br[u].v[k];
+                    si.v[k] = (1.0f - v) * mi + st.bi[u].v[k];
+                }
+                float* orow = obase + (size_t)(tw + u) * 4 * C;
+                vec_store_stream<4>(orow, sr);
+                vec_store_stream<4>(orow + C, si);
+                vec_store_stream<4>(orow + 2 * C, dr);
+                vec_store_stream<4>(orow + 3 * C, di);
+            }
+        }
+    }
+
+    // The whole block program. `ex.all(f)` runs f(thread, state) for every thread of the block
+    // and then synchronises the block (device: the calling thread, then __syncthreads(); host
+    // emulation: a loop over the threads); `ex.run(f)` does the same without the barrier.
+    // `ex.blocks()` is the grid size.
+    template <class Exec>
+    FL_HD static void run_block(const Params& p, int block, float* smem, Exec& ex) {
+        const SpanShape& s = p.s;
+        if (p.stages & 1) {
+            for (int item = block; item < s.items; item += ex.blocks()) {
+                const Item it = decode(s, item);
+                ex.run([&](int t, State& st) { st.run = affine_identity(); });
+                for (int q = it.tiles - 1; q >= 0; --q) {
+                    ex.all([&](int t, State& st) {
+                        tile_load<false>(p, it, q, t, st);
+                        tile_compose(p, it, q, t, smem, st);
+                    });
+                    ex.all([&](int t, State& st) { fold_tile(p, it, t, smem, st); });
+                }
+                ex.run([&](int t, State& st) { publish_run(p, item, t, st); });
+            }
+        }
+        if (p.stages & 6) {
+            for (int item = block; item < s.items; item += ex.blocks()) {
+                if (p.emu_round >= 0 && item != block + p.emu_round * ex.blocks()) continue;
+                const Item it = decode(s, item);
+                const int g = it.run / kGroupRuns;
+                const int group_last =
+                    (g + 1) * kGroupRuns - 1 < s.R - 1 ? (g + 1) * kGroupRuns - 1 : s.R - 1;
+                const bool owner = it.run == group_last;   // others wait for this block's group map
+                // The first tile of sweep 2 - loads and gate arithmetic, parked in shared memory -
+                // comes before a block's own waiting, but after the group map it owes the others.
+                auto first_tile = [&](int t, State& st) {
+                    if (p.stages & 2) {
+                        tile_load<true>(p, it, 0, t, st);
+                        tile_compose(p, it, 0, t, smem, st);
+                        stash(smem, t, st);
+                    }
+                };
+                ex.all([&](int t, State& st) {
+                    if (!owner) first_tile(t, st);
+                    if (t == 0) wait_flag(smem)[0] = 1u;
+                });
+                ex.all([&](int t, State&) { wait_maps<false>(p, it, g * kGroupRuns, it.run, t, smem); });
+                ex.all([&](int t, State&) { compose_shares<false>(p, it, g * kGroupRuns, it.run, t, smem); });
+                ex.all([&](int t, State& st) {
+                    group_join(p, item, it, t, smem);
+                    if (owner) first_tile(t, st);
+                });
+                ex.all([&](int t, State&) { wait_maps<true>(p, it, 0, g, t, smem); });
+                ex.all([&](int t, State&) { compose_shares<true>(p, it, 0, g, t, smem); });
+                ex.run([&](int t, State&) { prefix_join(p, item, it, t, smem); });
+                if (!(p.stages & 2)) continue;  // host emulation: every rank sends before any waits
+                for (int q = 0; q < it.tiles; ++q) {
+                    if (q > 0) {
+                        ex.all([&](int t, State& st) {
+                            tile_load<true>(p, it, q, t, st);
+                            tile_compose(p, it, q, t, smem, st);
+                        });
+                    } else {
+                        ex.all([&](int t, State& st) {
+                            enter_run(p, it, t, smem);
+                            unstash(smem, t, st);
+                        });
+                    }
+                    ex.all([&](int t, State&) { carries(p, it, q, t, smem); });
+                    // no barrier after the stores: the next tile's loads only write the map area,
+                    // which nobody reads before the barrier that follows them
+                    ex.run([&](int t, State& st) { emit(p, it, q, t, smem, st); });
+                }
+            }
+        }
+    }
+};
+
+}  // namespace fields

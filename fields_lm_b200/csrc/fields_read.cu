@@ -10,6 +10,7 @@
 #include "field_kernels.cuh"
 #include "field_singlepass.cuh"
 #include "field_walk.cuh"
+#include "field_span.cuh"
 #include "field_epilogue.cuh"
 
 #include "../../include/fields_read.h"
@@ -95,6 +96,48 @@ static int fill_unset(void* p, size_t bytes, Stream) {
 
 template <class K>
 static int resident_blocks() { return 4; }  // any positive distance exercises the prefetch path
+
+// Persistent kernels written as one block program over an executor (field_span.cuh): the
+// blocks run one after another, every phase as a loop over the block's threads.
+template <class K>
+struct EmuExec {
+    typename K::State* states;
+    int nblocks;
+    template <class F> void all(F f) { for (int t = 0; t < K::kThreads; ++t) f(t, states[t]); }
+    template <class F> void run(F f) { all(f); }
+    int blocks() const { return nblocks; }
+};
+
+template <class K>
+static int launch_span(const typename K::Params& p, int grid, Stream) {
+    std::vector<double> smem_store(K::kSmemFloats / 2 + 1);
+    float* smem = reinterpret_cast<float*>(smem_store.data());
+    std::vector<typename K::State> states(K::kThreads);
+    for (int block = 0; block < grid; ++block) {
+        EmuExec<K> ex{states.data(), grid};
+        typename K::Params q = p;
+        q.stages = p.stages & 1;  // every block's first sweep (and the scans) before any wait
+        K::run_block(q, block, smem, ex);
+    }
+    // second part item by item in index order (a block's later items may need maps that blocks
+    // with a higher index produce in an earlier round; on the GPU those run concurrently)
+    const int rounds = (p.s.items + grid - 1) / grid;
+    for (int round = 0; round < rounds; ++round) {
+        for (int block = 0; block < grid; ++block) {
+            EmuExec<K> ex{states.data(), grid};
+            typename K::Params q = p;
+            q.stages = p.stages & 6;
+            q.emu_round = round;
+            K::run_block(q, block, smem, ex);
+        }
+    }
+    return FIELDS_OK;
+}
+
+static int g_emu_span_stages = 3;
+
+template <class K>
+static int span_grid() { return 6; }  // a handful of blocks: several runs per chain, several items per block
 
 // Kernels whose number of barrier-separated phases depends on the extents.
 template <class K>
@@ -283,6 +326,80 @@ static int resident_blocks() {
         return 0;
     cached = per_sm * sms;
     return cached;
+}
+
+// Persistent block program over an executor: the calling thread, then a block barrier.
+template <class K>
+struct DeviceExec {
+    typename K::State& st;
+    template <class F> __device__ __forceinline__ void all(F f) { f((int)threadIdx.x, st); __syncthreads(); }
+    template <class F> __device__ __forceinline__ void run(F f) { f((int)threadIdx.x, st); }
+    __device__ __forceinline__ int blocks() const { return (int)gridDim.x; }
+};
+
+template <class K>
+__global__ void __launch_bounds__(K::kThreads, K::kMinBlocks) span_entry(const typename K::Params p) {
+    extern __shared__ __align__(16) float smem[];
+    typename K::State st;
+    DeviceExec<K> ex{st};
+    wait_for_previous_kernel();
+    K::run_block(p, (int)blockIdx.x, smem, ex);
+}
+
+// Blocks of span_entry<K> that the current device holds at once, asked once per device.
+template <class K>
+static int span_grid() {
+    static std::mutex mu;
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] <= 0) {
+        int per_sm = 0, sms = 0;
+        // (the opt-in to more than 48 KB of shared memory comes first: the query depends on it)
+        if (K::kSmemFloats * sizeof(float) > 48 * 1024 &&
+            cudaFuncSetAttribute(span_entry<K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)(K::kSmemFloats * sizeof(float))) != cudaSuccess)
+            return 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, span_entry<K>, K::kThreads,
+                                                          K::kSmemFloats * sizeof(float)) != cudaSuccess)
+            return 0;
+        cached[dev] = per_sm * sms;
+    }
+    return cached[dev];
+}
+
+// Cooperative launch (all blocks resident at once: they wait for one another), with the
+// programmatic-serialization attribute beside it where the driver accepts the pair.
+template <class K>
+static int launch_span(const typename K::Params& p, int grid, Stream st) {
+    if (grid <= 0) return FIELDS_ERR_LAUNCH;
+    constexpr size_t bytes = K::kSmemFloats * sizeof(float);
+    static bool ready[64] = {};
+    int rc = allow_shared_memory(span_entry<K>, bytes, ready);
+    if (rc) return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(K::kThreads);
+    cfg.dynamicSmemBytes = bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    static bool pair_refused = false;
+    cfg.numAttrs = (dependent_launch_enabled() && !pair_refused) ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, span_entry<K>, p);
+    if (e != cudaSuccess && cfg.numAttrs == 2) {
+        (void)cudaGetLastError();
+        pair_refused = true;
+        cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, span_entry<K>, p);
+    }
+    return check_cuda(e);
 }
 
 template <class K>
@@ -522,6 +639,53 @@ static WalkShape walk_shape(int B, int L, int C) {
 }
 
 static bool walk_wanted(int, int, Algo algo) { return algo == kAlgoWalk; }
+
+// ---------------------------------------------------------------------------
+// Sequence-sharded forward in one launch (field_span.cuh): plan.
+// ---------------------------------------------------------------------------
+using SpanFwd = FwdSpanSweep<6, 8, 2>;   // tile 48 steps, 8 warps
+constexpr int kSpanMaxItems = 1024;       // runs per launch over all chains (unless there are more chains)
+
+static long long span_item_bound(int B, int C) {
+    const long long chains = (long long)B * ((C + kGroup - 1) / kGroup);
+    return chains > kSpanMaxItems ? chains : kSpanMaxItems;
+}
+
+// Runs: as many per chain as the grid has blocks for, each a whole number of warp slices.
+template <class K>
+static SpanShape make_span_shape(int B, int L, int C, int grid) {
+    SpanShape s{};
+    s.B = B; s.L = L; s.C = C;
+    s.G = (C + kGroup - 1) / kGroup;
+    s.chains = B * s.G;
+    const int tiles = (L + K::kTile - 1) / K::kTile;
+    long long want = grid / s.chains;
+    const long long cap = span_item_bound(B, C) / s.chains;
+    if (want > cap) want = cap;
+    if (want > tiles) want = tiles;
+    if (want < 1) want = 1;
+    const int slice = K::kTile / 8 > 0 ? K::kTile / 8 : 1;   // run lengths in eighths of a tile
+    int steps = (int)((L + want - 1) / want);
+    steps = (steps + slice - 1) / slice * slice;
+    s.run_steps = steps;
+    s.R = (L + steps - 1) / steps;
+    s.items = s.chains * s.R;
+    return s;
+}
+
+// Mailbox = [slots of the exchange][board of the one-launch forward]. The board (the run maps
+// of the owner's own kernel, 4 KB per run) is never written by a peer.
+static size_t mailbox_slot_bytes(int P, int B, int C) {
+    return round_up((size_t)2 * P * B * 4 * C * sizeof(MailPair), 256);
+}
+// run maps of up to span_item_bound runs, then the maps of their groups of eight
+static size_t span_group_bound(int B, int C) {
+    const long long chains = (long long)B * ((C + kGroup - 1) / kGroup);
+    return (size_t)(span_item_bound(B, C) / 8 + chains);
+}
+static size_t mailbox_board_bytes(int B, int C) {
+    return ((size_t)span_item_bound(B, C) + span_group_bound(B, C)) * 2 * kGroup * 2 * sizeof(MailPair);
+}
 
 // ---------------------------------------------------------------------------
 // Built-in scratch for fields_read_forward_noalloc: one fixed buffer per GPU that
@@ -999,7 +1163,45 @@ int fields_read_backward_bf16(const void* raw, const float* tr, const float* ti,
 
 size_t fields_read_mailbox_bytes(int P, int B, int C) {
     if (P <= 0 || B <= 0 || C <= 0) return 0;
-    return (size_t)2 * P * B * 4 * C * sizeof(MailPair);
+    return mailbox_slot_bytes(P, B, C) + mailbox_board_bytes(B, C);
+}
+
+int fields_read_forward_sharded(const float* raw, const float* tr, const float* ti,
+                                const float* gamma, const float* state0, float* read,
+                                float* state_out, float* summary, void* const* mailboxes,
+                                unsigned* error_word, int rank, int P, unsigned epoch,
+                                unsigned max_polls, int B, int L, int C, void* stream) {
+    if (B < 0 || L <= 0 || C <= 0 || P <= 0 || P > kMaxRanks || rank < 0 || rank >= P || epoch == 0)
+        return FIELDS_ERR_ARGUMENT;
+    if (B == 0) return FIELDS_OK;
+    if (!raw || !tr || !ti || !gamma || !read || !mailboxes || !error_word) return FIELDS_ERR_ARGUMENT;
+    for (int r = 0; r < P; ++r)
+        if (!mailboxes[r] || (reinterpret_cast<uintptr_t>(mailboxes[r]) & 255u)) return FIELDS_ERR_ARGUMENT;
+    if (C % 4 != 0 || !aligned16(raw) || !aligned16(read) || !aligned16(tr) || !aligned16(ti) ||
+        !aligned16(gamma))
+        return FIELDS_ERR_UNSUPPORTED;
+    Stream st = reinterpret_cast<Stream>(stream);
+    const int grid_max = span_grid<SpanFwd>();
+    if (grid_max <= 0) return FIELDS_ERR_LAUNCH;
+    SpanFwdParams p{};
+    p.raw = raw; p.tr = tr; p.ti = ti; p.gamma = gamma; p.state0 = state0;
+    p.read = read; p.state_out = state_out; p.summary = summary;
+    p.s = make_span_shape<SpanFwd>(B, L, C, grid_max);
+    p.board = reinterpret_cast<MailPair*>(static_cast<char*>(mailboxes[rank]) +
+                                          mailbox_slot_bytes(P, B, C));
+    p.gboard = p.board + (size_t)span_item_bound(B, C) * 2 * kGroup * 2;
+    p.emu_round = -1;
+    p.error = error_word;
+    for (int r = 0; r < P; ++r) p.mailbox[r] = static_cast<MailPair*>(mailboxes[r]);
+    p.own = static_cast<const MailPair*>(mailboxes[rank]);
+    p.rank = rank; p.P = P; p.epoch = epoch;
+    p.max_polls = max_polls == 0 || max_polls > kMaxPolls ? kMaxPolls : max_polls;
+    p.stages = 3;
+#ifdef FIELDS_HOST_EMU
+    p.stages = g_emu_span_stages;  // the CPU tests run the ranks' first sweeps before any rank's wait
+#endif
+    const int grid = p.s.items < grid_max ? p.s.items : grid_max;
+    return launch_span<SpanFwd>(p, grid, st);
 }
 
 int fields_read_span_summary_put(const float* raw, const float* tr, const float* ti,
@@ -1114,6 +1316,13 @@ int fields_read_fold_mailbox_backward(const void* mailbox, const float* carry_en
     return launch<FoldMailbox>(p, (n + FoldMailbox::kThreads - 1) / FoldMailbox::kThreads,
                                reinterpret_cast<Stream>(stream));
 }
+
+#ifdef FIELDS_HOST_EMU
+// Host emulation only: which parts fields_read_forward_sharded runs (bit 0: first sweep,
+// bit 2: prefix maps and the store of the span's map into the mailboxes, bit 1: the same plus
+// the wait and the second sweep), so a test can emulate several ranks in turn.
+void fields_emu_span_stages(int stages) { g_emu_span_stages = stages; }
+#endif
 
 #ifndef FIELDS_HOST_EMU
 size_t fields_mixer_epilogue_bias_rows(long long N) {

@@ -8,7 +8,8 @@
  *
  * Conventions
  *   - every pointer is a DEVICE pointer to memory owned by the caller; the
- *     library allocates nothing, frees nothing and keeps no state between calls;
+ *     library allocates nothing, frees nothing and keeps no state between calls
+ *     (one exception: the built-in scratch of fields_read_forward_noalloc);
  *   - all tensors are contiguous float32 with the reference's layouts, channel
  *     fastest:  raw [B, L, 3C] = z_r | z_i | z_v,   read [B, L, 4C] =
  *     Re s | Im s | Re d | Im d,   states [B, 2C] = Re s | Im s;
@@ -208,6 +209,7 @@ int fields_read_step_bf16(const void *raw, const float *tr, const float *ti, con
  * Every rank owns a mailbox of fields_read_mailbox_bytes(P, B, C) bytes, zeroed once when it is
  * created, in memory its peers can write (peer access, IPC or symmetric memory); mailboxes[r] is
  * rank r's mailbox as seen from the calling GPU (a HOST array of P device pointers, P <= 16).
+ * (The size includes a board behind the slots that only the owner's own kernels use.)
  *
  * fields_read_span_summary_put: computes this rank's span summary and stores it, tagged with
  * `epoch`, into its slot of every rank's mailbox (plain 8-byte peer stores; no TMA, no
@@ -232,6 +234,44 @@ int fields_read_span_summary_put(const float *raw, const float *tr, const float 
 int fields_read_fold_mailbox(const void *mailbox, const float *state0, float *state,
                              unsigned *error_word, int rank, int P, unsigned epoch, int B, int C,
                              void *stream);
+
+/*
+ * The sequence-sharded forward of one rank in ONE launch (no counterpart in the reference, which
+ * runs a sequence on one GPU; its serial chunk-carry kernel,
+ * field_only_v4_chunked_triton_wiki100.py:519-550, is what the in-kernel scan replaces).
+ *
+ * Does what fields_read_span_summary_put + fields_read_fold_mailbox + fields_read_forward do,
+ * with one read of the span from HBM when its raw fits the L2 cache: persistent blocks sweep
+ * the span once to compose its map, the last block of every (batch row, 128 channels) chain
+ * scans the maps and stores the span's map into every rank's mailbox, every block waits (with
+ * a bound) for the P summaries of `epoch`, folds the earlier ranks onto state0 and sweeps its
+ * part of the span again, now from L2, writing `read`.
+ *
+ *   raw [B, L, 3C], read [B, L, 4C]   this rank's span
+ *   state0    [B, 2C] or NULL   state before the FIRST span (the same on every rank)
+ *   state_out [B, 2C] or NULL   state after this rank's span
+ *   summary   [B, 4, C] or NULL this span's own map, as fields_read_span_summary gives it
+ *   mailboxes, rank, P, epoch   as fields_read_span_summary_put; each mailbox 256-byte aligned,
+ *                               fields_read_mailbox_bytes(P, B, C) bytes, zeroed once
+ *   error_word  device word the caller zeroed; set to 1 if a wait ran out (`read` and
+ *               state_out then hold NaN from that point on)
+ *   max_polls   bound of every wait in polls (a poll is well under a microsecond);
+ *               0 = the library's default of 2^21, about a second
+ *
+ * No workspace: the kernel keeps its run maps on a board behind the slots of the rank's own
+ * mailbox (part of fields_read_mailbox_bytes), tagged with the epoch like the slots, so
+ * nothing is ever cleared. The launch is cooperative: all blocks are resident together,
+ * because they wait for one another and for the peers. With P = 1 nothing is exchanged (the
+ * mailbox only lends its board). Needs C % 4 == 0 and 16-byte aligned tensors
+ * (FIELDS_ERR_UNSUPPORTED otherwise). Like the other mailbox calls it takes the epoch as an
+ * argument and must not be replayed from a captured CUDA graph. Peer memory is written with
+ * plain 8-byte stores only.
+ */
+int fields_read_forward_sharded(const float *raw, const float *tr, const float *ti,
+                                const float *gamma, const float *state0, float *read,
+                                float *state_out, float *summary, void *const *mailboxes,
+                                unsigned *error_word, int rank, int P, unsigned epoch,
+                                unsigned max_polls, int B, int L, int C, void *stream);
 
 /*
  * The backward exchange through the same mailboxes (they and the epoch sequence are shared

@@ -80,6 +80,9 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.fields_read_span_summary_backward_put.restype = I
     lib.fields_read_fold_mailbox_backward.argtypes = [P, P, P, P, I, I, ctypes.c_uint, I, I, P]
     lib.fields_read_fold_mailbox_backward.restype = I
+    lib.fields_read_forward_sharded.argtypes = [P] * 10 + [I, I, ctypes.c_uint, ctypes.c_uint,
+                                                   I, I, I, P]
+    lib.fields_read_forward_sharded.restype = I
     lib.fields_read_device_status.argtypes = [P, P]
     lib.fields_read_device_status.restype = I
     return lib
@@ -373,3 +376,33 @@ def fold_mailbox(mailbox, rank, world, epoch, B, C, state0=None):
     if rc:
         raise RuntimeError(lib().fields_status_string(rc).decode())
     return out, int(err[0])
+
+
+class ShardedForward:
+    """One emulated rank of ``fields_read_forward_sharded``: buffers that live across the two
+    halves of the launch, which a test runs apart (all ranks' first sweeps, then all waits)."""
+
+    def __init__(self, raw, tr, ti, gamma, mailboxes, rank, state0=None):
+        self.B, self.L, _ = raw.shape
+        self.C = tr.size
+        self.a = [_f32(x) for x in (raw, tr, ti, gamma)]
+        self.s0 = None if state0 is None else _f32(state0)
+        self.read = _f32(np.full((self.B, self.L, 4 * self.C), np.nan))
+        self.state = _f32(np.full((self.B, 2 * self.C), np.nan))
+        self.summary = _f32(np.full((self.B, 4, self.C), np.nan))
+        self.err = np.zeros(1, dtype=np.uint32)
+        self.ptrs = (ctypes.c_void_p * len(mailboxes))(*[m.ctypes.data for m in mailboxes])
+        self.world, self.rank = len(mailboxes), rank
+
+    def run(self, stages, epoch):
+        lib().fields_emu_span_stages(stages)
+        try:
+            rc = lib().fields_read_forward_sharded(
+                _ptr(self.a[0]), _ptr(self.a[1]), _ptr(self.a[2]), _ptr(self.a[3]), _ptr(self.s0),
+                _ptr(self.read), _ptr(self.state), _ptr(self.summary), self.ptrs, _ptr(self.err),
+                self.rank, self.world, epoch, 0, self.B, self.L, self.C, None)
+        finally:
+            lib().fields_emu_span_stages(3)
+        if rc:
+            raise RuntimeError(lib().fields_status_string(rc).decode())
+        return self

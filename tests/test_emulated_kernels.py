@@ -399,3 +399,50 @@ def test_mailbox_exchange_carries_the_backward_too():
         for r, (a, b) in enumerate(spans):
             assert rel_err(states[r], want) < FP32_TOL or r == 0
             _, want = field_oracle.forward(raw[:, a:b], tr, ti, gm, state_in=want)
+
+
+@pytest.mark.parametrize("B,L,C,cuts", [
+    (1, 700, 512, [0, 233, 480, 700]),     # four chains, several runs per chain, ragged spans
+    (2, 90, 20, [0, 31, 64, 90]),          # one partly filled channel group
+    (3, 130, 132, [0, 130]),               # a single rank: nothing is exchanged
+    (9, 61, 260, [0, 7, 61]),              # more chains than blocks: several items per block
+])
+def test_sharded_forward_in_one_launch(B, L, C, cuts):
+    """fields_read_forward_sharded, emulated: every rank sweeps its span and stores its map into
+    all mailboxes, then every rank waits, folds and sweeps again. `read`, the span maps and the
+    end states equal the oracle's full-sequence pass; two calls alternate the mailbox parities."""
+    rng = np.random.default_rng(B * 1000 + L + C)
+    tr, ti, gm = _params(C, rng)
+    world = len(cuts) - 1
+    boxes = emu.make_mailboxes(world, B, C)
+    for epoch in (1, 2, 3):
+        raw = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+        s0 = rng.standard_normal((B, 2 * C)).astype(np.float32) if epoch != 2 else None
+        ranks = [emu.ShardedForward(raw[:, a:b], tr, ti, gm, boxes, r, state0=s0)
+                 for r, (a, b) in enumerate(zip(cuts[:-1], cuts[1:]))]
+        for stage in (1, 4, 2):     # all first sweeps, all sends, then the waits and second sweeps
+            for op in ranks:
+                op.run(stage, epoch)
+        want_read, _ = field_oracle.forward(raw, tr, ti, gm, state_in=s0)
+        got = np.concatenate([op.read for op in ranks], axis=1)
+        assert rel_err(got, want_read) < FP32_TOL
+        state = None if s0 is None else s0.astype(np.float64)
+        for op, (a, b) in zip(ranks, zip(cuts[:-1], cuts[1:])):
+            assert int(op.err[0]) == 0
+            assert rel_err(op.summary, field_oracle.span_summary(raw[:, a:b], tr, ti, gm)) < FP32_TOL
+            _, state = field_oracle.forward(raw[:, a:b], tr, ti, gm, state_in=state)
+            assert rel_err(op.state, state) < FP32_TOL
+
+
+def test_sharded_forward_reports_a_missing_summary():
+    """A rank whose peer never ran: the wait runs out (at once in the emulation), the error word
+    is set and the outputs hold NaN; the rank before it is unaffected in its own arithmetic."""
+    rng = np.random.default_rng(77)
+    B, L, C = 1, 200, 128
+    tr, ti, gm = _params(C, rng)
+    raw = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+    boxes = emu.make_mailboxes(2, B, C)
+    late = emu.ShardedForward(raw[:, 100:], tr, ti, gm, boxes, 1)
+    for stage in (1, 4, 2):  # rank 0 never stored its summary
+        late.run(stage, 1)
+    assert int(late.err[0]) == 1 and np.isnan(late.read).all() and np.isnan(late.state).all()

@@ -11,7 +11,7 @@ import pytest
 import torch
 
 import fields_lm_b200
-from conftest import BF16_TOL
+from conftest import BF16_TOL, FP32_TOL
 from oracle import full_model, ref
 
 pytestmark = [pytest.mark.gpu,
@@ -28,18 +28,30 @@ def test_training_step_matches_the_reference_triton_path():
 
     loss_ref = float(full_model.training_step(model, ids, labels))
     grads_ref = full_model.gradients(model)
+    reads_ref = full_model.reads_by_block(model, ids)
+    # the floor: the reference against itself with its other "exact" launch geometry (16/64)
+    full_model.set_triton_geometry(model, 16, 64)
     full_model.training_step(model, ids, labels)
-    noise, _ = full_model.compare_gradients(full_model.gradients(model), grads_ref)
+    floor, _ = full_model.compare_gradients(full_model.gradients(model), grads_ref)
+    floor_norm, _ = full_model.norm_relative(full_model.gradients(model), grads_ref)
+    full_model.set_triton_geometry(model, 32, 64)
 
     assert fields_lm_b200.install(model) == 1     # one module namespace for all 18 blocks
     try:
         loss_new = float(full_model.training_step(model, ids, labels))
         grads_new = full_model.gradients(model)
+        reads_new = full_model.reads_by_block(model, ids)
     finally:
         fields_lm_b200.uninstall(model)
-    assert set(grads_new) == set(grads_ref)
+    assert set(grads_new) == set(grads_ref) and len(reads_new) == len(reads_ref) == 18
     assert all(torch.isfinite(g).all() for g in grads_new.values())
+    # the first Field block sees identical inputs on both sides: operator-level parity in situ
+    first = float((reads_new[0] - reads_ref[0]).abs().max() / reads_ref[0].abs().max())
+    assert first < FP32_TOL, first
     assert abs(loss_new - loss_ref) <= BF16_TOL * abs(loss_ref)
+    worst_norm, where_norm = full_model.norm_relative(grads_new, grads_ref)
+    assert worst_norm <= max(BF16_TOL, 3 * floor_norm), (worst_norm, where_norm, floor_norm)
+    # element-wise max error: single bfloat16 flips in 24 stacked layers move individual
+    # gradient entries; held to what the reference's own second geometry does to them
     worst, where = full_model.compare_gradients(grads_new, grads_ref)
-    # the reference re-run against itself differs by `noise` (atomics, bf16 GEMM splits)
-    assert worst <= max(BF16_TOL, 2 * noise), (worst, where, noise)
+    assert worst <= max(BF16_TOL, 3 * floor), (worst, where, floor)

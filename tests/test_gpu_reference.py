@@ -163,7 +163,7 @@ def test_installed_block_equals_the_triton_block_under_autocast():
     ours = step()
     fields_lm_b200.uninstall(gpu)
     for a, b in zip(ours, triton_out):
-        assert rel_err(a, b) < 2e-3
+        assert rel_err(a, b) < 2 ** -6   # a few bfloat16 ulps of the largest entry
 
 
 def test_reference_kernel_self_test_passes_with_the_operator_installed():

@@ -49,6 +49,14 @@ def _worker(rank, world, port, L, out_dir):
         assert p2p.status() == 0
         assert float((read3 - read).abs().max()) <= 2e-6 * float(read.abs().max())
         assert float((state3 - state).abs().max()) <= 2e-6 * float(state.abs().max())
+        # the whole sharded forward as one cooperative launch per rank
+        fused = seqpar.SequenceParallelForwardFused(B, hi - lo, C, dev)
+        for _ in range(4):
+            read4, state4 = fused(span, tr, ti, gm)
+        torch.cuda.synchronize()
+        assert fused.status() == 0
+        assert float((read4 - read).abs().max()) <= 2e-6 * float(read.abs().max())
+        assert float((state4 - state).abs().max()) <= 2e-6 * float(state.abs().max())
         if rank == 0:
             with torch.no_grad():
                 full, full_state = field_read_with_state(raw.to(dev), tr, ti, gm, None)
