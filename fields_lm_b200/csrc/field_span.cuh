@@ -11,17 +11,15 @@
 //             allows); a block walks its run from the last tile to the first, evaluates the
 //             gates and composes the run's affine map (reference :493-509). Loads are
 //             ordinary (cached) loads: what was read last stays in L2.
-//   scan      two levels, no counters and no flags: a block stores its run's map on the
-//             rank's board as (value, epoch) pairs. Runs are grouped by eight; the block that
-//             owns a group's last run composes the group's map from the board and stores it
-//             the same way. A block's prefix - the map from the span's start to the start of
-//             its run - is then at most seven run maps of its own group after at most
-//             (runs / 8) group maps, fetched in two round trips. While a block waits, one
-//             warp polls one channel of what is missing, a lane per map (bounded); the others
-//             sit at the barrier and then fetch their own channels, re-reading the rare cell
-//             whose tag is not there yet. The block that owns the chain's last run thereby holds the
-//             span's own map and stores it into every rank's mailbox over NVLink (8-byte
-//             value+tag peer stores, as PutSummary does).
+//   scan      a block stores its run's map on the rank's board and counts itself in on the
+//             chain's counter, one release-acquire atomic; the counter word carries the call's
+//             epoch as a tag and so restarts by itself. Every block waits (one thread polls,
+//             bounded) until its chain is complete and then composes, itself, the maps of the
+//             runs before its own: the map from the span's start to the start of its run. All
+//             loads are independent, two threads share a channel, so the longest chain of
+//             dependent work is half the runs of a chain. The block that owns the chain's last
+//             run thereby holds the span's own map and stores it into every rank's mailbox
+//             over NVLink (8-byte value+tag peer stores, as PutSummary does).
 //   wait      the block waits (bounded) for the summaries of all P ranks in its own mailbox,
 //             folds the earlier ranks onto the initial state and applies its prefix map: the
 //             state entering its run. The first tile of sweep 2 is loaded and its gates are
@@ -34,8 +32,8 @@
 //
 // Blocks wait for one another (scan) and for peers (mailbox), so all blocks of the grid must
 // be resident: the launch is cooperative and the grid is sized from the occupancy query.
-// The board lives behind the mailbox's slots (memory zeroed once that only this rank's
-// kernels touch), and tags are the mailbox's epochs, which never repeat: nothing is cleared.
+// The board (run maps and counters) lives behind the mailbox's slots, memory that only this
+// rank's kernels touch; counters are tagged with the mailbox's epochs: nothing is cleared.
 // Every wait is bounded; on expiry the block records the error word, poisons its state with
 // NaN and finishes. Peer memory is touched by plain stores only (no TMA, no multicast).
 //
@@ -65,8 +63,9 @@ struct SpanFwdParams {
     float* read;             // [B, L, 4C]
     float* state_out;        // [B, 2C] or null: state after this rank's span
     float* summary;          // [B, 4, C] or null: this span's own map
-    MailPair* board;         // [items][2][128][2] run maps as (value, epoch) pairs, rank-local
-    MailPair* gboard;        // [groups][chains][2][128][2] maps of groups of eight runs
+    float* runmap;           // [items][128][4] run maps, on the rank's board
+    unsigned* count;         // [chains] (epoch tag << 12 | runs arrived), on the rank's board
+    unsigned* ready;         // [chains] epoch of the last completed chain, 64 words apart
     int emu_round;           // host emulation: only the block's item of this round (-1: all)
     unsigned* error;         // error word (0 = ok)
     MailPair* mailbox[kMaxRanks];  // every rank's mailbox slots as seen from this GPU
@@ -224,91 +223,82 @@ struct FwdSpanSweep {
         st.run = affine_then(a, st.run.ar, st.run.ai, st.run.br, st.run.bi);
     }
 
-    // Board cell of (item, half, channel): 16 bytes = two (value, epoch) pairs,
-    // half 0 = (Re A, Im A), half 1 = (Re B, Im B).
-    FL_HD static MailPair* board_at(const Params& p, size_t item, int half, int ch) {
-        return p.board + ((item * 2 + half) * kGroup + ch) * 2;
+    // ---- scan: one tagged counter per chain, every block composes its own prefix ----
+    // Run maps sit on the rank's board as plain float4 per channel. A chain's counter word
+    // holds (epoch tag << 12 | runs arrived); it restarts by itself when the tag changes, so
+    // nothing is cleared between launches.
+    FL_HD static float* runmap_at(const Params& p, size_t item, int ch) {
+        return p.runmap + (item * kGroup + ch) * 4;
     }
-    struct Cell { float a, b; unsigned ta, tb; };
-    FL_HD static void cell_store(MailPair* q, float a, float b, unsigned tag) {
-#if FL_DEVICE_CODE
-        asm volatile("st.volatile.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(q),
-                     "r"(__float_as_uint(a)), "r"(tag), "r"(__float_as_uint(b)), "r"(tag)
-                     : "memory");
-#else
-        q[0].value = a; q[0].tag = tag; q[1].value = b; q[1].tag = tag;
-#endif
-    }
-    // (a 16-byte access may be performed as two 8-byte ones: each pair carries its own tag)
-    FL_HD static Cell cell_load(const MailPair* q) {
-        Cell c;
-#if FL_DEVICE_CODE
-        unsigned a, b;
-        asm volatile("ld.volatile.global.v4.b32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(a), "=r"(c.ta), "=r"(b), "=r"(c.tb) : "l"(q) : "memory");
-        c.a = __uint_as_float(a);
-        c.b = __uint_as_float(b);
-#else
-        c.a = q[0].value; c.ta = q[0].tag; c.b = q[1].value; c.tb = q[1].tag;
-#endif
-        return c;
-    }
+    FL_HD static unsigned tag_of(unsigned epoch) { return (epoch & 0xFFFFFu) << 12; }
 
-    // end of sweep 1, channel threads: the run's map goes on the board, tagged with the epoch
+    // end of sweep 1, channel threads: the run's map becomes visible to the chain's other blocks
     FL_HD static void publish_run(const Params& p, int item, int thread, State& st) {
         if (thread >= kGroup) return;
-        cell_store(board_at(p, (size_t)item, 0, thread), st.run.ar, st.run.ai, p.epoch);
-        cell_store(board_at(p, (size_t)item, 1, thread), st.run.br, st.run.bi, p.epoch);
+        float* q = runmap_at(p, (size_t)item, thread);
+#if FL_DEVICE_CODE
+        __stcg(reinterpret_cast<float4*>(q), make_float4(st.run.ar, st.run.ai, st.run.br, st.run.bi));
+#else
+        q[0] = st.run.ar; q[1] = st.run.ai; q[2] = st.run.br; q[3] = st.run.bi;
+#endif
+    }
+    // Runs after the block barrier that follows publish_run: the barrier orders the block's
+    // stores before thread 0's arrival, which is a release (and acquire) at GPU scope, so
+    // whoever sees the chain complete also sees every run's map.
+    FL_HD static void arrive(const Params& p, const Item& it, int thread) {
+        if (thread != 0) return;
+        unsigned* word = p.count + it.chain;
+        const unsigned tag = tag_of(p.epoch);
+#if FL_DEVICE_CODE
+        unsigned cur = *reinterpret_cast<volatile unsigned*>(word);
+        for (;;) {
+            const unsigned want = (cur & ~0xFFFu) == tag ? cur + 1u : (tag | 1u);
+            unsigned old;
+            asm volatile("atom.cas.acq_rel.gpu.global.b32 %0, [%1], %2, %3;"
+                         : "=r"(old) : "l"(word), "r"(cur), "r"(want) : "memory");
+            if (old == cur) {
+                cur = want;
+                break;
+            }
+            cur = old;
+        }
+        // the last run in: the chain's ready word (a word of its own, so that the blocks polling
+        // it stay off the counter's line) takes the epoch
+        if (cur == (tag | (unsigned)p.s.R))
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ready + 64 * it.chain), "r"(p.epoch)
+                         : "memory");
+#else
+        *word = (*word & ~0xFFFu) == tag ? *word + 1u : (tag | 1u);
+        if (*word == (tag | (unsigned)p.s.R)) p.ready[64 * it.chain] = p.epoch;
+#endif
     }
 
-    static constexpr int kGroupRuns = 8;   // runs per group of the two-level scan
-    FL_HD static MailPair* gboard_at(const Params& p, int g, int chain, int half, int ch) {
-        return p.gboard + ((((size_t)g * p.s.chains + chain) * 2 + half) * kGroup + ch) * 2;
-    }
-    // the two cells of a map on either board
-    struct MapRef { const MailPair* c0; const MailPair* c1; };
-    FL_HD static MapRef run_ref(const Params& p, const Item& it, int run, int ch) {
-        const size_t item = (size_t)run * p.s.chains + it.chain;
-        return MapRef{board_at(p, item, 0, ch), board_at(p, item, 1, ch)};
-    }
-    FL_HD static MapRef group_ref(const Params& p, const Item& it, int g, int ch) {
-        return MapRef{gboard_at(p, g, it.chain, 0, ch), gboard_at(p, g, it.chain, 1, ch)};
-    }
-    FL_HD static bool map_there(const Cell& a, const Cell& b, unsigned epoch) {
-        return a.ta == epoch && a.tb == epoch && b.ta == epoch && b.tb == epoch;
-    }
     FL_HD static unsigned* wait_flag(float* smem) {
         return reinterpret_cast<unsigned*>(smem + kSumFloats + kCarryFloats + kRunFloats);
     }
-
-    // Warp 0 waits (bounded) until channel 0 of maps [lo, hi) of one board carries the epoch,
-    // a lane per map, so a check of all of them is one round trip. GROUPS: the group board,
-    // else the run board. Clears the block's wait flag on expiry.
-    template <bool GROUPS>
-    FL_HD static void wait_maps(const Params& p, const Item& it, int lo, int hi, int thread,
-                                float* smem) {
-        if (thread >= 32) return;
-        bool ok = true;
-        for (int k = lo + thread; k < hi && ok; k += 32) {
-            const MapRef r = GROUPS ? group_ref(p, it, k, 0) : run_ref(p, it, k, 0);
-            bool there = map_there(cell_load(r.c0), cell_load(r.c1), p.epoch);
+    // thread 0: bounded wait until every run of the chain has arrived in this call
+    FL_HD static void wait_chain(const Params& p, const Item& it, int thread, float* smem) {
+        if (thread != 0) return;
+        const unsigned want = p.epoch;
+        const unsigned* word = p.ready + 64 * it.chain;
 #if FL_DEVICE_CODE
-            unsigned polls = 0;
-            while (!there && ++polls < p.max_polls) {
-                __nanosleep(polls < 4096 ? 40 : 256);
-                there = map_there(cell_load(r.c0), cell_load(r.c1), p.epoch);
-            }
-#endif
-            ok = there;
+        unsigned v, polls = 0;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
+        while (v != want && ++polls < p.max_polls) {
+            __nanosleep(polls < 64 ? 64 : 256);
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
         }
-        if (!ok) wait_flag(smem)[0] = 0u;
+        wait_flag(smem)[0] = v == want ? 1u : 0u;
+#else
+        wait_flag(smem)[0] = *word == want ? 1u : 0u;
+#endif
     }
 
-    // Composes, in order, maps [lo, hi) of one board for this thread's channel. kThreads / 128
-    // threads share a channel and split the range; four maps are in flight per thread. A cell
-    // whose tag is not there yet (thread 0 saw channel 0 only) is read again, bounded.
+    // Map from the span's start to the start of this run = the maps of the chain's earlier
+    // runs in order. kThreads / 128 threads share a channel, each composes a contiguous share
+    // of those runs, eight independent loads in flight; channel threads join the shares.
     static constexpr int kShares = kThreads / kGroup;
-    static constexpr int kWindow = 4;
+    static constexpr int kWindow = 8;
     FL_HD static float* share_at(float* smem, int h, int ch) {
         return smem + kSumFloats + ((size_t)h * kGroup + ch) * 4;   // the carry area, free here
     }
@@ -317,107 +307,65 @@ struct FwdSpanSweep {
     }
     static_assert((kShares + 1) * kGroup * 4 <= kCarryFloats, "shares and prefix fit the carry area");
 
-    template <bool GROUPS>
-    FL_HD static void compose_shares(const Params& p, const Item& it, int lo, int hi, int thread,
-                                     float* smem) {
+    FL_HD static Pub4 map_load(const float* q) {
+#if FL_DEVICE_CODE
+        const float4 t = __ldcg(reinterpret_cast<const float4*>(q));   // another block's store: L2
+        return Pub4{t.x, t.y, t.z, t.w};
+#else
+        return Pub4{q[0], q[1], q[2], q[3]};
+#endif
+    }
+
+    FL_HD static void prefix_shares(const Params& p, const Item& it, int thread, float* smem) {
         const int ch = thread % kGroup, h = thread / kGroup;
         if (h >= kShares) return;
-        const int n = hi - lo;
+        const int n = it.run;  // runs before this one
         const int per = (n + kShares - 1) / kShares;
-        const int a = lo + (h * per < n ? h * per : n);
-        const int b = a + per < hi ? a + per : hi;
+        const int lo = h * per < n ? h * per : n;
+        const int hi = lo + per < n ? lo + per : n;
         Affine m = affine_identity();
-        bool ok = wait_flag(smem)[0] != 0u;
-        if (it.cg * kGroup + ch < p.s.C && ok) {
-            int j = a;
-            unsigned polls = 0;
-            while (j < b && ok) {
-                float va[kWindow], vb[kWindow], vc[kWindow], vd[kWindow];
-                bool all = true;
-#pragma unroll
-                for (int u = 0; u < kWindow; ++u) {
-                    if (j + u < b) {
-                        const MapRef r = GROUPS ? group_ref(p, it, j + u, ch) : run_ref(p, it, j + u, ch);
-                        const Cell c0 = cell_load(r.c0), c1 = cell_load(r.c1);
-                        all = all && map_there(c0, c1, p.epoch);
-                        va[u] = c0.a; vb[u] = c0.b; vc[u] = c1.a; vd[u] = c1.b;
-                    }
-                }
-                if (all) {
-#pragma unroll
-                    for (int u = 0; u < kWindow; ++u)
-                        if (j + u < b) m = affine_then(m, va[u], vb[u], vc[u], vd[u]);
-                    j += kWindow;
-                    polls = 0;
-                    continue;
-                }
-                // rare: a tag is not there yet (thread 0 saw channel 0 only): the window again
-#if FL_DEVICE_CODE
-                if (++polls < p.max_polls) {
-                    __nanosleep(40);
-                    continue;
-                }
-#endif
-                ok = false;
-            }
-        }
-        if (!ok) {  // a map never came: the error word, and NaN from here on
+        if (wait_flag(smem)[0] == 0u) {  // the chain never completed: NaN from here on
+            m.ar = m.ai = m.br = m.bi = nanf("");
 #if FL_DEVICE_CODE
             atomicExch(p.error, 1u);
 #else
             *p.error = 1u;
 #endif
-            m.ar = m.ai = m.br = m.bi = nanf("");
+        } else if (it.cg * kGroup + ch < p.s.C) {
+            const float* base = runmap_at(p, (size_t)it.chain, ch);
+            const size_t stride = (size_t)p.s.chains * kGroup * 4;
+            int j = lo;
+            for (; j + kWindow <= hi; j += kWindow) {
+                Pub4 v[kWindow];
+#pragma unroll
+                for (int u = 0; u < kWindow; ++u) v[u] = map_load(base + (size_t)(j + u) * stride);
+#pragma unroll
+                for (int u = 0; u < kWindow; ++u) m = affine_then(m, v[u].x, v[u].y, v[u].z, v[u].w);
+            }
+            for (; j < hi; ++j) {
+                const Pub4 v = map_load(base + (size_t)j * stride);
+                m = affine_then(m, v.x, v.y, v.z, v.w);
+            }
         }
         float* o = share_at(smem, h, ch);
         o[0] = m.ar; o[1] = m.ai; o[2] = m.br; o[3] = m.bi;
     }
 
-    FL_HD static Affine join_shares(float* smem, int thread) {
+    // channel threads: join the shares; the owner of the chain's last run appends its own map,
+    // which gives the span's map, and sends it to every rank
+    FL_HD static void prefix_join(const Params& p, int item, const Item& it, int thread, float* smem) {
+        const SpanShape& s = p.s;
+        const int c = it.cg * kGroup + thread;
+        if (thread >= kGroup || c >= s.C) return;
         Affine m = affine_identity();
 #pragma unroll
         for (int h = 0; h < kShares; ++h) {
             const float* q = share_at(smem, h, thread);
             m = affine_then(m, q[0], q[1], q[2], q[3]);
         }
-        return m;
-    }
-
-    // channel threads, after the in-group shares: the map from the group's start to this run
-    // is kept; the owner of the group's last run appends its own map and stores the group's map
-    FL_HD static void group_join(const Params& p, int item, const Item& it, int thread, float* smem) {
-        const SpanShape& s = p.s;
-        if (thread >= kGroup || it.cg * kGroup + thread >= s.C) return;
-        const Affine m = join_shares(smem, thread);
-        const int g = it.run / kGroupRuns;
-        const int last = (g + 1) * kGroupRuns - 1 < s.R - 1 ? (g + 1) * kGroupRuns - 1 : s.R - 1;
-        if (it.run == last) {
-            const Cell o0 = cell_load(board_at(p, (size_t)item, 0, thread));  // this block's own stores
-            const Cell o1 = cell_load(board_at(p, (size_t)item, 1, thread));
-            const Affine t = affine_then(m, o0.a, o0.b, o1.a, o1.b);
-            cell_store(gboard_at(p, g, it.chain, 0, thread), t.ar, t.ai, p.epoch);
-            cell_store(gboard_at(p, g, it.chain, 1, thread), t.br, t.bi, p.epoch);
-        }
-        prefix_at(smem, 0)[thread] = m.ar;
-        prefix_at(smem, 1)[thread] = m.ai;
-        prefix_at(smem, 2)[thread] = m.br;
-        prefix_at(smem, 3)[thread] = m.bi;
-    }
-
-    // channel threads, after the shares over the earlier groups: prefix = (earlier groups) then
-    // (earlier runs of the own group); the owner of the chain's last run appends its own map,
-    // which gives the span's map, and sends it to every rank
-    FL_HD static void prefix_join(const Params& p, int item, const Item& it, int thread, float* smem) {
-        const SpanShape& s = p.s;
-        const int c = it.cg * kGroup + thread;
-        if (thread >= kGroup || c >= s.C) return;
-        const Affine groups = join_shares(smem, thread);
-        const Affine m = affine_then(groups, prefix_at(smem, 0)[thread], prefix_at(smem, 1)[thread],
-                                     prefix_at(smem, 2)[thread], prefix_at(smem, 3)[thread]);
         if (it.run == s.R - 1) {
-            const Cell o0 = cell_load(board_at(p, (size_t)item, 0, thread));
-            const Cell o1 = cell_load(board_at(p, (size_t)item, 1, thread));
-            const Affine t = affine_then(m, o0.a, o0.b, o1.a, o1.b);
+            const Pub4 own = map_load(runmap_at(p, (size_t)item, thread));
+            const Affine t = affine_then(m, own.x, own.y, own.z, own.w);
             if (p.summary) {
                 float* o = p.summary + (size_t)it.b * 4 * s.C + c;
                 o[0] = t.ar; o[s.C] = t.ai; o[2 * (size_t)s.C] = t.br; o[3 * (size_t)s.C] = t.bi;
@@ -566,38 +514,25 @@ struct FwdSpanSweep {
                     });
                     ex.all([&](int t, State& st) { fold_tile(p, it, t, smem, st); });
                 }
-                ex.run([&](int t, State& st) { publish_run(p, item, t, st); });
+                ex.all([&](int t, State& st) { publish_run(p, item, t, st); });
+                ex.run([&](int t, State&) { arrive(p, it, t); });
             }
         }
         if (p.stages & 6) {
             for (int item = block; item < s.items; item += ex.blocks()) {
                 if (p.emu_round >= 0 && item != block + p.emu_round * ex.blocks()) continue;
                 const Item it = decode(s, item);
-                const int g = it.run / kGroupRuns;
-                const int group_last =
-                    (g + 1) * kGroupRuns - 1 < s.R - 1 ? (g + 1) * kGroupRuns - 1 : s.R - 1;
-                const bool owner = it.run == group_last;   // others wait for this block's group map
                 // The first tile of sweep 2 - loads and gate arithmetic, parked in shared memory -
-                // comes before a block's own waiting, but after the group map it owes the others.
-                auto first_tile = [&](int t, State& st) {
+                // comes before the waiting; thread 0 then waits for the chain.
+                ex.all([&](int t, State& st) {
                     if (p.stages & 2) {
                         tile_load<true>(p, it, 0, t, st);
                         tile_compose(p, it, 0, t, smem, st);
                         stash(smem, t, st);
                     }
-                };
-                ex.all([&](int t, State& st) {
-                    if (!owner) first_tile(t, st);
-                    if (t == 0) wait_flag(smem)[0] = 1u;
+                    wait_chain(p, it, t, smem);
                 });
-                ex.all([&](int t, State&) { wait_maps<false>(p, it, g * kGroupRuns, it.run, t, smem); });
-                ex.all([&](int t, State&) { compose_shares<false>(p, it, g * kGroupRuns, it.run, t, smem); });
-                ex.all([&](int t, State& st) {
-                    group_join(p, item, it, t, smem);
-                    if (owner) first_tile(t, st);
-                });
-                ex.all([&](int t, State&) { wait_maps<true>(p, it, 0, g, t, smem); });
-                ex.all([&](int t, State&) { compose_shares<true>(p, it, 0, g, t, smem); });
+                ex.all([&](int t, State&) { prefix_shares(p, it, t, smem); });
                 ex.run([&](int t, State&) { prefix_join(p, item, it, t, smem); });
                 if (!(p.stages & 2)) continue;  // host emulation: every rank sends before any waits
                 for (int q = 0; q < it.tiles; ++q) {

@@ -678,13 +678,13 @@ static SpanShape make_span_shape(int B, int L, int C, int grid) {
 static size_t mailbox_slot_bytes(int P, int B, int C) {
     return round_up((size_t)2 * P * B * 4 * C * sizeof(MailPair), 256);
 }
-// run maps of up to span_item_bound runs, then the maps of their groups of eight
-static size_t span_group_bound(int B, int C) {
-    const long long chains = (long long)B * ((C + kGroup - 1) / kGroup);
-    return (size_t)(span_item_bound(B, C) / 8 + chains);
+// counters (one word per chain), then the run maps of up to span_item_bound runs (2 KB each)
+// (a counter word and, 256 bytes apart from one another, a ready word per chain)
+static size_t board_count_bytes(int B, int C) {
+    return round_up((size_t)B * ((C + kGroup - 1) / kGroup) * 65 * sizeof(unsigned), 256);
 }
 static size_t mailbox_board_bytes(int B, int C) {
-    return ((size_t)span_item_bound(B, C) + span_group_bound(B, C)) * 2 * kGroup * 2 * sizeof(MailPair);
+    return board_count_bytes(B, C) + (size_t)span_item_bound(B, C) * kGroup * 4 * sizeof(float);
 }
 
 // ---------------------------------------------------------------------------
@@ -1187,9 +1187,10 @@ int fields_read_forward_sharded(const float* raw, const float* tr, const float* 
     p.raw = raw; p.tr = tr; p.ti = ti; p.gamma = gamma; p.state0 = state0;
     p.read = read; p.state_out = state_out; p.summary = summary;
     p.s = make_span_shape<SpanFwd>(B, L, C, grid_max);
-    p.board = reinterpret_cast<MailPair*>(static_cast<char*>(mailboxes[rank]) +
-                                          mailbox_slot_bytes(P, B, C));
-    p.gboard = p.board + (size_t)span_item_bound(B, C) * 2 * kGroup * 2;
+    char* board = static_cast<char*>(mailboxes[rank]) + mailbox_slot_bytes(P, B, C);
+    p.count = reinterpret_cast<unsigned*>(board);
+    p.ready = p.count + p.s.chains;
+    p.runmap = reinterpret_cast<float*>(board + board_count_bytes(B, C));
     p.emu_round = -1;
     p.error = error_word;
     for (int r = 0; r < P; ++r) p.mailbox[r] = static_cast<MailPair*>(mailboxes[r]);
