@@ -39,9 +39,9 @@ SYMBOLS = {
     "fields_read_span_summary_put": (_I, [_P] * 6 + [_I, _I, ctypes.c_uint, _P, _SZ, _I, _I, _I, _P]),
     "fields_read_forward_sharded": (_I, [_P] * 10 + [_I, _I, ctypes.c_uint, ctypes.c_uint,
                                               _I, _I, _I, _P]),
-    "fields_read_fold_mailbox": (_I, [_P, _P, _P, _P, _I, _I, ctypes.c_uint, _I, _I, _P]),
+    "fields_read_fold_mailbox": (_I, [_P, _P, _P, _P, _I, _I, ctypes.c_uint, ctypes.c_uint, _I, _I, _P]),
     "fields_read_span_summary_backward_put": (_I, [_P] * 6 + [_I, _I, ctypes.c_uint, _P, _SZ, _I, _I, _I, _P]),
-    "fields_read_fold_mailbox_backward": (_I, [_P, _P, _P, _P, _I, _I, ctypes.c_uint, _I, _I, _P]),
+    "fields_read_fold_mailbox_backward": (_I, [_P, _P, _P, _P, _I, _I, ctypes.c_uint, ctypes.c_uint, _I, _I, _P]),
     "fields_read_norm_grad_combine": (_I, [_P, _P, _P, _P, ctypes.c_longlong, _I, _P]),
     "fields_mixer_epilogue_bias_rows": (_SZ, [ctypes.c_longlong]),
     "fields_mixer_epilogue_forward": (_I, [_P] * 7 + [ctypes.c_float, _I, ctypes.c_longlong, _I, _P]),

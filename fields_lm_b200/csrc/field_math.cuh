@@ -64,36 +64,6 @@ FL_HD float fast_rcp(float x) {
 #endif
 }
 
-// min(x, cap) that keeps a NaN in x (fminf would drop it)
-FL_HD float min_keep_nan(float x, float cap) {
-#if FL_DEVICE_CODE
-    float y;
-    asm("min.NaN.f32 %0, %1, %2;" : "=f"(y) : "f"(x), "f"(cap));
-    return y;
-#else
-    return x > cap ? cap : x;
-#endif
-}
-
-// The three gates of one channel-step need three reciprocals 1/(2^a + 1), 1/(2^b + 1),
-// 1/(2^c + 1). The special-function unit is the busiest pipe of these kernels (an ex2 and
-// an rcp per gate), so the three share ONE rcp: r = 1 / (d_a d_b d_c), 1/d_a = r d_b d_c and
-// so on - five extra multiplies on the FMA pipe, which has room. The exponents are capped
-// at 40 so that the product stays finite (2^120); beyond the cap tanh is 1 and the sigmoid
-// below 1e-12 in fp32 anyway.
-constexpr float kExpCap = 40.0f;
-struct Rcp3 { float a, b, c; };
-FL_HD Rcp3 rcp3_of_exp2_plus_one(float xa, float xb, float xc) {
-    const float da = fast_exp2(min_keep_nan(xa, kExpCap)) + 1.0f;
-    const float db = fast_exp2(min_keep_nan(xb, kExpCap)) + 1.0f;
-    const float dc = fast_exp2(min_keep_nan(xc, kExpCap)) + 1.0f;
-    const float ab = da * db;
-    const float r = fast_rcp(ab * dc);
-    const float rc = r * ab;
-    const float rdc = r * dc;
-    return Rcp3{rdc * db, rdc * da, rc};
-}
-
 FL_HD float sigmoidf_fast(float x) { return fast_rcp(1.0f + fast_exp2(-kLog2e * x)); }
 
 FL_HD float tanhf_fast(float x) {
@@ -352,15 +322,11 @@ FL_HD F2 sigmoid2(const F2& z) {
 FL_HD Gate2 make_gate2(const F2& zr, const F2& zi, const F2& zv) {
     Gate2 g;
     const F2 one = splat2(1.0f), k2 = splat2(2.0f * kLog2e), m2 = splat2(-2.0f);
-    // one shared reciprocal per channel for the three gates (see rcp3_of_exp2_plus_one)
-    const F2 xr = mul2(zr, k2), xi = mul2(zi, k2), xv = mul2(zv, splat2(-kLog2e));
-    const Rcp3 lo = rcp3_of_exp2_plus_one(xr.x, xi.x, xv.x);
-    const Rcp3 hi = rcp3_of_exp2_plus_one(xr.y, xi.y, xv.y);
-    g.rr = F2{lo.a, hi.a};
-    g.ri = F2{lo.b, hi.b};
-    g.sig = F2{lo.c, hi.c};
+    g.rr = rcp2(add2(exp2_2(mul2(zr, k2)), one));
+    g.ri = rcp2(add2(exp2_2(mul2(zi, k2)), one));
     g.inj_r = fma2(g.rr, m2, one);
     g.inj_i = fma2(g.ri, m2, one);
+    g.sig = sigmoid2(zv);
     g.vac = mul2(g.sig, splat2(kVacMax));
     g.keep = fma2(g.sig, splat2(-kVacMax), one);
     return g;
@@ -386,11 +352,9 @@ struct Gate {
 
 FL_HD Gate make_gate(float zr, float zi, float zv) {
     Gate g;
-    // tanh(x) = 1 - 2 / (2^(2 log2e x) + 1), sigmoid(x) = 1 / (2^(-log2e x) + 1): one shared rcp
-    const Rcp3 r = rcp3_of_exp2_plus_one((2.0f * kLog2e) * zr, (2.0f * kLog2e) * zi, -kLog2e * zv);
-    g.inj_r = 1.0f - 2.0f * r.a;
-    g.inj_i = 1.0f - 2.0f * r.b;
-    g.sig = r.c;
+    g.inj_r = tanhf_fast(zr);
+    g.inj_i = tanhf_fast(zi);
+    g.sig = sigmoidf_fast(zv);
     g.vac = kVacMax * g.sig;
     return g;
 }

@@ -1774,7 +1774,8 @@ struct FoldMailbox {
                 MailPair m = mail_load(q + (size_t)k * p.C);
 #if FL_DEVICE_CODE
                 unsigned polls = 0;
-                while (m.tag != p.epoch && ++polls < p.max_polls) {
+                // a slot that is late ends the waiting for all that follow it: one bound per call
+                while (m.tag != p.epoch && !failed && ++polls < p.max_polls) {
                     backoff(polls);
                     m = mail_load(q + (size_t)k * p.C);
                 }

@@ -12,9 +12,9 @@
 //             gates and composes the run's affine map (reference :493-509). Loads are
 //             ordinary (cached) loads: what was read last stays in L2.
 //   scan      a block stores its run's map on the rank's board and counts itself in on the
-//             chain's counter, one release-acquire atomic; the counter word carries the call's
-//             epoch as a tag and so restarts by itself. Every block waits (one thread polls,
-//             bounded) until its chain is complete and then composes, itself, the maps of the
+//             chain's counter, one release-acquire atomic; the last one in resets the counter
+//             and writes the call's epoch into the chain's ready word. Every block waits (one
+//             thread polls that word, bounded) and then composes, itself, the maps of the
 //             runs before its own: the map from the span's start to the start of its run. All
 //             loads are independent, two threads share a channel, so the longest chain of
 //             dependent work is half the runs of a chain. The block that owns the chain's last
@@ -32,8 +32,8 @@
 //
 // Blocks wait for one another (scan) and for peers (mailbox), so all blocks of the grid must
 // be resident: the launch is cooperative and the grid is sized from the occupancy query.
-// The board (run maps and counters) lives behind the mailbox's slots, memory that only this
-// rank's kernels touch; counters are tagged with the mailbox's epochs: nothing is cleared.
+// The board (run maps, counters, ready words) lives behind the mailbox's slots, memory zeroed
+// once that only this rank's kernels touch; nothing is cleared between launches.
 // Every wait is bounded; on expiry the block records the error word, poisons its state with
 // NaN and finishes. Peer memory is touched by plain stores only (no TMA, no multicast).
 //
@@ -64,7 +64,7 @@ struct SpanFwdParams {
     float* state_out;        // [B, 2C] or null: state after this rank's span
     float* summary;          // [B, 4, C] or null: this span's own map
     float* runmap;           // [items][128][4] run maps, on the rank's board
-    unsigned* count;         // [chains] (epoch tag << 12 | runs arrived), on the rank's board
+    unsigned* count;         // [chains] runs arrived (zero between launches), on the rank's board
     unsigned* ready;         // [chains] epoch of the last completed chain, 64 words apart
     int emu_round;           // host emulation: only the block's item of this round (-1: all)
     unsigned* error;         // error word (0 = ok)
@@ -223,14 +223,13 @@ struct FwdSpanSweep {
         st.run = affine_then(a, st.run.ar, st.run.ai, st.run.br, st.run.bi);
     }
 
-    // ---- scan: one tagged counter per chain, every block composes its own prefix ----
-    // Run maps sit on the rank's board as plain float4 per channel. A chain's counter word
-    // holds (epoch tag << 12 | runs arrived); it restarts by itself when the tag changes, so
-    // nothing is cleared between launches.
+    // ---- scan: one counter per chain, every block composes its own prefix ----
+    // Run maps sit on the rank's board as plain float4 per channel. A chain's counter counts
+    // the runs that have arrived; the last one in sets it back to zero and writes the call's
+    // epoch into the chain's ready word, so nothing is cleared between launches.
     FL_HD static float* runmap_at(const Params& p, size_t item, int ch) {
         return p.runmap + (item * kGroup + ch) * 4;
     }
-    FL_HD static unsigned tag_of(unsigned epoch) { return (epoch & 0xFFFFFu) << 12; }
 
     // end of sweep 1, channel threads: the run's map becomes visible to the chain's other blocks
     FL_HD static void publish_run(const Params& p, int item, int thread, State& st) {
@@ -248,28 +247,22 @@ struct FwdSpanSweep {
     FL_HD static void arrive(const Params& p, const Item& it, int thread) {
         if (thread != 0) return;
         unsigned* word = p.count + it.chain;
-        const unsigned tag = tag_of(p.epoch);
 #if FL_DEVICE_CODE
-        unsigned cur = *reinterpret_cast<volatile unsigned*>(word);
-        for (;;) {
-            const unsigned want = (cur & ~0xFFFu) == tag ? cur + 1u : (tag | 1u);
-            unsigned old;
-            asm volatile("atom.cas.acq_rel.gpu.global.b32 %0, [%1], %2, %3;"
-                         : "=r"(old) : "l"(word), "r"(cur), "r"(want) : "memory");
-            if (old == cur) {
-                cur = want;
-                break;
-            }
-            cur = old;
-        }
-        // the last run in: the chain's ready word (a word of its own, so that the blocks polling
-        // it stay off the counter's line) takes the epoch
-        if (cur == (tag | (unsigned)p.s.R))
+        unsigned old;
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(word) : "memory");
+        if (old == (unsigned)p.s.R - 1u) {
+            // the last run in: the counter goes back to zero for the next launch (nobody else
+            // touches it now) and the chain's ready word - a word of its own, so that the
+            // blocks polling it stay off the counter's line - takes the epoch
+            *word = 0u;
             asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ready + 64 * it.chain), "r"(p.epoch)
                          : "memory");
+        }
 #else
-        *word = (*word & ~0xFFFu) == tag ? *word + 1u : (tag | 1u);
-        if (*word == (tag | (unsigned)p.s.R)) p.ready[64 * it.chain] = p.epoch;
+        if (++*word == (unsigned)p.s.R) {
+            *word = 0u;
+            p.ready[64 * it.chain] = p.epoch;
+        }
 #endif
     }
 

@@ -170,9 +170,13 @@ __device__ __forceinline__ void wait_for_previous_kernel() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+// (the environment is read once, at the first launch)
 static bool dependent_launch_enabled() {
-    const char* e = std::getenv("FIELDS_READ_PDL");
-    return !(e && e[0] == '0');
+    static const bool enabled = [] {
+        const char* e = std::getenv("FIELDS_READ_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return enabled;
 }
 
 template <class K>
@@ -313,19 +317,21 @@ static int fill_unset(void* p, size_t bytes, Stream st) {
                                  0, st, FillParams{static_cast<uint4*>(p), n});
 }
 
-// Blocks of kernel K that the GPU holds at once (occupancy x SM count), asked once.
+// Blocks of kernel K that the current GPU holds at once (occupancy x SM count), asked once per device.
 template <class K>
 static int resident_blocks() {
-    static int cached = 0;
-    if (cached > 0) return cached;
+    static std::mutex mu;
+    static int cached[64] = {};
     int per_sm = 0, dev = 0, sms = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] > 0) return cached[dev];
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
         cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, stateful_entry<K>, K::kThreads,
                                                       K::kSmemFloats * sizeof(float)) != cudaSuccess)
         return 0;
-    cached = per_sm * sms;
-    return cached;
+    cached[dev] = per_sm * sms;
+    return cached[dev];
 }
 
 // Persistent block program over an executor: the calling thread, then a block barrier.
@@ -671,6 +677,11 @@ static SpanShape make_span_shape(int B, int L, int C, int grid) {
     s.R = (L + steps - 1) / steps;
     s.items = s.chains * s.R;
     return s;
+}
+
+// Bound of a device-side wait in polls: the caller's, or the library's default.
+static unsigned poll_bound(unsigned max_polls) {
+    return max_polls == 0 || max_polls > kMaxPolls ? kMaxPolls : max_polls;
 }
 
 // Mailbox = [slots of the exchange][board of the one-launch forward]. The board (the run maps
@@ -1196,7 +1207,7 @@ int fields_read_forward_sharded(const float* raw, const float* tr, const float* 
     for (int r = 0; r < P; ++r) p.mailbox[r] = static_cast<MailPair*>(mailboxes[r]);
     p.own = static_cast<const MailPair*>(mailboxes[rank]);
     p.rank = rank; p.P = P; p.epoch = epoch;
-    p.max_polls = max_polls == 0 || max_polls > kMaxPolls ? kMaxPolls : max_polls;
+    p.max_polls = poll_bound(max_polls);
     p.stages = 3;
 #ifdef FIELDS_HOST_EMU
     p.stages = g_emu_span_stages;  // the CPU tests run the ranks' first sweeps before any rank's wait
@@ -1291,28 +1302,28 @@ int fields_read_span_summary_backward_put(const float* raw, const float* tr, con
 }
 
 int fields_read_fold_mailbox(const void* mailbox, const float* state0, float* state,
-                             unsigned* error_word, int rank, int P, unsigned epoch, int B, int C,
-                             void* stream) {
+                             unsigned* error_word, int rank, int P, unsigned epoch,
+                             unsigned max_polls, int B, int C, void* stream) {
     if (B < 0 || C <= 0 || P <= 0 || P > kMaxRanks || rank < 0 || rank >= P || epoch == 0)
         return FIELDS_ERR_ARGUMENT;
     if (B == 0) return FIELDS_OK;
     if (!mailbox || !state || !error_word) return FIELDS_ERR_ARGUMENT;
     FoldMailbox::Params p{static_cast<const MailPair*>(mailbox), state0, state, error_word,
-                          rank, P, B, C, epoch, kMaxPolls, 0};
+                          rank, P, B, C, epoch, poll_bound(max_polls), 0};
     const long long n = (long long)B * C;
     return launch<FoldMailbox>(p, (n + FoldMailbox::kThreads - 1) / FoldMailbox::kThreads,
                                reinterpret_cast<Stream>(stream));
 }
 
 int fields_read_fold_mailbox_backward(const void* mailbox, const float* carry_end, float* carry,
-                                      unsigned* error_word, int rank, int P, unsigned epoch, int B,
-                                      int C, void* stream) {
+                                      unsigned* error_word, int rank, int P, unsigned epoch,
+                                      unsigned max_polls, int B, int C, void* stream) {
     if (B < 0 || C <= 0 || P <= 0 || P > kMaxRanks || rank < 0 || rank >= P || epoch == 0)
         return FIELDS_ERR_ARGUMENT;
     if (B == 0) return FIELDS_OK;
     if (!mailbox || !carry || !error_word) return FIELDS_ERR_ARGUMENT;
     FoldMailbox::Params p{static_cast<const MailPair*>(mailbox), carry_end, carry, error_word,
-                          rank, P, B, C, epoch, kMaxPolls, 1};
+                          rank, P, B, C, epoch, poll_bound(max_polls), 1};
     const long long n = (long long)B * C;
     return launch<FoldMailbox>(p, (n + FoldMailbox::kThreads - 1) / FoldMailbox::kThreads,
                                reinterpret_cast<Stream>(stream));

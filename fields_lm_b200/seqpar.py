@@ -229,9 +229,11 @@ class SequenceParallelForwardP2P:
     they must not be replayed from a captured CUDA graph.
     """
 
-    def __init__(self, batch: int, span_length: int, channels: int, device, group=None):
+    def __init__(self, batch: int, span_length: int, channels: int, device, group=None,
+                 max_polls: int = 0):
         import ctypes
         import os
+        self.max_polls = int(max_polls)  # bound of the device-side waits; 0: about a second
         # The mailboxes are written with plain peer stores only; binding them to an NVLink
         # multicast object buys nothing and ties every rank's memory to the others' lifetime.
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -271,7 +273,7 @@ class SequenceParallelForwardP2P:
         rc = lib.fields_read_fold_mailbox(self.mail.data_ptr(),
                                           None if state0 is None else state0.data_ptr(),
                                           self.state_in.data_ptr(), self.error.data_ptr(),
-                                          self.rank, self.world, self.epoch, B, C, st)
+                                          self.rank, self.world, self.epoch, self.max_polls, B, C, st)
         _lib.check(rc, "fields_read_fold_mailbox")
         rc = lib.fields_read_forward(*args, self.state_in.data_ptr(), self.read.data_ptr(),
                                      self.state_out.data_ptr(), self.ws.data_ptr(), self.nbytes,
@@ -282,6 +284,19 @@ class SequenceParallelForwardP2P:
     def status(self) -> int:
         """0, or 1 if some call since construction gave up waiting for a peer's summary (syncs)."""
         return int(self.error.item())
+
+    def check_status(self) -> None:
+        """Raises if a device-side wait of this object ever ran out (one small device-to-host
+        read: call it where the step synchronises anyway, e.g. next to reading the loss).
+
+        The waits tolerate about a second of skew between the ranks by default (``max_polls``
+        of the constructor, in polls of well under a microsecond each). A rank that is later
+        than that - a checkpoint write, a stalled loader - makes the others give up: their
+        outputs hold NaN from that call on, never stale data, and this method reports it."""
+        if self.status():
+            raise _lib.FieldsLibraryError(
+                "a sequence-parallel exchange gave up waiting for a peer's summary "
+                f"(FIELDS_ERR_TIMEOUT, rank {self.rank} of {self.world}): outputs since then hold NaN")
 
 
 class SequenceParallelForwardFused(SequenceParallelForwardP2P):
@@ -297,10 +312,6 @@ class SequenceParallelForwardFused(SequenceParallelForwardP2P):
     kernel argument).
     """
 
-    def __init__(self, batch: int, span_length: int, channels: int, device, group=None,
-                 max_polls: int = 0):
-        super().__init__(batch, span_length, channels, device, group)
-        self.max_polls = int(max_polls)
 
     def __call__(self, raw_span, tr, ti, gamma, state0: Optional[torch.Tensor] = None):
         B, L, C = self.B, self.L, self.C
@@ -328,12 +339,16 @@ class SequenceParallelTrainStepP2P(SequenceParallelForwardP2P):
     NCCL (one all_reduce). Like the forward, not for replay from a captured CUDA graph.
     """
 
-    def __init__(self, batch: int, span_length: int, channels: int, device, group=None):
-        super().__init__(batch, span_length, channels, device, group)
+    def __init__(self, batch: int, span_length: int, channels: int, device, group=None,
+                 max_polls: int = 0):
+        super().__init__(batch, span_length, channels, device, group, max_polls)
         f32 = dict(device=self.device, dtype=torch.float32)
         self.carry = torch.empty(batch, 2 * channels, **f32)
         self.grad_raw = torch.empty(batch, span_length, 3 * channels, **f32)
-        self.grad_par = torch.empty(3, channels, **f32)
+        # [3 C] parameter gradients + one word: the ranks' error words, summed by the same
+        # all_reduce, so every rank learns of a timeout anywhere without another collective
+        self.reduced = torch.zeros(3 * channels + 1, **f32)
+        self.grad_par = self.reduced[:3 * channels].view(3, channels)
         self.nbytes_bwd = self.lib.fields_read_workspace_bytes(batch, span_length, channels, 1)
         self.ws_bwd = torch.empty(max(self.nbytes_bwd, 256), dtype=torch.uint8, device=self.device)
 
@@ -356,7 +371,7 @@ class SequenceParallelTrainStepP2P(SequenceParallelForwardP2P):
         _lib.check(rc, "fields_read_span_summary_backward_put")
         rc = lib.fields_read_fold_mailbox_backward(self.mail.data_ptr(), None, self.carry.data_ptr(),
                                                    self.error.data_ptr(), self.rank, self.world,
-                                                   self.epoch, B, C, st)
+                                                   self.epoch, self.max_polls, B, C, st)
         _lib.check(rc, "fields_read_fold_mailbox_backward")
         g = self.grad_par
         rc = lib.fields_read_backward(*args, gamma.data_ptr(), self.state_in.data_ptr(),
@@ -366,8 +381,14 @@ class SequenceParallelTrainStepP2P(SequenceParallelForwardP2P):
                                       self.ws_bwd.data_ptr(), self.nbytes_bwd, B, L, C, st)
         _lib.check(rc, "fields_read_backward")
         if self.world > 1:
-            dist.all_reduce(g, group=self.group)
+            self.reduced[-1:].copy_(self.error)
+            dist.all_reduce(self.reduced, group=self.group)
         return self.grad_raw, g
+
+    def status(self) -> int:
+        """Number of ranks whose waits have run out, as of the last backward (syncs); before the
+        first backward, this rank's own error word."""
+        return int(self.reduced[-1].item()) or int(self.error.item())
 
 
 def span_bounds(length: int, world: int, rank: int) -> Tuple[int, int]:

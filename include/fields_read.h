@@ -219,6 +219,9 @@ int fields_read_step_bf16(const void *raw, const float *tr, const float *ti, con
  * summaries of all P ranks for `epoch`, then writes the state entering the rank's span to
  * `state` [B, 2C] (state0 as in fields_read_fold_summaries). If a summary does not arrive in
  * time it sets *error_word (a device word the caller zeroed) to 1 and fills `state` with NaN.
+ * `max_polls` bounds the wait for the whole call (a poll is well under a microsecond; 0 = the
+ * library's default of 2^21, about a second of skew between the ranks): once one slot has run
+ * out, the slots after it are not waited for.
  *
  * `epoch` is a per-call counter kept by the caller: the same on all ranks, never 0, increased
  * by one for every exchange on a mailbox. Two parities alternate inside the mailbox and every
@@ -232,8 +235,8 @@ int fields_read_span_summary_put(const float *raw, const float *tr, const float 
                                  int rank, int P, unsigned epoch, void *workspace,
                                  size_t workspace_bytes, int B, int L, int C, void *stream);
 int fields_read_fold_mailbox(const void *mailbox, const float *state0, float *state,
-                             unsigned *error_word, int rank, int P, unsigned epoch, int B, int C,
-                             void *stream);
+                             unsigned *error_word, int rank, int P, unsigned epoch,
+                             unsigned max_polls, int B, int C, void *stream);
 
 /*
  * The sequence-sharded forward of one rank in ONE launch (no counterpart in the reference, which
@@ -289,7 +292,7 @@ int fields_read_span_summary_backward_put(const float *raw, const float *tr, con
                                           int C, void *stream);
 int fields_read_fold_mailbox_backward(const void *mailbox, const float *carry_end, float *carry,
                                       unsigned *error_word, int rank, int P, unsigned epoch,
-                                      int B, int C, void *stream);
+                                      unsigned max_polls, int B, int C, void *stream);
 
 /* Text of the last CUDA runtime error seen by the calling thread inside this library. */
 const char *fields_last_cuda_error(void);

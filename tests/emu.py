@@ -74,11 +74,11 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.fields_read_mailbox_bytes.restype = SZ
     lib.fields_read_span_summary_put.argtypes = [P] * 6 + [I, I, ctypes.c_uint, P, SZ, I, I, I, P]
     lib.fields_read_span_summary_put.restype = I
-    lib.fields_read_fold_mailbox.argtypes = [P, P, P, P, I, I, ctypes.c_uint, I, I, P]
+    lib.fields_read_fold_mailbox.argtypes = [P, P, P, P, I, I, ctypes.c_uint, ctypes.c_uint, I, I, P]
     lib.fields_read_fold_mailbox.restype = I
     lib.fields_read_span_summary_backward_put.argtypes = [P] * 6 + [I, I, ctypes.c_uint, P, SZ, I, I, I, P]
     lib.fields_read_span_summary_backward_put.restype = I
-    lib.fields_read_fold_mailbox_backward.argtypes = [P, P, P, P, I, I, ctypes.c_uint, I, I, P]
+    lib.fields_read_fold_mailbox_backward.argtypes = [P, P, P, P, I, I, ctypes.c_uint, ctypes.c_uint, I, I, P]
     lib.fields_read_fold_mailbox_backward.restype = I
     lib.fields_read_forward_sharded.argtypes = [P] * 10 + [I, I, ctypes.c_uint, ctypes.c_uint,
                                                    I, I, I, P]
@@ -361,7 +361,7 @@ def fold_mailbox_backward(mailbox, rank, world, epoch, B, C, carry_end=None):
     out = _f32(np.full((B, 2 * C), np.nan))
     err = np.zeros(1, dtype=np.uint32)
     rc = lib().fields_read_fold_mailbox_backward(_ptr(mailbox), _ptr(c0), _ptr(out), _ptr(err), rank,
-                                                 world, epoch, B, C, None)
+                                                 world, epoch, 0, B, C, None)
     if rc:
         raise RuntimeError(lib().fields_status_string(rc).decode())
     return out, int(err[0])
@@ -372,7 +372,7 @@ def fold_mailbox(mailbox, rank, world, epoch, B, C, state0=None):
     out = _f32(np.full((B, 2 * C), np.nan))
     err = np.zeros(1, dtype=np.uint32)
     rc = lib().fields_read_fold_mailbox(_ptr(mailbox), _ptr(s0), _ptr(out), _ptr(err), rank, world,
-                                        epoch, B, C, None)
+                                        epoch, 0, B, C, None)
     if rc:
         raise RuntimeError(lib().fields_status_string(rc).decode())
     return out, int(err[0])

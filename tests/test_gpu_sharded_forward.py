@@ -130,3 +130,26 @@ def test_argument_errors():
     odd = Rank(dev, 1, 8, 3)
     p3 = torch.ones(3, device=dev)
     assert odd(torch.zeros(1, 8, 9, device=dev), p3, p3, p3, 1) == 5   # C % 4 != 0
+
+
+@pytest.mark.parametrize("backward", [False, True])
+def test_fold_mailbox_gives_up_after_max_polls(backward):
+    """The three-launch exchange's wait: a zeroed mailbox in which no summary ever arrives. With
+    the bound set to 2,000 polls the call ends at once, sets the error word and writes NaN; one
+    late slot ends the waiting for all that follow it (one bound per call, not per slot)."""
+    import time
+    from fields_lm_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    P, B, C = 8, 1, 512
+    mail = torch.zeros(lib.fields_read_mailbox_bytes(P, B, C), dtype=torch.uint8, device=dev)
+    state = torch.zeros(B, 2 * C, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    fn = lib.fields_read_fold_mailbox_backward if backward else lib.fields_read_fold_mailbox
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    assert fn(mail.data_ptr(), None, state.data_ptr(), err.data_ptr(), 3, P, 1, 2000, B, C,
+              torch.cuda.current_stream(dev).cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 0.5      # 4 P slots x 2,000 polls each would take far longer
+    assert int(err.item()) == 1 and bool(torch.isnan(state).all())
