@@ -77,35 +77,30 @@ struct SpanFwdParams {
     SpanShape s;
 };
 
-template <int TS, int WARPS, int MIN_BLOCKS>
+// CH steps per chunk (two chunks of a warp are in flight), WARPS warps, MIN_BLOCKS blocks per SM.
+template <int CH, int WARPS, int MIN_BLOCKS>
 struct FwdSpanSweep {
     using Params = SpanFwdParams;
     static constexpr int kThreads = 32 * WARPS;
     static constexpr int kMinBlocks = MIN_BLOCKS;
-    static constexpr int kTile = TS * WARPS;
-    static constexpr int kSumFloats = WARPS * 4 * kGroup;    // warp maps; scan: segment maps
-    static constexpr int kCarryFloats = WARPS * 2 * kGroup;  // state entering each warp's steps
-    static constexpr int kRunFloats = 2 * kGroup;            // running state of the run
+    static constexpr int kRunQuantum = WARPS;                // run lengths are multiples of this
+    static constexpr int kSumFloats = WARPS * 4 * kGroup;    // the warps' maps, kept from sweep 1 to sweep 2
+    static constexpr int kCarryFloats = WARPS * 2 * kGroup;  // scan: shares and prefix; then each warp's entering state
     static constexpr int kFlagFloats = 4;                    // the wait flag
-    static constexpr int kStashFloats = 3 * TS * 4 * kThreads;  // the first tile of sweep 2, parked
-    static constexpr int kSmemFloats = kSumFloats + kCarryFloats + kRunFloats + kFlagFloats + kStashFloats;
+    static constexpr int kSmemFloats = kSumFloats + kCarryFloats + kFlagFloats;
     static_assert(kThreads >= kGroup, "one thread per channel is needed for the carries");
 
-    struct State {
-        Vec<4> br[TS], bi[TS], vac[TS];  // sweep 2: gamma*v*inj and vacancy of the warp's steps
-        Affine run;                      // sweep 1: map of the run so far (channel threads)
-    };
+    struct State {};  // nothing lives in registers across block barriers
 
     FL_HD static float* sum_at(float* smem, int w, int k) { return smem + (w * 4 + k) * kGroup; }
     FL_HD static float* carry_at(float* smem, int w, int k) {
         return smem + kSumFloats + (w * 2 + k) * kGroup;
     }
-    FL_HD static float* run_at(float* smem, int k) { return smem + kSumFloats + kCarryFloats + k * kGroup; }
 
     struct Item {
         int chain, run, b, cg;
         int lo, hi;   // steps of the run
-        int tiles;
+        int per;      // steps per warp: warp w owns [lo + w per, lo + (w + 1) per) within the run
     };
     FL_HD static Item decode(const SpanShape& s, int item) {
         Item it;
@@ -115,68 +110,96 @@ struct FwdSpanSweep {
         it.cg = it.chain % s.G;
         it.lo = it.run * s.run_steps;
         it.hi = it.lo + s.run_steps < s.L ? it.lo + s.run_steps : s.L;
-        it.tiles = (it.hi - it.lo + kTile - 1) / kTile;
+        it.per = (it.hi - it.lo + WARPS - 1) / WARPS;
         return it;
     }
+    FL_HD static void warp_steps(const Item& it, int warp, int& wlo, int& whi) {
+        wlo = it.lo + warp * it.per < it.hi ? it.lo + warp * it.per : it.hi;
+        whi = wlo + it.per < it.hi ? wlo + it.per : it.hi;
+    }
 
-    // Issues the loads of the warp's TS steps of one tile into the state's registers (nothing
-    // waits for them here). STREAM: the rows are not needed again (evict first).
-    template <bool STREAM>
-    FL_HD static void tile_load(const Params& p, const Item& it, int q, int thread, State& st) {
-        const SpanShape& s = p.s;
-        const int lane = thread & 31, warp = thread >> 5;
-        const int C = s.C;
-        const int c0 = it.cg * kGroup + lane * 4;
-        const int tw = it.lo + q * kTile + warp * TS;
-        if (c0 >= C) return;
-        const float* base = p.raw + ((size_t)it.b * s.L) * 3 * C + c0;
+    // One chunk of a warp: CH consecutive rows of the three raw planes, four channels per lane.
+    struct Chunk { Vec<4> zr[CH], zi[CH], zv[CH]; };
+
+    // Issues the loads of rows [t0, t0 + CH) clipped to [wlo, whi) (nothing waits for them here).
+    // KEEP: the rows are read again by sweep 2, so they go to L2 and stay; else evict first.
+    template <bool KEEP>
+    FL_HD static void chunk_load(Chunk& c, const float* base, int C, int t0, int wlo, int whi) {
 #pragma unroll
-        for (int u = 0; u < TS; ++u) {
-            if (tw + u < it.hi) {
-                const float* row = base + (size_t)(tw + u) * 3 * C;
-                if constexpr (STREAM) {
-                    st.br[u] = vec_load_stream<4>(row);
-                    st.bi[u] = vec_load_stream<4>(row + C);
-                    st.vac[u] = vec_load_stream<4>(row + 2 * C);
-                } else {  // stays in L2 for sweep 2, bypasses L1
-                    st.br[u] = vec_load_l2<4>(row);
-                    st.bi[u] = vec_load_l2<4>(row + C);
-                    st.vac[u] = vec_load_l2<4>(row + 2 * C);
+        for (int u = 0; u < CH; ++u) {
+            const int t = t0 + u;
+            if (t >= wlo && t < whi) {
+                const float* row = base + (size_t)t * 3 * C;
+                if constexpr (KEEP) {
+                    c.zr[u] = vec_load_l2<4>(row);
+                    c.zi[u] = vec_load_l2<4>(row + C);
+                    c.zv[u] = vec_load_l2<4>(row + 2 * C);
+                } else {
+                    c.zr[u] = vec_load_stream<4>(row);
+                    c.zi[u] = vec_load_stream<4>(row + C);
+                    c.zv[u] = vec_load_stream<4>(row + 2 * C);
                 }
             }
         }
     }
 
-    // Turns the loaded rows into (b_r, b_i, vacancy) in place - they stay in `st` for the
-    // recurrence of sweep 2 - and composes the warp's map into shared memory.
-    FL_HD static void tile_compose(const Params& p, const Item& it, int q, int thread, float* smem,
-                                   State& st) {
+    // The map "first the step (a, b), then m":  s -> A (a s + b) + B.
+    FL_HD static Affine step_before(const Affine& m, float a_r, float a_i, float b_r, float b_i) {
+        Affine o;
+        o.br = m.ar * b_r - m.ai * b_i + m.br;
+        o.bi = m.ar * b_i + m.ai * b_r + m.bi;
+        o.ar = m.ar * a_r - m.ai * a_i;
+        o.ai = m.ar * a_i + m.ai * a_r;
+        return o;
+    }
+
+    // sweep 1, one chunk: the steps go in front of the warp's map so far, last row first
+    FL_HD static void chunk_fold(const Chunk& c, Affine (&m)[4], const Vec<4>& lr, const Vec<4>& li,
+                                 const Vec<4>& gm, int t0, int wlo, int whi) {
+#pragma unroll
+        for (int u = CH - 1; u >= 0; --u) {
+            const int t = t0 + u;
+            if (t >= wlo && t < whi) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const Gate g = make_gate(c.zr[u].v[k], c.zi[u].v[k], c.zv[u].v[k]);
+                    const float keep = 1.0f - g.vac;
+                    const float bs = gm.v[k] * g.vac;
+                    m[k] = step_before(m[k], keep * lr.v[k], keep * li.v[k], bs * g.inj_r, bs * g.inj_i);
+                }
+            }
+        }
+    }
+
+    // Sweep 1 of one warp: its steps from the last chunk to the first, two chunks in flight, no
+    // block barrier anywhere; the warp's map goes to shared memory (reference :493-509).
+    FL_HD static void sweep1_warp(const Params& p, const Item& it, int thread, float* smem) {
         const SpanShape& s = p.s;
         const int lane = thread & 31, warp = thread >> 5;
+        const int C = s.C;
         const int c0 = it.cg * kGroup + lane * 4;
-        const int tw = it.lo + q * kTile + warp * TS;
         Affine m[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) m[k] = affine_identity();
-        if (c0 < s.C) {
+        int wlo, whi;
+        warp_steps(it, warp, wlo, whi);
+        if (c0 < C && wlo < whi) {
             const Vec<4> lr = vec_load<4>(p.tr + c0);
             const Vec<4> li = vec_load<4>(p.ti + c0);
             const Vec<4> gm = vec_load<4>(p.gamma + c0);
-#pragma unroll
-            for (int u = 0; u < TS; ++u) {
-                if (tw + u < it.hi) {
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const Gate g = make_gate(st.br[u].v[k], st.bi[u].v[k], st.vac[u].v[k]);
-                        const float keep = 1.0f - g.vac;
-                        const float bs = gm.v[k] * g.vac;
-                        st.br[u].v[k] = bs * g.inj_r;
-                        st.bi[u].v[k] = bs * g.inj_i;
-                        st.vac[u].v[k] = g.vac;
-                        m[k] = affine_then(m[k], keep * lr.v[k], keep * li.v[k], st.br[u].v[k],
-                                           st.bi[u].v[k]);
-                    }
-                }
+            const float* base = p.raw + ((size_t)it.b * s.L) * 3 * C + c0;
+            Chunk a, b;
+            // chunk k covers rows [whi - (k + 1) CH, whi - k CH)
+            int t0 = whi - CH;
+            chunk_load<true>(a, base, C, t0, wlo, whi);
+            while (t0 + CH > wlo) {
+                chunk_load<true>(b, base, C, t0 - CH, wlo, whi);
+                chunk_fold(a, m, lr, li, gm, t0, wlo, whi);
+                t0 -= CH;
+                if (t0 + CH <= wlo) break;
+                chunk_load<true>(a, base, C, t0 - CH, wlo, whi);
+                chunk_fold(b, m, lr, li, gm, t0, wlo, whi);
+                t0 -= CH;
             }
         }
         Vec<4> o0, o1, o2, o3;
@@ -190,39 +213,6 @@ struct FwdSpanSweep {
         vec_store<4>(sum_at(smem, warp, 3) + lane * 4, o3);
     }
 
-    // The first tile of sweep 2 is computed before the scan; its (b_r, b_i, vacancy) wait in
-    // shared memory meanwhile, so the scan has the registers to itself.
-    FL_HD static float* stash_at(float* smem, int k, int thread) {
-        return smem + kSumFloats + kCarryFloats + kRunFloats + kFlagFloats + ((size_t)k * kThreads + thread) * 4;
-    }
-    FL_HD static void stash(float* smem, int thread, const State& st) {
-#pragma unroll
-        for (int u = 0; u < TS; ++u) {
-            vec_store<4>(stash_at(smem, 3 * u + 0, thread), st.br[u]);
-            vec_store<4>(stash_at(smem, 3 * u + 1, thread), st.bi[u]);
-            vec_store<4>(stash_at(smem, 3 * u + 2, thread), st.vac[u]);
-        }
-    }
-    FL_HD static void unstash(float* smem, int thread, State& st) {
-#pragma unroll
-        for (int u = 0; u < TS; ++u) {
-            st.br[u] = vec_load<4>(stash_at(smem, 3 * u + 0, thread));
-            st.bi[u] = vec_load<4>(stash_at(smem, 3 * u + 1, thread));
-            st.vac[u] = vec_load<4>(stash_at(smem, 3 * u + 2, thread));
-        }
-    }
-
-    // sweep 1, channel threads: the tile's map goes in front of the run's map so far
-    FL_HD static void fold_tile(const Params& p, const Item& it, int thread, float* smem, State& st) {
-        if (thread >= kGroup || it.cg * kGroup + thread >= p.s.C) return;
-        Affine a = affine_identity();
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w)
-            a = affine_then(a, sum_at(smem, w, 0)[thread], sum_at(smem, w, 1)[thread],
-                            sum_at(smem, w, 2)[thread], sum_at(smem, w, 3)[thread]);
-        st.run = affine_then(a, st.run.ar, st.run.ai, st.run.br, st.run.bi);
-    }
-
     // ---- scan: one counter per chain, every block composes its own prefix ----
     // Run maps sit on the rank's board as plain float4 per channel. A chain's counter counts
     // the runs that have arrived; the last one in sets it back to zero and writes the call's
@@ -231,14 +221,22 @@ struct FwdSpanSweep {
         return p.runmap + (item * kGroup + ch) * 4;
     }
 
-    // end of sweep 1, channel threads: the run's map becomes visible to the chain's other blocks
-    FL_HD static void publish_run(const Params& p, int item, int thread, State& st) {
+    // end of sweep 1, channel threads: the run's map = the warps' maps in time order; it becomes
+    // visible to the chain's other blocks
+    FL_HD static void publish_run(const Params& p, int item, const Item& it, int thread, float* smem) {
         if (thread >= kGroup) return;
+        Affine m = affine_identity();
+        if (it.cg * kGroup + thread < p.s.C) {
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w)
+                m = affine_then(m, sum_at(smem, w, 0)[thread], sum_at(smem, w, 1)[thread],
+                                sum_at(smem, w, 2)[thread], sum_at(smem, w, 3)[thread]);
+        }
         float* q = runmap_at(p, (size_t)item, thread);
 #if FL_DEVICE_CODE
-        __stcg(reinterpret_cast<float4*>(q), make_float4(st.run.ar, st.run.ai, st.run.br, st.run.bi));
+        __stcg(reinterpret_cast<float4*>(q), make_float4(m.ar, m.ai, m.br, m.bi));
 #else
-        q[0] = st.run.ar; q[1] = st.run.ai; q[2] = st.run.br; q[3] = st.run.bi;
+        q[0] = m.ar; q[1] = m.ai; q[2] = m.br; q[3] = m.bi;
 #endif
     }
     // Runs after the block barrier that follows publish_run: the barrier orders the block's
@@ -267,7 +265,7 @@ struct FwdSpanSweep {
     }
 
     FL_HD static unsigned* wait_flag(float* smem) {
-        return reinterpret_cast<unsigned*>(smem + kSumFloats + kCarryFloats + kRunFloats);
+        return reinterpret_cast<unsigned*>(smem + kSumFloats + kCarryFloats);
     }
     // thread 0: bounded wait until every run of the chain has arrived in this call
     FL_HD static void wait_chain(const Params& p, const Item& it, int thread, float* smem) {
@@ -385,7 +383,8 @@ struct FwdSpanSweep {
         prefix_at(smem, 3)[thread] = m.bi;
     }
 
-    // channel threads: state entering the run = prefix map of (earlier ranks folded onto state0)
+    // channel threads: state entering the run = prefix map of (earlier ranks folded onto
+    // state0); from it, through the warps' maps of sweep 1, the state entering each warp's steps
     FL_HD static void enter_run(const Params& p, const Item& it, int thread, float* smem) {
         const SpanShape& s = p.s;
         const int c = it.cg * kGroup + thread;
@@ -415,6 +414,9 @@ struct FwdSpanSweep {
                 if (!failed && r < p.rank) affine_apply(Affine{v[0], v[1], v[2], v[3]}, sr, si);
             }
         }
+        // (this thread's prefix entries share their place with carries it writes below: read first)
+        const Affine pre{prefix_at(smem, 0)[thread], prefix_at(smem, 1)[thread],
+                         prefix_at(smem, 2)[thread], prefix_at(smem, 3)[thread]};
         if (failed) {
 #if FL_DEVICE_CODE
             atomicExch(p.error, 1u);
@@ -423,20 +425,8 @@ struct FwdSpanSweep {
 #endif
             sr = si = nanf("");
         } else {
-            affine_apply(Affine{prefix_at(smem, 0)[thread], prefix_at(smem, 1)[thread],
-                                prefix_at(smem, 2)[thread], prefix_at(smem, 3)[thread]},
-                         sr, si);
+            affine_apply(pre, sr, si);
         }
-        run_at(smem, 0)[thread] = sr;
-        run_at(smem, 1)[thread] = si;
-    }
-
-    // sweep 2, channel threads: state entering each warp's steps, running state moves on
-    FL_HD static void carries(const Params& p, const Item& it, int q, int thread, float* smem) {
-        const SpanShape& s = p.s;
-        const int c = it.cg * kGroup + thread;
-        if (thread >= kGroup || c >= s.C) return;
-        float sr = run_at(smem, 0)[thread], si = run_at(smem, 1)[thread];
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
             carry_at(smem, w, 0)[thread] = sr;
@@ -445,47 +435,70 @@ struct FwdSpanSweep {
                                 sum_at(smem, w, 2)[thread], sum_at(smem, w, 3)[thread]},
                          sr, si);
         }
-        run_at(smem, 0)[thread] = sr;
-        run_at(smem, 1)[thread] = si;
-        if (p.state_out && it.run == s.R - 1 && q == it.tiles - 1) {
+        if (p.state_out && it.run == s.R - 1) {
             p.state_out[(size_t)it.b * 2 * s.C + c] = sr;
             p.state_out[(size_t)it.b * 2 * s.C + s.C + c] = si;
         }
     }
 
-    // sweep 2: recurrence over the warp's steps from its carry, streaming stores
-    FL_HD static void emit(const Params& p, const Item& it, int q, int thread, float* smem, State& st) {
-        const SpanShape& s = p.s;
-        const int lane = thread & 31, warp = thread >> 5;
-        const int C = s.C;
-        const int c0 = it.cg * kGroup + lane * 4;
-        if (c0 >= C) return;
-        const int tw = it.lo + q * kTile + warp * TS;
-        const Vec<4> lr = vec_load<4>(p.tr + c0);
-        const Vec<4> li = vec_load<4>(p.ti + c0);
-        Vec<4> sr = vec_load<4>(carry_at(smem, warp, 0) + lane * 4);
-        Vec<4> si = vec_load<4>(carry_at(smem, warp, 1) + lane * 4);
-        float* obase = p.read + ((size_t)it.b * s.L) * 4 * C + c0;
+    // sweep 2, one chunk: gates, recurrence and displaced readout of its rows in time order,
+    // streaming stores (reference :599-622)
+    FL_HD static void chunk_emit(const Chunk& c, Vec<4>& sr, Vec<4>& si, const Vec<4>& lr,
+                                 const Vec<4>& li, const Vec<4>& gm, float* obase, int C, int t0,
+                                 int wlo, int whi) {
 #pragma unroll
-        for (int u = 0; u < TS; ++u) {
-            if (tw + u < it.hi) {
+        for (int u = 0; u < CH; ++u) {
+            const int t = t0 + u;
+            if (t >= wlo && t < whi) {
                 Vec<4> dr, di;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
+                    const Gate g = make_gate(c.zr[u].v[k], c.zi[u].v[k], c.zv[u].v[k]);
                     float mr, mi;
                     cmul(lr.v[k], li.v[k], sr.v[k], si.v[k], mr, mi);
-                    const float v = st.vac[u].v[k];
-                    dr.v[k] = v * mr;
-                    di.v[k] = v * mi;
-                    sr.v[k] = (1.0f - v) * mr + st.br[u].v[k];
-                    si.v[k] = (1.0f - v) * mi + st.bi[u].v[k];
+                    dr.v[k] = g.vac * mr;
+                    di.v[k] = g.vac * mi;
+                    const float bs = gm.v[k] * g.vac;
+                    sr.v[k] = (1.0f - g.vac) * mr + bs * g.inj_r;
+                    si.v[k] = (1.0f - g.vac) * mi + bs * g.inj_i;
                 }
-                float* orow = obase + (size_t)(tw + u) * 4 * C;
+                float* orow = obase + (size_t)t * 4 * C;
                 vec_store_stream<4>(orow, sr);
                 vec_store_stream<4>(orow + C, si);
                 vec_store_stream<4>(orow + 2 * C, dr);
                 vec_store_stream<4>(orow + 3 * C, di);
             }
+        }
+    }
+
+    // Sweep 2 of one warp: its steps first to last from its entering state, two chunks in
+    // flight, no block barrier anywhere.
+    FL_HD static void sweep2_warp(const Params& p, const Item& it, int thread, float* smem) {
+        const SpanShape& s = p.s;
+        const int lane = thread & 31, warp = thread >> 5;
+        const int C = s.C;
+        const int c0 = it.cg * kGroup + lane * 4;
+        int wlo, whi;
+        warp_steps(it, warp, wlo, whi);
+        if (c0 >= C || wlo >= whi) return;
+        const Vec<4> lr = vec_load<4>(p.tr + c0);
+        const Vec<4> li = vec_load<4>(p.ti + c0);
+        const Vec<4> gm = vec_load<4>(p.gamma + c0);
+        Vec<4> sr = vec_load<4>(carry_at(smem, warp, 0) + lane * 4);
+        Vec<4> si = vec_load<4>(carry_at(smem, warp, 1) + lane * 4);
+        const float* base = p.raw + ((size_t)it.b * s.L) * 3 * C + c0;
+        float* obase = p.read + ((size_t)it.b * s.L) * 4 * C + c0;
+        Chunk a, b;
+        int t0 = wlo;
+        chunk_load<false>(a, base, C, t0, wlo, whi);
+        while (t0 < whi) {
+            chunk_load<false>(b, base, C, t0 + CH, wlo, whi);
+            chunk_emit(a, sr, si, lr, li, gm, obase, C, t0, wlo, whi);
+            t0 += CH;
+            if (t0 >= whi) break;
+            chunk_load<false>(a, base, C, t0 + CH, wlo, whi);
+            chunk_emit(b, sr, si, lr, li, gm, obase, C, t0, wlo, whi);
+            t0 += CH;
         }
     }
 
@@ -496,18 +509,15 @@ struct FwdSpanSweep {
     template <class Exec>
     FL_HD static void run_block(const Params& p, int block, float* smem, Exec& ex) {
         const SpanShape& s = p.s;
+        // A block with one item keeps its warps' maps in shared memory from sweep 1 to sweep 2;
+        // otherwise (more items than blocks; the host emulation, which runs the parts apart)
+        // the second part composes them again, from L2.
+        const bool keeps_maps = s.items <= ex.blocks() && p.stages == 3;
         if (p.stages & 1) {
             for (int item = block; item < s.items; item += ex.blocks()) {
                 const Item it = decode(s, item);
-                ex.run([&](int t, State& st) { st.run = affine_identity(); });
-                for (int q = it.tiles - 1; q >= 0; --q) {
-                    ex.all([&](int t, State& st) {
-                        tile_load<false>(p, it, q, t, st);
-                        tile_compose(p, it, q, t, smem, st);
-                    });
-                    ex.all([&](int t, State& st) { fold_tile(p, it, t, smem, st); });
-                }
-                ex.all([&](int t, State& st) { publish_run(p, item, t, st); });
+                ex.all([&](int t, State&) { sweep1_warp(p, it, t, smem); });
+                ex.all([&](int t, State&) { publish_run(p, item, it, t, smem); });
                 ex.run([&](int t, State&) { arrive(p, it, t); });
             }
         }
@@ -515,36 +525,13 @@ struct FwdSpanSweep {
             for (int item = block; item < s.items; item += ex.blocks()) {
                 if (p.emu_round >= 0 && item != block + p.emu_round * ex.blocks()) continue;
                 const Item it = decode(s, item);
-                // The first tile of sweep 2 - loads and gate arithmetic, parked in shared memory -
-                // comes before the waiting; thread 0 then waits for the chain.
-                ex.all([&](int t, State& st) {
-                    if (p.stages & 2) {
-                        tile_load<true>(p, it, 0, t, st);
-                        tile_compose(p, it, 0, t, smem, st);
-                        stash(smem, t, st);
-                    }
-                    wait_chain(p, it, t, smem);
-                });
+                if (!keeps_maps && (p.stages & 2)) ex.run([&](int t, State&) { sweep1_warp(p, it, t, smem); });
+                ex.all([&](int t, State&) { wait_chain(p, it, t, smem); });
                 ex.all([&](int t, State&) { prefix_shares(p, it, t, smem); });
-                ex.run([&](int t, State&) { prefix_join(p, item, it, t, smem); });
+                ex.all([&](int t, State&) { prefix_join(p, item, it, t, smem); });
                 if (!(p.stages & 2)) continue;  // host emulation: every rank sends before any waits
-                for (int q = 0; q < it.tiles; ++q) {
-                    if (q > 0) {
-                        ex.all([&](int t, State& st) {
-                            tile_load<true>(p, it, q, t, st);
-                            tile_compose(p, it, q, t, smem, st);
-                        });
-                    } else {
-                        ex.all([&](int t, State& st) {
-                            enter_run(p, it, t, smem);
-                            unstash(smem, t, st);
-                        });
-                    }
-                    ex.all([&](int t, State&) { carries(p, it, q, t, smem); });
-                    // no barrier after the stores: the next tile's loads only write the map area,
-                    // which nobody reads before the barrier that follows them
-                    ex.run([&](int t, State& st) { emit(p, it, q, t, smem, st); });
-                }
+                ex.all([&](int t, State&) { enter_run(p, it, t, smem); });
+                ex.all([&](int t, State&) { sweep2_warp(p, it, t, smem); });
             }
         }
     }

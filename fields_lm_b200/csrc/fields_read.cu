@@ -649,7 +649,7 @@ static bool walk_wanted(int, int, Algo algo) { return algo == kAlgoWalk; }
 // ---------------------------------------------------------------------------
 // Sequence-sharded forward in one launch (field_span.cuh): plan.
 // ---------------------------------------------------------------------------
-using SpanFwd = FwdSpanSweep<6, 8, 2>;   // tile 48 steps, 8 warps
+using SpanFwd = FwdSpanSweep<2, 8, 2>;   // chunks of 2 steps (two in flight per warp), 8 warps, 2 blocks per SM
 constexpr int kSpanMaxItems = 1024;       // runs per launch over all chains (unless there are more chains)
 
 static long long span_item_bound(int B, int C) {
@@ -664,15 +664,13 @@ static SpanShape make_span_shape(int B, int L, int C, int grid) {
     s.B = B; s.L = L; s.C = C;
     s.G = (C + kGroup - 1) / kGroup;
     s.chains = B * s.G;
-    const int tiles = (L + K::kTile - 1) / K::kTile;
     long long want = grid / s.chains;
     const long long cap = span_item_bound(B, C) / s.chains;
     if (want > cap) want = cap;
-    if (want > tiles) want = tiles;
+    if (want > (L + K::kRunQuantum - 1) / K::kRunQuantum) want = (L + K::kRunQuantum - 1) / K::kRunQuantum;
     if (want < 1) want = 1;
-    const int slice = K::kTile / 8 > 0 ? K::kTile / 8 : 1;   // run lengths in eighths of a tile
     int steps = (int)((L + want - 1) / want);
-    steps = (steps + slice - 1) / slice * slice;
+    steps = (steps + K::kRunQuantum - 1) / K::kRunQuantum * K::kRunQuantum;
     s.run_steps = steps;
     s.R = (L + steps - 1) / steps;
     s.items = s.chains * s.R;
