@@ -598,6 +598,7 @@ def decode_leg(device, tr, ti, gamma, peak_gbs: float, iters: int = 200):
         graph.replay()
     ms_graph = timed_loop(graph.replay, iters, stream) / iters
     nbytes = DECODE_BATCH * DECODE_BLOCKS * DECODE_BYTES_PER_SEQ_BLOCK
+    parity = decode_parity(device)
 
     def gbs(ms):
         return nbytes / (ms * 1e-3) / 1e9
@@ -606,7 +607,39 @@ def decode_leg(device, tr, ti, gamma, peak_gbs: float, iters: int = 200):
             "bytes_per_token_step": nbytes,
             "plain": {"ms": ms_plain, "achieved": gbs(ms_plain), "frac": gbs(ms_plain) / peak_gbs},
             "cuda_graph": {"ms": ms_graph, "achieved": gbs(ms_graph), "frac": gbs(ms_graph) / peak_gbs},
+            "parity": parity,
             "note": "3.9 MB per launch: launch-latency scale, far below what HBM could move"}
+
+
+def decode_parity(device, steps: int = 4, checked: int = 2):
+    """Decode at its stated size against the reference: ids -> embedding -> 18 reference Field
+    blocks (d_model 1,024, seed 0), batch 256, prefix 2,048, then `steps` single-token steps with
+    bf16 per-step inputs and fp32 carried states; the oracle is the reference's full-sequence
+    CPU pass (backend "reference") over prefix + steps tokens for the first `checked` sequences."""
+    from oracle import decode_stack, ref
+    if not ref.available():
+        return {"unavailable": ref.why_unavailable()}
+    try:
+        cpu, gpu = decode_stack.build_pair(device)
+        prefix = 2048
+        ids = decode_stack.token_ids(DECODE_BATCH, prefix + steps)
+        want_out, want_states = decode_stack.reference_full_pass(cpu, ids[:checked])
+        got, trail = decode_stack.prefill_then_steps(gpu, ids, prefix, autocast_steps=True)
+
+        def rel(a, b):
+            return float((a - b).abs().max() / b.abs().max().clamp_min(1e-6))
+        out = {"what": f"{DECODE_BLOCKS} reference Field blocks, batch {DECODE_BATCH}, prefix "
+                       f"{prefix}, {steps} steps under bf16 autocast vs the reference's fp32 CPU "
+                       f"full pass of the first {checked} sequences",
+               "step_output_rel": rel(got[:checked].cpu(), want_out[:, prefix:]),
+               "carried_state_rel": max(rel(st[:checked].cpu(), want_states[b][:, -1])
+                                        for b, st in enumerate(trail[-1])),
+               "tolerance": BF16_TOL}
+        del cpu, gpu, trail, got
+        torch.cuda.empty_cache()
+        return out
+    except Exception as exc:
+        return {"unavailable": f"decode parity failed: {exc!r}"[:400]}
 
 
 class SpanOps:
@@ -682,6 +715,62 @@ def span_leg(device, stream, tr, ti, gamma, iters: int = 50):
         out[f"{tokens}_tokens"] = row
         del ops
     return out
+
+
+class TensorExperiment:
+    """The tcgen05 restatement of the bfloat16 forward (an experiment, not the production path)
+    beside the production bfloat16 forward kernel, on the training shape."""
+
+    def __init__(self, device, tr, ti, gamma):
+        from fields_lm_b200 import _lib
+        self.lib = _lib.load()
+        self.par = (tr, ti, gamma)
+        self.raw16 = synthetic_inputs(1, B, L)[0].to(device).bfloat16()
+        self.read_tc = torch.empty(B, L, 4 * C, device=device, dtype=torch.bfloat16)
+        self.read_sp = torch.empty(B, L, 4 * C, device=device, dtype=torch.bfloat16)
+        self.err = torch.zeros(1, dtype=torch.int32, device=device)
+        self.n = self.lib.fields_read_workspace_bytes(B, L, C, 0)
+        self.ws = torch.empty(max(self.n, 256), dtype=torch.uint8, device=device)
+        self.st = torch.cuda.current_stream(device).cuda_stream
+
+    def tensor(self):
+        tr, ti, gm = self.par
+        rc = self.lib.fields_read_forward_bf16_tensor(
+            self.raw16.data_ptr(), tr.data_ptr(), ti.data_ptr(), gm.data_ptr(), None,
+            self.read_tc.data_ptr(), None, self.err.data_ptr(), B, L, C, self.st)
+        if rc:
+            raise RuntimeError(f"fields_read_forward_bf16_tensor status {rc}")
+
+    def single_pass(self):
+        tr, ti, gm = self.par
+        rc = self.lib.fields_read_forward_bf16(
+            self.raw16.data_ptr(), tr.data_ptr(), ti.data_ptr(), gm.data_ptr(), None,
+            self.read_sp.data_ptr(), None, self.ws.data_ptr(), self.n, B, L, C, self.st)
+        if rc:
+            raise RuntimeError(f"fields_read_forward_bf16 status {rc}")
+
+
+def tensor_leg(device, stream, tr, ti, gamma, iters: int = 50):
+    """Times the tcgen05 experiment against the production bfloat16 forward (8 x 2,048 tokens)."""
+    try:
+        ex = TensorExperiment(device, tr, ti, gamma)
+        out = {"what": "forward of 8 x 2,048 tokens on the bfloat16 boundary: the prefix-ratio "
+                       "contraction on tcgen05 (experiment) beside the production single-pass kernel; "
+                       "its 2 x 128 x 128 x 64 flop per 128-step tile and 32 channels are "
+                       f"{2 * 128 * 128 * 64 * (L // 128) * B * (C // 32) / 1e9:.1f} GFLOP per call"}
+        for name, fn in (("tcgen05_ms", ex.tensor), ("single_pass_ms", ex.single_pass)):
+            for _ in range(3):
+                fn()
+            out[name] = timed_loop(fn, iters, stream) / iters
+        out["status"] = int(ex.err.item())
+        out["rel_vs_single_pass"] = float((ex.read_tc.float() - ex.read_sp.float()).abs().max() /
+                                          ex.read_sp.float().abs().max())
+        out["tolerance"] = BF16_TOL
+        flop = 2 * 128 * 128 * 64 * (L // 128) * B * (C // 32)
+        out["tensor_tflops_if_only_mma"] = flop / (out["tcgen05_ms"] * 1e-3) / 1e12
+        return out
+    except Exception as exc:
+        return {"unavailable": repr(exc)[:300]}
 
 
 def timed_loop(fn, steps: int, stream) -> float:
@@ -802,6 +891,16 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         op.backward(raw_d, tr_d, ti_d, gm_d, grad_read)
     for _ in range(max(args.warmup, 3)):
         step()
+    if args.profile_tensor:
+        # profiler capture of the tcgen05 experiment beside the production bf16 forward
+        ex = TensorExperiment(device, tr_d, ti_d, gm_d)
+        for _ in range(2 + args.steps):
+            ex.tensor()
+            ex.single_pass()
+        torch.cuda.synchronize()
+        print(f"profile run: {args.steps} tensor-experiment and single-pass bf16 forwards, "
+              f"status {int(ex.err.item())}")
+        return
     if args.profile_span:
         # profiler capture of the one-launch sharded forward on one span, no peers, no JSON line
         ops = SpanOps(device, args.profile_span, tr_d, ti_d, gm_d)
@@ -996,6 +1095,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     decode = decode_leg(device, tr_d, ti_d, gm_d, peak_gbs=measured_peaks()[0]) if not dist_on else None
     block = block_leg(device, stream) if not dist_on else None
     spans = span_leg(device, stream, tr_d, ti_d, gm_d) if not dist_on else None
+    tensor = tensor_leg(device, stream, tr_d, ti_d, gm_d) if not dist_on else None
     # the reference's Triton kernels on this GPU, same tensors (rank 0's GPU only)
     triton = None
     if rank == 0 and not args.no_triton:
@@ -1101,6 +1201,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "decode_step": decode,
         "field_block": block,
         "sharded_span_one_gpu": spans,
+        "tcgen05_experiment": tensor,
         "triton_reference": triton,
         "full_model": full_model,
         "gpu_launches": KERNEL_LAUNCHES_PER_STEP * args.steps,
@@ -1130,6 +1231,8 @@ def main():
                     help="time plain launches instead of a CUDA graph of the step")
     ap.add_argument("--block-breakdown", action="store_true",
                     help="print the kernel-time table of one fused mixer step and exit")
+    ap.add_argument("--profile-tensor", action="store_true",
+                    help="run only the tcgen05 experiment and the bf16 single-pass forward (for ncu)")
     ap.add_argument("--profile-span", type=int, default=0, metavar="TOKENS",
                     help="run only the one-launch sharded forward on a span of TOKENS (for ncu)")
     ap.add_argument("--profile", action="store_true",

@@ -25,6 +25,7 @@ SYMBOLS = {
     "fields_read_state_rows": (_I, [_I]),
     "fields_read_backward_from_states": (_I, [_P] * 14 + [_SZ, _I, _I, _I, _P]),
     "fields_read_forward_bf16": (_I, [_P] * 8 + [_SZ, _I, _I, _I, _P]),
+    "fields_read_forward_bf16_tensor": (_I, [_P] * 8 + [_I, _I, _I, _P]),
     "fields_read_forward_bf16_stats": (_I, [_P] * 9 + [_SZ, _I, _I, _I, _P]),
     "fields_read_backward_bf16": (_I, [_P] * 14 + [_SZ, _I, _I, _I, _P]),
     "fields_read_device_status": (_I, [_P, _P]),

@@ -11,6 +11,7 @@
 #include "field_singlepass.cuh"
 #include "field_walk.cuh"
 #include "field_span.cuh"
+#include "field_tensor.cuh"
 #include "field_epilogue.cuh"
 
 #include "../../include/fields_read.h"
@@ -1325,6 +1326,33 @@ int fields_read_fold_mailbox_backward(const void* mailbox, const float* carry_en
     const long long n = (long long)B * C;
     return launch<FoldMailbox>(p, (n + FoldMailbox::kThreads - 1) / FoldMailbox::kThreads,
                                reinterpret_cast<Stream>(stream));
+}
+
+int fields_read_forward_bf16_tensor(const void* raw, const float* tr, const float* ti,
+                                    const float* gamma, const float* state_in, void* read,
+                                    float* state_out, unsigned* error_word, int B, int L, int C,
+                                    void* stream) {
+    if (B < 0 || L <= 0 || C <= 0) return FIELDS_ERR_ARGUMENT;
+    if (B == 0) return FIELDS_OK;
+    if (!raw || !read || !tr || !ti || !gamma || !error_word) return FIELDS_ERR_ARGUMENT;
+    if (C % 4 || !aligned8(raw) || !aligned8(read)) return FIELDS_ERR_UNSUPPORTED;
+    TensorFwdParams p{static_cast<const uint16_t*>(raw), tr, ti, gamma, state_in,
+                      static_cast<uint16_t*>(read), state_out, error_word, B, L, C, kMaxPolls};
+    const long long grid = (long long)B * ((C + kTcChannels - 1) / kTcChannels);
+    if (grid > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
+#ifdef FIELDS_HOST_EMU
+    (void)stream;
+    std::vector<double> store(kTcSmemBytesEmu / 8 + 2);
+    for (long long block = 0; block < grid; ++block)
+        FwdTensorChain::run_block_emu(p, (int)block, reinterpret_cast<char*>(store.data()));
+    return FIELDS_OK;
+#else
+    static bool ready[64] = {};
+    const int rc = allow_shared_memory(tensor_chain_entry, (size_t)kTcSmemBytes, ready);
+    if (rc) return rc;
+    return launch_on<TensorFwdParams>(tensor_chain_entry, (unsigned)grid, kTcThreads, kTcSmemBytes,
+                                      reinterpret_cast<Stream>(stream), p);
+#endif
 }
 
 #ifdef FIELDS_HOST_EMU

@@ -146,6 +146,26 @@ int fields_read_backward_bf16(const void *raw, const float *tr, const float *ti,
                               size_t workspace_bytes, int B, int L, int C, void *stream);
 
 /*
+ * EXPERIMENT, not the production path: the forward of fields_read_forward_bf16 with the
+ * intra-chunk part of the recurrence computed as a dense contraction on the tensor cores
+ * (tcgen05.mma, bf16 operands from shared memory, fp32 accumulator in tensor memory). No
+ * counterpart in the reference, whose kernels use no tensor-core instruction
+ * (field_only_v4_chunked_triton_wiki100.py:443-909). Inside sub-chunks of 16 steps the state is
+ * s_t = P_t (s_in + sum_{j<=t} b_j / P_j) with P the prefix product of the per-step complex
+ * decays; the sum over j is a product with a lower-triangular all-ones matrix shared by every
+ * channel. The quotients are rounded to bfloat16, so the result meets the bfloat16 tolerance
+ * (2e-2 relative) only. One CTA walks a (batch row, 32 channels) chain in tiles of 128 steps;
+ * its elementwise work equals the scan's, so it is no faster - it exists to put a measured
+ * tensor-pipe utilisation beside the scan kernels. Same tensors as fields_read_forward_bf16;
+ * no workspace. error_word: a device word the caller zeroed, set to 1 if a bounded wait for the
+ * tensor cores ran out. C % 4 == 0, 8-byte aligned raw / read (FIELDS_ERR_UNSUPPORTED otherwise).
+ */
+int fields_read_forward_bf16_tensor(const void *raw, const float *tr, const float *ti,
+                                    const float *gamma, const float *state_in, void *read,
+                                    float *state_out, unsigned *error_word, int B, int L, int C,
+                                    void *stream);
+
+/*
  * Sequence sharding (no counterpart in the reference, which runs a sequence on one GPU;
  * the arithmetic is the chunk-summary composition of
  * field_only_v4_chunked_triton_wiki100.py:503-509 and :539-550 applied to a whole span).

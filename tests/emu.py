@@ -406,3 +406,24 @@ class ShardedForward:
         if rc:
             raise RuntimeError(lib().fields_status_string(rc).decode())
         return self
+
+
+def forward_bf16_tensor(raw_bits, tr, ti, gamma, state_in=None):
+    """The tensor-core experiment's forward with the contraction emulated by a plain loop over the
+    same shared-memory operand layouts. Returns (read bits, state_out, error word)."""
+    B, L, C3 = raw_bits.shape
+    C = tr.size
+    raw_a = _u16(raw_bits)
+    a = [_f32(x) for x in (tr, ti, gamma)]
+    s_in = None if state_in is None else _f32(state_in)
+    read = _u16(np.zeros((B, L, 4 * C), np.uint16), fill=0x7FC0)
+    state = _f32(np.full((B, 2 * C), np.nan))
+    err = np.zeros(1, dtype=np.uint32)
+    fn = lib().fields_read_forward_bf16_tensor
+    fn.argtypes = [P] * 8 + [I, I, I, P]
+    fn.restype = I
+    rc = fn(_ptr(raw_a), _ptr(a[0]), _ptr(a[1]), _ptr(a[2]), _ptr(s_in), _ptr(read), _ptr(state),
+            _ptr(err), B, L, C, None)
+    if rc:
+        raise RuntimeError(lib().fields_status_string(rc).decode())
+    return read, state, int(err[0])

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 import emu
-from conftest import FP32_TOL, rel_err
+from conftest import BF16_TOL, FP32_TOL, rel_err
 from oracle import field_oracle
 
 
@@ -446,3 +446,22 @@ def test_sharded_forward_reports_a_missing_summary():
     for stage in (1, 4, 2):  # rank 0 never stored its summary
         late.run(stage, 1)
     assert int(late.err[0]) == 1 and np.isnan(late.read).all() and np.isnan(late.state).all()
+
+
+@pytest.mark.parametrize("B,L,C", [(1, 300, 32), (2, 130, 20), (1, 128, 64), (2, 17, 36)])
+def test_tensor_core_formulation_of_the_forward(B, L, C):
+    """The prefix-ratio restatement (sub-chunks of 16 steps, quotients b / P rounded to bfloat16,
+    summed by a triangular all-ones matrix) with the contraction emulated over the operand
+    layouts the tensor cores read: within the bfloat16 tolerance of the oracle, including
+    saturated vacancy gates (|a| at its minimum, where 1 / |P| is largest)."""
+    rng = np.random.default_rng(B * 100 + L + C)
+    tr, ti, gm = _params(C, rng)
+    raw = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+    raw[:, L // 3: L // 3 + 40, 2 * C:] = 30.0      # vacancy saturated for a stretch
+    raw_b = _bits(raw)
+    s0 = rng.standard_normal((B, 2 * C)).astype(np.float32)
+    ref_read, ref_state = field_oracle.forward(_unbits(raw_b), tr, ti, gm, state_in=s0)
+    read_b, state, err = emu.forward_bf16_tensor(raw_b, tr, ti, gm, state_in=s0)
+    assert err == 0
+    assert rel_err(_unbits(read_b), ref_read) < BF16_TOL
+    assert rel_err(state, ref_state) < BF16_TOL
