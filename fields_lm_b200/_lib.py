@@ -58,6 +58,16 @@ class FieldsLibraryError(RuntimeError):
     """The CUDA library is missing or a call into it returned a non-zero status."""
 
 
+def open_library(path: Path) -> ctypes.CDLL:
+    """Opens a build of the library and declares every symbol of the C ABI on it."""
+    lib = ctypes.CDLL(str(path))
+    for name, (restype, argtypes) in SYMBOLS.items():
+        fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
 def load() -> ctypes.CDLL:
     global _lib
     if _lib is not None:
@@ -66,13 +76,8 @@ def load() -> ctypes.CDLL:
         raise FieldsLibraryError(
             f"{LIB_PATH.name} has not been built; run `python -m fields_lm_b200.build` "
             "(needs nvcc). There is no CPU fallback for the Field kernels.")
-    lib = ctypes.CDLL(str(LIB_PATH))
-    for name, (restype, argtypes) in SYMBOLS.items():
-        fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
-        fn.restype = restype
-        fn.argtypes = argtypes
-    _lib = lib
-    return lib
+    _lib = open_library(LIB_PATH)
+    return _lib
 
 
 def check(status: int, what: str) -> None:

@@ -37,19 +37,37 @@ def is_stale() -> bool:
     return LIB.stat().st_mtime < newest
 
 
-def build_library(force: bool = False, verbose: bool = False) -> Path:
-    if not force and not is_stale():
-        return LIB
-    cmd = [_nvcc(), *NVCC_FLAGS]
+def _compile(out: Path, extra, verbose: bool) -> Path:
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", str(LIB), *map(str, SOURCES)]
+    out.parent.mkdir(parents=True, exist_ok=True)
+    cmd += ["-o", str(out), *map(str, SOURCES)]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if verbose:
         print(proc.stderr)
     if proc.returncode:
         raise RuntimeError("nvcc failed:\n" + proc.stderr)
-    return LIB
+    return out
+
+
+def build_library(force: bool = False, verbose: bool = False) -> Path:
+    if not force and not is_stale():
+        return LIB
+    return _compile(LIB, [], verbose)
+
+
+# The test build: the same library plus the measured alternatives (other tile shapes, two-sweep
+# forward, tile-resident backward, chain walkers, vectorised three-phase kernels), selected per
+# call through environment variables. Only the GPU tests load it; it lives under tests/.
+VARIANTS_LIB = PKG.parent / "tests" / "_variants" / "libfields_read_variants.so"
+
+
+def build_variants(force: bool = False, verbose: bool = False) -> Path:
+    newest = max(p.stat().st_mtime for p in SOURCES + HEADERS)
+    if not force and VARIANTS_LIB.exists() and VARIANTS_LIB.stat().st_mtime >= newest:
+        return VARIANTS_LIB
+    return _compile(VARIANTS_LIB, ["-DFIELDS_ALL_VARIANTS"], verbose)
 
 
 if __name__ == "__main__":

@@ -9,7 +9,9 @@
 // test infrastructure; it is never loaded by the package.
 #include "field_kernels.cuh"
 #include "field_singlepass.cuh"
+#ifdef FIELDS_ALL_VARIANTS
 #include "field_walk.cuh"
+#endif
 #include "field_span.cuh"
 #include "field_tensor.cuh"
 #include "field_epilogue.cuh"
@@ -171,14 +173,19 @@ __device__ __forceinline__ void wait_for_previous_kernel() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
+static bool dependent_launch_from_env() {
+    const char* e = std::getenv("FIELDS_READ_PDL");
+    return !(e && e[0] == '0');
+}
+#ifdef FIELDS_ALL_VARIANTS
+static bool dependent_launch_enabled() { return dependent_launch_from_env(); }  // test build: per call
+#else
 // (the environment is read once, at the first launch)
 static bool dependent_launch_enabled() {
-    static const bool enabled = [] {
-        const char* e = std::getenv("FIELDS_READ_PDL");
-        return !(e && e[0] == '0');
-    }();
+    static const bool enabled = dependent_launch_from_env();
     return enabled;
 }
+#endif
 
 template <class K>
 __global__ void __launch_bounds__(K::kThreads) kernel_entry(const typename K::Params p) {
@@ -531,8 +538,14 @@ static SpPlan make_sp_plan(int B, int L, int C, int tile_steps) {
 
 enum Algo { kAlgoAuto = 0, kAlgoThreePhase = 1, kAlgoSinglePass = 2, kAlgoWalk = 3 };
 
-// FIELDS_READ_ALGO = three_phase | single_pass | walk selects the kernels (default: single pass
-// whenever 16-byte accesses are possible, else three-phase). FIELDS_FWD_VARIANT / FIELDS_BWD_VARIANT pick a tuning alternative.
+// The product library runs one kernel family: single pass wherever 128-bit accesses are
+// possible, the scalar three-phase kernels otherwise. The measured alternatives (other tile
+// shapes, the two-sweep forward, the direct-load and tile-resident backward, the chain walkers,
+// the vectorised three-phase kernels, L2 prefetch) are compiled only into the test build
+// (FIELDS_ALL_VARIANTS), which picks them per call from the environment:
+//   FIELDS_READ_ALGO = three_phase | single_pass | walk, FIELDS_FWD_VARIANT, FIELDS_BWD_VARIANT,
+//   FIELDS_READ_PREFETCH.
+#ifdef FIELDS_ALL_VARIANTS
 static Algo algo_from_env() {
     const char* e = std::getenv("FIELDS_READ_ALGO");
     if (!e) return kAlgoAuto;
@@ -542,21 +555,30 @@ static Algo algo_from_env() {
     if (v == "walk") return kAlgoWalk;
     return kAlgoAuto;
 }
+#else
+static Algo algo_from_env() { return kAlgoAuto; }
+#endif
 
 // Instantiations of the single-pass kernels. The first of each list is the default; the
 // others are tuning alternatives selected with FIELDS_FWD_VARIANT / FIELDS_BWD_VARIANT.
 //   forward  <steps per warp, warps, blocks per SM the registers must allow>
 using FwdSp0 = FwdSinglePass<6, 8, 2>;        // tile 48 steps, 128 registers, no spills
+#ifdef FIELDS_ALL_VARIANTS
 using FwdSp1 = FwdSinglePass<4, 8, 2>;        // tile 32
 //   two-sweep forward <steps per warp, warps, unroll, blocks per SM, ring slots>
 using FwdSp2 = FwdTwoSweep<8, 4, 2, 4, 3>;    // tile 32, 16 warps per SM
+#endif
 //   backward <steps per warp, warps, sweep-1 unroll, sweep-2 unroll, blocks per SM, rings, ring slots>
 using BwdSp0 = BwdSinglePass<8, 4, 2, 1, 3, true, 3>;  // tile 32, 3-slot cp.async rings, 12 warps per SM
+#ifdef FIELDS_ALL_VARIANTS
 using BwdSp1 = BwdSinglePass<8, 4, 2, 1, 4>;           // direct loads, 16 warps per SM
+#endif
 //   backward with recomputed states <steps per warp, warps, steps per ring slot, blocks per SM, ring slots>
 using BwdSp2 = BwdRecompute<8, 4, 1, 3, 2>;   // 73 KB per block, 12 warps per SM
 //   tile resident in shared memory, recomputed states <steps per warp, warps, blocks per SM>
+#ifdef FIELDS_ALL_VARIANTS
 using BwdSp3 = BwdTileResident<4, 4, 3>;      // tile 16, 68 KB per block, 12 warps per SM
+#endif
 //   bfloat16 raw / read / grad_read / grad_raw (bits as uint16_t); state and arithmetic stay fp32
 using FwdSpBf16 = FwdSinglePass<6, 8, 2, uint16_t>;
 using FwdSpBf16Stats = FwdSinglePass<6, 8, 2, uint16_t, true>;  // also writes per-token sums of squares
@@ -564,19 +586,25 @@ using BwdSpBf16 = BwdSinglePass<8, 4, 2, 1, 3, true, 3, uint16_t>;
 constexpr int kSpMinTile = 32;     // smallest time tile of any forward instantiation above (workspace bound)
 constexpr int kSpMinTileBwd = 16;  // same for the backward
 
+#ifdef FIELDS_ALL_VARIANTS
 static int variant_from_env(const char* name) {
     const char* e = std::getenv(name);
     return e ? std::atoi(e) : 0;
 }
+#endif
 
-// FIELDS_READ_PREFETCH = 1 switches the L2 prefetch of the single-pass kernels on (distance =
-// number of resident blocks); any larger number sets the distance. Default: off - it gained
-// 5 to 9 % on the batch-8 forward and lost as much on the backward and on long sequences.
+// L2 prefetch of the next tile (test build: FIELDS_READ_PREFETCH = 1 for a distance of the
+// number of resident blocks, a larger number for that distance). It gained 5 to 9 % on the
+// batch-8 forward and lost as much on the backward and on long sequences: off in the product.
+#ifdef FIELDS_ALL_VARIANTS
 static int prefetch_from_env(int resident) {
     const char* e = std::getenv("FIELDS_READ_PREFETCH");
     const int v = e ? std::atoi(e) : 0;
     return v == 1 ? resident : (v > 1 ? v : 0);
 }
+#else
+static int prefetch_from_env(int) { return 0; }
+#endif
 
 template <class K, typename IO = float>
 static int run_forward_single_pass(const IO* raw, const float* tr, const float* ti,
@@ -630,6 +658,7 @@ static size_t sp_backward_bytes(int B, int L, int C, int tile_steps) {
     return pl.bytes + (size_t)3 * B * pl.s.NT * C * sizeof(float);
 }
 
+#ifdef FIELDS_ALL_VARIANTS
 // ---------------------------------------------------------------------------
 // Chain walkers: one block per (batch row, 32 channels) walks the whole sequence, no
 // inter-block communication, bitwise reproducible. Measured slower than the single-pass
@@ -646,6 +675,8 @@ static WalkShape walk_shape(int B, int L, int C) {
 }
 
 static bool walk_wanted(int, int, Algo algo) { return algo == kAlgoWalk; }
+
+#endif  // FIELDS_ALL_VARIANTS
 
 // ---------------------------------------------------------------------------
 // Sequence-sharded forward in one launch (field_span.cuh): plan.
@@ -800,26 +831,35 @@ int fields_read_forward(const float* raw, const float* tr, const float* ti, cons
         (reinterpret_cast<uintptr_t>(workspace) & 255u))
         return FIELDS_ERR_WORKSPACE;
     const Algo algo = algo_from_env();
+#ifdef FIELDS_ALL_VARIANTS
     if (vec4 && walk_wanted(B, C, algo)) {
         WalkFwdParams wp{raw, tr, ti, gamma, state_in, read, state_out,
                          walk_shape<FwdWalker>(B, L, C)};
         return launch_walk<FwdWalker>(wp, (long long)B * wp.s.G, st);
     }
+#endif
     if (vec4 && algo != kAlgoThreePhase) {
 #define FIELDS_FWD_SP(K)                                                                      \
     return run_forward_single_pass<K>(raw, tr, ti, gamma, state_in, read, state_out, workspace, \
                                       B, L, C, st)
+#ifdef FIELDS_ALL_VARIANTS
         switch (variant_from_env("FIELDS_FWD_VARIANT")) {
             case 1: FIELDS_FWD_SP(FwdSp1);
             case 2: FIELDS_FWD_SP(FwdSp2);
             default: FIELDS_FWD_SP(FwdSp0);
         }
+#else
+        FIELDS_FWD_SP(FwdSp0);
+#endif
 #undef FIELDS_FWD_SP
     }
     float* ws = static_cast<float*>(workspace);
     FwdParams p{raw, tr, ti, gamma, state_in, read, state_out,
                 ws + pl.sum_off, ws + pl.carry_off, pl.s};
-    return vec4 ? run_forward<4>(p, st) : run_forward<1>(p, st);
+#ifdef FIELDS_ALL_VARIANTS
+    if (vec4) return run_forward<4>(p, st);
+#endif
+    return run_forward<1>(p, st);
 }
 
 int fields_read_backward(const float* raw, const float* tr, const float* ti, const float* gamma,
@@ -860,6 +900,7 @@ int fields_read_backward(const float* raw, const float* tr, const float* ti, con
         workspace_bytes < fields_read_workspace_bytes(B, L, C, FIELDS_PASS_BACKWARD) ||
         (reinterpret_cast<uintptr_t>(workspace) & 255u))
         return FIELDS_ERR_WORKSPACE;
+#ifdef FIELDS_ALL_VARIANTS
     if (vec4 && walk_wanted(B, C, algo_from_env())) {
         float* partial = static_cast<float*>(workspace);
         WalkBwdParams wp{raw, tr, ti, gamma, state_in, read, grad_read, grad_state_out, grad_raw,
@@ -872,24 +913,32 @@ int fields_read_backward(const float* raw, const float* tr, const float* ti, con
         rp.s = Shape{B, L, C, L, 1, wp.s.G};
         return launch<BwdReduce>(rp, 3LL * ((C + 31) / 32), st);
     }
+#endif
     if (vec4 && algo_from_env() != kAlgoThreePhase) {
 #define FIELDS_BWD_SP(K)                                                                        \
     return run_backward_single_pass<K>(raw, tr, ti, gamma, state_in, read, grad_read,          \
                                        grad_state_out, grad_raw, grad_tr, grad_ti, grad_gamma, \
                                        grad_state_in, workspace, B, L, C, st)
+#ifdef FIELDS_ALL_VARIANTS
         switch (variant_from_env("FIELDS_BWD_VARIANT")) {
             case 1: FIELDS_BWD_SP(BwdSp1);
             case 2: FIELDS_BWD_SP(BwdSp2);
             case 3: FIELDS_BWD_SP(BwdSp3);
             default: FIELDS_BWD_SP(BwdSp0);
         }
+#else
+        FIELDS_BWD_SP(BwdSp0);
+#endif
 #undef FIELDS_BWD_SP
     }
     float* ws = static_cast<float*>(workspace);
     BwdParams p{raw, tr, ti, gamma, state_in, read, grad_read, grad_state_out, grad_raw,
                 grad_state_in, ws + pl.sum_off, ws + pl.carry_off, ws + pl.partial_off,
                 grad_tr, grad_ti, grad_gamma, pl.s};
-    return vec4 ? run_backward<4>(p, st) : run_backward<1>(p, st);
+#ifdef FIELDS_ALL_VARIANTS
+    if (vec4) return run_backward<4>(p, st);
+#endif
+    return run_backward<1>(p, st);
 }
 
 

@@ -38,3 +38,15 @@ def golden_small():
 @pytest.fixture(scope="session")
 def golden_config1():
     return np.load(GOLDEN / "config1.npz")
+
+
+@pytest.fixture
+def variants_library(monkeypatch):
+    """Routes the package through the test build of the CUDA library, which also holds the
+    measured kernel alternatives and picks them per call from FIELDS_READ_ALGO /
+    FIELDS_FWD_VARIANT / FIELDS_BWD_VARIANT / FIELDS_READ_PREFETCH / FIELDS_READ_PDL. The product
+    library reads none of these per call."""
+    from fields_lm_b200 import _lib, build
+    path = build.VARIANTS_LIB if build.VARIANTS_LIB.exists() else build.build_variants()
+    monkeypatch.setattr(_lib, "_lib", _lib.open_library(path))
+    return path

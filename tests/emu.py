@@ -29,7 +29,7 @@ def build() -> Path:
     if OUT.exists() and OUT.stat().st_mtime >= max(d.stat().st_mtime for d in deps):
         return OUT
     OUT.parent.mkdir(parents=True, exist_ok=True)
-    cmd = ["g++", "-x", "c++", "-std=c++17", "-O2", "-fPIC", "-shared", "-DFIELDS_HOST_EMU",
+    cmd = ["g++", "-x", "c++", "-std=c++17", "-O2", "-fPIC", "-shared", "-DFIELDS_HOST_EMU", "-DFIELDS_ALL_VARIANTS",
            "-Wall", "-Wno-unknown-pragmas", "-Wno-maybe-uninitialized", "-o", str(OUT), str(SRC)]
     subprocess.run(cmd, check=True)
     return OUT

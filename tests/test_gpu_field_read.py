@@ -15,9 +15,13 @@ from oracle import field_oracle
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=["walk", "single_pass", "three_phase"])
+@pytest.fixture(autouse=True, params=["product", "walk", "single_pass", "three_phase"])
 def algo(request, monkeypatch):
-    """Every test runs on both kernel families (the library reads the variable at each call)."""
+    """Every test runs on the product library and, through the test build of the same source
+    (which reads the variable at each call), on every kernel family."""
+    if request.param == "product":
+        return "single_pass"
+    request.getfixturevalue("variants_library")
     monkeypatch.setenv("FIELDS_READ_ALGO", request.param)
     return request.param
 
@@ -86,7 +90,7 @@ def test_library_is_loaded_from_the_tree():
     from fields_lm_b200 import _lib
     _lib.load()
     with open("/proc/self/maps") as f:
-        assert "libfields_read.so" in f.read()
+        assert "libfields_read" in f.read()
 
 
 def test_golden_small_cases(dev, golden_small):
@@ -121,11 +125,12 @@ def test_shape_sweep(dev, L, C):
 
 
 @pytest.mark.parametrize("variant", ["1", "2", "3"])
-def test_single_pass_alternatives(dev, algo, monkeypatch, variant):
+def test_single_pass_alternatives(dev, algo, monkeypatch, variant, request):
     """The selectable alternatives of the single-pass kernels (tile shapes, two-sweep forward,
     backward with recomputed states, tile-resident backward) against the oracle."""
     if algo != "single_pass":
         pytest.skip("variants exist for the single-pass kernels only")
+    request.getfixturevalue("variants_library")
     monkeypatch.setenv("FIELDS_FWD_VARIANT", variant)
     monkeypatch.setenv("FIELDS_BWD_VARIANT", variant)
     rng = np.random.default_rng(int(variant))
@@ -240,9 +245,9 @@ def test_backward_over_spans_equals_one_backward_pass(dev, C):
         assert rel_err(g_par[k], want[1 + k]) < FP32_TOL
 
 
-def test_ordinary_launches_give_the_same_results(dev, monkeypatch):
+def test_ordinary_launches_give_the_same_results(dev, monkeypatch, variants_library):
     """FIELDS_READ_PDL=0: plain launches and a memset instead of dependent launches and the fill
-    kernel."""
+    kernel (the test build reads the variable per call; the product library once)."""
     monkeypatch.setenv("FIELDS_READ_PDL", "0")
     rng = np.random.default_rng(77)
     B, L, C = 2, 300, 512
