@@ -89,10 +89,11 @@ def field_mixers(model):
 
 def set_triton_geometry(model, block_c: int, chunk_t: int) -> None:
     """Launch geometry of the reference's Triton kernels for every Field mixer. The reference
-    promoted 32/64 over 16/64 as "exact" in its own sweep
-    (``official_source/field_fusion_gap_closure_v33.py:4-6,38-41``); a different chunk length
-    composes the same recurrence in a different order, i.e. perturbs ``read`` at fp32 rounding
-    level. Running the reference against itself that way measures how far such a perturbation
+    treats its geometries as interchangeable ("exact", its own sweep:
+    ``official_source/field_fusion_gap_closure_v33.py:4-6,38-41``; candidates
+    ``official_source/field_fusion_gap_kernel_v32.py:836-847``). The channel block does not
+    touch the arithmetic; a different chunk length composes the same recurrence in a
+    different order, i.e. perturbs ``read`` at fp32 rounding level. Running the reference against itself that way measures how far such a perturbation
     travels through the 24 bf16 layers - the floor under any comparison of two exact kernels."""
     for m in field_mixers(model):
         m.triton_block_c, m.triton_chunk_t = int(block_c), int(chunk_t)
