@@ -608,9 +608,11 @@ struct BwdSinglePass {
     static constexpr int kCarryFloats = WARPS * 2 * kGroup;
     // ASYNC: every thread lands its next batches of inputs in a private ring of STAGES slots in shared
     // memory with cp.async while it computes on the current batch, so loads stay in flight
-    // without holding registers. A cell is one 16-byte vector of one thread.
+    // without holding registers. A cell is four elements of one thread: 16 bytes of float, 8 of
+    // bfloat16 (packed, so a warp's cells of one plane are contiguous in both cases).
+    static constexpr int kCellFloats = (int)sizeof(IO);
     static constexpr int kCells = U1_ * 5 > U2_ * 9 ? U1_ * 5 : U2_ * 9;
-    static constexpr int kRingFloats = ASYNC ? STAGES * kCells * 32 * WARPS * 4 : 0;
+    static constexpr int kRingFloats = ASYNC ? STAGES * kCells * 32 * WARPS * kCellFloats : 0;
     static constexpr int kSmemFloats = kSumFloats + kCarryFloats + kRingFloats;
     static constexpr int kClaimAfter = 2;
     FL_HD static constexpr bool barrier_after(int ph) { return ph != 1; }
@@ -627,7 +629,7 @@ struct BwdSinglePass {
     }
     FL_HD static float* cell_at(float* smem, int stage, int idx, int thread) {
         return smem + kSumFloats + kCarryFloats +
-               ((size_t)(stage * kCells + idx) * kThreads + thread) * 4;
+               ((size_t)(stage * kCells + idx) * kThreads + thread) * kCellFloats;
     }
     // Warms L2 with the first-sweep inputs (z_v, grad_read) of the tile this block takes next.
     FL_HD static void prefetch(const Params& p, int tile, int thread) {

@@ -93,7 +93,7 @@ FL_HD void async_copy16(float* smem_dst, const float* gmem_src) {
 #endif
 }
 
-// Four elements (16 bytes of float, 8 bytes of bf16) into a 16-byte shared-memory cell.
+// Four elements (16 bytes of float, 8 bytes of bf16) into a shared-memory cell aligned to its size.
 FL_HD void async_copy4(float* cell, const float* src) { async_copy16(cell, src); }
 
 FL_HD void async_copy4(float* cell, const uint16_t* src) {
