@@ -473,6 +473,48 @@ def triton_reference_leg(device, stream, raw, grad_read, tr, ti, gamma, steps, o
         return {"unavailable": f"reference Triton path failed on this box: {exc!r}"[:600]}
 
 
+def real_scan_leg(device, stream, steps: int):
+    """The softpatch mixer's scan at its size in the full model (8 x 2,048 tokens, rank 64, one
+    decay per token expanded over the channels), forward + backward through autograd: the
+    reference's `hierarchical_scan` (PyTorch ops on this GPU) and `fields_lm_b200.linear_scan`."""
+    import fields_lm_b200
+    from oracle import ref
+    if not ref.available():
+        return {"unavailable": ref.why_unavailable()}
+    canon = ref.load_canon()
+    gen = torch.Generator().manual_seed(5)
+    rank = 64
+    boundary0 = torch.rand(B, L, generator=gen).clamp(0.01, 0.99).to(device)
+    z0 = torch.randn(B, L, rank, generator=gen).to(device)
+    g = torch.randn(B, L, rank, generator=gen).to(device)
+    out = {"workload": f"hierarchical_scan(a, drive, block=32) forward + backward, a = 1 - boundary "
+                       f"expanded over {rank} channels, {B} x {L} tokens, fp32, through autograd"}
+    results = {}
+    for name, fn in (("reference_pytorch_ops", canon.hierarchical_scan),
+                     ("this_library", fields_lm_b200.linear_scan)):
+        boundary = boundary0.clone().requires_grad_(True)
+        z = z0.clone().requires_grad_(True)
+
+        def step():
+            boundary.grad = z.grad = None
+            a = (1.0 - boundary)[..., None].expand_as(z)
+            state = fn(a, boundary[..., None] * z, block=32)
+            state.backward(g)
+            return state
+        for _ in range(3):
+            step()
+        n = max(10, min(steps, 50))
+        out[name] = {"ms": timed_loop(step, n, stream) / n}
+        state = step()
+        results[name] = [state.detach(), boundary.grad.clone(), z.grad.clone()]
+    rel = [float((a - b).abs().max() / b.abs().max())
+           for a, b in zip(results["this_library"], results["reference_pytorch_ops"])]
+    out["parity_vs_reference"] = {"state_rel": rel[0], "grad_boundary_rel": rel[1],
+                                  "grad_z_rel": rel[2], "tolerance": FP32_TOL}
+    out["speedup"] = out["reference_pytorch_ops"]["ms"] / out["this_library"]["ms"]
+    return out
+
+
 def recurrence_kernel_share(step, device):
     """Share of one step's GPU kernel time spent in Field-recurrence kernels (torch profiler)."""
     from torch.profiler import ProfilerActivity, profile
@@ -515,7 +557,7 @@ def full_model_leg(device, stream, iters: int = 3):
         runs = {}
         for name in ("reference_triton_kernels", "operator_installed"):
             if name == "operator_installed":
-                fields_lm_b200.install(model)
+                fields_lm_b200.install(model, scan=True)   # Field read + the softpatch mixer's scan
             for _ in range(2):
                 step()
             ms = timed_loop(step, iters, stream) / iters
@@ -1102,6 +1144,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     block = block_leg(device, stream) if not dist_on else None
     spans = span_leg(device, stream, tr_d, ti_d, gm_d) if not dist_on else None
     tensor = tensor_leg(device, stream, tr_d, ti_d, gm_d) if not dist_on else None
+    real_scan = real_scan_leg(device, stream, args.steps) if not dist_on else None
     # the reference's Triton kernels on this GPU, same tensors (rank 0's GPU only)
     triton = None
     if rank == 0 and not args.no_triton:
@@ -1208,6 +1251,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "field_block": block,
         "sharded_span_one_gpu": spans,
         "tcgen05_experiment": tensor,
+        "real_scan": real_scan,
         "triton_reference": triton,
         "full_model": full_model,
         "gpu_launches": KERNEL_LAUNCHES_PER_STEP * args.steps,

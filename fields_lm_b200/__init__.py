@@ -9,7 +9,10 @@ Public surface:
 * :func:`field_read_step` - one recurrent step for incremental decoding;
 * :func:`fields_lm_b200.seqpar.sequence_parallel_field_read` - sequence-sharded forward;
 * :func:`install` / :func:`uninstall` - rebind the operator inside a built model;
-* :mod:`fields_lm_b200.mixer` - mirror of the reference's mixer/block modules;
+* :func:`linear_scan` - the reference's ``hierarchical_scan`` for real fp32 CUDA tensors
+  (the softpatch mixer's call site), :func:`install_scan` to put it in place;
+* :mod:`fields_lm_b200.mixer` - the fused mixer forward, prefill and single-token step on the
+  reference's own mixer / block objects;
 * :mod:`fields_lm_b200.build` - compiles the CUDA library.
 
 The CUDA library is required: nothing here falls back to a CPU or PyTorch path.
@@ -17,7 +20,8 @@ The CUDA library is required: nothing here falls back to a CPU or PyTorch path.
 from .decode import field_read_step
 from .field_read import (FieldReadFunction, field_read_with_state, fused_field_read,
                          fused_field_read_bf16, fused_field_read_bf16_stats)
-from .install import install, uninstall
+from .install import install, install_scan, uninstall
+from .scan import linear_scan, linear_scan_with_state
 
 __all__ = ["FieldReadFunction", "field_read_step", "field_read_with_state", "fused_field_read", "fused_field_read_bf16", "fused_field_read_bf16_stats", "install",
-           "uninstall"]
+           "install_scan", "linear_scan", "linear_scan_with_state", "uninstall"]

@@ -13,6 +13,7 @@ LIB_PATH = PKG / "libfields_read.so"
 _P = ctypes.c_void_p
 _I = ctypes.c_int
 _SZ = ctypes.c_size_t
+_LL = ctypes.c_longlong
 
 # name -> (restype, argtypes); every symbol include/fields_read.h declares
 SYMBOLS = {
@@ -32,6 +33,9 @@ SYMBOLS = {
     "fields_read_selftest_wait": (_I, [_P, _SZ, ctypes.c_uint, _P]),
     "fields_read_step": (_I, [_P] * 6 + [_I, _I, _P]),
     "fields_read_step_bf16": (_I, [_P] * 6 + [_I, _I, _P]),
+    "fields_scan_workspace_bytes": (_SZ, [_I, _I, _I]),
+    "fields_scan_forward": (_I, [_P, _LL, _LL, _I] + [_P] * 5 + [_SZ, _I, _I, _I, _P]),
+    "fields_scan_backward": (_I, [_P, _LL, _LL, _I] + [_P] * 8 + [_SZ, _I, _I, _I, _P]),
     "fields_read_span_summary": (_I, [_P] * 6 + [_SZ, _I, _I, _I, _P]),
     "fields_read_fold_summaries": (_I, [_P, _P, _P, _I, _I, _I, _I, _P]),
     "fields_read_span_summary_backward": (_I, [_P] * 6 + [_SZ, _I, _I, _I, _P]),

@@ -14,6 +14,7 @@
 #endif
 #include "field_span.cuh"
 #include "field_tensor.cuh"
+#include "field_scan.cuh"
 #include "field_epilogue.cuh"
 
 #include "../../include/fields_read.h"
@@ -1106,6 +1107,33 @@ int fields_read_fold_summaries_backward(const float* summaries, const float* car
 
 }  // extern "C"
 
+// ---------------------------------------------------------------------------
+// Real-valued scan (field_scan.cuh): plan and launches.
+// ---------------------------------------------------------------------------
+static ScanShape make_scan_shape(int B, int L, int C, long long a_batch, long long a_step,
+                                 int a_chan) {
+    ScanShape s{};
+    s.B = B; s.L = L; s.C = C;
+    s.NT = (L + kScanChunk - 1) / kScanChunk;
+    s.CG = (C + 31) / 32;
+    s.a_batch = a_batch; s.a_step = a_step; s.a_chan = a_chan;
+    return s;
+}
+
+static size_t scan_workspace_floats(int B, int L, int C) {
+    return (size_t)3 * B * ((L + kScanChunk - 1) / kScanChunk) * C;
+}
+
+static int scan_check(const void* workspace, size_t workspace_bytes, int B, int L, int C,
+                      long long a_batch, long long a_step, int a_chan) {
+    if (a_chan != 0 && a_chan != 1) return FIELDS_ERR_ARGUMENT;
+    if (a_batch < 0 || a_step < 0) return FIELDS_ERR_ARGUMENT;
+    if (!workspace || workspace_bytes < scan_workspace_floats(B, L, C) * sizeof(float) ||
+        (reinterpret_cast<uintptr_t>(workspace) & 15u))
+        return FIELDS_ERR_WORKSPACE;
+    return FIELDS_OK;
+}
+
 template <typename IO>
 static int run_step(const IO* raw, const float* tr, const float* ti, const float* gamma,
                     float* state, IO* read, int B, int C, void* stream) {
@@ -1131,6 +1159,81 @@ int fields_read_step_bf16(const void* raw, const float* tr, const float* ti, con
                               static_cast<uint16_t*>(read), B, C, stream);
 }
 
+
+size_t fields_scan_workspace_bytes(int B, int L, int C) {
+    if (B <= 0 || L <= 0 || C <= 0) return 0;
+    return scan_workspace_floats(B, L, C) * sizeof(float);
+}
+
+int fields_scan_forward(const float* a, long long a_batch, long long a_step, int a_chan,
+                        const float* drive, const float* state_in, float* states,
+                        float* state_out, void* workspace, size_t workspace_bytes, int B, int L,
+                        int C, void* stream) {
+    if (B < 0 || L < 0 || C <= 0) return FIELDS_ERR_ARGUMENT;
+    Stream st = reinterpret_cast<Stream>(stream);
+    if (B == 0) return FIELDS_OK;
+    if (L == 0) {
+        if (!state_out) return FIELDS_OK;
+        if (!state_in) return fill_zero(state_out, (size_t)B * C, st);
+#ifdef FIELDS_HOST_EMU
+        std::memcpy(state_out, state_in, (size_t)B * C * sizeof(float));
+        return FIELDS_OK;
+#else
+        return check_cuda(cudaMemcpyAsync(state_out, state_in, (size_t)B * C * sizeof(float),
+                                          cudaMemcpyDeviceToDevice, st));
+#endif
+    }
+    if (!a || !drive || !states) return FIELDS_ERR_ARGUMENT;
+    int rc = scan_check(workspace, workspace_bytes, B, L, C, a_batch, a_step, a_chan);
+    if (rc) return rc;
+    const ScanShape s = make_scan_shape(B, L, C, a_batch, a_step, a_chan);
+    float* ws = static_cast<float*>(workspace);
+    const size_t plane = (size_t)B * s.NT * C;
+    ScanFwdParams p{a, drive, state_in, states, state_out, ws, ws + plane, ws + 2 * plane, s};
+    const long long chunk_blocks = (scan_items(s) + kScanWarps - 1) / kScanWarps;
+    const long long chan_blocks = ((long long)B * C + ScanCarry::kThreads - 1) / ScanCarry::kThreads;
+    rc = launch<ScanChunkMap>(p, chunk_blocks, st);
+    if (!rc) rc = launch<ScanCarry>(p, chan_blocks, st);
+    if (!rc) rc = launch<ScanEmit>(p, chunk_blocks, st);
+    return rc;
+}
+
+int fields_scan_backward(const float* a, long long a_batch, long long a_step, int a_chan,
+                         const float* states, const float* state_in, const float* grad_states,
+                         const float* grad_state_out, float* grad_a, float* grad_drive,
+                         float* grad_state_in, void* workspace, size_t workspace_bytes, int B,
+                         int L, int C, void* stream) {
+    if (B < 0 || L < 0 || C <= 0) return FIELDS_ERR_ARGUMENT;
+    Stream st = reinterpret_cast<Stream>(stream);
+    if (B == 0) return FIELDS_OK;
+    if (L == 0) {
+        if (!grad_state_in) return FIELDS_OK;
+        if (!grad_state_out) return fill_zero(grad_state_in, (size_t)B * C, st);
+#ifdef FIELDS_HOST_EMU
+        std::memcpy(grad_state_in, grad_state_out, (size_t)B * C * sizeof(float));
+        return FIELDS_OK;
+#else
+        return check_cuda(cudaMemcpyAsync(grad_state_in, grad_state_out,
+                                          (size_t)B * C * sizeof(float), cudaMemcpyDeviceToDevice,
+                                          st));
+#endif
+    }
+    if (!a || !states || !grad_states || !grad_a || !grad_drive) return FIELDS_ERR_ARGUMENT;
+    int rc = scan_check(workspace, workspace_bytes, B, L, C, a_batch, a_step, a_chan);
+    if (rc) return rc;
+    const ScanShape s = make_scan_shape(B, L, C, a_batch, a_step, a_chan);
+    float* ws = static_cast<float*>(workspace);
+    const size_t plane = (size_t)B * s.NT * C;
+    ScanBwdParams p{a, states, state_in, grad_states, grad_state_out, grad_a, grad_drive,
+                    grad_state_in, ws, ws + plane, ws + 2 * plane, s};
+    const long long chunk_blocks = (scan_items(s) + kScanWarps - 1) / kScanWarps;
+    const long long chan_blocks =
+        ((long long)B * C + ScanCarryBwd::kThreads - 1) / ScanCarryBwd::kThreads;
+    rc = launch<ScanChunkMapBwd>(p, chunk_blocks, st);
+    if (!rc) rc = launch<ScanCarryBwd>(p, chan_blocks, st);
+    if (!rc) rc = launch<ScanEmitBwd>(p, chunk_blocks, st);
+    return rc;
+}
 
 int fields_read_selftest_wait(void* workspace, size_t workspace_bytes, unsigned max_polls,
                               void* stream) {

@@ -14,6 +14,13 @@ Every model build executes that file into a fresh module object, so the patch is
 applied per model: find the mixers, take the globals of their ``forward`` and
 rebind the name. The reference files and their SHA-256 digests stay as they are,
 and ``backend`` stays ``"triton"``.
+
+A third, smaller boundary (``scan=True``): the softpatch mixer runs the reference's
+``hierarchical_scan`` on a real rank-64 state
+(``official_source/field_hybrid_speed_optimization_v6.py:333-335``, looked up on the module it
+holds as ``v3_global``; the older ``BoundaryStateMixer`` looks it up as a global of its own
+module). ``install`` replaces that name with ``fields_lm_b200.scan.scan_entry(original)``, which
+runs real fp32 CUDA calls on this library and hands every other call to the original.
 """
 from __future__ import annotations
 
@@ -25,8 +32,11 @@ from .field_read import fused_field_read
 
 _NAME = "fused_field_read"
 _MIXER_CLASS = "IndependentVacancyField"
+_SCAN_NAME = "hierarchical_scan"
+_SCAN_CLASSES = ("FastBoundaryStateMixer", "BoundaryStateMixer")
 _saved: Dict[int, object] = {}
 _saved_forward: Dict[type, object] = {}
+_saved_scan: Dict[int, object] = {}
 
 
 def _mixer_classes(model: torch.nn.Module) -> List[type]:
@@ -50,9 +60,40 @@ def _namespaces(model: torch.nn.Module) -> List[dict]:
     return out
 
 
-def install(model: torch.nn.Module, fn=fused_field_read, fused_mixer: bool = False) -> int:
+def _scan_namespaces(model: torch.nn.Module) -> List[dict]:
+    """The module dictionaries in which the model's softpatch mixers look up the scan."""
+    seen, out = set(), []
+    for module in model.modules():
+        if type(module).__name__ not in _SCAN_CLASSES:
+            continue
+        ns = type(module).forward.__globals__
+        holder = ns.get("v3_global")
+        if holder is not None and hasattr(holder, _SCAN_NAME):
+            ns = vars(holder)
+        if _SCAN_NAME in ns and id(ns) not in seen:
+            seen.add(id(ns))
+            out.append(ns)
+    return out
+
+
+def install_scan(model: torch.nn.Module) -> int:
+    """Routes the softpatch mixers' real-valued scan through this library. Returns the number of
+    module namespaces patched (0 if the model has no softpatch mixer)."""
+    from .scan import scan_entry
+    spaces = _scan_namespaces(model)
+    for ns in spaces:
+        if id(ns) in _saved_scan:
+            continue
+        _saved_scan[id(ns)] = ns[_SCAN_NAME]
+        ns[_SCAN_NAME] = scan_entry(ns[_SCAN_NAME])
+    return len(spaces)
+
+
+def install(model: torch.nn.Module, fn=fused_field_read, fused_mixer: bool = False,
+            scan: bool = False) -> int:
     """Rebinds ``fused_field_read`` for every Field mixer in ``model``; with ``fused_mixer`` also
-    routes the mixers' ``forward`` through ``fused_mixer_forward`` where that applies.
+    routes the mixers' ``forward`` through ``fused_mixer_forward`` where that applies; with
+    ``scan`` also the softpatch mixers' ``hierarchical_scan`` (:func:`install_scan`).
 
     Returns the number of module namespaces patched (one per model build).
     Raises if the model holds no Field mixer with the Triton backend boundary.
@@ -76,12 +117,17 @@ def install(model: torch.nn.Module, fn=fused_field_read, fused_mixer: bool = Fal
                 return y if y is not None else _original(self, x)
 
             cls.forward = forward
+    if scan:
+        install_scan(model)
     return len(spaces)
 
 
 def uninstall(model: torch.nn.Module) -> int:
-    """Restores the original operator in every namespace ``install`` changed."""
+    """Restores the original operator (and scan) in every namespace ``install`` changed."""
     n = 0
+    for ns in _scan_namespaces(model):
+        if id(ns) in _saved_scan:
+            ns[_SCAN_NAME] = _saved_scan.pop(id(ns))
     for cls in _mixer_classes(model):
         if cls in _saved_forward:
             cls.forward = _saved_forward.pop(cls)

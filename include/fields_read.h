@@ -223,6 +223,34 @@ int fields_read_step_bf16(const void *raw, const float *tr, const float *ti, con
                           float *state, void *read, int B, int C, void *stream);
 
 /*
+ * Real-valued first-order scan  s_t = a_t s_{t-1} + drive_t  over [B, L, C] fp32: the second call
+ * site of the reference's scan primitive, hierarchical_scan(a, drive, block=32)
+ * (field_only_v4_chunked_triton_wiki100.py:347-391) as the softpatch mixer calls it on a rank-64
+ * state (official_source/field_hybrid_speed_optimization_v6.py:333-335).
+ *   a            element (b, t, c) at a[b * a_batch + t * a_step + c * a_chan], strides in floats,
+ *                a_chan 0 or 1: the reference passes one decay per token expanded over the channels
+ *                (a_batch = L, a_step = 1, a_chan = 0); a dense tensor is (L * C, C, 1)
+ *   drive        [B, L, C]
+ *   state_in     [B, C] or NULL (zero, the reference's contract)
+ *   states       [B, L, C] out: s_t for every step
+ *   state_out    [B, C] or NULL
+ *   workspace    fields_scan_workspace_bytes(B, L, C) bytes, 16-byte aligned
+ * Backward: grad_a is written densely [B, L, C] also for a broadcast `a` (the caller sums over
+ * the broadcast dimension, as autograd does for an expanded tensor); states is the forward output.
+ * Three launches each way (chunk maps, carries, states); results are bitwise reproducible.
+ */
+size_t fields_scan_workspace_bytes(int B, int L, int C);
+int fields_scan_forward(const float *a, long long a_batch, long long a_step, int a_chan,
+                        const float *drive, const float *state_in, float *states,
+                        float *state_out, void *workspace, size_t workspace_bytes, int B, int L,
+                        int C, void *stream);
+int fields_scan_backward(const float *a, long long a_batch, long long a_step, int a_chan,
+                         const float *states, const float *state_in, const float *grad_states,
+                         const float *grad_state_out, float *grad_a, float *grad_drive,
+                         float *grad_state_in, void *workspace, size_t workspace_bytes, int B,
+                         int L, int C, void *stream);
+
+/*
  * The same exchange without a collective library: span summaries travel between the GPUs of a
  * node through peer-writable memory (NVLink / NVSwitch). No counterpart in the reference.
  *

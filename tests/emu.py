@@ -85,6 +85,13 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.fields_read_forward_sharded.restype = I
     lib.fields_read_device_status.argtypes = [P, P]
     lib.fields_read_device_status.restype = I
+    LL = ctypes.c_longlong
+    lib.fields_scan_workspace_bytes.argtypes = [I, I, I]
+    lib.fields_scan_workspace_bytes.restype = SZ
+    lib.fields_scan_forward.argtypes = [P, LL, LL, I] + [P] * 5 + [SZ, I, I, I, P]
+    lib.fields_scan_forward.restype = I
+    lib.fields_scan_backward.argtypes = [P, LL, LL, I] + [P] * 8 + [SZ, I, I, I, P]
+    lib.fields_scan_backward.restype = I
     return lib
 
 
@@ -427,3 +434,44 @@ def forward_bf16_tensor(raw_bits, tr, ti, gamma, state_in=None):
     if rc:
         raise RuntimeError(lib().fields_status_string(rc).decode())
     return read, state, int(err[0])
+
+
+def _scan_layout(a, B, L, C):
+    """(buffer, batch stride, step stride, channel stride) of a dense [B, L, C] or per-token
+    [B, L] decay, as fields_scan_forward takes it."""
+    a = _f32(a)
+    return (a, L, 1, 0) if a.ndim == 2 else (a, L * C, C, 1)
+
+
+def scan_forward(a, b, state_in=None, want_state=True):
+    """Emulated fields_scan_forward; ``a`` is [B, L, C] or one decay per token [B, L]."""
+    b = _f32(b)
+    B, L, C = b.shape
+    a, ab, at, ac = _scan_layout(a, B, L, C)
+    sin = None if state_in is None else _f32(state_in)
+    states = _f32(np.full((B, L, C), np.nan))
+    sout = _f32(np.full((B, C), np.nan)) if want_state else None
+    nbytes = lib().fields_scan_workspace_bytes(B, L, C)
+    ws = _aligned(max(nbytes, 16))
+    rc = lib().fields_scan_forward(_ptr(a), ab, at, ac, _ptr(b), _ptr(sin), _ptr(states),
+                                   _ptr(sout), _ptr(ws), nbytes, B, L, C, None)
+    assert rc == 0, rc
+    return states, sout
+
+
+def scan_backward(a, states, grad_states, state_in=None, grad_state_out=None, want_state_grad=False):
+    """Emulated fields_scan_backward. Returns (grad_a dense, grad_b, grad_state_in or None)."""
+    states, g = _f32(states), _f32(grad_states)
+    B, L, C = states.shape
+    a, ab, at, ac = _scan_layout(a, B, L, C)
+    sin = None if state_in is None else _f32(state_in)
+    gso = None if grad_state_out is None else _f32(grad_state_out)
+    ga, gb = _f32(np.full((B, L, C), np.nan)), _f32(np.full((B, L, C), np.nan))
+    gsi = _f32(np.full((B, C), np.nan)) if want_state_grad else None
+    nbytes = lib().fields_scan_workspace_bytes(B, L, C)
+    ws = _aligned(max(nbytes, 16))
+    rc = lib().fields_scan_backward(_ptr(a), ab, at, ac, _ptr(states), _ptr(sin), _ptr(g),
+                                    _ptr(gso), _ptr(ga), _ptr(gb), _ptr(gsi), _ptr(ws), nbytes,
+                                    B, L, C, None)
+    assert rc == 0, rc
+    return ga, gb, gsi

@@ -12,7 +12,10 @@ PyTorch autograd on CPU, and writes:
   built under ``torch.manual_seed(0)``, input ``x ~ N(0,1)`` of shape
   ``[1, 256, 1024]``: the operator's inputs in full, its outputs every 4th
   step plus the last step, the mixer/block outputs every 4th step, and a hash
-  of every weight so that a test can rebuild the same block from the seed.
+  of every weight so that a test can rebuild the same block from the seed;
+* ``scan_small.npz`` — the reference's ``hierarchical_scan(a, b, 32)`` on real inputs with
+  autograd: dense decays and one decay per token expanded over the channels (the softpatch
+  mixer's call), ragged lengths around the block size of 32.
 
 The fixtures travel with the repository; the reference does not.
 """
@@ -93,6 +96,35 @@ def make_small(canon) -> dict:
     return out
 
 
+# (name, B, L, C, decay per token broadcast over the channels?, range of a)
+SCAN_CASES = [
+    ("softpatch_shape", 2, 70, 64, True, (0.01, 0.99)),
+    ("single_step", 1, 1, 3, False, (0.0, 1.0)),
+    ("ragged_dense", 3, 45, 5, False, (0.0, 1.0)),
+    ("one_block", 1, 32, 8, True, (0.01, 0.99)),
+    ("block_plus_one", 2, 33, 40, True, (0.01, 0.99)),
+    ("signed_decay", 2, 100, 33, False, (-1.0, 1.0)),
+]
+
+
+def make_scan(canon) -> dict:
+    out = {}
+    gen = torch.Generator().manual_seed(20240609)
+    for name, B, L, C, per_token, (lo, hi) in SCAN_CASES:
+        shape = (B, L) if per_token else (B, L, C)
+        a0 = (lo + (hi - lo) * torch.rand(shape, generator=gen)).requires_grad_(True)
+        a = a0[..., None].expand(B, L, C) if per_token else a0
+        b = torch.randn(B, L, C, generator=gen).requires_grad_(True)
+        g = torch.randn(B, L, C, generator=gen)
+        states = canon.hierarchical_scan(a, b, 32)
+        states.backward(g)
+        for key, val in (("a", a0), ("b", b), ("grad_states", g), ("states", states),
+                         ("grad_a", a0.grad), ("grad_b", b.grad)):
+            out[f"{name}/{key}"] = val.detach().numpy().copy()
+    out["cases"] = np.array([c[0] for c in SCAN_CASES])
+    return out
+
+
 def weight_digest(module: torch.nn.Module) -> str:
     h = hashlib.sha256()
     for name, p in sorted(module.state_dict().items()):
@@ -136,9 +168,16 @@ def make_config1(canon) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference-root", required=True, type=Path)
+    ap.add_argument("--only-scan", action="store_true", help="write scan_small.npz only")
     args = ap.parse_args()
     torch.set_num_threads(1)  # fixed reduction order inside the reference's GEMMs
     canon, sha = load_canon(args.reference_root)
+    scan = make_scan(canon)
+    scan["canon_sha256"] = np.array(sha)
+    np.savez_compressed(HERE / "scan_small.npz", **scan)
+    print("scan_small.npz", (HERE / "scan_small.npz").stat().st_size, "bytes")
+    if args.only_scan:
+        return
     small = make_small(canon)
     small["canon_sha256"] = np.array(sha)
     np.savez_compressed(HERE / "op_small.npz", **small)

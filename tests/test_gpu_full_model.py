@@ -36,7 +36,8 @@ def test_training_step_matches_the_reference_triton_path():
     floor_norm, _ = full_model.norm_relative(full_model.gradients(model), grads_ref)
     full_model.set_triton_geometry(model, 32, 64)
 
-    assert fields_lm_b200.install(model) == 1     # one module namespace for all 18 blocks
+    # one module namespace for all 18 blocks; the softpatch mixer's scan goes along
+    assert fields_lm_b200.install(model, scan=True) == 1
     try:
         loss_new = float(full_model.training_step(model, ids, labels))
         grads_new = full_model.gradients(model)
@@ -55,3 +56,38 @@ def test_training_step_matches_the_reference_triton_path():
     # gradient entries; held to what the reference's own second geometry does to them
     worst, where = full_model.compare_gradients(grads_new, grads_ref)
     assert worst <= max(BF16_TOL, 3 * floor), (worst, where, floor)
+
+
+def test_softpatch_mixer_with_the_scan_installed():
+    """The reference's ``FastBoundaryStateMixer`` of the built model (block 11's softpatch: a
+    learned boundary score, a rank-64 real scan, an up projection), fp32, first on the
+    reference's ``hierarchical_scan`` then with ``install_scan``: output and all gradients."""
+    device = torch.device("cuda", 0)
+    model, _ = full_model.build(device, model_seed=0)
+    mixer = model.core_model.softpatch
+    assert type(mixer).__name__ == "FastBoundaryStateMixer"
+    gen = torch.Generator().manual_seed(21)
+    dim = mixer.down.in_features
+    x0 = torch.randn(2, 700, dim, generator=gen).to(device)
+    gy = torch.randn(2, 700, dim, generator=gen).to(device)
+    tokens = torch.randint(0, 16384, (2, 700), generator=gen).to(device)
+
+    def run():
+        mixer.zero_grad(set_to_none=True)
+        x = x0.clone().requires_grad_(True)
+        y = mixer(x, tokens)
+        y.backward(gy)
+        return [y.detach(), x.grad] + [p.grad for p in mixer.parameters() if p.grad is not None]
+
+    want = run()
+    assert fields_lm_b200.install_scan(model) == 1
+    try:
+        got = run()
+    finally:
+        fields_lm_b200.uninstall(model)
+    again = run()                                  # the original is back
+    assert len(got) == len(want) >= 5
+    for a, b in zip(got, want):
+        assert float((a - b).abs().max()) <= 2e-5 * float(b.abs().max())
+    for a, b in zip(again, want):
+        assert float((a - b).abs().max()) <= 1e-6 * float(b.abs().max())
