@@ -515,6 +515,69 @@ def real_scan_leg(device, stream, steps: int):
     return out
 
 
+def block_64k_leg(device, stream, dist_on: bool, rank: int, world: int, iters: int = 10):
+    """Block-level strong scaling: the forward of ONE of the reference's Field blocks (staged
+    copy, seed-0 weights, d_model 1,024, bf16 autocast, no_grad) over 1 x 65,536 tokens. On one
+    GPU the whole sequence with the operator installed; on N GPUs every rank runs its span of the
+    tokens through the same block and only the operator communicates (the one-launch sharded
+    forward, summaries over NVLink peer stores); the projections, norms, gate and SwiGLU are
+    token-parallel. The gathered output is compared with rank 0's single-GPU pass."""
+    import fields_lm_b200
+    from oracle import ref
+    if not ref.available():
+        return {"unavailable": ref.why_unavailable()}
+    from fields_lm_b200 import seqpar
+    canon, block = reference_field_block(device)
+    block.eval()
+    gen = torch.Generator().manual_seed(2)
+    x_full = torch.randn(1, LONG_L, D_MODEL, generator=gen)
+    lo, hi = seqpar.span_bounds(LONG_L, world, rank) if dist_on else (0, LONG_L)
+    x = x_full[:, lo:hi].contiguous().to(device)
+    sp = seqpar.SequenceParallelForwardFused(1, hi - lo, C, device) if dist_on else None
+
+    def sharded_read(raw, tr, ti, gamma, block_c=None, chunk_t=None):
+        read, _ = sp(raw.contiguous(), tr.contiguous(), ti.contiguous(), gamma.contiguous())
+        return read
+
+    fields_lm_b200.install(block, sharded_read if dist_on else fields_lm_b200.fused_field_read)
+
+    def run():
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            return block(x)
+    try:
+        for _ in range(3):
+            run()
+        barrier(dist_on)
+        ms = max_over_ranks(timed_loop(run, iters, stream) / iters, dist_on, device)
+        barrier(dist_on)
+        y = run().float()
+        status = sp.status() if sp is not None else 0
+    finally:
+        fields_lm_b200.uninstall(block)
+    out = {"workload": "forward of one reference FieldBlock (mixer + SwiGLU, d_model 1,024) over "
+                       f"1 x {LONG_L} tokens, bf16 autocast, no_grad" +
+                       (f", tokens sharded over {world} GPUs, operator through "
+                        "fields_read_forward_sharded" if dist_on else " on one GPU"),
+           "scaling": "strong", "n_gpus": world, "ms": ms, "tokens_per_s": LONG_L / (ms * 1e-3),
+           "status": status, "parity": None}
+    if dist_on:
+        parts = [torch.empty_like(y) for _ in range(world)] if rank == 0 else None
+        # spans have equal length here (65,536 divides by the world sizes of one node)
+        torch.distributed.gather(y, parts, dst=0)
+        if rank == 0:
+            del sp
+            fields_lm_b200.install(block)
+            try:
+                with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+                    want = block(x_full.to(device)).float()
+            finally:
+                fields_lm_b200.uninstall(block)
+            got = torch.cat(parts, dim=1)
+            out["parity"] = {"y_rel_vs_single_gpu": float((got - want).abs().max() / want.abs().max()),
+                             "tolerance": BF16_TOL, "ranks": world}
+    return out
+
+
 def recurrence_kernel_share(step, device):
     """Share of one step's GPU kernel time spent in Field-recurrence kernels (torch profiler)."""
     from torch.profiler import ProfilerActivity, profile
@@ -1153,6 +1216,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                                       max(5, min(args.steps, 30)), read0.detach(), graw0)
         del read0, graw0
     full_model = full_model_leg(device, stream) if (not dist_on and not args.no_full_model) else None
+    block_64k = None
+    if not args.no_triton:   # needs the staged reference, like the Triton leg
+        try:
+            block_64k = block_64k_leg(device, stream, dist_on, rank, world)
+        except Exception as exc:
+            block_64k = {"unavailable": repr(exc)[:400]}
 
     # end to end: pinned host -> device, forward + backward, results back to pinned host.
     # The process first moves onto the CPUs next to its GPU (NVML's ideal affinity for the device),
@@ -1249,6 +1318,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     "tokens_per_s": world * B * L / (bf16["ms_per_step"] * 1e-3)},
         "decode_step": decode,
         "field_block": block,
+        "field_block_64k": block_64k,
         "sharded_span_one_gpu": spans,
         "tcgen05_experiment": tensor,
         "real_scan": real_scan,

@@ -7,6 +7,7 @@ Public surface:
 * :func:`fused_field_read_bf16_stats` - the same plus the per-token sum of squares an RMS norm needs;
 * :func:`field_read_with_state` - the operator with carried state in and out;
 * :func:`field_read_step` - one recurrent step for incremental decoding;
+* :class:`FieldStackDecoder` - stateful prefill -> decode for a field-only language model;
 * :func:`fields_lm_b200.seqpar.sequence_parallel_field_read` - sequence-sharded forward;
 * :func:`install` / :func:`uninstall` - rebind the operator inside a built model;
 * :func:`linear_scan` - the reference's ``hierarchical_scan`` for real fp32 CUDA tensors
@@ -17,11 +18,11 @@ Public surface:
 
 The CUDA library is required: nothing here falls back to a CPU or PyTorch path.
 """
-from .decode import field_read_step
+from .decode import FieldStackDecoder, field_read_step
 from .field_read import (FieldReadFunction, field_read_with_state, fused_field_read,
                          fused_field_read_bf16, fused_field_read_bf16_stats)
 from .install import install, install_scan, uninstall
 from .scan import linear_scan, linear_scan_with_state
 
-__all__ = ["FieldReadFunction", "field_read_step", "field_read_with_state", "fused_field_read", "fused_field_read_bf16", "fused_field_read_bf16_stats", "install",
+__all__ = ["FieldReadFunction", "FieldStackDecoder", "field_read_step", "field_read_with_state", "fused_field_read", "fused_field_read_bf16", "fused_field_read_bf16_stats", "install",
            "install_scan", "linear_scan", "linear_scan_with_state", "uninstall"]
