@@ -40,6 +40,7 @@ struct SpShape {
     int G;         // 128-channel groups
     int prefetch;  // non-zero: blocks warm L2 with the inputs of the tile that many positions ahead
     unsigned max_polls;  // bound of every wait for another block's publication
+    int stride;    // persistent kernels: a block takes tiles block, block + stride, ...; 0: one tile per block
 };
 
 // Prefetches `planes` consecutive 128-channel plane chunks of `steps` rows into L2:
@@ -96,7 +97,16 @@ FL_HD SpTile sp_decode(const SpShape& s, unsigned ticket) {
 }
 
 // IO = float, or uint16_t for bfloat16 raw / read (the state, the maps and all arithmetic stay fp32).
-template <int TS, int WARPS, int MIN_BLOCKS, typename IO = float, bool STATS = false>
+//
+// STAGED: the kernel runs as persistent blocks (a block takes tiles block, block + stride, ... in
+// that order, which keeps "every tile a block waits for has a smaller index and is running or
+// done"), and every thread keeps one staging cell per (step, plane) of its rows in shared memory.
+// As soon as a thread has moved its rows of the current tile from the cells into registers it
+// starts the cp.async copies of its rows of the block's NEXT tile into the same cells; they land
+// while the block publishes its map, looks back and runs the recurrence, so the next tile starts
+// from shared memory instead of waiting for HBM.
+template <int TS, int WARPS, int MIN_BLOCKS, typename IO = float, bool STATS = false,
+          bool STAGED = false>
 struct FwdSinglePass {
     using Params = SpFwdParamsT<IO>;
     static constexpr int kThreads = 32 * WARPS;
@@ -108,9 +118,37 @@ struct FwdSinglePass {
     static constexpr int kSplitPhase = 2;  // host emulation: phases < 2 of all blocks run first
     static constexpr int kSumFloats = WARPS * 4 * kGroup;
     static constexpr int kCarryFloats = WARPS * 2 * kGroup;
-    static constexpr int kSmemFloats = kSumFloats + kCarryFloats;
+    static constexpr bool kStaged = STAGED;
+    static constexpr int kCellFloats = (int)sizeof(IO);  // four elements: 16 bytes of float, 8 of bfloat16
+    static constexpr int kStageFloats = STAGED ? TS * 3 * kThreads * kCellFloats : 0;
+    static constexpr int kSmemFloats = kSumFloats + kCarryFloats + kStageFloats;
     static constexpr int kClaimAfter = 2;  // the next tile is claimed after the look-back phase
     FL_HD static constexpr bool barrier_after(int ph) { return ph != 1; }
+    FL_HD static float* cell_at(float* smem, int idx, int thread) {
+        return smem + kSumFloats + kCarryFloats + ((size_t)idx * kThreads + thread) * kCellFloats;
+    }
+
+    // Starts the copies of this thread's rows of `tile` into its staging cells (one commit group).
+    FL_HD static void stage(const Params& p, int tile, int thread, float* smem) {
+        const SpShape& s = p.s;
+        const SpTile tl = sp_decode(s, (unsigned)tile);
+        const int lane = thread & 31, warp = thread >> 5;
+        const int c0 = tl.cg * kGroup + lane * 4;
+        if (c0 < s.C) {
+            const int tw = tl.n * kTile + warp * TS;
+            const IO* base = p.raw + ((size_t)tl.b * s.L) * 3 * s.C + c0;
+#pragma unroll
+            for (int u = 0; u < TS; ++u) {
+                if (tw + u < s.L) {
+                    const IO* row = base + (size_t)(tw + u) * 3 * s.C;
+                    async_copy4(cell_at(smem, u * 3 + 0, thread), row);
+                    async_copy4(cell_at(smem, u * 3 + 1, thread), row + s.C);
+                    async_copy4(cell_at(smem, u * 3 + 2, thread), row + 2 * s.C);
+                }
+            }
+        }
+        async_commit();
+    }
 
     struct State {
         Vec<4> br[TS], bi[TS], vac[TS];  // raw on load, then gamma*v*inj and vacancy
@@ -144,18 +182,43 @@ struct FwdSinglePass {
             Affine m[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) m[k] = affine_identity();
+            if constexpr (STAGED) {
+                // The rows were started into this thread's cells by the previous tile of this
+                // block (by the kernel entry for the block's first tile; by this very call in
+                // the host emulation, where a copy is synchronous).
+#if !FL_DEVICE_CODE
+                stage(p, block, thread, smem);
+#endif
+                async_wait_pending<0>();
+                if (chan_ok) {
+#pragma unroll
+                    for (int u = 0; u < TS; ++u) {
+                        if (tw + u < s.L) {
+                            st.br[u] = cell_load4<IO>(cell_at(smem, u * 3 + 0, thread));
+                            st.bi[u] = cell_load4<IO>(cell_at(smem, u * 3 + 1, thread));
+                            st.vac[u] = cell_load4<IO>(cell_at(smem, u * 3 + 2, thread));
+                        }
+                    }
+                }
+                // the cells are free again: the block's next tile starts towards them now
+                const long long next = (long long)block + s.stride;
+                if (s.stride > 0 && next < (long long)s.B * s.G * s.NT)
+                    stage(p, (int)next, thread, smem);
+            }
             if (chan_ok) {
                 const Vec<4> lr = vec_load<4>(p.tr + c0);
                 const Vec<4> li = vec_load<4>(p.ti + c0);
                 const Vec<4> gm = vec_load<4>(p.gamma + c0);
-                const IO* base = p.raw + ((size_t)tl.b * s.L) * 3 * C + c0;
+                if constexpr (!STAGED) {
+                    const IO* base = p.raw + ((size_t)tl.b * s.L) * 3 * C + c0;
 #pragma unroll
-                for (int u = 0; u < TS; ++u) {
-                    if (tw + u < s.L) {
-                        const IO* row = base + (size_t)(tw + u) * 3 * C;
-                        st.br[u] = io_load4_stream(row);
-                        st.bi[u] = io_load4_stream(row + C);
-                        st.vac[u] = io_load4_stream(row + 2 * C);
+                    for (int u = 0; u < TS; ++u) {
+                        if (tw + u < s.L) {
+                            const IO* row = base + (size_t)(tw + u) * 3 * C;
+                            st.br[u] = io_load4_stream(row);
+                            st.bi[u] = io_load4_stream(row + C);
+                            st.vac[u] = io_load4_stream(row + 2 * C);
+                        }
                     }
                 }
 #pragma unroll
@@ -285,6 +348,7 @@ struct FwdSinglePass {
 template <int TS, int WARPS, int U_, int MIN_BLOCKS, int STAGES, typename IO = float>
 struct FwdTwoSweep {
     using Params = SpFwdParamsT<IO>;
+    static constexpr bool kStaged = false;
     static constexpr int kThreads = 32 * WARPS;
     static constexpr int kMinBlocks = MIN_BLOCKS;
     static constexpr int kTile = TS * WARPS;

@@ -97,6 +97,13 @@ static int fill_unset(void* p, size_t bytes, Stream) {
     return FIELDS_OK;
 }
 
+// A staged kernel in the emulation: one tile per block, every tile stages its own rows.
+template <class K>
+static int launch_persistent(const typename K::Params& p, long long grid, long long first_wave,
+                             Stream st) {
+    return launch_stateful<K>(p, grid, first_wave, st);
+}
+
 
 template <class K>
 static int resident_blocks() { return 4; }  // any positive distance exercises the prefetch path
@@ -266,6 +273,24 @@ __global__ void __launch_bounds__(K::kThreads, K::kMinBlocks) stateful_entry(con
     run_phases<K, K::kClaimAfter + 1, K::kPhases - 1>(p, tile, smem, st);
 }
 
+// Persistent form for kernels with staging cells (K::kStaged): a block takes tiles blockIdx.x,
+// blockIdx.x + stride, ... in that order. The grid never exceeds what the GPU holds at once, so
+// every tile a block waits for (a smaller index) belongs to a block that is running; the waits
+// are bounded all the same. The first tile's rows are started here, every later tile's rows by
+// phase 0 of the tile before it.
+template <class K>
+__global__ void __launch_bounds__(K::kThreads, K::kMinBlocks) persistent_entry(const typename K::Params p) {
+    extern __shared__ __align__(16) float smem[];
+    typename K::State st;
+    const long long tiles = (long long)p.s.B * p.s.G * p.s.NT;
+    wait_for_previous_kernel();
+    if ((long long)blockIdx.x < tiles) K::stage(p, (int)blockIdx.x, (int)threadIdx.x, smem);
+    for (long long tile = blockIdx.x; tile < tiles; tile += p.s.stride) {
+        run_phases<K, 0, K::kPhases - 1>(p, (int)tile, smem, st);
+        __syncthreads();  // the map and carry areas are written again by the next tile
+    }
+}
+
 // Kernels that need more than the default 48 KB of dynamic shared memory opt in once per device.
 // `ready` is the caller's per-kernel, per-device record (kernels of equal signature share a
 // function-pointer type, so the record cannot live in this template).
@@ -341,6 +366,41 @@ static int resident_blocks() {
         return 0;
     cached[dev] = per_sm * sms;
     return cached[dev];
+}
+
+// Launch of a staged kernel as persistent blocks: as many as the GPU holds at once (asked once
+// per device, after the opt-in to its shared memory), never more than there are tiles.
+template <class K>
+static int launch_persistent(typename K::Params p, long long tiles, long long, Stream st) {
+    if (tiles <= 0) return FIELDS_OK;
+    if (tiles > 0x7fffffffLL) return FIELDS_ERR_UNSUPPORTED;
+    constexpr size_t bytes = K::kSmemFloats * sizeof(float);
+    static bool ready[64] = {};
+    int rc = allow_shared_memory(persistent_entry<K>, bytes, ready);
+    if (rc) return rc;
+    static std::mutex mu;
+    static int cached[64] = {};
+    int dev = 0, resident = 0;
+    rc = check_cuda(cudaGetDevice(&dev));
+    if (rc) return rc;
+    if (dev < 0 || dev >= 64) return FIELDS_ERR_UNSUPPORTED;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (cached[dev] == 0) {
+            int per_sm = 0, sms = 0;
+            rc = check_cuda(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+            if (!rc)
+                rc = check_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                    &per_sm, persistent_entry<K>, K::kThreads, bytes));
+            if (rc) return rc;
+            if (per_sm * sms <= 0) return FIELDS_ERR_UNSUPPORTED;
+            cached[dev] = per_sm * sms;
+        }
+        resident = cached[dev];
+    }
+    const long long grid = tiles < resident ? tiles : resident;
+    p.s.stride = (int)grid;
+    return launch_on<typename K::Params>(persistent_entry<K>, (unsigned)grid, K::kThreads, bytes, st, p);
 }
 
 // Persistent block program over an executor: the calling thread, then a block barrier.
@@ -568,6 +628,8 @@ using FwdSp0 = FwdSinglePass<6, 8, 2>;        // tile 48 steps, 128 registers, n
 using FwdSp1 = FwdSinglePass<4, 8, 2>;        // tile 32
 //   two-sweep forward <steps per warp, warps, unroll, blocks per SM, ring slots>
 using FwdSp2 = FwdTwoSweep<8, 4, 2, 4, 3>;    // tile 32, 16 warps per SM
+//   staged: persistent blocks, the next tile's rows land in shared memory during the current tile
+using FwdSp3 = FwdSinglePass<5, 8, 2, float, false, true>;  // tile 40, 74 KB per block
 #endif
 //   backward <steps per warp, warps, sweep-1 unroll, sweep-2 unroll, blocks per SM, rings, ring slots>
 using BwdSp0 = BwdSinglePass<8, 4, 2, 1, 3, true, 3>;  // tile 32, 3-slot cp.async rings, 12 warps per SM
@@ -616,7 +678,7 @@ static int run_forward_single_pass(const IO* raw, const float* tr, const float* 
                                    float* state_out, void* workspace, int B, int L, int C,
                                    Stream st, float* sumsq = nullptr) {
     SpPlan pl = make_sp_plan(B, L, C, K::kTile);
-    pl.s.prefetch = prefetch_from_env(resident_blocks<K>());
+    if constexpr (!K::kStaged) pl.s.prefetch = prefetch_from_env(resident_blocks<K>());
     char* ws = static_cast<char*>(workspace);
     unsigned* ctrl = reinterpret_cast<unsigned*>(ws);
     int rc = fill_unset(ws, pl.bytes, st);  // error word and every publication slot
@@ -625,7 +687,8 @@ static int run_forward_single_pass(const IO* raw, const float* tr, const float* 
                        reinterpret_cast<float*>(ws + pl.agg_off),
                        reinterpret_cast<float*>(ws + pl.incl_off), ctrl, pl.s};
     p.sumsq = sumsq;
-    return launch_stateful<K>(p, pl.tiles, (long long)B * pl.s.G, st);
+    if constexpr (K::kStaged) return launch_persistent<K>(p, pl.tiles, (long long)B * pl.s.G, st);
+    else return launch_stateful<K>(p, pl.tiles, (long long)B * pl.s.G, st);
 }
 
 template <class K, typename IO = float>
@@ -850,6 +913,7 @@ int fields_read_forward(const float* raw, const float* tr, const float* ti, cons
         switch (variant_from_env("FIELDS_FWD_VARIANT")) {
             case 1: FIELDS_FWD_SP(FwdSp1);
             case 2: FIELDS_FWD_SP(FwdSp2);
+            case 3: FIELDS_FWD_SP(FwdSp3);
             default: FIELDS_FWD_SP(FwdSp0);
         }
 #else
