@@ -45,6 +45,8 @@
 
 namespace fields {
 
+constexpr int kSpanMailWindow = 2;  // ranks whose slots a thread of the one-launch forward fetches together
+
 struct SpanShape {
     int B, L, C;
     int G;          // 128-channel groups
@@ -393,25 +395,43 @@ struct FwdSpanSweep {
         float si = p.state0 ? p.state0[(size_t)it.b * 2 * s.C + s.C + c] : 0.0f;
         bool failed = false;
         if (p.P > 1) {
-            for (int r = 0; r < p.P && !failed; ++r) {
-                const MailPair* q =
-                    p.own + (((size_t)(p.epoch & 1u) * p.P + r) * s.B + it.b) * 4 * s.C + c;
-                float v[4];
+            // two ranks' slots are fetched together (one L2 round trip for 8 pairs); a slot
+            // found empty is then polled on its own, with the caller's bound
+            for (int r0 = 0; r0 < p.P; r0 += kSpanMailWindow) {
+                MailPair got[kSpanMailWindow][4];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    MailPair m = mail_load(q + (size_t)k * s.C);
-#if FL_DEVICE_CODE
-                    unsigned polls = 0;
-                    // a summary that is late ends the waiting for all that follow it
-                    while (m.tag != p.epoch && !failed && ++polls < p.max_polls) {
-                        backoff(polls);
-                        m = mail_load(q + (size_t)k * s.C);
+                for (int w = 0; w < kSpanMailWindow; ++w) {
+                    if (r0 + w < p.P) {
+                        const MailPair* q = p.own +
+                            (((size_t)(p.epoch & 1u) * p.P + r0 + w) * s.B + it.b) * 4 * s.C + c;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) got[w][k] = mail_load(q + (size_t)k * s.C);
                     }
-#endif
-                    if (m.tag != p.epoch) failed = true;
-                    v[k] = m.value;
                 }
-                if (!failed && r < p.rank) affine_apply(Affine{v[0], v[1], v[2], v[3]}, sr, si);
+#pragma unroll
+                for (int w = 0; w < kSpanMailWindow; ++w) {
+                    if (r0 + w < p.P) {
+                        const int r = r0 + w;
+                        const MailPair* q = p.own +
+                            (((size_t)(p.epoch & 1u) * p.P + r) * s.B + it.b) * 4 * s.C + c;
+                        float v[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            MailPair m = got[w][k];
+#if FL_DEVICE_CODE
+                            unsigned polls = 0;
+                            // a summary that is late ends the waiting for all that follow it
+                            while (m.tag != p.epoch && !failed && ++polls < p.max_polls) {
+                                backoff(polls);
+                                m = mail_load(q + (size_t)k * s.C);
+                            }
+#endif
+                            if (m.tag != p.epoch) failed = true;
+                            v[k] = m.value;
+                        }
+                        if (!failed && r < p.rank) affine_apply(Affine{v[0], v[1], v[2], v[3]}, sr, si);
+                    }
+                }
             }
         }
         // (this thread's prefix entries share their place with carries it writes below: read first)
