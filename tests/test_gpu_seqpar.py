@@ -21,6 +21,11 @@ def _worker(rank, world, port, L, out_dir):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
                             timeout=datetime.timedelta(seconds=90))
+    problems = []   # checked only after every rank's kernels are done and the ranks have met
+
+    def check(ok, what):
+        if not ok:
+            problems.append(f"rank {rank}: {what}")
     try:
         from fields_lm_b200 import field_read_with_state, seqpar
         gen = torch.Generator().manual_seed(123)
@@ -39,24 +44,24 @@ def _worker(rank, world, port, L, out_dir):
         for _ in range(2):
             read2, state2 = op(span, tr, ti, gm)
         torch.cuda.synchronize()
-        assert float((read2 - read).abs().max()) <= 2e-6 * float(read.abs().max())
-        assert float((state2 - state).abs().max()) <= 2e-6 * float(state.abs().max())
+        check(float((read2 - read).abs().max()) <= 2e-6 * float(read.abs().max()), "NCCL read")
+        check(float((state2 - state).abs().max()) <= 2e-6 * float(state.abs().max()), "NCCL state")
         # the same exchange through peer memory instead of NCCL; several calls alternate parities
         p2p = seqpar.SequenceParallelForwardP2P(B, hi - lo, C, dev)
         for _ in range(3):
             read3, state3 = p2p(span, tr, ti, gm)
         torch.cuda.synchronize()
-        assert p2p.status() == 0
-        assert float((read3 - read).abs().max()) <= 2e-6 * float(read.abs().max())
-        assert float((state3 - state).abs().max()) <= 2e-6 * float(state.abs().max())
+        check(p2p.status() == 0, "peer-memory exchange timed out")
+        check(float((read3 - read).abs().max()) <= 2e-6 * float(read.abs().max()), "P2P read")
+        check(float((state3 - state).abs().max()) <= 2e-6 * float(state.abs().max()), "P2P state")
         # the whole sharded forward as one cooperative launch per rank
         fused = seqpar.SequenceParallelForwardFused(B, hi - lo, C, dev)
         for _ in range(4):
             read4, state4 = fused(span, tr, ti, gm)
         torch.cuda.synchronize()
-        assert fused.status() == 0
-        assert float((read4 - read).abs().max()) <= 2e-6 * float(read.abs().max())
-        assert float((state4 - state).abs().max()) <= 2e-6 * float(state.abs().max())
+        check(fused.status() == 0, "one-launch forward timed out")
+        check(float((read4 - read).abs().max()) <= 2e-6 * float(read.abs().max()), "fused read")
+        check(float((state4 - state).abs().max()) <= 2e-6 * float(state.abs().max()), "fused state")
         if rank == 0:
             with torch.no_grad():
                 full, full_state = field_read_with_state(raw.to(dev), tr, ti, gm, None)
@@ -65,8 +70,12 @@ def _worker(rank, world, port, L, out_dir):
                      ti=ti.cpu().numpy(), gm=gm.cpu().numpy())
         np.savez(os.path.join(out_dir, f"rank{rank}.npz"), read=read.cpu().numpy(),
                  state=state.cpu().numpy(), lo=lo, hi=hi)
+        # every rank leaves in order, with nothing in flight, also when a check failed
+        torch.cuda.synchronize()
+        dist.barrier()
     finally:
         dist.destroy_process_group()
+    assert not problems, problems
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
@@ -95,6 +104,11 @@ def _train_worker(rank, world, port, L, out_dir):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
                             timeout=datetime.timedelta(seconds=90))
+    problems = []   # checked only after every rank's kernels are done and the ranks have met
+
+    def check(ok, what):
+        if not ok:
+            problems.append(f"rank {rank}: {what}")
     try:
         from fields_lm_b200 import seqpar
         gen = torch.Generator().manual_seed(321)
@@ -118,19 +132,21 @@ def _train_worker(rank, world, port, L, out_dir):
             step.forward(span.detach(), tr.detach(), ti.detach(), gm.detach())
             g_raw, g_par = step.backward(span.detach(), tr.detach(), ti.detach(), gm.detach(), g_span)
         torch.cuda.synchronize()
-        assert float((g_raw - span.grad).abs().max()) <= 1e-5 * float(span.grad.abs().max())
+        check(float((g_raw - span.grad).abs().max()) <= 1e-5 * float(span.grad.abs().max()), "NCCL grad_raw")
         for k, t in enumerate((tr, ti, gm)):
-            assert float((g_par[k] - t.grad).abs().max()) <= 1e-5 * float(t.grad.abs().max())
+            check(float((g_par[k] - t.grad).abs().max()) <= 1e-5 * float(t.grad.abs().max()),
+                  f"NCCL parameter gradient {k}")
         # and with both exchanges through peer memory
         p2p = seqpar.SequenceParallelTrainStepP2P(B, hi - lo, C, dev)
         for _ in range(3):
             p2p.forward(span.detach(), tr.detach(), ti.detach(), gm.detach())
             g_raw2, g_par2 = p2p.backward(span.detach(), tr.detach(), ti.detach(), gm.detach(), g_span)
         torch.cuda.synchronize()
-        assert p2p.status() == 0
-        assert float((g_raw2 - span.grad).abs().max()) <= 1e-5 * float(span.grad.abs().max())
+        check(p2p.status() == 0, "peer-memory exchange timed out")
+        check(float((g_raw2 - span.grad).abs().max()) <= 1e-5 * float(span.grad.abs().max()), "P2P grad_raw")
         for k, t in enumerate((tr, ti, gm)):
-            assert float((g_par2[k] - t.grad).abs().max()) <= 1e-5 * float(t.grad.abs().max())
+            check(float((g_par2[k] - t.grad).abs().max()) <= 1e-5 * float(t.grad.abs().max()),
+                  f"P2P parameter gradient {k}")
         if rank == 0:
             np.savez(os.path.join(out_dir, "inputs.npz"), raw=raw.numpy(), grad=grad.numpy(),
                      tr=tr.detach().cpu().numpy(), ti=ti.detach().cpu().numpy(),
@@ -138,8 +154,11 @@ def _train_worker(rank, world, port, L, out_dir):
         np.savez(os.path.join(out_dir, f"rank{rank}.npz"), lo=lo, hi=hi,
                  grad_raw=span.grad.cpu().numpy(), grad_tr=tr.grad.cpu().numpy(),
                  grad_ti=ti.grad.cpu().numpy(), grad_gamma=gm.grad.cpu().numpy())
+        torch.cuda.synchronize()
+        dist.barrier()
     finally:
         dist.destroy_process_group()
+    assert not problems, problems
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")

@@ -71,6 +71,41 @@ def test_noalloc_forward_matches_ordinary_forward_twice_in_a_row():
         assert not bool(torch.isnan(got_read).any())
 
 
+def test_noalloc_forward_allocates_nothing_and_covers_the_scalar_kernels():
+    """The property the entry point exists for: after the first call on a device (which asks
+    for the address of the built-in buffer), a call changes neither the driver's free memory
+    nor the caching allocator's books. Also a channel count that is not a multiple of four
+    (the three-phase scalar kernels on the shared buffer), and the per-device address on a
+    second GPU where the box has one."""
+    from fields_lm_b200 import _lib
+    lib = _lib.load()
+    devices = [0] + ([1] if torch.cuda.device_count() >= 2 else [])
+    for index in devices:
+        dev = torch.device("cuda", index)
+        with torch.cuda.device(dev):
+            stream = torch.cuda.current_stream(dev).cuda_stream
+            B, L, C = 2, 257, 131
+            args = _inputs(dev, B, L, C, 20 + index)
+            want_read, want_state = _ordinary(lib, *args, B, L, C, stream)
+            read = torch.empty(B, L, 4 * C, device=dev)
+            out = torch.empty(B, 2 * C, device=dev)
+
+            def call():
+                rc = lib.fields_read_forward_noalloc(*[a.data_ptr() for a in args], read.data_ptr(),
+                                                     out.data_ptr(), B, L, C, stream)
+                assert rc == 0, lib.fields_status_string(rc)
+                torch.cuda.synchronize(dev)
+            call()                                        # first call on this device
+            free_before, _ = torch.cuda.mem_get_info(dev)
+            held_before = (torch.cuda.memory_allocated(dev), torch.cuda.memory_reserved(dev))
+            call()
+            free_after, _ = torch.cuda.mem_get_info(dev)
+            assert free_after == free_before
+            assert (torch.cuda.memory_allocated(dev), torch.cuda.memory_reserved(dev)) == held_before
+            assert rel_err(read.cpu().numpy(), want_read.cpu().numpy()) < FP32_TOL
+            assert rel_err(out.cpu().numpy(), want_state.cpu().numpy()) < FP32_TOL
+
+
 def test_noalloc_forward_refuses_extents_beyond_its_buffer():
     from fields_lm_b200 import _lib
     lib = _lib.load()
