@@ -41,6 +41,7 @@ struct SpShape {
     int prefetch;  // non-zero: blocks warm L2 with the inputs of the tile that many positions ahead
     unsigned max_polls;  // bound of every wait for another block's publication
     int stride;    // persistent kernels: a block takes tiles block, block + stride, ...; 0: one tile per block
+    int ticket;    // non-zero: blocks take their tile from a counter in the workspace header
 };
 
 // Prefetches `planes` consecutive 128-channel plane chunks of `steps` rows into L2:

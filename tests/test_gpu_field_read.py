@@ -257,6 +257,19 @@ def test_ordinary_launches_give_the_same_results(dev, monkeypatch, variants_libr
     check_against_oracle(dev, raw, tr, ti, gm, grad)
 
 
+def test_tiles_handed_out_by_ticket_give_the_same_results(dev, monkeypatch, variants_library):
+    """FIELDS_TILE_TICKET=1 (test build): blocks take their tile from a counter in the workspace
+    header instead of their block index, so no tile waits for a block that has not started,
+    whatever order the hardware dispatches blocks in. Several waves of tiles per chain."""
+    monkeypatch.setenv("FIELDS_TILE_TICKET", "1")
+    rng = np.random.default_rng(78)
+    for B, L, C in ((2, 4500, 512), (3, 70, 132)):
+        tr, ti, gm = _init_params(C)
+        raw = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+        grad = rng.standard_normal((B, L, 4 * C)).astype(np.float32)
+        check_against_oracle(dev, raw, tr, ti, gm, grad)
+
+
 def _config2_inputs(B=8, L=2048, C=512):
     """bf16-rounded activations held in fp32, as autocast hands them to the operator."""
     gen = torch.Generator().manual_seed(1)
