@@ -40,7 +40,6 @@ struct SpShape {
     int G;         // 128-channel groups
     int prefetch;  // non-zero: blocks warm L2 with the inputs of the tile that many positions ahead
     unsigned max_polls;  // bound of every wait for another block's publication
-    int stride;    // persistent kernels: a block takes tiles block, block + stride, ...; 0: one tile per block
     int ticket;    // non-zero: blocks take their tile from a counter in the workspace header
 };
 
@@ -99,13 +98,20 @@ FL_HD SpTile sp_decode(const SpShape& s, unsigned ticket) {
 
 // IO = float, or uint16_t for bfloat16 raw / read (the state, the maps and all arithmetic stay fp32).
 //
-// STAGED: the kernel runs as persistent blocks (a block takes tiles block, block + stride, ... in
-// that order, which keeps "every tile a block waits for has a smaller index and is running or
-// done"), and every thread keeps one staging cell per (step, plane) of its rows in shared memory.
-// As soon as a thread has moved its rows of the current tile from the cells into registers it
-// starts the cp.async copies of its rows of the block's NEXT tile into the same cells; they land
-// while the block publishes its map, looks back and runs the recurrence, so the next tile starts
-// from shared memory instead of waiting for HBM.
+// STAGED: the kernel runs as persistent blocks that take their tiles from a ticket counter in the
+// workspace header, one tile ahead: while a block works on a tile it already holds the ticket
+// of its next one. Every thread keeps one staging cell per (step, plane) of its rows in shared
+// memory; once the block has moved the current tile's rows from the cells into registers
+// (phase 0) every thread starts the cp.async copies of its rows of the NEXT tile into the same
+// cells. They land while the block publishes its map, looks back and runs the recurrence, so the
+// next tile starts from shared memory instead of waiting for HBM. Tickets are taken in time-major
+// tile order by blocks that are running, so every tile a block waits for is held by a running
+// block (as its current or its next tile): progress does not depend on how many blocks the GPU
+// holds at once or on the order it starts them in. The atomic of a ticket is issued at the top
+// of a tile and its result is used after phase 0, so its latency is off the critical path.
+// (Holding two tickets ahead, so that a thread could start the next tile's copies right after
+// its own cell loads, was measured and was much slower: 80 us against 43 us. A ticket taken
+// early is a tile that its chain's successors wait for while its block is still busy.)
 template <int TS, int WARPS, int MIN_BLOCKS, typename IO = float, bool STATS = false,
           bool STAGED = false>
 struct FwdSinglePass {
@@ -122,7 +128,11 @@ struct FwdSinglePass {
     static constexpr bool kStaged = STAGED;
     static constexpr int kCellFloats = (int)sizeof(IO);  // four elements: 16 bytes of float, 8 of bfloat16
     static constexpr int kStageFloats = STAGED ? TS * 3 * kThreads * kCellFloats : 0;
-    static constexpr int kSmemFloats = kSumFloats + kCarryFloats + kStageFloats;
+    static constexpr int kSmemFloats = kSumFloats + kCarryFloats + kStageFloats + (STAGED ? 4 : 0);
+    // the word through which thread 0 hands the block's next ticket to the other threads
+    FL_HD static unsigned* ticket_at(float* smem) {
+        return reinterpret_cast<unsigned*>(smem + kSumFloats + kCarryFloats + kStageFloats);
+    }
     static constexpr int kClaimAfter = 2;  // the next tile is claimed after the look-back phase
     FL_HD static constexpr bool barrier_after(int ph) { return ph != 1; }
     FL_HD static float* cell_at(float* smem, int idx, int thread) {
@@ -184,9 +194,9 @@ struct FwdSinglePass {
 #pragma unroll
             for (int k = 0; k < 4; ++k) m[k] = affine_identity();
             if constexpr (STAGED) {
-                // The rows were started into this thread's cells by the previous tile of this
-                // block (by the kernel entry for the block's first tile; by this very call in
-                // the host emulation, where a copy is synchronous).
+                // The rows were started into this thread's cells by the kernel entry while the
+                // block's previous tile ran (by this very call in the host emulation, where a
+                // copy is synchronous).
 #if !FL_DEVICE_CODE
                 stage(p, block, thread, smem);
 #endif
@@ -201,10 +211,8 @@ struct FwdSinglePass {
                         }
                     }
                 }
-                // the cells are free again: the block's next tile starts towards them now
-                const long long next = (long long)block + s.stride;
-                if (s.stride > 0 && next < (long long)s.B * s.G * s.NT)
-                    stage(p, (int)next, thread, smem);
+                // (on the device the kernel entry starts the next tile's rows towards the cells
+                // after the barrier that follows this phase)
             }
             if (chan_ok) {
                 const Vec<4> lr = vec_load<4>(p.tr + c0);
