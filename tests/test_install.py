@@ -101,3 +101,56 @@ def test_install_fused_mixer_wraps_and_restores_the_class_forward():
         assert fields_lm_b200.uninstall(block) == 1
     assert cls.forward is original
     assert mirror.fused_field_read is fields_lm_b200.fused_field_read
+
+
+def _softpatch_like(via_holder: bool):
+    """A module laid out like the reference's softpatch mixers: ``FastBoundaryStateMixer`` finds
+    the scan on a module it holds as ``v3_global``, ``BoundaryStateMixer`` as a global of its
+    own file (official_source/field_hybrid_speed_optimization_v6.py:333-335 and
+    field_hybrid_attentionfree_qualification_v3.py:460)."""
+    import types
+    calls = []
+
+    def hierarchical_scan(a, b, block=32):
+        calls.append((a.dtype, a.device.type))
+        return b
+
+    home = types.ModuleType("scan_home_for_test")
+    home.hierarchical_scan = hierarchical_scan
+    if via_holder:
+        source = ("import torch\nv3_global = None\n"
+                  "class FastBoundaryStateMixer(torch.nn.Module):\n"
+                  "    def forward(self, a, b):\n"
+                  "        return v3_global.hierarchical_scan(a, b, block=32)\n")
+    else:
+        source = ("import torch\n"
+                  "class BoundaryStateMixer(torch.nn.Module):\n"
+                  "    def forward(self, a, b):\n"
+                  "        return hierarchical_scan(a, b, block=32)\n")
+    user = types.ModuleType("scan_user_for_test")
+    exec(source, user.__dict__)
+    if via_holder:
+        user.v3_global = home
+        return user.FastBoundaryStateMixer(), home.__dict__, calls
+    user.hierarchical_scan = hierarchical_scan
+    return user.BoundaryStateMixer(), user.__dict__, calls
+
+
+@pytest.mark.parametrize("via_holder", [True, False])
+def test_install_scan_rebinds_where_the_softpatch_mixer_looks(via_holder):
+    mixer, namespace, calls = _softpatch_like(via_holder)
+    model = torch.nn.Sequential(mixer)
+    original = namespace["hierarchical_scan"]
+    assert fields_lm_b200.install_scan(model) == 1
+    assert namespace["hierarchical_scan"] is not original
+    assert namespace["hierarchical_scan"].__wrapped__ is original
+    assert fields_lm_b200.install_scan(model) == 1          # idempotent: not wrapped twice
+    assert namespace["hierarchical_scan"].__wrapped__ is original
+    # CPU and complex calls still reach the reference's own function through the replacement
+    a = torch.rand(1, 5, 3)
+    mixer(a, a)
+    mixer(a.to(torch.complex64), a.to(torch.complex64))
+    assert calls == [(torch.float32, "cpu"), (torch.complex64, "cpu")]
+    fields_lm_b200.uninstall(model)
+    assert namespace["hierarchical_scan"] is original
+    assert fields_lm_b200.install_scan(torch.nn.Linear(2, 2)) == 0
