@@ -1279,6 +1279,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "traffic_source": "ncu dram__bytes_read+write of the two single-pass kernels, "
                               "profiles/single_pass_fwd_bwd_8x2048_ncu.md",
             "peak_source": f"of {peak_kind}",
+            "frac_of_nominal_8_tb_s": achieved / 8000.0,
             "kernel": "whole step per GPU: fill + FwdSinglePass + fill + BwdSinglePass + BwdReduce, dependent launches",
             "algorithmic_bytes_per_token": BYTES_PER_TOKEN,
             "forward": {"ms": ms_fwd, "achieved": fwd_gbs, "frac": fwd_gbs / peak},
