@@ -1093,11 +1093,34 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         # the three-launch form over the same mailboxes, then NCCL all_gather. A form is used
         # only if every rank could build it and two warm-up calls report no timeout.
         sp_fwd, exchange, alternatives = None, None, {}
+        long_call, best_ms = None, None
+
+        def replayed(cand):
+            """The call captured once in a CUDA graph (the kernel keeps its epoch on the device)."""
+            cur = torch.cuda.current_stream(device)
+            side = torch.cuda.Stream(device)
+            side.wait_stream(cur)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                cand(long_raw, tr_d, ti_d, gm_d)
+                with torch.cuda.graph(graph, stream=side):
+                    cand(long_raw, tr_d, ti_d, gm_d)
+            cur.wait_stream(side)
+            torch.cuda.synchronize(device)
+
+            def run():
+                graph.replay()
+                return cand.read, cand.state_out
+            return run
+
         forms = (("one cooperative launch per rank, summaries over NVLink peer stores",
-                  lambda: seqpar.SequenceParallelForwardFused(1, hi - lo, C, device)),
+                  lambda: seqpar.SequenceParallelForwardFused(1, hi - lo, C, device), False),
+                 ("the same launch replayed from a CUDA graph, epoch kept on the device",
+                  lambda: seqpar.SequenceParallelForwardFused(1, hi - lo, C, device,
+                                                              device_epoch=True), True),
                  ("three launches per rank, summaries over NVLink peer stores",
-                  lambda: seqpar.SequenceParallelForwardP2P(1, hi - lo, C, device)))
-        for label, make in forms:
+                  lambda: seqpar.SequenceParallelForwardP2P(1, hi - lo, C, device), False))
+        for label, make, as_graph in forms:
             try:
                 cand = make()
                 built = True
@@ -1105,23 +1128,37 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                 print(f"{label}: unavailable ({exc!r})", file=sys.stderr)
                 cand, built = None, False
             healthy = False
+            call = None
             if all_agree(built):
                 for _ in range(3):
                     cand(long_raw, tr_d, ti_d, gm_d)
                 healthy = all_agree(cand.status() == 0)
+            if healthy and as_graph:
+                try:
+                    call = replayed(cand)
+                except Exception as exc:
+                    print(f"{label}: capture failed ({exc!r})", file=sys.stderr)
+                    call = None
+                healthy = all_agree(call is not None)
+            elif healthy:
+                call = (lambda c: (lambda: c(long_raw, tr_d, ti_d, gm_d)))(cand)
             if healthy:
+                for _ in range(2):
+                    call()
                 barrier(dist_on)
-                ms = max_over_ranks(timed_loop(lambda: cand(long_raw, tr_d, ti_d, gm_d),
-                                               long_steps, stream) / long_steps, dist_on, device)
+                ms = max_over_ranks(timed_loop(call, long_steps, stream) / long_steps, dist_on, device)
+                healthy = all_agree(cand.status() == 0)
+            if healthy:
                 alternatives[label] = ms
-                if sp_fwd is None:
-                    sp_fwd, exchange = cand, label
+                if best_ms is None or ms < best_ms:
+                    best_ms, sp_fwd, exchange, long_call = ms, cand, label, call
         healthy = sp_fwd is not None
         if not healthy:
             print("peer-memory exchange not usable here; using NCCL all_gather", file=sys.stderr)
             sp_fwd = seqpar.SequenceParallelForward(1, hi - lo, C, device)
             exchange = "three launches per rank, nccl all_gather"
-        long_fwd = lambda: sp_fwd(long_raw, tr_d, ti_d, gm_d)
+            long_call = lambda: sp_fwd(long_raw, tr_d, ti_d, gm_d)
+        long_fwd = long_call
     else:
         exchange, alternatives = None, None
         long_op = DirectOp(device, 1, LONG_L)

@@ -74,6 +74,10 @@ struct SpanFwdParams {
     const MailPair* own;     // this rank's own slots
     int rank, P;
     unsigned epoch, max_polls;
+    unsigned* epoch_word;    // null, or two words on the rank's board: [0] the epoch of the last
+                             // completed call, [1] blocks of the running call that have finished.
+                             // Then the kernel takes its epoch from there and the call carries none,
+                             // so a captured CUDA graph can replay it.
     int stages;              // bit 0: sweep 1, bit 1: prefix, exchange and sweep 2; bit 2 (host emulation,
                              // which runs the ranks in turn): prefix and the sending half of the exchange only
     SpanShape s;

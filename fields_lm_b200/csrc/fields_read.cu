@@ -451,7 +451,27 @@ __global__ void __launch_bounds__(K::kThreads, K::kMinBlocks) span_entry(const t
     typename K::State st;
     DeviceExec<K> ex{st};
     wait_for_previous_kernel();
-    K::run_block(p, (int)blockIdx.x, smem, ex);
+    if (p.epoch_word == nullptr) {
+        K::run_block(p, (int)blockIdx.x, smem, ex);
+        return;
+    }
+    // Epoch kept on the device: every block reads the last completed epoch when it starts; the
+    // block that finishes last (all others have read it long before) stores the new one. The
+    // ranks' counters advance together because every rank makes the same calls.
+    typename K::Params q = p;
+    unsigned last;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(last) : "l"(p.epoch_word) : "memory");
+    q.epoch = last + 1u ? last + 1u : 1u;   // never 0
+    K::run_block(q, (int)blockIdx.x, smem, ex);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(p.epoch_word + 1, 1u) == gridDim.x - 1) {
+            p.epoch_word[1] = 0;
+            __threadfence();
+            asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p.epoch_word), "r"(q.epoch) : "memory");
+        }
+    }
 }
 
 // Blocks of span_entry<K> that the current device holds at once, asked once per device.
@@ -836,8 +856,12 @@ static size_t mailbox_slot_bytes(int P, int B, int C) {
 }
 // counters (one word per chain), then the run maps of up to span_item_bound runs (2 KB each)
 // (a counter word and, 256 bytes apart from one another, a ready word per chain)
+// ... and, 64 words behind them, the two words of the device-resident epoch
+static size_t board_epoch_offset(int B, int C) {
+    return ((size_t)B * ((C + kGroup - 1) / kGroup) * 65 + 64) * sizeof(unsigned);
+}
 static size_t board_count_bytes(int B, int C) {
-    return round_up((size_t)B * ((C + kGroup - 1) / kGroup) * 65 * sizeof(unsigned), 256);
+    return round_up(board_epoch_offset(B, C) + 64 * sizeof(unsigned), 256);
 }
 static size_t mailbox_board_bytes(int B, int C) {
     return board_count_bytes(B, C) + (size_t)span_item_bound(B, C) * kGroup * 4 * sizeof(float);
@@ -1448,8 +1472,11 @@ int fields_read_forward_sharded(const float* raw, const float* tr, const float* 
                                 float* state_out, float* summary, void* const* mailboxes,
                                 unsigned* error_word, int rank, int P, unsigned epoch,
                                 unsigned max_polls, int B, int L, int C, void* stream) {
-    if (B < 0 || L <= 0 || C <= 0 || P <= 0 || P > kMaxRanks || rank < 0 || rank >= P || epoch == 0)
+    if (B < 0 || L <= 0 || C <= 0 || P <= 0 || P > kMaxRanks || rank < 0 || rank >= P)
         return FIELDS_ERR_ARGUMENT;
+#ifdef FIELDS_HOST_EMU
+    if (epoch == 0) return FIELDS_ERR_ARGUMENT;  // the emulation runs a call as several partial launches
+#endif
     if (B == 0) return FIELDS_OK;
     if (!raw || !tr || !ti || !gamma || !read || !mailboxes || !error_word) return FIELDS_ERR_ARGUMENT;
     for (int r = 0; r < P; ++r)
@@ -1473,6 +1500,8 @@ int fields_read_forward_sharded(const float* raw, const float* tr, const float* 
     for (int r = 0; r < P; ++r) p.mailbox[r] = static_cast<MailPair*>(mailboxes[r]);
     p.own = static_cast<const MailPair*>(mailboxes[rank]);
     p.rank = rank; p.P = P; p.epoch = epoch;
+    // epoch 0: the epoch lives on the rank's board and the kernel advances it itself
+    p.epoch_word = epoch == 0 ? reinterpret_cast<unsigned*>(board + board_epoch_offset(B, C)) : nullptr;
     p.max_polls = poll_bound(max_polls);
     p.stages = 3;
 #ifdef FIELDS_HOST_EMU

@@ -308,21 +308,29 @@ class SequenceParallelForwardFused(SequenceParallelForwardP2P):
     second sweep starts with the rows the first one read last), and there are no launch gaps
     between the stages. ``max_polls`` bounds every device-side wait (0: the library's default,
     about a second of rank skew); a wait that runs out sets the status word and leaves NaN in
-    the outputs instead of hanging. Not for replay from a captured CUDA graph (the epoch is a
-    kernel argument).
+    the outputs instead of hanging. By default the epoch is a kernel argument, so the call must
+    not be replayed from a captured CUDA graph; with ``device_epoch=True`` the epoch lives in the
+    rank's mailbox and the kernel advances it itself: the call can then be captured and
+    replayed (every rank replays the same number of times), and this object's mailboxes must
+    not be used by calls that pass their own epochs.
     """
 
+    def __init__(self, batch: int, span_length: int, channels: int, device, group=None,
+                 max_polls: int = 0, device_epoch: bool = False):
+        super().__init__(batch, span_length, channels, device, group, max_polls)
+        self.device_epoch = bool(device_epoch)
 
     def __call__(self, raw_span, tr, ti, gamma, state0: Optional[torch.Tensor] = None):
         B, L, C = self.B, self.L, self.C
         if tuple(raw_span.shape) != (B, L, 3 * C) or not raw_span.is_contiguous():
             raise ValueError(f"expected a contiguous [{B}, {L}, {3 * C}] span")
-        self.epoch = self.epoch + 1 if self.epoch < 0xFFFFFFFE else 1
+        if not self.device_epoch:
+            self.epoch = self.epoch + 1 if self.epoch < 0xFFFFFFFE else 1
         rc = self.lib.fields_read_forward_sharded(
             raw_span.data_ptr(), tr.data_ptr(), ti.data_ptr(), gamma.data_ptr(),
             None if state0 is None else state0.data_ptr(), self.read.data_ptr(),
             self.state_out.data_ptr(), None, self.peers, self.error.data_ptr(), self.rank,
-            self.world, self.epoch, self.max_polls, B, L, C,
+            self.world, 0 if self.device_epoch else self.epoch, self.max_polls, B, L, C,
             torch.cuda.current_stream(self.device).cuda_stream)
         _lib.check(rc, "fields_read_forward_sharded")
         return self.read, self.state_out

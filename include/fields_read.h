@@ -314,9 +314,14 @@ int fields_read_fold_mailbox(const void *mailbox, const float *state0, float *st
  * nothing is ever cleared. The launch is cooperative: all blocks are resident together,
  * because they wait for one another and for the peers. With P = 1 nothing is exchanged (the
  * mailbox only lends its board). Needs C % 4 == 0 and 16-byte aligned tensors
- * (FIELDS_ERR_UNSUPPORTED otherwise). Like the other mailbox calls it takes the epoch as an
- * argument and must not be replayed from a captured CUDA graph. Peer memory is written with
- * plain 8-byte stores only.
+ * (FIELDS_ERR_UNSUPPORTED otherwise). Peer memory is written with plain 8-byte stores only.
+ *
+ * epoch > 0: the caller's per-call counter, as for the other mailbox calls; such a call must
+ * not be replayed from a captured CUDA graph (the graph would repeat the epoch).
+ * epoch == 0: the epoch lives on the rank's board; the kernel reads it when it starts and its
+ * last block advances it, so the call carries no per-call value and a captured graph can
+ * replay it. Every rank must then make the same sequence of calls on these mailboxes, and the
+ * mailboxes must not be shared with calls that pass their own epochs.
  */
 int fields_read_forward_sharded(const float *raw, const float *tr, const float *ti,
                                 const float *gamma, const float *state0, float *read,

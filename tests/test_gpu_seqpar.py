@@ -59,6 +59,14 @@ def _worker(rank, world, port, L, out_dir):
         for _ in range(4):
             read4, state4 = fused(span, tr, ti, gm)
         torch.cuda.synchronize()
+        # the same with the epoch kept on the device (the form a captured graph can replay)
+        fused_dev = seqpar.SequenceParallelForwardFused(B, hi - lo, C, dev, device_epoch=True)
+        for _ in range(4):
+            read5, state5 = fused_dev(span, tr, ti, gm)
+        torch.cuda.synchronize()
+        check(fused_dev.status() == 0, "one-launch forward with a device epoch timed out")
+        check(float((read5 - read).abs().max()) <= 2e-6 * float(read.abs().max()), "device-epoch read")
+        check(float((state5 - state).abs().max()) <= 2e-6 * float(state.abs().max()), "device-epoch state")
         check(fused.status() == 0, "one-launch forward timed out")
         check(float((read4 - read).abs().max()) <= 2e-6 * float(read.abs().max()), "fused read")
         check(float((state4 - state).abs().max()) <= 2e-6 * float(state.abs().max()), "fused state")

@@ -119,12 +119,55 @@ def test_an_absent_peer_ends_the_wait_with_the_error_word_set():
     assert int(solo.err.item()) == 0 and bool(torch.isfinite(solo.read).all())
 
 
+def test_device_epoch_calls_and_cuda_graph_replay():
+    """epoch 0: the epoch lives on the rank's board and the kernel advances it, so the same call
+    can be issued again and again, directly and replayed from a captured CUDA graph (with new
+    data in the same buffers each time)."""
+    dev = torch.device("cuda", 0)
+    rng = np.random.default_rng(9)
+    B, L, C = 2, 3000, 512
+    tr, ti, gm = _params(C, rng)
+    t = [torch.from_numpy(a).to(dev) for a in (tr, ti, gm)]
+    op = Rank(dev, B, L, C)
+    raw = torch.empty(B, L, 3 * C, device=dev)
+
+    def fresh():
+        data = rng.standard_normal((B, L, 3 * C)).astype(np.float32)
+        raw.copy_(torch.from_numpy(data))
+        return data
+
+    def check(data):
+        torch.cuda.synchronize()
+        want, want_state = field_oracle.forward(data, tr, ti, gm)
+        assert int(op.err.item()) == 0
+        assert rel_err(op.read.cpu().numpy(), want) < FP32_TOL
+        assert rel_err(op.state.cpu().numpy(), want_state) < FP32_TOL
+
+    for _ in range(3):                       # direct calls, epochs 1, 2, 3 kept on the device
+        data = fresh()
+        assert op(raw, *t, 0) == 0
+        check(data)
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        op.stream = side.cuda_stream
+        assert op(raw, *t, 0) == 0           # warm-up on the capture stream
+        with torch.cuda.graph(graph, stream=side):
+            assert op(raw, *t, 0) == 0
+    torch.cuda.current_stream(dev).wait_stream(side)
+    torch.cuda.synchronize()
+    for _ in range(4):
+        data = fresh()
+        graph.replay()
+        check(data)
+
+
 def test_argument_errors():
     dev = torch.device("cuda", 0)
     op = Rank(dev, 1, 8, 4)
     p = torch.ones(4, device=dev)
     raw = torch.zeros(1, 8, 12, device=dev)
-    assert op(raw, p, p, p, 0) == 1                       # epoch 0 is reserved
     op.rank = 1
     assert op(raw, p, p, p, 1) == 1                       # rank outside [0, P)
     odd = Rank(dev, 1, 8, 3)
