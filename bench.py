@@ -1196,7 +1196,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         del sp_fwd  # its buffers; the training step holds its own
         if healthy:
             trainer = seqpar.SequenceParallelTrainStepP2P(1, hi - lo, C, device)
-            train_api = "seqpar.SequenceParallelTrainStepP2P (peer-memory exchanges, one all_reduce)"
+            train_api = ("seqpar.SequenceParallelTrainStepP2P (summaries and the parameter-gradient "
+                         "sum over NVLink peer stores, no collective library in the step)")
         else:
             trainer = seqpar.SequenceParallelTrainStep(1, hi - lo, C, device)
             train_api = "seqpar.SequenceParallelTrainStep (NCCL all_gather x2, all_reduce)"
@@ -1220,6 +1221,24 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     except Exception as exc:  # the headline line must still be printed
         print(f"train_64k leg failed: {exc!r}", file=sys.stderr)
         ms_train = None
+    # the same step with the parameter-gradient sum through one NCCL all_reduce, for comparison
+    ms_train_nccl = None
+    if dist_on and healthy and ms_train is not None:
+        try:
+            other = seqpar.SequenceParallelTrainStepP2P(1, hi - lo, C, device, nccl_reduce=True)
+
+            def other_train():
+                other.forward(long_raw, tr_d, ti_d, gm_d)
+                other.backward(long_raw, tr_d, ti_d, gm_d, long_grad)
+            for _ in range(3):
+                other_train()
+            barrier(dist_on)
+            ms_train_nccl = max_over_ranks(timed_loop(other_train, train_steps, stream) / train_steps,
+                                           dist_on, device)
+            barrier(dist_on)
+            del other
+        except Exception as exc:
+            print(f"train_64k NCCL-reduce comparison failed: {exc!r}", file=sys.stderr)
     train_parity = None
     if dist_on and ms_train is not None:
         full_op = full_long["op"]
@@ -1350,6 +1369,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "tokens_per_s": LONG_L / (ms_train * 1e-3),
             "achieved": LONG_L * BYTES_PER_TOKEN / (ms_train * 1e-3) / 1e9,
             "frac": LONG_L * BYTES_PER_TOKEN / (ms_train * 1e-3) / 1e9 / (peak * world),
+            "ms_with_nccl_all_reduce_of_parameter_gradients": ms_train_nccl,
             "parity": train_parity},
         "bf16_io": {**bf16, "achieved": B * L * BYTES_PER_TOKEN / 2 / (bf16["ms_per_step"] * 1e-3) / 1e9,
                     "frac": B * L * BYTES_PER_TOKEN / 2 / (bf16["ms_per_step"] * 1e-3) / 1e9 / peak,

@@ -45,6 +45,8 @@ SYMBOLS = {
     "fields_read_forward_sharded": (_I, [_P] * 10 + [_I, _I, ctypes.c_uint, ctypes.c_uint,
                                               _I, _I, _I, _P]),
     "fields_read_fold_mailbox": (_I, [_P, _P, _P, _P, _I, _I, ctypes.c_uint, ctypes.c_uint, _I, _I, _P]),
+    "fields_read_sum_over_ranks": (_I, [_P, _P, _I, _P, _P, _I, _I, ctypes.c_uint, ctypes.c_uint,
+                                       _I, _I, _P]),
     "fields_read_span_summary_backward_put": (_I, [_P] * 6 + [_I, _I, ctypes.c_uint, _P, _SZ, _I, _I, _I, _P]),
     "fields_read_fold_mailbox_backward": (_I, [_P, _P, _P, _P, _I, _I, ctypes.c_uint, ctypes.c_uint, _I, _I, _P]),
     "fields_read_norm_grad_combine": (_I, [_P, _P, _P, _P, ctypes.c_longlong, _I, _P]),

@@ -1894,4 +1894,72 @@ struct FoldMailbox {
     }
 };
 
+// ---------------------------------------------------------------------------
+// Sum of a short vector over the ranks through the same mailboxes (the 3 C parameter-gradient
+// sums of a sequence-sharded backward pass, plus the ranks' status words): every rank stores
+// its n values, tagged with the call's epoch, into its slot of EVERY rank's reduction region
+// (plain 8-byte peer stores), then waits with a bound until all P slots of its own region carry
+// the epoch and adds them in rank order, so every rank gets the same bits. One launch, no
+// collective library. Region: [2 parities][P ranks][n_max] pairs behind the mailbox's board.
+// ---------------------------------------------------------------------------
+struct SumMailbox {
+    struct Params {
+        const float* values;           // [n] this rank's addends
+        float* out;                    // [n] the sum over the ranks
+        MailPair* region[kMaxRanks];   // every rank's reduction region (peer pointers), index = rank
+        unsigned* error;               // error word (0 = ok), set to 1 if a wait ran out
+        int rank, P, n, n_max;
+        unsigned epoch, max_polls;
+        int stages;                    // bit 0: store, bit 1: wait and add (the host emulation runs the ranks in turn)
+    };
+    static constexpr int kThreads = 128;
+    static constexpr int kPhases = 1;
+    static constexpr int kSmemFloats = 0;
+
+    FL_HD static void phase0(const Params& p, int block, int thread, float*) {
+        const int i = block * kThreads + thread;
+        if (i >= p.n) return;
+        const size_t parity = (size_t)(p.epoch & 1u) * p.P;
+        if (p.stages & 1) {
+            const float v = p.values[i];
+            for (int r = 0; r < p.P; ++r)
+                mail_store(p.region[r] + (parity + p.rank) * p.n_max + i, v, p.epoch);
+        }
+        if (!(p.stages & 2)) return;
+        const MailPair* own = p.region[p.rank];
+        float acc = 0.0f;
+        bool failed = false;
+        for (int r0 = 0; r0 < p.P; r0 += kMailWindow) {
+            MailPair got[kMailWindow];
+#pragma unroll
+            for (int w = 0; w < kMailWindow; ++w)
+                if (r0 + w < p.P) got[w] = mail_load(own + (parity + r0 + w) * p.n_max + i);
+#pragma unroll
+            for (int w = 0; w < kMailWindow; ++w) {
+                if (r0 + w < p.P) {
+                    MailPair m = got[w];
+#if FL_DEVICE_CODE
+                    unsigned polls = 0;
+                    while (m.tag != p.epoch && !failed && ++polls < p.max_polls) {
+                        backoff(polls);
+                        m = mail_load(own + (parity + r0 + w) * p.n_max + i);
+                    }
+#endif
+                    if (m.tag != p.epoch) failed = true;
+                    acc += m.value;
+                }
+            }
+        }
+        if (failed) {
+#if FL_DEVICE_CODE
+            atomicExch(p.error, 1u);
+#else
+            *p.error = 1u;
+#endif
+            acc = nanf("");
+        }
+        p.out[i] = acc;
+    }
+};
+
 }  // namespace fields

@@ -863,6 +863,11 @@ static size_t board_epoch_offset(int B, int C) {
 static size_t board_count_bytes(int B, int C) {
     return round_up(board_epoch_offset(B, C) + 64 * sizeof(unsigned), 256);
 }
+// Behind the board: the reduction region of fields_read_sum_over_ranks, [2][P][n_max] pairs.
+static int mailbox_sum_capacity(int C) { return 3 * C + 64; }
+static size_t mailbox_sum_bytes(int P, int C) {
+    return round_up((size_t)2 * P * mailbox_sum_capacity(C) * sizeof(MailPair), 256);
+}
 static size_t mailbox_board_bytes(int B, int C) {
     return board_count_bytes(B, C) + (size_t)span_item_bound(B, C) * kGroup * 4 * sizeof(float);
 }
@@ -1464,7 +1469,32 @@ int fields_read_backward_bf16(const void* raw, const float* tr, const float* ti,
 
 size_t fields_read_mailbox_bytes(int P, int B, int C) {
     if (P <= 0 || B <= 0 || C <= 0) return 0;
-    return mailbox_slot_bytes(P, B, C) + mailbox_board_bytes(B, C);
+    return mailbox_slot_bytes(P, B, C) + mailbox_board_bytes(B, C) + mailbox_sum_bytes(P, C);
+}
+
+int fields_read_sum_over_ranks(const float* values, float* out, int n, void* const* mailboxes,
+                               unsigned* error_word, int rank, int P, unsigned epoch,
+                               unsigned max_polls, int B, int C, void* stream) {
+    if (B <= 0 || C <= 0 || P <= 0 || P > kMaxRanks || rank < 0 || rank >= P || epoch == 0 || n < 0 ||
+        n > mailbox_sum_capacity(C))
+        return FIELDS_ERR_ARGUMENT;
+    if (n == 0) return FIELDS_OK;
+    if (!values || !out || !mailboxes || !error_word) return FIELDS_ERR_ARGUMENT;
+    SumMailbox::Params p{};
+    p.values = values; p.out = out; p.error = error_word;
+    const size_t off = mailbox_slot_bytes(P, B, C) + mailbox_board_bytes(B, C);
+    for (int r = 0; r < P; ++r) {
+        if (!mailboxes[r] || (reinterpret_cast<uintptr_t>(mailboxes[r]) & 7u)) return FIELDS_ERR_ARGUMENT;
+        p.region[r] = reinterpret_cast<MailPair*>(static_cast<char*>(mailboxes[r]) + off);
+    }
+    p.rank = rank; p.P = P; p.n = n; p.n_max = mailbox_sum_capacity(C);
+    p.epoch = epoch; p.max_polls = poll_bound(max_polls);
+    p.stages = 3;
+#ifdef FIELDS_HOST_EMU
+    p.stages = g_emu_span_stages & 3;  // the CPU tests run every rank's stores before any rank's wait
+#endif
+    return launch<SumMailbox>(p, (n + SumMailbox::kThreads - 1) / SumMailbox::kThreads,
+                              reinterpret_cast<Stream>(stream));
 }
 
 int fields_read_forward_sharded(const float* raw, const float* tr, const float* ti,

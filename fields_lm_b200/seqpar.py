@@ -343,15 +343,20 @@ class SequenceParallelTrainStepP2P(SequenceParallelForwardP2P):
     puts the span's dual summary into every mailbox under the next epoch
     (``fields_read_span_summary_backward_put``), waits with a bound for all of them and folds
     the later spans, last first (``fields_read_fold_mailbox_backward``), and runs
-    ``fields_read_backward`` with that carry. Only the 3 C parameter-gradient floats go through
-    NCCL (one all_reduce). Like the forward, not for replay from a captured CUDA graph.
+    ``fields_read_backward`` with that carry. The 3 C parameter-gradient sums (and the ranks'
+    status words beside them) are added over the ranks through the same mailboxes too
+    (``fields_read_sum_over_ranks``: peer stores, bounded wait, addition in rank order, so every
+    rank holds the same bits); ``nccl_reduce=True`` sends them through one NCCL all_reduce
+    instead. Like the forward, not for replay from a captured CUDA graph.
     """
 
     def __init__(self, batch: int, span_length: int, channels: int, device, group=None,
-                 max_polls: int = 0):
+                 max_polls: int = 0, nccl_reduce: bool = False):
         super().__init__(batch, span_length, channels, device, group, max_polls)
+        self.nccl_reduce = bool(nccl_reduce)
         f32 = dict(device=self.device, dtype=torch.float32)
         self.carry = torch.empty(batch, 2 * channels, **f32)
+        self.addends = torch.zeros(3 * channels + 1, **f32)
         self.grad_raw = torch.empty(batch, span_length, 3 * channels, **f32)
         # [3 C] parameter gradients + one word: the ranks' error words, summed by the same
         # all_reduce, so every rank learns of a timeout anywhere without another collective
@@ -382,21 +387,34 @@ class SequenceParallelTrainStepP2P(SequenceParallelForwardP2P):
                                                    self.epoch, self.max_polls, B, C, st)
         _lib.check(rc, "fields_read_fold_mailbox_backward")
         g = self.grad_par
+        # this rank's sums land in `addends` when they still have to cross the ranks
+        own = self.addends[:3 * C].view(3, C) if self.world > 1 and not self.nccl_reduce else g
         rc = lib.fields_read_backward(*args, gamma.data_ptr(), self.state_in.data_ptr(),
                                       self.read.data_ptr(), grad_read_span.data_ptr(),
                                       self.carry.data_ptr(), self.grad_raw.data_ptr(),
-                                      g[0].data_ptr(), g[1].data_ptr(), g[2].data_ptr(), None,
+                                      own[0].data_ptr(), own[1].data_ptr(), own[2].data_ptr(), None,
                                       self.ws_bwd.data_ptr(), self.nbytes_bwd, B, L, C, st)
         _lib.check(rc, "fields_read_backward")
-        if self.world > 1:
+        if self.world > 1 and self.nccl_reduce:
             self.reduced[-1:].copy_(self.error)
             dist.all_reduce(self.reduced, group=self.group)
+        elif self.world > 1:
+            self.addends[-1:].copy_(self.error)
+            self.epoch = self.epoch + 1 if self.epoch < 0xFFFFFFFE else 1
+            rc = lib.fields_read_sum_over_ranks(self.addends.data_ptr(), self.reduced.data_ptr(),
+                                                3 * C + 1, self.peers, self.error.data_ptr(),
+                                                self.rank, self.world, self.epoch, self.max_polls,
+                                                B, C, st)
+            _lib.check(rc, "fields_read_sum_over_ranks")
         return self.grad_raw, g
 
     def status(self) -> int:
         """Number of ranks whose waits have run out, as of the last backward (syncs); before the
         first backward, this rank's own error word."""
-        return int(self.reduced[-1].item()) or int(self.error.item())
+        seen = float(self.reduced[-1].item())
+        if seen != seen:          # the sum itself gave up waiting: NaN
+            return self.world
+        return int(seen) or int(self.error.item())
 
 
 def span_bounds(length: int, world: int, rank: int) -> Tuple[int, int]:

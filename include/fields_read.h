@@ -330,6 +330,24 @@ int fields_read_forward_sharded(const float *raw, const float *tr, const float *
                                 unsigned max_polls, int B, int L, int C, void *stream);
 
 /*
+ * Sum of a short fp32 vector over the ranks through the same mailboxes, in one launch and without
+ * a collective library: the 3 C parameter-gradient sums of a sequence-sharded backward pass (and
+ * the ranks' status words beside them). No counterpart in the reference, which sums its
+ * partials on one GPU (field_only_v4_chunked_triton_wiki100.py:1098-1105).
+ *   values  [n] this rank's addends, out [n] the sum over the ranks, n <= 3 C + 64
+ *   mailboxes, rank, P, epoch, max_polls   as for fields_read_fold_mailbox; the call takes the
+ *            next epoch of the shared sequence; B and C are those the mailboxes were sized with
+ * Every rank stores its values, tagged with the epoch, into every rank's reduction region
+ * (part of fields_read_mailbox_bytes, behind the board) with plain 8-byte peer stores, waits
+ * with a bound until its own region holds all P contributions and adds them in rank order:
+ * every rank gets the same bits. A contribution that never arrives sets the error word and
+ * leaves NaN in out.
+ */
+int fields_read_sum_over_ranks(const float *values, float *out, int n, void *const *mailboxes,
+                               unsigned *error_word, int rank, int P, unsigned epoch,
+                               unsigned max_polls, int B, int C, void *stream);
+
+/*
  * The backward exchange through the same mailboxes (they and the epoch sequence are shared
  * with the forward exchange: every exchange, in either direction, takes the next epoch).
  * fields_read_span_summary_backward_put stores the span's dual summary (see

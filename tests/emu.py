@@ -83,6 +83,8 @@ def declare(lib: ctypes.CDLL) -> ctypes.CDLL:
     lib.fields_read_forward_sharded.argtypes = [P] * 10 + [I, I, ctypes.c_uint, ctypes.c_uint,
                                                    I, I, I, P]
     lib.fields_read_forward_sharded.restype = I
+    lib.fields_read_sum_over_ranks.argtypes = [P, P, I, P, P, I, I, ctypes.c_uint, ctypes.c_uint, I, I, P]
+    lib.fields_read_sum_over_ranks.restype = I
     lib.fields_read_device_status.argtypes = [P, P]
     lib.fields_read_device_status.restype = I
     LL = ctypes.c_longlong
@@ -475,3 +477,25 @@ def scan_backward(a, states, grad_states, state_in=None, grad_state_out=None, wa
                                     B, L, C, None)
     assert rc == 0, rc
     return ga, gb, gsi
+
+
+def sum_over_ranks(values_by_rank, mailboxes, epoch, B, C, absent=()):
+    """Emulated fields_read_sum_over_ranks for all ranks of a job: first every present rank's
+    stores, then every present rank's wait-and-add. Returns ([sum per rank], [error word per rank])."""
+    world = len(mailboxes)
+    ptrs = (ctypes.c_void_p * world)(*[m.ctypes.data for m in mailboxes])
+    vals = [_f32(v) for v in values_by_rank]
+    outs = [_f32(np.full(v.shape, np.nan)) for v in vals]
+    errs = [np.zeros(1, dtype=np.uint32) for _ in range(world)]
+    try:
+        for stages in (1, 2):
+            lib().fields_emu_span_stages(stages)
+            for r in range(world):
+                if r in absent:
+                    continue
+                rc = lib().fields_read_sum_over_ranks(_ptr(vals[r]), _ptr(outs[r]), vals[r].size, ptrs,
+                                                      _ptr(errs[r]), r, world, epoch, 0, B, C, None)
+                assert rc == 0, rc
+    finally:
+        lib().fields_emu_span_stages(3)
+    return outs, [int(e[0]) for e in errs]

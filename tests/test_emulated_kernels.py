@@ -401,6 +401,42 @@ def test_mailbox_exchange_carries_the_backward_too():
             _, want = field_oracle.forward(raw[:, a:b], tr, ti, gm, state_in=want)
 
 
+def test_sum_over_ranks_through_the_mailboxes():
+    """The parameter-gradient sum of a sharded backward pass without a collective library: every
+    rank stores its addends into all mailboxes and adds what arrived in rank order, so all ranks
+    hold the same bits; the exchange shares mailboxes and epochs with the summary exchanges; a
+    rank that never stores makes the others report the timeout."""
+    rng = np.random.default_rng(33)
+    B, C, world = 2, 20, 3
+    tr, ti, gm = _params(C, rng)
+    boxes = emu.make_mailboxes(world, B, C)
+    n = 3 * C + 1
+    raw = rng.standard_normal((B, 12, 3 * C)).astype(np.float32)
+    for epoch in (1, 2, 3, 4):
+        if epoch == 2:   # a summary exchange in between, on the same mailboxes
+            for r in range(world):
+                emu.span_summary_put(raw, tr, ti, gm, boxes, r, epoch)
+            continue
+        vals = [rng.standard_normal(n).astype(np.float32) for _ in range(world)]
+        outs, errs = emu.sum_over_ranks(vals, boxes, epoch, B, C)
+        want = (vals[0] + vals[1]) + vals[2]          # rank order, fp32
+        assert errs == [0, 0, 0]
+        for out in outs:
+            np.testing.assert_array_equal(out, want)
+    vals = [rng.standard_normal(n).astype(np.float32) for _ in range(world)]
+    outs, errs = emu.sum_over_ranks(vals, boxes, 5, B, C, absent=(1,))
+    assert errs[0] == 1 and errs[2] == 1 and np.isnan(outs[0]).all() and np.isnan(outs[2]).all()
+    lib = emu.lib()
+    ptrs = (emu.ctypes.c_void_p * world)(*[m.ctypes.data for m in boxes])
+    v = emu._f32(np.zeros(3 * C + 65))
+    err = np.zeros(1, dtype=np.uint32)
+    args = (emu._ptr(v), emu._ptr(v))
+    assert lib.fields_read_sum_over_ranks(*args, 3 * C + 65, ptrs, emu._ptr(err), 0, world, 1, 0, B, C, None) == 1
+    assert lib.fields_read_sum_over_ranks(*args, 4, ptrs, emu._ptr(err), 0, world, 0, 0, B, C, None) == 1
+    assert lib.fields_read_sum_over_ranks(*args, 4, ptrs, emu._ptr(err), 3, world, 1, 0, B, C, None) == 1
+    assert lib.fields_read_sum_over_ranks(*args, 0, ptrs, emu._ptr(err), 0, world, 1, 0, B, C, None) == 0
+
+
 @pytest.mark.parametrize("B,L,C,cuts", [
     (1, 700, 512, [0, 233, 480, 700]),     # four chains, several runs per chain, ragged spans
     (2, 90, 20, [0, 31, 64, 90]),          # one partly filled channel group

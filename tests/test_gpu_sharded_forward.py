@@ -163,6 +163,51 @@ def test_device_epoch_calls_and_cuda_graph_replay():
         check(data)
 
 
+def test_sum_over_ranks_alone_and_with_an_absent_peer():
+    """fields_read_sum_over_ranks on one GPU: with P = 1 the sum is the rank's own vector; as rank
+    1 of 2 whose peer never stores, the bounded wait ends with the error word set and NaN in the
+    result (nothing hangs), and the mailbox works again under the next epoch."""
+    from fields_lm_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    B, C = 1, 512
+    n = 3 * C + 1
+    st = torch.cuda.current_stream(dev).cuda_stream
+    vals = torch.randn(n, device=dev)
+    out = torch.full((n,), float("nan"), device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def boxes(P):
+        size = lib.fields_read_mailbox_bytes(P, B, C)
+        mail = [torch.zeros(size, dtype=torch.uint8, device=dev) for _ in range(P)]
+        return mail, (ctypes.c_void_p * P)(*[m.data_ptr() for m in mail])
+
+    mail, ptrs = boxes(1)
+    for epoch in (1, 2, 3):
+        vals.normal_()
+        assert lib.fields_read_sum_over_ranks(vals.data_ptr(), out.data_ptr(), n, ptrs, err.data_ptr(),
+                                              0, 1, epoch, 0, B, C, st) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(out, vals) and int(err.item()) == 0
+    mail2, ptrs2 = boxes(2)
+    assert lib.fields_read_sum_over_ranks(vals.data_ptr(), out.data_ptr(), n, ptrs2, err.data_ptr(),
+                                          1, 2, 1, 2000, B, C, st) == 0
+    torch.cuda.synchronize()
+    assert int(err.item()) == 1 and bool(torch.isnan(out).all())
+    # both ranks of the next epoch, played by this GPU one after the other: rank 0 stores and
+    # gives up (its peer has not stored yet), then rank 1 finds both contributions
+    err.zero_()
+    other = torch.randn(n, device=dev)
+    scratch = torch.empty(n, device=dev)
+    lib.fields_read_sum_over_ranks(other.data_ptr(), scratch.data_ptr(), n, ptrs2, err.data_ptr(),
+                                   0, 2, 2, 50, B, C, st)
+    err.zero_()
+    assert lib.fields_read_sum_over_ranks(vals.data_ptr(), out.data_ptr(), n, ptrs2, err.data_ptr(),
+                                          1, 2, 2, 0, B, C, st) == 0
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0 and torch.equal(out, other + vals)
+
+
 def test_argument_errors():
     dev = torch.device("cuda", 0)
     op = Rank(dev, 1, 8, 4)
